@@ -1,0 +1,98 @@
+"""ctypes binding of libfmoe_b200.so (declared in include/fmoe_b200.h).
+
+The library is the product: there is no fallback.  Importing this module
+without the built library raises, and every call converts a negative status
+into ``RuntimeError`` carrying the library's error text.
+"""
+import ctypes
+import os
+from ctypes import c_int32, c_int64, c_size_t, c_void_p, c_char_p, POINTER
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libfmoe_b200.so")
+
+F32, F16, BF16 = 0, 1, 2
+ACT_NONE, ACT_RELU, ACT_GELU = 0, 1, 2
+MAX_EXPERTS = 4096
+
+
+class Move(ctypes.Structure):
+    """Mirror of fmoe_move_t."""
+    _fields_ = [("peer", c_int32), ("is_send", c_int32), ("src_row", c_int64), ("dst_row", c_int64),
+                ("rows", c_int64), ("local", c_int32), ("step", c_int32)]
+
+
+class MlpParams(ctypes.Structure):
+    """Mirror of fmoe_mlp_params_t."""
+    _fields_ = [(n, c_void_p) for n in ("w1", "w2", "b1", "b2", "gw1", "gw2", "gb1", "gb2")]
+
+
+def _load():
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python -m fastermoe_b200.build` "
+            "(there is no CPU or PyTorch fallback for the CUDA operators)")
+    # NCCL is bound lazily with dlopen(RTLD_NOLOAD) inside the library; importing
+    # torch first makes sure the copy it ships is the one found.
+    return ctypes.CDLL(LIB_PATH, mode=ctypes.RTLD_GLOBAL)
+
+
+lib = _load()
+
+P = c_void_p
+I32, I64 = c_int32, c_int64
+
+_SIGS = {
+    "fmoe_last_error_string": (c_char_p, []),
+    "fmoe_version": (c_int32, []),
+    "fmoe_built_for_sm": (c_int32, []),
+    "fmoe_routing_scratch_bytes": (c_size_t, [I64, I32]),
+    "fmoe_expert_count": (I32, [P, P, I64, I32, P]),
+    "fmoe_assign_pos": (I32, [P, P, P, I64, I32, P, P]),
+    "fmoe_count_and_pos": (I32, [P, I64, I32, P, P, P, P, P, P]),
+    "fmoe_limit_by_capacity": (I32, [P, P, P, I32, I32, P]),
+    "fmoe_prune_gate_by_capacity": (I32, [P, P, P, I64, I32, P, P]),
+    "fmoe_local_scatter": (I32, [P, P, P, I64, I64, I64, I32, P]),
+    "fmoe_local_gather": (I32, [P, P, P, I64, I64, I64, P, P]),
+    "fmoe_local_gather_inv": (I32, [P, P, P, I64, I64, P]),
+    "fmoe_local_gather_sum": (I32, [P, P, P, I64, I32, I64, I32, P]),
+    "fmoe_combine_forward": (I32, [P, P, P, P, I64, I32, I64, I32, P]),
+    "fmoe_combine_backward": (I32, [P, P, P, P, P, P, I64, I32, I64, I32, P]),
+    "fmoe_linear_scratch_bytes": (c_size_t, [I64, I64, I64, I32, I32]),
+    "fmoe_linear_forward": (I32, [P, P, P, P, P, P, I64, I64, I64, I32, I32, I32, P]),
+    "fmoe_linear_backward": (I32, [P, P, P, P, P, P, P, P, I64, I64, I64, I32, I32, I32, I32, P, P]),
+    "fmoe_comm_unique_id": (I32, [P]),
+    "fmoe_comm_init": (I32, [P, I32, I32, I32, POINTER(c_void_p)]),
+    "fmoe_comm_destroy": (I32, [P]),
+    "fmoe_comm_rank": (I32, [P, POINTER(c_int32), POINTER(c_int32)]),
+    "fmoe_expert_exchange": (I32, [P, P, P, P, P, I32, I32, P]),
+    "fmoe_plan_global_scatter": (I32, [P, P, P, I32, I32, I32, P, I32, POINTER(c_int32), POINTER(c_int64)]),
+    "fmoe_global_scatter": (I32, [P, P, P, P, P, P, I64, I64, I64, I32, I32, P]),
+    "fmoe_global_gather": (I32, [P, P, P, P, P, P, I64, I64, I64, I32, I32, P]),
+    "fmoe_exchange_cache_info": (I32, [P, P, P, I32, I32, P]),
+    "fmoe_model_broadcast": (I32, [P, P, I64, I32, P]),
+    "fmoe_gradient_reduce": (I32, [P, P, I64, I32, I32, P]),
+    "fmoe_generate_cached_count": (I32, [P, P, P, P, I32, I32, I32, P]),
+    "fmoe_fused_compute_ptrs": (I32, [P, P, P, I32, I32, I32, P, P, P]),
+    "fmoe_fused_scratch_bytes": (c_size_t, [I64, I64, I64, I64, I32, I32, I32]),
+    "fmoe_fused_forward": (I32, [P, P, P, P, P, P, P, P, P, P, I64, I64, I64, I64, I32, I32, I32, I32, I32, P, P, P]),
+    "fmoe_fused_backward": (I32, [P, P, P, P, P, P, P, P, P, P, P, P, P, I64, I64, I64, I64, I32, I32, I32, I32, I32, P, P, P]),
+}
+
+EXPORTS = tuple(_SIGS)
+
+for _name, (_res, _args) in _SIGS.items():
+    _fn = getattr(lib, _name)
+    _fn.restype = _res
+    _fn.argtypes = _args
+
+
+def last_error():
+    s = lib.fmoe_last_error_string()
+    return s.decode("utf-8", "replace") if s else ""
+
+
+def check(status, what):
+    """Raise RuntimeError for a negative status returned by the library."""
+    if status != 0:
+        raise RuntimeError(f"{what} failed (status {status}): {last_error()}")

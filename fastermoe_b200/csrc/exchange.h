@@ -1,0 +1,48 @@
+// Communicator state and the run-time NCCL binding shared by the exchange and
+// smart-schedule code.
+#pragma once
+#include <nccl.h>
+#include <cuda_runtime.h>
+#include <vector>
+#include "../../include/fmoe_b200.h"
+
+namespace fmoe {
+
+struct NcclApi {
+    ncclResult_t (*GetUniqueId)(ncclUniqueId*);
+    ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int);
+    ncclResult_t (*CommDestroy)(ncclComm_t);
+    ncclResult_t (*CommUserRank)(const ncclComm_t, int*);
+    ncclResult_t (*CommCount)(const ncclComm_t, int*);
+    ncclResult_t (*AllGather)(const void*, void*, size_t, ncclDataType_t, ncclComm_t, cudaStream_t);
+    ncclResult_t (*Send)(const void*, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t);
+    ncclResult_t (*Recv)(void*, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t);
+    ncclResult_t (*GroupStart)();
+    ncclResult_t (*GroupEnd)();
+    ncclResult_t (*Broadcast)(const void*, void*, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t);
+    ncclResult_t (*Reduce)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, int, ncclComm_t, cudaStream_t);
+    const char* (*GetErrorString)(ncclResult_t);
+};
+
+extern NcclApi g_nccl;
+int ensure_nccl_loaded();
+
+struct Comm {
+    ncclComm_t comm = nullptr;
+    int rank = 0, world = 1, device = 0;
+    std::vector<cudaEvent_t> events;  // pool reused by the smart schedule
+};
+
+#define FMOE_NCCL_TRY(expr)                                                              \
+    do {                                                                                 \
+        ncclResult_t r__ = (expr);                                                       \
+        if (r__ != ncclSuccess)                                                          \
+            return ::fmoe::fail(FMOE_ERR_NCCL, "%s failed: %s", #expr,                   \
+                                ::fmoe::g_nccl.GetErrorString(r__));                     \
+    } while (0)
+
+// Row moves of global_scatter for this rank (see fmoe_plan_global_scatter).
+int plan_scatter(const int64_t* lec, const int64_t* gec, const uint8_t* stored, int rank, int E, int W,
+                 std::vector<fmoe_move_t>& moves, int64_t* recv_rows, int64_t* send_rows);
+
+}  // namespace fmoe

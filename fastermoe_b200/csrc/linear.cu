@@ -1,0 +1,60 @@
+// fmoe_linear entry points: argument checks and back-end selection.
+#include "common.cuh"
+#include "gemm.h"
+#include <cstdlib>
+
+using namespace fmoe;
+
+namespace {
+
+// FMOE_B200_GEMM=simt forces the FFMA kernels (used by tests to cross-check the
+// tensor-core kernels); anything else lets the shape decide.
+bool force_simt() {
+    const char* p = getenv("FMOE_B200_GEMM");
+    return p && p[0] == 's';
+}
+
+int check_common(int64_t n_rows, int64_t in_feat, int64_t out_feat, int n_expert, int dtype, int act,
+                 const int64_t* seg) {
+    FMOE_REQUIRE(n_rows >= 0 && in_feat > 0 && out_feat > 0 && n_expert > 0,
+                 "linear: bad sizes rows=%lld in=%lld out=%lld experts=%d", (long long)n_rows,
+                 (long long)in_feat, (long long)out_feat, n_expert);
+    FMOE_REQUIRE(dtype_size(dtype) != 0, "linear: unknown dtype %d", dtype);
+    FMOE_REQUIRE(act >= FMOE_ACT_NONE && act <= FMOE_ACT_GELU, "linear: unknown activation %d", act);
+    FMOE_REQUIRE(seg != nullptr, "linear: seg_offsets pointer is null");
+    return 0;
+}
+
+}  // namespace
+
+extern "C" size_t fmoe_linear_scratch_bytes(int64_t n_rows, int64_t in_feat, int64_t out_feat,
+                                            int32_t n_expert, int32_t dtype) {
+    return tc_backward_scratch_bytes(n_rows, in_feat, out_feat, n_expert, dtype);
+}
+
+extern "C" int fmoe_linear_forward(const void* x, const void* weight, const void* bias,
+                                   const int64_t* seg_offsets, void* y, void* pre_act, int64_t n_rows,
+                                   int64_t in_feat, int64_t out_feat, int32_t n_expert, int32_t dtype,
+                                   int32_t activation, fmoe_stream_t stream) {
+    if (int rc = check_common(n_rows, in_feat, out_feat, n_expert, dtype, activation, seg_offsets)) return rc;
+    if (n_rows == 0) return 0;
+    FMOE_REQUIRE(x && weight && y, "linear_forward: null pointer");
+    LinearArgs a{x, weight, bias, seg_offsets, y, pre_act, n_rows, in_feat, out_feat, n_expert, dtype, activation};
+    if (!force_simt() && tc_forward_supported(a)) return tc_linear_forward(a, (cudaStream_t)stream);
+    return simt_linear_forward(a, (cudaStream_t)stream);
+}
+
+extern "C" int fmoe_linear_backward(const void* grad_y, const void* x, const void* weight,
+                                    const int64_t* seg_offsets, const void* act_pre, void* grad_x,
+                                    void* grad_w, void* grad_b, int64_t n_rows, int64_t in_feat,
+                                    int64_t out_feat, int32_t n_expert, int32_t dtype,
+                                    int32_t activation, int32_t accumulate, void* scratch,
+                                    fmoe_stream_t stream) {
+    if (int rc = check_common(n_rows, in_feat, out_feat, n_expert, dtype, activation, seg_offsets)) return rc;
+    FMOE_REQUIRE(n_rows == 0 || (grad_y && weight), "linear_backward: null pointer");
+    FMOE_REQUIRE(!grad_w || x || n_rows == 0, "linear_backward: weight gradient needs the forward input");
+    LinearBwdArgs a{grad_y, x, weight, seg_offsets, act_pre, grad_x, grad_w, grad_b, n_rows, in_feat,
+                    out_feat, n_expert, dtype, activation, accumulate, scratch};
+    if (!force_simt() && tc_backward_supported(a)) return tc_linear_backward(a, (cudaStream_t)stream);
+    return simt_linear_backward(a, (cudaStream_t)stream);
+}

@@ -1,0 +1,417 @@
+// Routing kernels: expert histogram, stable bucketing of gate entries into
+// expert segments, capacity limiting and capacity pruning.
+//
+// They replace the reference's atomic kernels (cuda/local_exchange.cuh:5-61,
+// cuda/balancing.cuh:5-46) by a deterministic counting sort:
+//   1. tile_hist:   every warp owns a contiguous tile of the flat gate array
+//                   and builds the tile's histogram in shared memory with
+//                   __match_any_sync (one add per distinct expert per 32 entries);
+//   2. scan_tiles:  per expert, exclusive prefix over tiles (in place);
+//   3. finalize:    per-expert totals -> segment starts / limits, and the
+//                   in-place side effects the reference's operators have;
+//   4. apply:       every warp walks its tile again in order, ranks entries by
+//                   (expert, flat index) and writes positions or pruned gates.
+// Gate entries are read with 16-byte loads; within an expert segment positions
+// ascend with the flat index, so results are identical from run to run.
+#include "common.cuh"
+
+namespace fmoe {
+namespace {
+
+constexpr int kWarps = 8;             // warps per block in the tile kernels
+constexpr int kThreads = kWarps * 32;
+constexpr unsigned kFull = 0xffffffffu;
+
+enum Mode { MODE_COUNT_POS = 0, MODE_ASSIGN = 1, MODE_PRUNE = 2 };
+
+struct Geom {
+    int chunks;       // 64-entry chunks per warp tile
+    int64_t n_tiles;  // number of warp tiles
+    int64_t tile;     // entries per tile = chunks*64
+};
+
+Geom make_geom(int64_t n, int n_expert) {
+    Geom g;
+    int64_t chunks = 4;  // 256 entries per warp tile
+    // Keep the per-tile histogram table under 64 MiB.
+    const int64_t budget = (int64_t)64 << 20;
+    while (ceil_div(n, chunks * 64) * n_expert * 4 > budget) chunks *= 2;
+    g.chunks = (int)chunks;
+    g.tile = chunks * 64;
+    g.n_tiles = n > 0 ? ceil_div(n, g.tile) : 0;
+    return g;
+}
+
+// Scratch layout (all offsets 16-byte aligned).
+struct Scratch {
+    int32_t* totals;     // [E]
+    int64_t* seg_start;  // [E]
+    int32_t* limit;      // [E]
+    int32_t* hist;       // [n_tiles][E]
+};
+
+size_t align16(size_t x) { return (x + 15) & ~(size_t)15; }
+
+size_t scratch_bytes(int64_t n, int n_expert) {
+    Geom g = make_geom(n, n_expert);
+    return align16((size_t)n_expert * 4) + align16((size_t)n_expert * 8) +
+           align16((size_t)n_expert * 4) + align16((size_t)g.n_tiles * n_expert * 4) + 16;
+}
+
+Scratch carve(void* scratch, int64_t n, int n_expert) {
+    Scratch s;
+    char* p = (char*)scratch;
+    s.totals = (int32_t*)p;
+    p += align16((size_t)n_expert * 4);
+    s.seg_start = (int64_t*)p;
+    p += align16((size_t)n_expert * 8);
+    s.limit = (int32_t*)p;
+    p += align16((size_t)n_expert * 4);
+    s.hist = (int32_t*)p;
+    return s;
+}
+
+__device__ __forceinline__ int sanitize(int64_t v, int n_expert) {
+    return (v >= 0 && v < (int64_t)n_expert) ? (int)v : -1;
+}
+
+// Loads the expert ids of the 64 entries [c, c+64) of the gate array so that
+// lane l holds entry c+l in `ea` and entry c+32+l in `eb`.  With `vec` the
+// loads are 16 bytes per lane (two consecutive int64) followed by a shuffle
+// transpose; `c` is then a multiple of 2 entries from a 16-byte aligned base.
+__device__ __forceinline__ void load_chunk(const int64_t* __restrict__ gate, int64_t n, int64_t c,
+                                           int lane, bool vec, int n_expert, int& ea, int& eb) {
+    if (vec && c + 64 <= n) {
+        const longlong2 v = __ldg(reinterpret_cast<const longlong2*>(gate + c) + lane);
+        const int h0 = sanitize(v.x, n_expert), h1 = sanitize(v.y, n_expert);
+        const int src = lane >> 1;
+        const int a0 = __shfl_sync(kFull, h0, src), a1 = __shfl_sync(kFull, h1, src);
+        const int b0 = __shfl_sync(kFull, h0, 16 + src), b1 = __shfl_sync(kFull, h1, 16 + src);
+        ea = (lane & 1) ? a1 : a0;
+        eb = (lane & 1) ? b1 : b0;
+    } else {
+        const int64_t ia = c + lane, ib = c + 32 + lane;
+        ea = ia < n ? sanitize(__ldg(gate + ia), n_expert) : -1;
+        eb = ib < n ? sanitize(__ldg(gate + ib), n_expert) : -1;
+    }
+}
+
+// One add per distinct expert among the 32 lanes.
+__device__ __forceinline__ void hist_round(int e, int lane, int32_t* my) {
+    const unsigned m = __match_any_sync(kFull, e);
+    if (e >= 0 && lane == __ffs(m) - 1) my[e] += __popc(m);
+    __syncwarp();
+}
+
+__global__ void __launch_bounds__(kThreads)
+tile_hist_kernel(const int64_t* __restrict__ gate, int64_t n, int n_expert, int chunks,
+                 int64_t n_tiles, int32_t* __restrict__ hist, bool vec) {
+    extern __shared__ int32_t sh[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    int32_t* my = sh + (size_t)warp * n_expert;
+    const int64_t tile = (int64_t)blockIdx.x * kWarps + warp;
+    if (tile >= n_tiles) return;
+    for (int e = lane; e < n_expert; e += 32) my[e] = 0;
+    __syncwarp();
+    const int64_t base = tile * (int64_t)chunks * 64;
+    for (int it = 0; it < chunks; ++it) {
+        const int64_t c = base + (int64_t)it * 64;
+        if (c >= n) break;
+        int ea, eb;
+        load_chunk(gate, n, c, lane, vec, n_expert, ea, eb);
+        hist_round(ea, lane, my);
+        hist_round(eb, lane, my);
+    }
+    int32_t* out = hist + tile * n_expert;
+    for (int e = lane; e < n_expert; e += 32) out[e] = my[e];
+}
+
+// Block e: exclusive prefix over tiles of hist[.][e], in place; totals[e] = sum.
+__global__ void __launch_bounds__(256)
+scan_tiles_kernel(int32_t* __restrict__ hist, int64_t n_tiles, int n_expert,
+                  int32_t* __restrict__ totals) {
+    __shared__ int32_t part[256];
+    const int e = blockIdx.x;
+    const int t = threadIdx.x;
+    const int64_t per = (n_tiles + 255) / 256;
+    const int64_t lo = t * per, hi = min(lo + per, n_tiles);
+    int32_t s = 0;
+    for (int64_t i = lo; i < hi; ++i) s += hist[i * n_expert + e];
+    part[t] = s;
+    __syncthreads();
+    // Hillis-Steele inclusive scan of 256 partial sums.
+    for (int off = 1; off < 256; off <<= 1) {
+        int32_t v = t >= off ? part[t - off] : 0;
+        __syncthreads();
+        part[t] += v;
+        __syncthreads();
+    }
+    int32_t run = part[t] - s;  // exclusive prefix of this thread's chunk
+    for (int64_t i = lo; i < hi; ++i) {
+        const int32_t h = hist[i * n_expert + e];
+        hist[i * n_expert + e] = run;
+        run += h;
+    }
+    if (t == 255) totals[e] = part[255];
+}
+
+// Single block.  Turns totals into segment starts and applies the side effects
+// of the operator being emulated.
+__global__ void __launch_bounds__(1024)
+finalize_kernel(int mode, int n_expert, const int32_t* __restrict__ totals,
+                int64_t* __restrict__ seg_start, int32_t* __restrict__ limit,
+                int64_t* __restrict__ lec64, int64_t* __restrict__ offsets,
+                int32_t* __restrict__ inout /* cum_count or ec */) {
+    __shared__ int64_t part[1024];
+    const int t = threadIdx.x;
+    if (mode == MODE_ASSIGN) {
+        for (int e = t; e < n_expert; e += 1024) {
+            const int32_t s = inout[e] - totals[e];
+            seg_start[e] = s;
+            inout[e] = s;
+        }
+        return;
+    }
+    if (mode == MODE_PRUNE) {
+        for (int e = t; e < n_expert; e += 1024) {
+            const int32_t l = inout[e];
+            limit[e] = l;
+            inout[e] = l - totals[e];
+            seg_start[e] = 0;
+        }
+        return;
+    }
+    // MODE_COUNT_POS: exclusive prefix of totals over experts.
+    const int per = (n_expert + 1023) / 1024;
+    const int lo = t * per, hi = min(lo + per, n_expert);
+    int64_t s = 0;
+    for (int e = lo; e < hi; ++e) s += totals[e];
+    part[t] = s;
+    __syncthreads();
+    for (int off = 1; off < 1024; off <<= 1) {
+        int64_t v = t >= off ? part[t - off] : 0;
+        __syncthreads();
+        part[t] += v;
+        __syncthreads();
+    }
+    int64_t run = part[t] - s;
+    for (int e = lo; e < hi; ++e) {
+        seg_start[e] = run;
+        if (offsets) offsets[e] = run;
+        if (lec64) lec64[e] = totals[e];
+        run += totals[e];
+    }
+    if (t == 1023 && offsets) offsets[n_expert] = part[1023];
+}
+
+// Rank of this lane's entry among the lanes with the same expert, then advance
+// the warp's running counters.  Returns the rank within the expert's bucket
+// counted from the start of the whole array (or from seg_start).
+__device__ __forceinline__ int64_t rank_round(int e, int lane, int64_t* run) {
+    const unsigned m = __match_any_sync(kFull, e);
+    int64_t r = -1;
+    if (e >= 0) r = run[e] + __popc(m & ((1u << lane) - 1u));
+    __syncwarp();
+    if (e >= 0 && lane == __ffs(m) - 1) run[e] += __popc(m);
+    __syncwarp();
+    return r;
+}
+
+__global__ void __launch_bounds__(kThreads)
+apply_kernel(int mode, const int64_t* __restrict__ gate, int64_t n, int n_expert, int chunks,
+             int64_t n_tiles, const int32_t* __restrict__ base, const int64_t* __restrict__ seg_start,
+             const int32_t* __restrict__ limit, const int64_t* __restrict__ total_ptr,
+             int64_t* __restrict__ pos, int64_t* __restrict__ inv, int64_t* __restrict__ new_gate,
+             bool vec) {
+    extern __shared__ int64_t shl[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    int64_t* run = shl + (size_t)warp * n_expert;
+    const int64_t tile = (int64_t)blockIdx.x * kWarps + warp;
+    if (tile >= n_tiles) return;
+    const int32_t* b = base + tile * n_expert;
+    for (int e = lane; e < n_expert; e += 32) run[e] = seg_start[e] + b[e];
+    __syncwarp();
+    const int64_t total = (mode == MODE_COUNT_POS && total_ptr) ? *total_ptr : n;
+    const int64_t tb = tile * (int64_t)chunks * 64;
+    for (int it = 0; it < chunks; ++it) {
+        const int64_t c = tb + (int64_t)it * 64;
+        if (c >= n) break;
+        int ea, eb;
+        load_chunk(gate, n, c, lane, vec, n_expert, ea, eb);
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int e = half ? eb : ea;
+            const int64_t i = c + half * 32 + lane;
+            const int64_t r = rank_round(e, lane, run);
+            if (i < n) {
+                if (mode == MODE_PRUNE) {
+                    new_gate[i] = (e >= 0 && r < (int64_t)limit[e]) ? (int64_t)e : (int64_t)-1;
+                } else {
+                    if (e >= 0) pos[r] = i;
+                    if (inv) inv[i] = r;  // -1 for skipped entries
+                    // Slots past the number of kept entries are never a target
+                    // of the scatter above; mark them empty.
+                    if (mode == MODE_COUNT_POS && i >= total) pos[i] = -1;
+                }
+            }
+        }
+    }
+}
+
+// Plain histogram: shared-memory counters per block, one global atomic per
+// non-empty counter per block.
+__global__ void __launch_bounds__(kThreads)
+expert_count_kernel(const int64_t* __restrict__ gate, int64_t n, int n_expert,
+                    int32_t* __restrict__ expert_count, bool vec) {
+    extern __shared__ int32_t sh[];
+    for (int e = threadIdx.x; e < n_expert; e += kThreads) sh[e] = 0;
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t n_chunks = (n + 63) / 64;
+    for (int64_t ch = (int64_t)blockIdx.x * kWarps + warp; ch < n_chunks;
+         ch += (int64_t)gridDim.x * kWarps) {
+        int ea, eb;
+        load_chunk(gate, n, ch * 64, lane, vec, n_expert, ea, eb);
+        unsigned m = __match_any_sync(kFull, ea);
+        if (ea >= 0 && lane == __ffs(m) - 1) atomicAdd(&sh[ea], __popc(m));
+        m = __match_any_sync(kFull, eb);
+        if (eb >= 0 && lane == __ffs(m) - 1) atomicAdd(&sh[eb], __popc(m));
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < n_expert; e += kThreads) {
+        const int32_t v = sh[e];
+        if (v) atomicAdd(expert_count + e, v);
+    }
+}
+
+__global__ void limit_by_capacity_kernel(const int64_t* __restrict__ ec, int32_t* __restrict__ cap,
+                                         int64_t* __restrict__ eca, int n_expert, int n_worker) {
+    const int e = blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= n_expert) return;
+    int32_t left = cap[e];
+    for (int w = 0; w < n_worker; ++w) {
+        const int32_t proposal = (int32_t)ec[(int64_t)w * n_expert + e];
+        int64_t grant;
+        if (left >= proposal) grant = proposal;
+        else if (left >= 0) grant = left;
+        else grant = 0;
+        eca[(int64_t)w * n_expert + e] = grant;
+        left -= proposal;
+    }
+    cap[e] = left;
+}
+
+int check_routing_args(const void* gate, int64_t n, int n_expert) {
+    FMOE_REQUIRE(n >= 0, "routing: negative entry count %lld", (long long)n);
+    FMOE_REQUIRE(n == 0 || gate != nullptr, "routing: gate pointer is null");
+    FMOE_REQUIRE(n_expert > 0 && n_expert <= FMOE_MAX_EXPERTS,
+                 "routing: n_expert_total=%d outside [1,%d]", n_expert, FMOE_MAX_EXPERTS);
+    FMOE_REQUIRE(n < ((int64_t)1 << 31), "routing: %lld entries exceed the int32 count range",
+                 (long long)n);
+    return 0;
+}
+
+int set_smem(const void* fn, size_t bytes) {
+    if (bytes > 48 * 1024)
+        FMOE_CUDA_TRY(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+    return 0;
+}
+
+// hist -> scan -> finalize -> apply on `stream`.
+int run_bucket(int mode, const int64_t* gate, int64_t n, int n_expert, void* scratch,
+               int64_t* lec64, int64_t* offsets, int32_t* inout, int64_t* pos, int64_t* inv,
+               int64_t* new_gate, cudaStream_t st) {
+    FMOE_REQUIRE(scratch != nullptr, "routing: scratch pointer is null");
+    FMOE_REQUIRE(((uintptr_t)scratch & 15) == 0, "routing: scratch must be 16-byte aligned");
+    const Geom g = make_geom(n, n_expert);
+    const Scratch s = carve(scratch, n, n_expert);
+    const bool vec = ((uintptr_t)gate & 15) == 0;
+    const size_t sm_hist = (size_t)kWarps * n_expert * 4, sm_apply = (size_t)kWarps * n_expert * 8;
+    if (int rc = set_smem((const void*)tile_hist_kernel, sm_hist)) return rc;
+    if (int rc = set_smem((const void*)apply_kernel, sm_apply)) return rc;
+    const unsigned blocks = (unsigned)ceil_div(g.n_tiles, kWarps);
+    if (g.n_tiles > 0) {
+        tile_hist_kernel<<<blocks, kThreads, sm_hist, st>>>(gate, n, n_expert, g.chunks, g.n_tiles,
+                                                             s.hist, vec);
+        FMOE_CHECK_LAUNCH();
+    }
+    scan_tiles_kernel<<<n_expert, 256, 0, st>>>(s.hist, g.n_tiles, n_expert, s.totals);
+    FMOE_CHECK_LAUNCH();
+    finalize_kernel<<<1, 1024, 0, st>>>(mode, n_expert, s.totals, s.seg_start, s.limit, lec64,
+                                        offsets, inout);
+    FMOE_CHECK_LAUNCH();
+    if (g.n_tiles > 0) {
+        apply_kernel<<<blocks, kThreads, sm_apply, st>>>(mode, gate, n, n_expert, g.chunks, g.n_tiles,
+                                                          s.hist, s.seg_start, s.limit,
+                                                          offsets ? offsets + n_expert : nullptr, pos,
+                                                          inv, new_gate, vec);
+        FMOE_CHECK_LAUNCH();
+    }
+    return 0;
+}
+
+}  // namespace
+}  // namespace fmoe
+
+using namespace fmoe;
+
+extern "C" size_t fmoe_routing_scratch_bytes(int64_t n, int32_t n_expert_total) {
+    if (n < 0 || n_expert_total <= 0) return 0;
+    return scratch_bytes(n, n_expert_total);
+}
+
+extern "C" int fmoe_expert_count(const int64_t* gate_idx, int32_t* expert_count, int64_t n,
+                                 int32_t n_expert_total, fmoe_stream_t stream) {
+    if (int rc = check_routing_args(gate_idx, n, n_expert_total)) return rc;
+    FMOE_REQUIRE(expert_count != nullptr, "expert_count: output pointer is null");
+    if (n == 0) return 0;
+    const bool vec = ((uintptr_t)gate_idx & 15) == 0;
+    const int64_t n_chunks = ceil_div(n, 64);
+    const unsigned blocks = (unsigned)std::min<int64_t>(ceil_div(n_chunks, kWarps), (int64_t)sm_count() * 8);
+    const size_t smem = (size_t)n_expert_total * 4;
+    expert_count_kernel<<<blocks, kThreads, smem, (cudaStream_t)stream>>>(gate_idx, n, n_expert_total,
+                                                                           expert_count, vec);
+    FMOE_CHECK_LAUNCH();
+    return 0;
+}
+
+extern "C" int fmoe_assign_pos(int32_t* cum_count, const int64_t* gate, int64_t* pos, int64_t n,
+                               int32_t n_expert_total, void* scratch, fmoe_stream_t stream) {
+    if (int rc = check_routing_args(gate, n, n_expert_total)) return rc;
+    FMOE_REQUIRE(cum_count != nullptr, "assign_pos: cum_count pointer is null");
+    FMOE_REQUIRE(n == 0 || pos != nullptr, "assign_pos: pos pointer is null");
+    return run_bucket(MODE_ASSIGN, gate, n, n_expert_total, scratch, nullptr, nullptr, cum_count, pos,
+                      nullptr, nullptr, (cudaStream_t)stream);
+}
+
+extern "C" int fmoe_count_and_pos(const int64_t* gate, int64_t n, int32_t n_expert_total,
+                                  int64_t* lec64, int64_t* offsets, int64_t* pos, int64_t* inv,
+                                  void* scratch, fmoe_stream_t stream) {
+    if (int rc = check_routing_args(gate, n, n_expert_total)) return rc;
+    FMOE_REQUIRE(n == 0 || pos != nullptr, "count_and_pos: pos pointer is null");
+    FMOE_REQUIRE(offsets != nullptr, "count_and_pos: offsets pointer is null");
+    return run_bucket(MODE_COUNT_POS, gate, n, n_expert_total, scratch, lec64, offsets, nullptr, pos,
+                      inv, nullptr, (cudaStream_t)stream);
+}
+
+extern "C" int fmoe_prune_gate_by_capacity(const int64_t* gate_idx, int64_t* new_gate_idx, int32_t* ec,
+                                           int64_t n, int32_t n_expert_total, void* scratch,
+                                           fmoe_stream_t stream) {
+    if (int rc = check_routing_args(gate_idx, n, n_expert_total)) return rc;
+    FMOE_REQUIRE(ec != nullptr, "prune_gate_by_capacity: expert_count pointer is null");
+    FMOE_REQUIRE(n == 0 || new_gate_idx != nullptr, "prune_gate_by_capacity: output pointer is null");
+    return run_bucket(MODE_PRUNE, gate_idx, n, n_expert_total, scratch, nullptr, nullptr, ec, nullptr,
+                      nullptr, new_gate_idx, (cudaStream_t)stream);
+}
+
+extern "C" int fmoe_limit_by_capacity(const int64_t* ec, int32_t* cap, int64_t* eca, int32_t n_expert,
+                                      int32_t n_worker, fmoe_stream_t stream) {
+    FMOE_REQUIRE(ec && cap && eca, "limit_by_capacity: null pointer");
+    FMOE_REQUIRE(n_expert > 0 && n_worker > 0, "limit_by_capacity: n_expert=%d n_worker=%d", n_expert,
+                 n_worker);
+    const int threads = 128;
+    limit_by_capacity_kernel<<<(unsigned)ceil_div(n_expert, threads), threads, 0, (cudaStream_t)stream>>>(
+        ec, cap, eca, n_expert, n_worker);
+    FMOE_CHECK_LAUNCH();
+    return 0;
+}

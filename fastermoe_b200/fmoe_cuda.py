@@ -1,0 +1,462 @@
+r"""Drop-in module for the reference's ``fmoe_cuda`` extension.
+
+Every function registered by the reference's pybind11 module
+(cuda/fmoe_cuda.cpp:105-130) exists here under the same name, with the same
+positional arguments, in-place side effects and return values, and forwards to
+``libfmoe_b200.so`` through its C ABI (include/fmoe_b200.h).  Outputs are
+allocated with torch, work is queued on torch's current stream, and a failure
+raises ``RuntimeError`` (the reference exits the process).
+
+Two deliberate differences from the reference: operators do not block the
+host, and ``linear_forward`` / ``linear_backward`` accept the expert-count
+vector on either the CPU (as the reference requires) or the GPU.
+
+Functions past the "extended operators" marker have no counterpart in the
+reference's extension; they are the fused forms the layer in this package uses
+(bucketing in one call, permutation kernels, gate-score combine, activation
+fused into the expert GEMMs).
+"""
+import ctypes
+import os
+import threading
+
+import torch
+
+from . import _lib
+from ._lib import lib, check
+
+_DT = {torch.float32: _lib.F32, torch.float16: _lib.F16, torch.bfloat16: _lib.BF16}
+
+
+def _dtype_code(t):
+    try:
+        return _DT[t.dtype]
+    except KeyError:
+        raise RuntimeError(f"fmoe_cuda: unsupported dtype {t.dtype} (float32, float16, bfloat16)") from None
+
+
+def _ptr(t):
+    return ctypes.c_void_p(t.data_ptr()) if t is not None else None
+
+
+def _stream(device=None):
+    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def _check_cuda(*tensors):
+    for t in tensors:
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise RuntimeError("fmoe_cuda: expected a CUDA tensor")
+        if not t.is_contiguous():
+            raise RuntimeError("fmoe_cuda: expected a contiguous tensor")
+
+
+def _scratch(nbytes, device):
+    return torch.empty(max(int(nbytes), 16), dtype=torch.uint8, device=device)
+
+
+def _routing_scratch(n, n_expert, device):
+    return _scratch(lib.fmoe_routing_scratch_bytes(n, n_expert), device)
+
+
+# ---------------------------------------------------------------------------
+# local_exchange: cuda/fmoe_cuda.cpp:48-54
+# ---------------------------------------------------------------------------
+
+def expert_count(gate_idx, expert_count):
+    """Adds the histogram of ``gate_idx`` (int64, -1 ignored) into ``expert_count`` (int32)."""
+    _check_cuda(gate_idx, expert_count)
+    assert gate_idx.dtype == torch.int64 and expert_count.dtype == torch.int32
+    with torch.cuda.device(gate_idx.device):
+        check(lib.fmoe_expert_count(_ptr(gate_idx), _ptr(expert_count), gate_idx.numel(),
+                                    expert_count.numel(), _stream()), "expert_count")
+
+
+def assign_pos(cum_count, gate, pos):
+    """Fills ``pos`` with flat gate indices bucketed by expert; consumes ``cum_count``."""
+    _check_cuda(cum_count, gate, pos)
+    assert cum_count.dtype == torch.int32 and gate.dtype == torch.int64 and pos.dtype == torch.int64
+    n, e = gate.numel(), cum_count.numel()
+    with torch.cuda.device(gate.device):
+        scratch = _routing_scratch(n, e, gate.device)
+        check(lib.fmoe_assign_pos(_ptr(cum_count), _ptr(gate), _ptr(pos), n, e, _ptr(scratch),
+                                  _stream()), "assign_pos")
+
+
+# ---------------------------------------------------------------------------
+# balancing: cuda/fmoe_cuda.cpp:72-77
+# ---------------------------------------------------------------------------
+
+def limit_by_capacity(expert_count, capacity, n_expert, n_worker):
+    """Returns the granted counts [W*E] int64; decrements ``capacity`` (int32 [E])."""
+    _check_cuda(expert_count, capacity)
+    assert expert_count.dtype == torch.int64 and capacity.dtype == torch.int32
+    assert expert_count.numel() == n_expert * n_worker and capacity.numel() == n_expert
+    out = torch.empty_like(expert_count)
+    with torch.cuda.device(expert_count.device):
+        check(lib.fmoe_limit_by_capacity(_ptr(expert_count), _ptr(capacity), _ptr(out), n_expert,
+                                         n_worker, _stream()), "limit_by_capacity")
+    return out
+
+
+def prune_gate_by_capacity(gate_idx, expert_count, n_expert, n_worker):
+    """Returns a new gate tensor with entries beyond each expert's allowance set to -1."""
+    _check_cuda(gate_idx, expert_count)
+    assert gate_idx.dtype == torch.int64 and expert_count.dtype == torch.int32
+    assert expert_count.numel() == n_expert * n_worker
+    out = torch.empty_like(gate_idx)
+    n, e = gate_idx.numel(), expert_count.numel()
+    with torch.cuda.device(gate_idx.device):
+        scratch = _routing_scratch(n, e, gate_idx.device)
+        check(lib.fmoe_prune_gate_by_capacity(_ptr(gate_idx), _ptr(out), _ptr(expert_count), n, e,
+                                              _ptr(scratch), _stream()), "prune_gate_by_capacity")
+    return out
+
+
+# ---------------------------------------------------------------------------
+# parallel_linear: cuda/fmoe_cuda.cpp:57-69
+# ---------------------------------------------------------------------------
+
+_offset_cache = {}
+_offset_lock = threading.Lock()
+
+
+def offsets_from_counts(expert_count, device):
+    """Exclusive prefix sum (int64 [E+1], on ``device``) of a CPU or CUDA count vector."""
+    if expert_count.is_cuda:
+        off = torch.zeros(expert_count.numel() + 1, dtype=torch.int64, device=device)
+        torch.cumsum(expert_count.reshape(-1).to(torch.int64), 0, out=off[1:])
+        return off
+    key = id(expert_count)
+    with _offset_lock:
+        hit = _offset_cache.get(key)
+        if hit is not None and hit[0]() is expert_count and hit[1] == expert_count._version \
+                and hit[2].device == device:
+            return hit[2]
+    ec = expert_count.reshape(-1).to(torch.int64)
+    off = torch.zeros(ec.numel() + 1, dtype=torch.int64)
+    torch.cumsum(ec, 0, out=off[1:])
+    dev = off.to(device)
+    import weakref
+    with _offset_lock:
+        if len(_offset_cache) > 64:
+            _offset_cache.clear()
+        _offset_cache[key] = (weakref.ref(expert_count), expert_count._version, dev)
+    return dev
+
+
+def linear_forward(input_buf, expert_count, weight, bias=None):
+    """Y[seg_e] = X[seg_e] @ W_e^T + b_e for every expert (cuda/parallel_linear.cu:5-49)."""
+    off = offsets_from_counts(expert_count, input_buf.device)
+    return linear_forward_act(input_buf, off, weight, bias, _lib.ACT_NONE)[0]
+
+
+def linear_backward(grad_output_buf, input_buf, expert_count, weight, bias=None):
+    """Returns [dX, dW, db] (cuda/parallel_linear.cu:52-94); db is returned even without bias."""
+    off = offsets_from_counts(expert_count, input_buf.device)
+    gx, gw, gb = linear_backward_act(grad_output_buf, input_buf, off, weight, None, _lib.ACT_NONE,
+                                     need_bias=True)
+    return [gx, gw, gb]
+
+
+# ---------------------------------------------------------------------------
+# global_exchange: cuda/fmoe_cuda.cpp:8-44
+# ---------------------------------------------------------------------------
+
+_comms = {}
+_comm_lock = threading.Lock()
+
+
+def _comm(device):
+    c = _comms.get(device.index if device.index is not None else torch.cuda.current_device())
+    if c is None:
+        raise RuntimeError("fmoe_cuda: no communicator on this device; call ensure_nccl first")
+    return c
+
+
+def ensure_nccl(group, t):
+    """Creates this device's expert-parallel communicator once (cuda/global_exchange.cu:107-119).
+
+    ``group`` is a ``torch.distributed`` process group (``None`` = default group);
+    it is only used to broadcast the 128-byte NCCL unique id from its rank 0.
+    """
+    import torch.distributed as dist
+    dev = t.device.index if t.device.index is not None else torch.cuda.current_device()
+    with _comm_lock:
+        if dev in _comms:
+            return
+        rank = dist.get_rank(group)
+        world = dist.get_world_size(group)
+        ident = (ctypes.c_uint8 * 128)()
+        if rank == 0:
+            check(lib.fmoe_comm_unique_id(ident), "comm_unique_id")
+        box = [bytes(ident)]
+        src = dist.get_global_rank(group, 0) if group is not None else 0
+        dist.broadcast_object_list(box, src=src, group=group)
+        ident = (ctypes.c_uint8 * 128).from_buffer_copy(box[0])
+        handle = ctypes.c_void_p()
+        check(lib.fmoe_comm_init(ident, rank, world, dev, ctypes.byref(handle)), "comm_init")
+        _comms[dev] = handle
+
+
+def comm_rank(device):
+    r, w = ctypes.c_int32(), ctypes.c_int32()
+    check(lib.fmoe_comm_rank(_comm(device), ctypes.byref(r), ctypes.byref(w)), "comm_rank")
+    return r.value, w.value
+
+
+def destroy_comms():
+    """Destroys every communicator created by ensure_nccl (for orderly shutdown)."""
+    with _comm_lock:
+        for h in _comms.values():
+            lib.fmoe_comm_destroy(h)
+        _comms.clear()
+
+
+def expert_exchange(local_expert_count, n_expert, n_workers):
+    """Returns [all_expert_count[W,W,E], all_global_expert_count[W,W,E], global_expert_count[W*E]]."""
+    _check_cuda(local_expert_count)
+    assert local_expert_count.dtype == torch.int64 and local_expert_count.numel() == n_expert * n_workers
+    dev = local_expert_count.device
+    aec = local_expert_count.new_empty((n_workers, n_workers, n_expert))
+    agec = local_expert_count.new_empty((n_workers, n_workers, n_expert))
+    gec = torch.empty_like(local_expert_count)
+    with torch.cuda.device(dev):
+        check(lib.fmoe_expert_exchange(_comm(dev), _ptr(local_expert_count), _ptr(aec), _ptr(agec),
+                                       _ptr(gec), n_expert, n_workers, _stream()), "expert_exchange")
+    return [aec, agec, gec]
+
+
+def _host_i64(t):
+    t = t.detach()
+    if t.is_cuda:
+        t = t.cpu()
+    return t.reshape(-1).to(torch.int64).contiguous()
+
+
+def _host_flags(t):
+    t = t.detach()
+    if t.is_cuda:
+        t = t.cpu()
+    return t.reshape(-1).to(torch.uint8).contiguous()
+
+
+def _global_move(fn, name, buf, local_expert_count, global_expert_count, stored_models, batch_size,
+                 n_workers):
+    _check_cuda(buf)
+    lec, gec, st = _host_i64(local_expert_count), _host_i64(global_expert_count), _host_flags(stored_models)
+    n_expert = lec.numel() // n_workers
+    out = buf.new_empty((batch_size, buf.shape[1]))
+    row_bytes = buf.shape[1] * buf.element_size()
+    with torch.cuda.device(buf.device):
+        check(fn(_comm(buf.device), _ptr(buf), _ptr(out), _ptr(lec), _ptr(gec), _ptr(st), buf.shape[0],
+                 batch_size, row_bytes, n_expert, n_workers, _stream()), name)
+    return out
+
+
+def global_scatter(input_buf, local_expert_count, global_expert_count, stored_models, batch_size,
+                   n_workers):
+    """All-to-all-v of token rows to the experts' owners (cuda/global_exchange.cu:26-52)."""
+    return _global_move(lib.fmoe_global_scatter, "global_scatter", input_buf, local_expert_count,
+                        global_expert_count, stored_models, batch_size, n_workers)
+
+
+def global_gather(output_buf, local_expert_count, global_expert_count, stored_models, batch_size,
+                  n_workers):
+    """Inverse of global_scatter (cuda/global_exchange.cu:54-80)."""
+    return _global_move(lib.fmoe_global_gather, "global_gather", output_buf, local_expert_count,
+                        global_expert_count, stored_models, batch_size, n_workers)
+
+
+def exchange_cache_info(sent_models, num_expert, world_size):
+    """All-gathers the per-rank shadow flags; returns [sent_models, stored_models[W,E]]."""
+    _check_cuda(sent_models)
+    assert sent_models.dtype == torch.bool and sent_models.numel() == num_expert
+    stored = sent_models.new_zeros((world_size, num_expert))
+    with torch.cuda.device(sent_models.device):
+        check(lib.fmoe_exchange_cache_info(_comm(sent_models.device), _ptr(sent_models), _ptr(stored),
+                                           num_expert, world_size, _stream()), "exchange_cache_info")
+    return [sent_models, stored]
+
+
+def model_exchange(stored_models, local_params, params, num_expert, world_size):
+    """Broadcasts each shadowed (worker j, slot i) parameter buffer from its owner.
+
+    ``local_params[i]`` is this rank's flat buffer, ``params[j][i]`` the buffer that
+    receives worker j's copy (cuda/global_exchange.cuh:251-282).  Returns this rank.
+    """
+    flags = _host_flags(stored_models)
+    dev = local_params[0].device
+    rank, world = comm_rank(dev)
+    assert world == world_size
+    with torch.cuda.device(dev):
+        for i in range(num_expert):
+            for j in range(world_size):
+                if not flags[i + j * num_expert]:
+                    continue
+                buf = local_params[i] if j == rank else params[j][i]
+                _check_cuda(buf)
+                check(lib.fmoe_model_broadcast(_comm(dev), _ptr(buf), buf.numel() * buf.element_size(),
+                                               j, _stream()), "model_exchange")
+    return rank
+
+
+def generate_cached_count(local_expert_count, global_expert_count, stored_models, num_expert, world_size):
+    """fwd_expert_count [W*E] once shadowed experts run locally (cuda/global_exchange.cu:175-196)."""
+    _check_cuda(local_expert_count, global_expert_count, stored_models)
+    dev = local_expert_count.device
+    rank, _ = comm_rank(dev)
+    lec = local_expert_count.reshape(-1).to(torch.int64).contiguous()
+    gec = global_expert_count.reshape(-1).to(torch.int64).contiguous()
+    st = stored_models.reshape(-1).to(torch.uint8).contiguous()
+    out = torch.empty_like(lec)
+    with torch.cuda.device(dev):
+        check(lib.fmoe_generate_cached_count(_ptr(lec), _ptr(gec), _ptr(st), _ptr(out), rank, num_expert,
+                                             world_size, _stream()), "generate_cached_count")
+    return out
+
+
+def gradient_exchange(stored_models, local_grads, grads, num_expert, world_size):
+    """Sum-reduces shadow gradients to the owning rank, in place (cuda/global_exchange.cuh:322-348)."""
+    flags = _host_flags(stored_models)
+    dev = local_grads[0].device
+    rank, _ = comm_rank(dev)
+    with torch.cuda.device(dev):
+        for i in range(num_expert):
+            for j in range(world_size):
+                if not flags[i + j * num_expert]:
+                    continue
+                buf = local_grads[i] if j == rank else grads[j][i]
+                _check_cuda(buf)
+                check(lib.fmoe_gradient_reduce(_comm(dev), _ptr(buf), buf.numel(), _dtype_code(buf), j,
+                                               _stream()), "gradient_exchange")
+
+
+# ---------------------------------------------------------------------------
+# Extended operators (no counterpart in the reference's extension)
+# ---------------------------------------------------------------------------
+
+def count_and_pos(gate, n_expert_total, want_inv=True):
+    """One-call form of count_by_gate's bucketing (fmoe/functions.py:19-41).
+
+    Returns ``(lec int64[E_tot], offsets int64[E_tot+1], pos int64[n], inv int64[n] or None)``.
+    ``pos`` has one slot per gate entry; slots past ``offsets[-1]`` hold -1.
+    Nothing is copied to the host.
+    """
+    _check_cuda(gate)
+    assert gate.dtype == torch.int64
+    n, dev = gate.numel(), gate.device
+    lec = torch.empty(n_expert_total, dtype=torch.int64, device=dev)
+    off = torch.empty(n_expert_total + 1, dtype=torch.int64, device=dev)
+    pos = torch.empty(n, dtype=torch.int64, device=dev)
+    inv = torch.empty(n, dtype=torch.int64, device=dev) if want_inv else None
+    with torch.cuda.device(dev):
+        scratch = _routing_scratch(n, n_expert_total, dev)
+        check(lib.fmoe_count_and_pos(_ptr(gate), n, n_expert_total, _ptr(lec), _ptr(off), _ptr(pos),
+                                     _ptr(inv), _ptr(scratch), _stream()), "count_and_pos")
+    return lec, off, pos, inv
+
+
+def local_scatter(inp, pos, pos_div=1, n_rows=None):
+    """out[i] = inp[pos[i] // pos_div]; rows with pos[i] < 0 are zero."""
+    _check_cuda(inp, pos)
+    n = pos.numel() if n_rows is None else n_rows
+    out = inp.new_empty((n, inp.shape[1]))
+    with torch.cuda.device(inp.device):
+        check(lib.fmoe_local_scatter(_ptr(inp), _ptr(pos), _ptr(out), n, inp.shape[0],
+                                     inp.shape[1] * inp.element_size(), pos_div, _stream()), "local_scatter")
+    return out
+
+
+def local_gather(buf, pos, out_rows):
+    """zeros(out_rows, d) with out[pos[i]] = buf[i] (index_copy_ semantics)."""
+    _check_cuda(buf, pos)
+    out = buf.new_empty((out_rows, buf.shape[1]))
+    with torch.cuda.device(buf.device):
+        inv = torch.empty(out_rows, dtype=torch.int64, device=buf.device)
+        check(lib.fmoe_local_gather(_ptr(buf), _ptr(pos), _ptr(out), pos.numel(), out_rows,
+                                    buf.shape[1] * buf.element_size(), _ptr(inv), _stream()), "local_gather")
+    return out
+
+
+def local_gather_inv(buf, inv):
+    """out[r] = buf[inv[r]] (zero row where inv[r] < 0)."""
+    _check_cuda(buf, inv)
+    out = buf.new_empty((inv.numel(), buf.shape[1]))
+    with torch.cuda.device(buf.device):
+        check(lib.fmoe_local_gather_inv(_ptr(buf), _ptr(inv), _ptr(out), inv.numel(),
+                                        buf.shape[1] * buf.element_size(), _stream()), "local_gather_inv")
+    return out
+
+
+def local_gather_sum(buf, inv, n_tokens, top_k):
+    """out[t] = sum_j buf[inv[t*top_k+j]] over valid slots (deterministic index_add_)."""
+    _check_cuda(buf, inv)
+    out = buf.new_empty((n_tokens, buf.shape[1]))
+    with torch.cuda.device(buf.device):
+        check(lib.fmoe_local_gather_sum(_ptr(buf), _ptr(inv), _ptr(out), n_tokens, top_k, buf.shape[1],
+                                        _dtype_code(buf), _stream()), "local_gather_sum")
+    return out
+
+
+def combine_forward(buf, inv, score):
+    """out[t] = sum_j score[t,j] * buf[inv[t*k+j]] (inv None: buf is already [T*k, d])."""
+    _check_cuda(buf, inv, score)
+    n_tokens, top_k = score.shape
+    assert score.dtype == buf.dtype
+    out = buf.new_empty((n_tokens, buf.shape[1]))
+    with torch.cuda.device(buf.device):
+        check(lib.fmoe_combine_forward(_ptr(buf), _ptr(inv), _ptr(score), _ptr(out), n_tokens, top_k,
+                                       buf.shape[1], _dtype_code(buf), _stream()), "combine_forward")
+    return out
+
+
+def combine_backward(grad_out, buf, inv, score, need_score_grad=True):
+    """Returns (grad_buf, grad_score) of combine_forward.  Rows of grad_buf that no
+    slot maps to are left unwritten."""
+    _check_cuda(grad_out, buf, inv, score)
+    n_tokens, top_k = score.shape
+    grad_buf = torch.empty_like(buf)
+    grad_score = torch.empty_like(score) if need_score_grad else None
+    with torch.cuda.device(buf.device):
+        check(lib.fmoe_combine_backward(_ptr(grad_out), _ptr(buf), _ptr(inv), _ptr(score), _ptr(grad_buf),
+                                        _ptr(grad_score), n_tokens, top_k, buf.shape[1], _dtype_code(buf),
+                                        _stream()), "combine_backward")
+    return grad_buf, grad_score
+
+
+def linear_forward_act(x, seg_offsets, weight, bias, activation, want_pre=False):
+    """Grouped GEMM with fused bias and activation.  Returns (y, pre_act or None)."""
+    _check_cuda(x, seg_offsets, weight, bias)
+    n_expert, out_feat, in_feat = weight.shape
+    assert x.shape[1] == in_feat and x.dtype == weight.dtype
+    assert seg_offsets.dtype == torch.int64 and seg_offsets.numel() == n_expert + 1
+    y = x.new_empty((x.shape[0], out_feat))
+    pre = x.new_empty((x.shape[0], out_feat)) if want_pre else None
+    with torch.cuda.device(x.device):
+        check(lib.fmoe_linear_forward(_ptr(x), _ptr(weight), _ptr(bias), _ptr(seg_offsets), _ptr(y),
+                                      _ptr(pre), x.shape[0], in_feat, out_feat, n_expert, _dtype_code(x),
+                                      activation, _stream()), "linear_forward")
+    return y, pre
+
+
+def linear_backward_act(grad_y, x, seg_offsets, weight, act_pre, activation, need_bias=True,
+                        need_input_grad=True, grad_w=None, grad_b=None, accumulate=False):
+    """Grouped GEMM backward.  ``act_pre`` (shape of x) fuses the backward of the
+    activation that produced ``x`` into the input gradient.  Returns (dX, dW, db)."""
+    _check_cuda(grad_y, x, seg_offsets, weight, act_pre)
+    n_expert, out_feat, in_feat = weight.shape
+    n_rows = grad_y.shape[0]
+    gx = x.new_empty((n_rows, in_feat)) if need_input_grad else None
+    gw = grad_w if grad_w is not None else torch.empty_like(weight)
+    gb = grad_b if grad_b is not None else (weight.new_empty((n_expert, out_feat)) if need_bias else None)
+    with torch.cuda.device(x.device):
+        nbytes = lib.fmoe_linear_scratch_bytes(n_rows, in_feat, out_feat, n_expert, _dtype_code(x))
+        scratch = _scratch(nbytes, x.device)
+        check(lib.fmoe_linear_backward(_ptr(grad_y), _ptr(x), _ptr(weight), _ptr(seg_offsets),
+                                       _ptr(act_pre), _ptr(gx), _ptr(gw), _ptr(gb), n_rows, in_feat,
+                                       out_feat, n_expert, _dtype_code(x), activation,
+                                       1 if accumulate else 0, _ptr(scratch), _stream()), "linear_backward")
+    return gx, gw, gb

@@ -1,0 +1,433 @@
+r"""Autograd glue between the MoE layer and the CUDA operators.
+
+Mirrors the public names of the reference's ``fmoe/functions.py`` (count_by_gate,
+prepare_forward, ensure_comm, MOECache, MOEScatter, MOELinear, MOEGather,
+AllGather, Slice) and adds the fused forms the layer uses on its fast path.
+
+Where the reference copies five count vectors to the host per forward
+(fmoe/functions.py:64-68), this module needs none at world_size 1 and one
+(the all-gathered count table, a few KB) otherwise.
+"""
+import torch
+from torch.autograd import Function
+
+from . import fmoe_cuda
+from . import _lib
+from .utils import get_torch_default_comm
+
+
+class ExpertCounts:
+    """Rows per expert for a grouped expert call.
+
+    ``offsets`` is a device int64 [E+1] exclusive prefix sum; ``counts_cpu`` the
+    per-expert counts on the host when they are known there (multi-GPU runs),
+    else ``None``.  Accepted wherever the reference passes ``fwd_expert_count``.
+    """
+
+    def __init__(self, offsets, counts_cpu=None):
+        self.offsets = offsets
+        self.counts_cpu = counts_cpu
+
+    @staticmethod
+    def wrap(counts, device):
+        if isinstance(counts, ExpertCounts):
+            return counts
+        cpu = counts if not counts.is_cuda else None
+        return ExpertCounts(fmoe_cuda.offsets_from_counts(counts, device), cpu)
+
+    def host_counts(self):
+        """Counts as a CPU tensor (copies from the device, with a sync, if unknown)."""
+        if self.counts_cpu is None:
+            off = self.offsets.cpu()
+            self.counts_cpu = off[1:] - off[:-1]
+        return self.counts_cpu
+
+
+def ensure_comm(t, comm):
+    """Creates the expert-parallel NCCL communicator of t's device (fmoe/functions.py:14-17)."""
+    if comm is None:
+        comm = get_torch_default_comm()
+    fmoe_cuda.ensure_nccl(comm, t)
+
+
+def count_by_gate(gate, num_expert, world_size, require_pos=True):
+    """Same contract as fmoe/functions.py:19-42.
+
+    Returns ``(pos, local_expert_count, all_expert_count, global_expert_count,
+    all_global_expert_count)`` as device tensors; ``pos`` has exactly as many
+    entries as gate entries that are not -1 (which costs one host read, as in
+    the reference).
+    """
+    with torch.no_grad():
+        n_tot = num_expert * world_size
+        if require_pos:
+            lec, off, pos_full, _ = fmoe_cuda.count_and_pos(gate.reshape(-1), n_tot, want_inv=False)
+        else:
+            lec32 = torch.zeros(n_tot, device=gate.device, dtype=torch.int32)
+            fmoe_cuda.expert_count(gate.reshape(-1), lec32)
+            lec = lec32.long()
+        if world_size > 1:
+            aec, agec, gec = fmoe_cuda.expert_exchange(lec, num_expert, world_size)
+        else:
+            gec = lec
+            aec = lec
+            agec = gec
+        pos = None
+        if require_pos:
+            pos = pos_full[: int(off[-1].item())]
+    return pos, lec, aec, gec, agec
+
+
+class Routing:
+    """Everything the layer derives from the gate indices for one forward."""
+    __slots__ = ("pos", "inv", "lec_dev", "offsets_dev", "n_rows", "lec", "gec", "aec", "agec", "rank")
+
+
+def route(gate, num_expert, world_size):
+    """Bucketing + count exchange with at most one device-to-host copy."""
+    r = Routing()
+    with torch.no_grad():
+        flat = gate.reshape(-1)
+        n_tot = num_expert * world_size
+        r.lec_dev, r.offsets_dev, r.pos, r.inv = fmoe_cuda.count_and_pos(flat, n_tot)
+        if world_size == 1:
+            r.n_rows = flat.numel()
+            r.lec = r.gec = r.aec = r.agec = None
+            r.rank = 0
+            return r
+        aec, _, _ = fmoe_cuda.expert_exchange(r.lec_dev, num_expert, world_size)
+        r.rank, _ = fmoe_cuda.comm_rank(gate.device)
+        r.aec = aec.cpu()
+        r.agec = r.aec.transpose(0, 1).contiguous()
+        r.lec = r.aec[r.rank].reshape(-1).contiguous()
+        r.gec = r.agec[r.rank].reshape(-1).contiguous()
+        r.n_rows = int(r.lec.sum())
+    return r
+
+
+def prepare_forward(gate, num_expert, world_size):
+    """Same return tuple as fmoe/functions.py:45-69 (count tensors on the CPU)."""
+    r = route(gate, num_expert, world_size)
+    if world_size == 1:
+        lec = r.lec_dev.cpu()
+        n = int(lec.sum())
+        return r.pos[:n], lec, lec, lec, lec, lec.view(1, num_expert).sum(dim=0)
+    fwd = r.gec.view(world_size, num_expert).sum(dim=0)
+    return r.pos[: r.n_rows], r.lec, r.gec, r.aec.reshape(-1), r.agec.reshape(-1), fwd
+
+
+def _local_scatter(inp, pos):
+    """out[i] = inp[pos[i]] (fmoe/functions.py:72-74)."""
+    return fmoe_cuda.local_scatter(inp.contiguous(), pos.contiguous())
+
+
+def _local_gather(inp, pos, out_batch_size, maybe_overlap=True):
+    """zeros(out_batch_size, d) then index_add_/index_copy_ at pos (fmoe/functions.py:77-84)."""
+    if maybe_overlap:
+        out = torch.zeros(out_batch_size, inp.shape[-1], dtype=inp.dtype, device=inp.device)
+        out.index_add_(0, pos, inp)
+        return out
+    return fmoe_cuda.local_gather(inp.contiguous(), pos.contiguous(), out_batch_size)
+
+
+def cached_count_host(lec, gec, stored, rank, num_expert, world_size):
+    """Host mirror of generate_cached_count (cuda/global_exchange.cu:189-195)."""
+    lec = lec.view(world_size, num_expert)
+    gec = gec.view(world_size, num_expert)
+    stored = stored.view(world_size, num_expert)
+    out = lec * stored.to(lec.dtype)
+    out[rank] += (gec * (~stored[rank]).to(gec.dtype)).sum(dim=0)
+    return out.reshape(-1)
+
+
+class MOECache(Function):
+    """Dynamic shadowing: fetch the parameters of overloaded workers' experts so
+    that their tokens are computed locally (fmoe/functions.py:121-194).
+
+    ``shadows`` maps worker index -> module that holds the fetched copy.  The
+    modules persist between calls (the reference deep-copies the experts every
+    forward); parameters and gradients are exchanged tensor by tensor, so no
+    flattened copies are made.
+    """
+
+    @staticmethod
+    def forward(ctx, inp, stored_workers, experts, shadows, world_size, rank):
+        ctx.stored_workers = stored_workers
+        ctx.experts, ctx.shadows, ctx.world_size, ctx.rank = experts, shadows, world_size, rank
+        flags = stored_workers.to(torch.bool)
+        with torch.no_grad():
+            local = list(experts.parameters())
+            for k, p in enumerate(local):
+                remote = [[list(shadows[j].parameters())[k].data] if (bool(flags[j]) and j != rank) else []
+                          for j in range(world_size)]
+                fmoe_cuda.model_exchange(flags, [p.data], remote, 1, world_size)
+        return inp.view_as(inp)
+
+    @staticmethod
+    def backward(ctx, grad_inp):
+        flags = ctx.stored_workers.to(torch.bool)
+        world_size, rank = ctx.world_size, ctx.rank
+        local = list(ctx.experts.parameters())
+        for k, p in enumerate(local):
+            if bool(flags[rank]) and p.grad is None:
+                p.grad = torch.zeros_like(p)
+            remote = []
+            for j in range(world_size):
+                if bool(flags[j]) and j != rank:
+                    q = list(ctx.shadows[j].parameters())[k]
+                    if q.grad is None:
+                        q.grad = torch.zeros_like(q)
+                    remote.append([q.grad])
+                else:
+                    remote.append([])
+            fmoe_cuda.gradient_exchange(flags, [p.grad] if bool(flags[rank]) else [p.data], remote, 1,
+                                        world_size)
+        for j in range(world_size):
+            if bool(flags[j]) and j != rank:
+                for q in ctx.shadows[j].parameters():
+                    q.grad = None
+        return grad_inp, None, None, None, None, None
+
+
+class MOEScatter(Function):
+    """Local scatter followed by the all-to-all-v (fmoe/functions.py:196-248).
+
+    ``pos`` holds row indices into ``inp`` (the caller divides by top_k, as the
+    reference's callers do).  The backward sums the k gradient rows of a token
+    with ``index_add_``-equivalent semantics.
+    """
+
+    @staticmethod
+    def forward(ctx, inp, pos, local_expert_count, global_expert_count, stored_models, fwd_batch_size,
+                world_size):
+        local_input_buf = _local_scatter(inp, pos)
+        if world_size > 1:
+            global_input_buf = fmoe_cuda.global_scatter(local_input_buf, local_expert_count,
+                                                        global_expert_count, stored_models,
+                                                        fwd_batch_size, world_size)
+        else:
+            global_input_buf = local_input_buf
+        ctx.moe_args = inp.shape[0], pos.shape[0], world_size
+        ctx.save_for_backward(pos, local_expert_count, global_expert_count, stored_models)
+        return global_input_buf
+
+    @staticmethod
+    def backward(ctx, global_grad_in):
+        pos, lec, gec, stored = ctx.saved_tensors
+        inp_batch_size, buf_batch_size, world_size = ctx.moe_args
+        global_grad_in = global_grad_in.contiguous()
+        if world_size > 1:
+            local_grad_in = fmoe_cuda.global_gather(global_grad_in, lec, gec, stored, buf_batch_size,
+                                                    world_size)
+        else:
+            local_grad_in = global_grad_in
+        grad_in = _local_gather(local_grad_in, pos, inp_batch_size)
+        return grad_in, None, None, None, None, None, None
+
+
+class MOEGather(Function):
+    """All-to-all-v back followed by the local gather (fmoe/functions.py:278-330)."""
+
+    @staticmethod
+    def forward(ctx, global_output_buf, pos, local_expert_count, global_expert_count, stored_models,
+                local_batch_size, world_size):
+        global_output_buf = global_output_buf.contiguous()
+        if world_size > 1:
+            local_output_buf = fmoe_cuda.global_gather(global_output_buf, local_expert_count,
+                                                       global_expert_count, stored_models, pos.shape[0],
+                                                       world_size)
+        else:
+            local_output_buf = global_output_buf
+        output = _local_gather(local_output_buf, pos, local_batch_size, maybe_overlap=False)
+        ctx.moe_args = (global_output_buf.shape[0], world_size)
+        ctx.save_for_backward(pos, local_expert_count, global_expert_count, stored_models)
+        return output
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        pos, lec, gec, stored = ctx.saved_tensors
+        fwd_batch_size, world_size = ctx.moe_args
+        grad_out_buf = _local_scatter(grad_out.contiguous(), pos)
+        if world_size > 1:
+            global_grad_out_buf = fmoe_cuda.global_scatter(grad_out_buf, lec, gec, stored, fwd_batch_size,
+                                                           world_size)
+        else:
+            global_grad_out_buf = grad_out_buf
+        return global_grad_out_buf, None, None, None, None, None, None
+
+
+class MOELinear(Function):
+    """Grouped expert linear layer (fmoe/functions.py:251-275)."""
+
+    @staticmethod
+    def forward(ctx, global_input_buf, fwd_expert_count, weight, bias=None):
+        counts = ExpertCounts.wrap(fwd_expert_count, global_input_buf.device)
+        x = global_input_buf.contiguous()
+        y, _ = fmoe_cuda.linear_forward_act(x, counts.offsets, weight.contiguous(), bias, _lib.ACT_NONE)
+        ctx.save_for_backward(x, counts.offsets, weight, bias)
+        return y
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        x, offsets, weight, bias = ctx.saved_tensors
+        gx, gw, gb = fmoe_cuda.linear_backward_act(grad_out.contiguous(), x, offsets, weight.contiguous(),
+                                                   None, _lib.ACT_NONE, need_bias=bias is not None,
+                                                   need_input_grad=ctx.needs_input_grad[0])
+        return gx, None, gw, gb
+
+
+# ---------------------------------------------------------------------------
+# Fused forms used by the layer's fast path
+# ---------------------------------------------------------------------------
+
+class MOEScatterFused(Function):
+    """Scatter with the division by top_k and the k-way gradient sum done in the
+    kernels: forward ``buf[i] = inp[pos[i] // k]``, backward
+    ``grad_inp[t] = sum_j grad_buf[inv[t*k+j]]`` in a fixed order.  With
+    world_size > 1 the all-to-all-v follows / precedes."""
+
+    @staticmethod
+    def forward(ctx, inp, pos, inv, top_k, n_rows, exch):
+        inp = inp.contiguous()
+        buf = fmoe_cuda.local_scatter(inp, pos, pos_div=top_k, n_rows=n_rows)
+        ctx.exch, ctx.top_k, ctx.n_tokens, ctx.n_rows = exch, top_k, inp.shape[0], n_rows
+        ctx.save_for_backward(inv)
+        if exch is not None:
+            buf = fmoe_cuda.global_scatter(buf, exch.lec, exch.gec, exch.stored, exch.fwd_batch_size,
+                                           exch.world_size)
+        return buf
+
+    @staticmethod
+    def backward(ctx, grad_buf):
+        (inv,) = ctx.saved_tensors
+        grad_buf = grad_buf.contiguous()
+        exch = ctx.exch
+        if exch is not None:
+            grad_buf = fmoe_cuda.global_gather(grad_buf, exch.lec, exch.gec, exch.stored, ctx.n_rows,
+                                               exch.world_size)
+        grad_inp = fmoe_cuda.local_gather_sum(grad_buf, inv, ctx.n_tokens, ctx.top_k)
+        return grad_inp, None, None, None, None, None
+
+
+class MOEGatherCombine(Function):
+    """Gather fused with the gate-score combine (fmoe/layers.py:319-322):
+    ``out[t] = sum_j score[t,j] * buf[inv[t*k+j]]``; rows of pruned entries
+    contribute zero, as the zero rows of the reference's ``_local_gather`` do."""
+
+    @staticmethod
+    def forward(ctx, buf, inv, score, n_rows, exch):
+        buf = buf.contiguous()
+        ctx.exch, ctx.global_rows = exch, buf.shape[0]
+        if exch is not None:
+            buf = fmoe_cuda.global_gather(buf, exch.lec, exch.gec, exch.stored, n_rows, exch.world_size)
+        score_c = score.contiguous().to(buf.dtype)
+        ctx.save_for_backward(buf, inv, score_c)
+        ctx.score_dtype = score.dtype
+        return fmoe_cuda.combine_forward(buf, inv, score_c)
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        buf, inv, score = ctx.saved_tensors
+        grad_buf, grad_score = fmoe_cuda.combine_backward(grad_out.contiguous(), buf, inv, score,
+                                                          need_score_grad=ctx.needs_input_grad[2])
+        exch = ctx.exch
+        if exch is not None:
+            grad_buf = fmoe_cuda.global_scatter(grad_buf, exch.lec, exch.gec, exch.stored, ctx.global_rows,
+                                                exch.world_size)
+        if grad_score is not None:
+            grad_score = grad_score.to(ctx.score_dtype)
+        return grad_buf, None, grad_score, None, None
+
+
+class Exchange:
+    """Host-side description of one layer call's all-to-all-v."""
+    __slots__ = ("lec", "gec", "stored", "fwd_batch_size", "world_size")
+
+    def __init__(self, lec, gec, stored, fwd_batch_size, world_size):
+        self.lec, self.gec, self.stored = lec, gec, stored
+        self.fwd_batch_size, self.world_size = fwd_batch_size, world_size
+
+
+_ACT_CODES = {"none": _lib.ACT_NONE, "relu": _lib.ACT_RELU, "gelu": _lib.ACT_GELU}
+
+
+def activation_code(fn):
+    """Maps a torch activation callable to the code of an activation the GEMM
+    epilogue can apply, or None when it must run as a separate torch op."""
+    import torch.nn.functional as F
+    if fn is None:
+        return _lib.ACT_NONE
+    if isinstance(fn, torch.nn.ReLU) or fn in (F.relu, torch.relu):
+        return _lib.ACT_RELU
+    if isinstance(fn, torch.nn.GELU):
+        return _lib.ACT_GELU if getattr(fn, "approximate", "none") == "none" else None
+    if fn is F.gelu:
+        return _lib.ACT_GELU
+    return None
+
+
+class FusedExpertMLP(Function):
+    """Linear -> activation -> Linear over all experts of a worker, with bias and
+    activation applied in the first GEMM's epilogue and the activation's backward
+    applied in the epilogue of the second layer's input-gradient GEMM."""
+
+    @staticmethod
+    def forward(ctx, x, offsets, w1, b1, w2, b2, act):
+        x = x.contiguous()
+        want_pre = act == _lib.ACT_GELU and (x.requires_grad or w1.requires_grad)
+        h, pre = fmoe_cuda.linear_forward_act(x, offsets, w1, b1, act, want_pre=want_pre)
+        y, _ = fmoe_cuda.linear_forward_act(h, offsets, w2, b2, _lib.ACT_NONE)
+        ctx.act = act
+        ctx.has_bias = (b1 is not None, b2 is not None)
+        ctx.save_for_backward(x, offsets, w1, w2, h, pre)
+        return y
+
+    @staticmethod
+    def backward(ctx, grad_y):
+        x, offsets, w1, w2, h, pre = ctx.saved_tensors
+        act = ctx.act
+        act_pre = None
+        if act == _lib.ACT_RELU:
+            act_pre = h
+        elif act == _lib.ACT_GELU:
+            act_pre = pre
+        gh, gw2, gb2 = fmoe_cuda.linear_backward_act(grad_y.contiguous(), h, offsets, w2, act_pre, act,
+                                                     need_bias=ctx.has_bias[1])
+        gx, gw1, gb1 = fmoe_cuda.linear_backward_act(gh, x, offsets, w1, None, _lib.ACT_NONE,
+                                                     need_bias=ctx.has_bias[0],
+                                                     need_input_grad=ctx.needs_input_grad[0])
+        return gx, None, gw1, gb1, gw2, gb2, None
+
+
+class AllGather(Function):
+    """All-gather along dim 0 over ``group`` with a slicing backward (fmoe/functions.py:333-352)."""
+
+    @staticmethod
+    def forward(ctx, inp, rank, world_size, group):
+        tensor_list = [torch.empty_like(inp) for _ in range(world_size)]
+        torch.distributed.all_gather(tensor_list, inp.contiguous(), group=group)
+        ctx.args = rank, inp.shape[0]
+        return torch.cat(tensor_list, dim=0)
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        rank, dim0 = ctx.args
+        return grad_out[rank * dim0: (rank + 1) * dim0], None, None, None
+
+
+class Slice(Function):
+    """Keeps this rank's slice of dim 0; backward all-gathers (fmoe/functions.py:355-375)."""
+
+    @staticmethod
+    def forward(ctx, inp, rank, world_size, group):
+        local = inp.shape[0] // world_size
+        start = local * rank
+        ctx.args = world_size, group
+        return inp[start: min(start + local, inp.shape[0])]
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        world_size, group = ctx.args
+        tensor_list = [torch.empty_like(grad_out) for _ in range(world_size)]
+        torch.distributed.all_gather(tensor_list, grad_out.contiguous(), group=group)
+        return torch.cat(tensor_list, dim=0), None, None, None

@@ -1,0 +1,363 @@
+/*
+ * fmoe_b200.h -- C ABI of libfmoe_b200.so, the sm_100a implementation of the
+ * FasterMoE mixture-of-experts layer hot path.
+ *
+ * Every entry point below replaces one operator that the reference registers
+ * in its pybind11 module `fmoe_cuda` (cuda/fmoe_cuda.cpp:105-130) or one torch
+ * index op that the reference's Python glue issues between those operators.
+ * The citation on each declaration names the reference interface it stands for.
+ *
+ * Conventions
+ *   - plain pointers and sizes only; no torch types.
+ *   - pointers are DEVICE pointers unless the parameter name ends in `_host`.
+ *   - nothing here allocates device memory or synchronises the host with the
+ *     device unless the comment says so; all work is queued on `stream`.
+ *   - return value: 0 on success, a negative FMOE_ERR_* code on failure; the
+ *     text of the last failure on the calling thread is returned by
+ *     fmoe_last_error_string().  Nothing in the library calls exit().
+ *   - count vectors use the reference's index convention
+ *     idx = expert + worker * n_expert   (cuda/global_exchange.cuh:84,101).
+ */
+#ifndef FMOE_B200_H
+#define FMOE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void* fmoe_stream_t; /* a cudaStream_t */
+typedef void* fmoe_comm_t;   /* opaque communicator created by fmoe_comm_init */
+
+enum {
+    FMOE_OK = 0,
+    FMOE_ERR_INVALID = -1,     /* bad argument (null pointer, size, alignment, dtype) */
+    FMOE_ERR_CUDA = -2,        /* a CUDA runtime/driver call failed */
+    FMOE_ERR_NCCL = -3,        /* an NCCL call failed or NCCL could not be loaded */
+    FMOE_ERR_UNSUPPORTED = -4, /* shape outside what the kernels handle */
+    FMOE_ERR_MISMATCH = -5     /* count vectors inconsistent with buffer sizes */
+};
+
+enum { FMOE_F32 = 0, FMOE_F16 = 1, FMOE_BF16 = 2 };
+enum { FMOE_ACT_NONE = 0, FMOE_ACT_RELU = 1, FMOE_ACT_GELU = 2 };
+
+const char* fmoe_last_error_string(void);
+/* Library version, and the compute capability it was built for (100). */
+int fmoe_version(void);
+int fmoe_built_for_sm(void);
+
+/* ------------------------------------------------------------------------
+ * Routing: counting, bucketing, capacity            (integer work, bit-exact)
+ * ---------------------------------------------------------------------- */
+
+/* Upper bound on n_expert_total accepted by the routing kernels. */
+#define FMOE_MAX_EXPERTS 4096
+
+/* Bytes of scratch that the bucketing kernels below need for `n` gate entries
+ * and `n_expert_total` experts (per-tile histograms). */
+size_t fmoe_routing_scratch_bytes(int64_t n, int32_t n_expert_total);
+
+/* expert_count(gate_idx, expert_count): cuda/fmoe_cuda.cpp:52-54,
+ * cuda/local_exchange.cu:22-32.  Adds, for every entry of gate_idx[0..n) that
+ * is not -1, one to expert_count[gate_idx[i]].  expert_count is int32 and is
+ * accumulated into (the caller zero-fills it, as fmoe/functions.py:21-24). */
+int fmoe_expert_count(const int64_t* gate_idx, int32_t* expert_count,
+                      int64_t n, int32_t n_expert_total, fmoe_stream_t stream);
+
+/* assign_pos(cum_count, gate, pos): cuda/fmoe_cuda.cpp:48-51,
+ * cuda/local_exchange.cu:5-20.  cum_count is the inclusive prefix sum of the
+ * expert counts; segment e of pos, [cum[e]-cnt[e], cum[e]), receives the flat
+ * indices i with gate[i]==e.  Inside a segment the reference's order is the
+ * arrival order of atomics; this library always writes ascending i, which is
+ * one of the orders the reference can produce.  Like the reference, cum_count
+ * is consumed: on return it holds cum[e]-cnt[e].
+ * scratch: fmoe_routing_scratch_bytes(n, n_expert_total) bytes. */
+int fmoe_assign_pos(int32_t* cum_count, const int64_t* gate, int64_t* pos,
+                    int64_t n, int32_t n_expert_total, void* scratch,
+                    fmoe_stream_t stream);
+
+/* Fused replacement of the sequence in count_by_gate (fmoe/functions.py:19-41):
+ * expert_count -> .long() -> cumsum -> assign_pos, without the host read of
+ * the total.  Outputs (any may be NULL except pos):
+ *   lec64[E_tot]      counts as int64
+ *   offsets[E_tot+1]  exclusive prefix sum as int64 (offsets[E_tot] = #kept)
+ *   pos[n]            bucketed flat indices; entries past offsets[E_tot] are -1
+ *   inv[n]            inverse: inv[i] = row of flat index i in pos, -1 if gate[i]==-1
+ */
+int fmoe_count_and_pos(const int64_t* gate, int64_t n, int32_t n_expert_total,
+                       int64_t* lec64, int64_t* offsets, int64_t* pos, int64_t* inv,
+                       void* scratch, fmoe_stream_t stream);
+
+/* limit_by_capacity(expert_count, capacity, n_expert, n_worker):
+ * cuda/fmoe_cuda.cpp:72-74, cuda/balancing.cu:7-20.  For each local expert e,
+ * sources w are served in ascending order: eca[w*E+e] = min(ec[w*E+e], what is
+ * left of cap[e]).  cap[e] is decremented by the sum of all requests, as the
+ * reference's atomicSub does. */
+int fmoe_limit_by_capacity(const int64_t* ec, int32_t* cap, int64_t* eca,
+                           int32_t n_expert, int32_t n_worker, fmoe_stream_t stream);
+
+/* prune_gate_by_capacity(gate_idx, expert_count, n_expert, n_worker):
+ * cuda/fmoe_cuda.cpp:75-77, cuda/balancing.cu:22-37.  The first ec[e] entries
+ * (lowest flat index) routed to expert e keep their value, the others become
+ * -1; ec[e] is decremented by the number of entries routed to e.  Entries that
+ * are already -1 stay -1 and are not counted (the reference leaves that case
+ * undefined). */
+int fmoe_prune_gate_by_capacity(const int64_t* gate_idx, int64_t* new_gate_idx,
+                                int32_t* ec, int64_t n, int32_t n_expert_total,
+                                void* scratch, fmoe_stream_t stream);
+
+/* ------------------------------------------------------------------------
+ * Token permutation                                  (byte copies, bit-exact)
+ * ---------------------------------------------------------------------- */
+
+/* _local_scatter: fmoe/functions.py:72-74 (torch.index_select).
+ * out[i,:] = inp[pos[i] / pos_div, :] for i in [0,n_rows).  The reference's
+ * callers pass pos//top_k (fmoe/layers.py:136); pos_div performs that division
+ * inside the kernel.  row_bytes = d_model * element size. */
+int fmoe_local_scatter(const void* inp, const int64_t* pos, void* out,
+                       int64_t n_rows, int64_t n_inp_rows, int64_t row_bytes,
+                       int32_t pos_div, fmoe_stream_t stream);
+
+/* _local_gather with maybe_overlap=False: fmoe/functions.py:77-84
+ * (zeros + index_copy_).  out has n_out_rows rows; out[pos[i],:] = buf[i,:],
+ * every other row is zero.  inv_scratch: n_out_rows int64 (inverse map built
+ * here) so that each output row is written exactly once. */
+int fmoe_local_gather(const void* buf, const int64_t* pos, void* out,
+                      int64_t n_rows, int64_t n_out_rows, int64_t row_bytes,
+                      int64_t* inv_scratch, fmoe_stream_t stream);
+
+/* Same as fmoe_local_gather when the caller already holds the inverse map
+ * (inv[r] = source row or -1), e.g. from fmoe_count_and_pos. */
+int fmoe_local_gather_inv(const void* buf, const int64_t* inv, void* out,
+                          int64_t n_out_rows, int64_t row_bytes, fmoe_stream_t stream);
+
+/* _local_gather with maybe_overlap=True as used by MOEScatter.backward:
+ * fmoe/functions.py:77-84,232-248 (zeros + index_add_ at pos//top_k).
+ * out[t,:] = sum_j buf[inv[t*top_k+j],:] over the j with inv >= 0, added in
+ * ascending j in fp32 (the reference adds with atomics in arbitrary order). */
+int fmoe_local_gather_sum(const void* buf, const int64_t* inv, void* out,
+                          int64_t n_tokens, int32_t top_k, int64_t d, int32_t dtype,
+                          fmoe_stream_t stream);
+
+/* Weighted combine: fmoe/layers.py:319-322 (bmm of score[T,1,k] with x[T,k,d]),
+ * optionally fused with the preceding local gather (inv != NULL):
+ *   out[t,:] = sum_j score[t,j] * src_row(t*k+j),
+ *   src_row(r) = inv ? (inv[r] >= 0 ? buf[inv[r]] : 0) : buf[r].
+ * score has the dtype of buf. */
+int fmoe_combine_forward(const void* buf, const int64_t* inv, const void* score,
+                         void* out, int64_t n_tokens, int32_t top_k, int64_t d,
+                         int32_t dtype, fmoe_stream_t stream);
+
+/* Backward of fmoe_combine_forward:
+ *   grad_buf[inv[r],:] = score[r] * grad_out[r / k,:]   (rows of grad_buf are
+ *       indexed through inv when inv != NULL, else grad_buf[r,:]),
+ *   grad_score[t,j]    = dot(grad_out[t,:], src_row(t*k+j))   (may be NULL). */
+int fmoe_combine_backward(const void* grad_out, const void* buf, const int64_t* inv,
+                          const void* score, void* grad_buf, void* grad_score,
+                          int64_t n_tokens, int32_t top_k, int64_t d, int32_t dtype,
+                          fmoe_stream_t stream);
+
+/* ------------------------------------------------------------------------
+ * Grouped expert GEMM (fmoe_linear)
+ * ---------------------------------------------------------------------- */
+
+/* Bytes of scratch needed by fmoe_linear_backward (split accumulation of the
+ * weight gradient). */
+size_t fmoe_linear_scratch_bytes(int64_t n_rows, int64_t in_feat, int64_t out_feat,
+                                 int32_t n_expert, int32_t dtype);
+
+/* linear_forward(input, expert_count, weight, bias): cuda/fmoe_cuda.cpp:57-62,
+ * cuda/parallel_linear.cu:5-49.  For each expert e with rows
+ * [seg_offsets[e], seg_offsets[e+1]):  Y = X * W_e^T (+ b_e), then the optional
+ * activation (the reference applies its activation as a separate torch call,
+ * fmoe/transformer.py:28).  X [n_rows,in_feat], W [E,out_feat,in_feat],
+ * bias [E,out_feat] or NULL, Y [n_rows,out_feat], all row-major, dtype as given;
+ * accumulation is fp32.  seg_offsets: DEVICE int64[E+1], exclusive prefix sum
+ * of the reference's expert_count.  pre_act (may be NULL): receives the value
+ * before the activation, which the backward of GELU needs. */
+int fmoe_linear_forward(const void* x, const void* weight, const void* bias,
+                        const int64_t* seg_offsets, void* y, void* pre_act,
+                        int64_t n_rows, int64_t in_feat, int64_t out_feat,
+                        int32_t n_expert, int32_t dtype, int32_t activation,
+                        fmoe_stream_t stream);
+
+/* linear_backward(grad_out, input, expert_count, weight, bias):
+ * cuda/fmoe_cuda.cpp:63-69, cuda/parallel_linear.cu:52-94.
+ *   dX[seg_e] = dY[seg_e] * W_e           [n_rows,in_feat]
+ *   dW_e      = dY[seg_e]^T * X[seg_e]    [E,out_feat,in_feat]  (zero if empty)
+ *   db_e      = column sums of dY[seg_e]  [E,out_feat]          (NULL to skip)
+ * Any of grad_x, grad_w, grad_b may be NULL to skip that product.
+ * When act_pre [n_rows,in_feat] != NULL, dX is multiplied element-wise by
+ * activation'(act_pre) before it is stored: the backward of the activation
+ * that produced x, which the reference runs as a separate kernel
+ * (cuda/fused_compute.cuh:155) or leaves to autograd.
+ * accumulate != 0 adds into dW/db instead of overwriting them (what the smart
+ * schedule's later pipeline steps do, cuda/fused_compute.cuh:120). */
+int fmoe_linear_backward(const void* grad_y, const void* x, const void* weight,
+                         const int64_t* seg_offsets, const void* act_pre,
+                         void* grad_x, void* grad_w, void* grad_b,
+                         int64_t n_rows, int64_t in_feat, int64_t out_feat,
+                         int32_t n_expert, int32_t dtype, int32_t activation,
+                         int32_t accumulate, void* scratch, fmoe_stream_t stream);
+
+/* ------------------------------------------------------------------------
+ * Expert-parallel exchange over NCCL
+ * ---------------------------------------------------------------------- */
+
+/* Replaces ensure_nccl (cuda/fmoe_cuda.cpp:44, cuda/global_exchange.cu:84-119):
+ * rank 0 obtains a 128-byte id, the host program broadcasts it (any channel),
+ * and every rank calls fmoe_comm_init with the CUDA device it computes on. */
+int fmoe_comm_unique_id(void* id128_host);
+int fmoe_comm_init(const void* id128_host, int32_t rank, int32_t world_size,
+                   int32_t device, fmoe_comm_t* comm_out);
+int fmoe_comm_destroy(fmoe_comm_t comm);
+int fmoe_comm_rank(fmoe_comm_t comm, int32_t* rank_out, int32_t* world_out);
+
+/* expert_exchange(local_expert_count, n_expert, n_workers):
+ * cuda/fmoe_cuda.cpp:8-10, cuda/global_exchange.cu:8-24.
+ * aec[src][dst][e] = all-gather of lec; agec[dst][src][e] = its transpose;
+ * gec = agec[rank].  All int64 on the device. */
+int fmoe_expert_exchange(fmoe_comm_t comm, const int64_t* lec, int64_t* aec,
+                         int64_t* agec, int64_t* gec, int32_t n_expert,
+                         int32_t n_workers, fmoe_stream_t stream);
+
+/* One entry of an exchange plan: `rows` rows move from row offset src_row of
+ * the source buffer to row offset dst_row of the destination buffer.
+ * peer == rank means a copy inside this GPU. */
+typedef struct {
+    int32_t peer;
+    int32_t is_send;  /* 1: this rank sends src rows to peer; 0: receives into dst */
+    int64_t src_row;  /* valid when is_send or local */
+    int64_t dst_row;  /* valid when !is_send or local */
+    int64_t rows;
+    int32_t local;    /* 1: device-to-device copy on this GPU */
+    int32_t step;     /* smart-schedule pipeline step the move belongs to (0 if unused) */
+} fmoe_move_t;
+
+/* Host-only planning of global_scatter (cuda/global_exchange.cuh:60-144): which
+ * row ranges go where, including the rows kept local for shadowed experts.
+ * Writes at most max_moves entries and returns the count in *n_moves, the
+ * number of rows of the receive buffer in *recv_rows.  The plan of
+ * global_gather (cuda/global_exchange.cuh:146-230) is the same list with
+ * source and destination swapped.  Touches no GPU. */
+int fmoe_plan_global_scatter(const int64_t* lec_host, const int64_t* gec_host,
+                             const uint8_t* stored_models_host, int32_t rank,
+                             int32_t n_expert, int32_t n_workers,
+                             fmoe_move_t* moves, int32_t max_moves,
+                             int32_t* n_moves, int64_t* recv_rows);
+
+/* global_scatter / global_gather: cuda/fmoe_cuda.cpp:11-22,
+ * cuda/global_exchange.cu:26-80.  Counts and flags are HOST pointers, as in the
+ * reference.  The whole exchange is one NCCL group.  out_rows is checked
+ * against the plan (FMOE_ERR_MISMATCH) before anything is queued.
+ * global_gather zero-fills local_out rows that receive nothing. */
+int fmoe_global_scatter(fmoe_comm_t comm, const void* local_in, void* global_out,
+                        const int64_t* lec_host, const int64_t* gec_host,
+                        const uint8_t* stored_models_host, int64_t in_rows,
+                        int64_t out_rows, int64_t row_bytes, int32_t n_expert,
+                        int32_t n_workers, fmoe_stream_t stream);
+int fmoe_global_gather(fmoe_comm_t comm, const void* global_in, void* local_out,
+                       const int64_t* lec_host, const int64_t* gec_host,
+                       const uint8_t* stored_models_host, int64_t in_rows,
+                       int64_t out_rows, int64_t row_bytes, int32_t n_expert,
+                       int32_t n_workers, fmoe_stream_t stream);
+
+/* exchange_cache_info(sent_models, num_expert, world_size):
+ * cuda/fmoe_cuda.cpp:24-27, cuda/global_exchange.cuh:232-249.  All-gather of
+ * n_expert flag bytes per rank. */
+int fmoe_exchange_cache_info(fmoe_comm_t comm, const uint8_t* sent_models,
+                             uint8_t* stored_models, int32_t n_expert,
+                             int32_t n_workers, fmoe_stream_t stream);
+
+/* model_exchange: cuda/fmoe_cuda.cpp:28-32, cuda/global_exchange.cuh:251-282.
+ * One broadcast of `bytes` bytes rooted at `root`; buf is the owner's flat
+ * parameter buffer on the root and the shadow buffer elsewhere. */
+int fmoe_model_broadcast(fmoe_comm_t comm, void* buf, int64_t bytes, int32_t root,
+                         fmoe_stream_t stream);
+
+/* gradient_exchange: cuda/fmoe_cuda.cpp:38-42, cuda/global_exchange.cuh:285-348.
+ * In-place sum-reduce of `count` elements to `root`. */
+int fmoe_gradient_reduce(fmoe_comm_t comm, void* buf, int64_t count, int32_t dtype,
+                         int32_t root, fmoe_stream_t stream);
+
+/* generate_cached_count: cuda/fmoe_cuda.cpp:33-37, cuda/global_exchange.cu:175-196.
+ * out[w*E+e] = lec[w*E+e]*stored[w*E+e]; out[rank*E+e] += sum_w gec[w*E+e] when
+ * stored[rank*E+e] is false.  All device pointers; int64 counts, byte flags. */
+int fmoe_generate_cached_count(const int64_t* lec, const int64_t* gec,
+                               const uint8_t* stored_models, int64_t* out,
+                               int32_t rank, int32_t n_expert, int32_t n_workers,
+                               fmoe_stream_t stream);
+
+/* ------------------------------------------------------------------------
+ * Smart schedule: pipelined exchange + two-layer expert MLP
+ * ---------------------------------------------------------------------- */
+
+typedef struct {
+    const void* w1;  /* [E, d_hidden, d_model] */
+    const void* w2;  /* [E, d_model, d_hidden] */
+    const void* b1;  /* [E, d_hidden] or NULL  */
+    const void* b2;  /* [E, d_model]  or NULL  */
+    void* gw1;       /* gradients, same shapes; used by fused_backward only */
+    void* gw2;
+    void* gb1;
+    void* gb2;
+} fmoe_mlp_params_t;
+
+/* Row offsets that the smart schedule uses (cuda/fused_compute.cuh:216-248):
+ * local_ptr[i] = exclusive prefix of lec; global_ptr[e*W+w] = exclusive prefix,
+ * expert-major then source, of the rows this rank still receives;
+ * local_global_ptr[i] = exclusive prefix of the rows kept local for shadowed
+ * experts.  Each output has E*W+1 entries.  Host-only. */
+int fmoe_fused_compute_ptrs(const int64_t* lec_host, const int64_t* gec_host,
+                            const uint8_t* stored_models_host, int32_t rank,
+                            int32_t n_expert, int32_t n_workers,
+                            int64_t* local_ptr, int64_t* global_ptr,
+                            int64_t* local_global_ptr);
+
+/* Scratch bytes for fmoe_fused_forward / fmoe_fused_backward. */
+size_t fmoe_fused_scratch_bytes(int64_t global_rows, int64_t local_rows,
+                                int64_t d_model, int64_t d_hidden, int32_t n_expert,
+                                int32_t n_workers, int32_t dtype);
+
+/* fused_forward: cuda/fmoe_cuda.cpp:80-87, cuda/fused_compute.cu:12-62,
+ * cuda/fused_compute.cuh:250-388.  params_host[w] is the parameter set of
+ * worker w's experts (own experts at index rank; shadows where
+ * stored_models says so; others ignored).  Buffers (caller-allocated):
+ * local_in [A,d], local_out [A,d], global_in [B,d], middle [B+S,h] where S is
+ * the number of rows kept local for shadowed experts, global_out [B,d].
+ * The exchange runs per peer on comm_stream, the expert GEMMs on `stream`,
+ * ordered with events; on return all work has been queued and `stream`
+ * waits for comm_stream.  pipeline_gran: peers per step (FMOE_FUSE_GRAN). */
+int fmoe_fused_forward(fmoe_comm_t comm, const void* local_in, void* local_out,
+                       void* global_in, void* middle, void* global_out,
+                       const fmoe_mlp_params_t* params_host,
+                       const int64_t* lec_host, const int64_t* gec_host,
+                       const uint8_t* stored_models_host,
+                       int64_t local_rows, int64_t global_rows,
+                       int64_t d_model, int64_t d_hidden, int32_t n_expert,
+                       int32_t n_workers, int32_t dtype, int32_t activation,
+                       int32_t pipeline_gran, void* scratch,
+                       fmoe_stream_t stream, fmoe_stream_t comm_stream);
+
+/* fused_backward: cuda/fmoe_cuda.cpp:88-100, cuda/fused_compute.cu:64-131,
+ * cuda/fused_compute.cuh:391-542.  Weight gradients are written into
+ * params_host[w].gw*: the own experts' are overwritten at the first pipeline
+ * step and accumulated afterwards; shadowed experts' are accumulated. */
+int fmoe_fused_backward(fmoe_comm_t comm, const void* grad_out_local, void* grad_in_local,
+                        const void* local_in, const void* global_in, const void* middle,
+                        void* global_grad_out, void* grad_middle, void* global_grad_in,
+                        const fmoe_mlp_params_t* params_host,
+                        const int64_t* lec_host, const int64_t* gec_host,
+                        const uint8_t* stored_models_host,
+                        int64_t local_rows, int64_t global_rows,
+                        int64_t d_model, int64_t d_hidden, int32_t n_expert,
+                        int32_t n_workers, int32_t dtype, int32_t activation,
+                        int32_t pipeline_gran, void* scratch,
+                        fmoe_stream_t stream, fmoe_stream_t comm_stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FMOE_B200_H */

@@ -1,0 +1,125 @@
+"""The CPU oracle against outputs recorded from the reference's own Python code
+(tests/golden/reference_cpu.npz, made by tests/golden/make_golden.py)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import moe_oracle as O
+
+LAYER_CASES = ["layer_e4_k2_gelu", "layer_e8_k3_gelu", "layer_e4_k2_relu", "layer_e16_k2_gelu"]
+
+
+def t(a):
+    return torch.from_numpy(np.asarray(a))
+
+
+@pytest.mark.parametrize("tag", LAYER_CASES)
+def test_layer_matches_reference(golden, tag):
+    z = {k.split("/", 1)[1]: golden[k] for k in golden.files if k.startswith(tag + "/")}
+    T, d, h, E, k, act, seed = z["meta"].tolist()
+    act = {2: "gelu", 1: "relu"}[act]
+    res = O.moe_layer_fwd_bwd(t(z["x"]), t(z["gate_w"]), t(z["gate_b"]), t(z["w1"]), t(z["b1"]), t(z["w2"]),
+                              t(z["b2"]), k, act=act)
+    assert np.array_equal(res["gate_idx"].numpy(), z["idx"])
+    np.testing.assert_allclose(res["gate_score"].numpy(), z["score"], rtol=1e-6, atol=1e-7)
+    np.testing.assert_allclose(res["out"].numpy(), z["out"], rtol=1e-5, atol=1e-6)
+    for name in ("x", "gate_w", "gate_b", "w1", "b1", "w2", "b2"):
+        np.testing.assert_allclose(res["grad_" + name].numpy(), z["grad_" + name], rtol=1e-5, atol=1e-6,
+                                   err_msg=name)
+
+
+def test_gate_returns_raw_logits(golden):
+    z = golden
+    idx, score, logits = O.naive_gate(t(z["layer_e4_k2_gelu/x"]), t(z["layer_e4_k2_gelu/gate_w"]),
+                                      t(z["layer_e4_k2_gelu/gate_b"]), 2)
+    assert np.array_equal(idx.numpy(), z["layer_e4_k2_gelu/idx"])
+    # not a softmax: rows do not sum to one
+    assert not np.allclose(z["layer_e4_k2_gelu/score"].sum(1), 1.0)
+    np.testing.assert_allclose(torch.gather(logits, 1, idx).numpy(), z["layer_e4_k2_gelu/score"], rtol=1e-6)
+
+
+def test_local_scatter_gather(golden):
+    inp, gate, pos = golden["local/inp"], golden["local/gate_idx"], golden["local/pos"]
+    assert np.array_equal(O.assign_pos(gate, 4), pos)
+    buf = inp[pos // 2]
+    assert np.array_equal(buf, golden["local/buf"])
+    back = np.zeros((24, inp.shape[1]), dtype=inp.dtype)
+    back[pos] = buf
+    assert np.array_equal(back, golden["local/back_copy"])
+    inv = O.inverse_pos(pos, 24)
+    add = np.zeros_like(inp)
+    for tok in range(12):
+        for j in range(2):
+            if inv[tok * 2 + j] >= 0:
+                add[tok] += buf[inv[tok * 2 + j]]
+    np.testing.assert_allclose(add, golden["local/back_add"], rtol=1e-6, atol=1e-7)
+
+
+@pytest.mark.parametrize("tag", ["skew40", "uniform", "zipf", "w2"])
+def test_policy(golden, tag):
+    aec = golden[f"policy/{tag}/aec"]
+    W, E, d_model, alpha = golden[f"policy/{tag}/meta"].tolist()
+    W, E, d_model = int(W), int(E), int(d_model)
+    agec = aec.transpose(1, 0, 2)
+    want = golden[f"policy/{tag}/res"]
+    got = O.global_policy(aec, agec, E, W, d_model, True, alpha)
+    assert np.array_equal(got, want)
+    # the product's host-side policy (same constants) must agree as well
+    os.environ["FMOE_ENABLE_DYNREP"] = "1"
+    try:
+        from fastermoe_b200.transformer import _gen_policy
+        pol = _gen_policy(alpha, constants="reference")
+    finally:
+        os.environ["FMOE_ENABLE_DYNREP"] = "0"
+    res = pol(t(aec).long(), t(agec.copy()).long(), E, W, d_model, True)
+    assert np.array_equal(res.numpy(), want)
+
+
+@pytest.mark.parametrize("tag", ["few_leaving", "many_leaving", "uniform"])
+def test_hir_gate(golden, tag):
+    z = {k.split("/", 2)[2]: golden[k] for k in golden.files if k.startswith(f"hir/{tag}/")}
+    W, E, d, T, rank, policy_on = z["meta"].tolist()
+    aec = z["aec"].copy()
+    stored = np.zeros(W * E, dtype=bool)
+    if policy_on:
+        # the recorded run replaced row `rank` of the table by the rank's own counts
+        idx0 = torch.topk(torch.nn.functional.linear(t(z["x"]), t(z["gate_w"]), t(z["gate_b"])), 2)[1]
+        aec[rank] = O.expert_count(idx0.numpy(), W * E).reshape(W, E)
+        st = O.global_policy(aec, aec.transpose(1, 0, 2), E, W, d, True, 4.0)
+        stored = np.repeat(st.any(1), E)
+    idx, score = O.hir_gate(t(z["x"]), t(z["gate_w"]), t(z["gate_b"]), E, W, rank // 4, stored)
+    assert np.array_equal(idx.numpy(), z["idx"])
+    np.testing.assert_allclose(score.numpy(), z["score"], rtol=1e-6, atol=1e-7)
+
+
+def test_routing_oracle_invariants():
+    rng = np.random.default_rng(0)
+    for n, E in [(0, 4), (1, 1), (257, 3), (4096, 64)]:
+        gate = rng.integers(-1, E, size=n)
+        cnt = O.expert_count(gate, E)
+        pos = O.assign_pos(gate, E)
+        assert cnt.sum() == (gate >= 0).sum() == len(pos)
+        assert np.array_equal(gate[pos], np.repeat(np.arange(E), cnt))
+        cap = rng.integers(0, max(1, n // max(E, 1)) + 2, size=E)
+        pruned, left = O.prune_gate_by_capacity(gate, cap)
+        kept = O.expert_count(pruned, E)
+        assert np.array_equal(kept, np.minimum(cnt, cap))
+        assert np.array_equal(left, cap - cnt)
+        assert np.all((pruned == gate) | (pruned == -1))
+
+
+def test_exchange_oracle_roundtrip():
+    rng = np.random.default_rng(1)
+    W, E, d = 4, 3, 5
+    lecs = [rng.integers(0, 6, size=W * E) for _ in range(W)]
+    for stored in (np.zeros(W * E, bool), np.repeat(np.array([False, True, False, False]), E)):
+        bufs = [rng.standard_normal((int(l.sum()), d)).astype(np.float32) for l in lecs]
+        g = O.global_scatter(bufs, lecs, stored, E, W)
+        _, _, gecs = O.expert_exchange(lecs, E, W)
+        for r in range(W):
+            assert g[r].shape[0] == O.generate_cached_count(lecs[r], gecs[r], stored, r, E, W).sum()
+        back = O.global_gather(g, lecs, stored, E, W)
+        for r in range(W):
+            assert np.array_equal(back[r], bufs[r])
