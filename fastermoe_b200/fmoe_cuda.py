@@ -28,6 +28,58 @@ from ._lib import lib, check
 _DT = {torch.float32: _lib.F32, torch.float16: _lib.F16, torch.bfloat16: _lib.BF16}
 
 
+# Kernel launches issued by one call of each C entry point (for launch accounting).
+_KERNELS = {"expert_count": 1, "assign_pos": 4, "count_and_pos": 4, "limit_by_capacity": 1,
+            "prune_gate_by_capacity": 4, "local_scatter": 1, "local_gather": 3, "local_gather_inv": 1,
+            "local_gather_sum": 1, "combine_forward": 1, "combine_backward": 1, "linear_forward": 1,
+            "linear_backward": 3, "expert_exchange": 2, "generate_cached_count": 1}
+
+
+class Profile:
+    """Optional per-call accounting: number of library calls / kernel launches and,
+    when ``timing`` is set, CUDA-event durations of each call on the current stream."""
+
+    def __init__(self, timing=False):
+        self.timing = timing
+        self.calls = {}
+        self.launches = 0
+        self.events = []
+
+    def durations_ms(self):
+        """{op name: [ms per call]}; synchronises the device."""
+        torch.cuda.synchronize()
+        out = {}
+        for name, a, b in self.events:
+            out.setdefault(name, []).append(a.elapsed_time(b))
+        return out
+
+
+_profile = None
+
+
+def set_profile(p):
+    """Installs (or with None removes) a Profile that every operator call reports to."""
+    global _profile
+    _profile = p
+
+
+def _run(name, fn, *args):
+    p = _profile
+    if p is None:
+        check(fn(*args), name)
+        return
+    p.calls[name] = p.calls.get(name, 0) + 1
+    p.launches += _KERNELS.get(name, 1)
+    if p.timing:
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        check(fn(*args), name)
+        b.record()
+        p.events.append((name, a, b))
+    else:
+        check(fn(*args), name)
+
+
 def _dtype_code(t):
     try:
         return _DT[t.dtype]
@@ -70,8 +122,8 @@ def expert_count(gate_idx, expert_count):
     _check_cuda(gate_idx, expert_count)
     assert gate_idx.dtype == torch.int64 and expert_count.dtype == torch.int32
     with torch.cuda.device(gate_idx.device):
-        check(lib.fmoe_expert_count(_ptr(gate_idx), _ptr(expert_count), gate_idx.numel(),
-                                    expert_count.numel(), _stream()), "expert_count")
+        _run("expert_count", lib.fmoe_expert_count, _ptr(gate_idx), _ptr(expert_count), gate_idx.numel(),
+                                    expert_count.numel(), _stream())
 
 
 def assign_pos(cum_count, gate, pos):
@@ -81,8 +133,8 @@ def assign_pos(cum_count, gate, pos):
     n, e = gate.numel(), cum_count.numel()
     with torch.cuda.device(gate.device):
         scratch = _routing_scratch(n, e, gate.device)
-        check(lib.fmoe_assign_pos(_ptr(cum_count), _ptr(gate), _ptr(pos), n, e, _ptr(scratch),
-                                  _stream()), "assign_pos")
+        _run("assign_pos", lib.fmoe_assign_pos, _ptr(cum_count), _ptr(gate), _ptr(pos), n, e, _ptr(scratch),
+                                  _stream())
 
 
 # ---------------------------------------------------------------------------
@@ -96,8 +148,8 @@ def limit_by_capacity(expert_count, capacity, n_expert, n_worker):
     assert expert_count.numel() == n_expert * n_worker and capacity.numel() == n_expert
     out = torch.empty_like(expert_count)
     with torch.cuda.device(expert_count.device):
-        check(lib.fmoe_limit_by_capacity(_ptr(expert_count), _ptr(capacity), _ptr(out), n_expert,
-                                         n_worker, _stream()), "limit_by_capacity")
+        _run("limit_by_capacity", lib.fmoe_limit_by_capacity, _ptr(expert_count), _ptr(capacity), _ptr(out), n_expert,
+                                         n_worker, _stream())
     return out
 
 
@@ -110,8 +162,8 @@ def prune_gate_by_capacity(gate_idx, expert_count, n_expert, n_worker):
     n, e = gate_idx.numel(), expert_count.numel()
     with torch.cuda.device(gate_idx.device):
         scratch = _routing_scratch(n, e, gate_idx.device)
-        check(lib.fmoe_prune_gate_by_capacity(_ptr(gate_idx), _ptr(out), _ptr(expert_count), n, e,
-                                              _ptr(scratch), _stream()), "prune_gate_by_capacity")
+        _run("prune_gate_by_capacity", lib.fmoe_prune_gate_by_capacity, _ptr(gate_idx), _ptr(out), _ptr(expert_count), n, e,
+                                              _ptr(scratch), _stream())
     return out
 
 
@@ -191,19 +243,19 @@ def ensure_nccl(group, t):
         world = dist.get_world_size(group)
         ident = (ctypes.c_uint8 * 128)()
         if rank == 0:
-            check(lib.fmoe_comm_unique_id(ident), "comm_unique_id")
+            _run("comm_unique_id", lib.fmoe_comm_unique_id, ident)
         box = [bytes(ident)]
         src = dist.get_global_rank(group, 0) if group is not None else 0
         dist.broadcast_object_list(box, src=src, group=group)
         ident = (ctypes.c_uint8 * 128).from_buffer_copy(box[0])
         handle = ctypes.c_void_p()
-        check(lib.fmoe_comm_init(ident, rank, world, dev, ctypes.byref(handle)), "comm_init")
+        _run("comm_init", lib.fmoe_comm_init, ident, rank, world, dev, ctypes.byref(handle))
         _comms[dev] = handle
 
 
 def comm_rank(device):
     r, w = ctypes.c_int32(), ctypes.c_int32()
-    check(lib.fmoe_comm_rank(_comm(device), ctypes.byref(r), ctypes.byref(w)), "comm_rank")
+    _run("comm_rank", lib.fmoe_comm_rank, _comm(device), ctypes.byref(r), ctypes.byref(w))
     return r.value, w.value
 
 
@@ -224,8 +276,8 @@ def expert_exchange(local_expert_count, n_expert, n_workers):
     agec = local_expert_count.new_empty((n_workers, n_workers, n_expert))
     gec = torch.empty_like(local_expert_count)
     with torch.cuda.device(dev):
-        check(lib.fmoe_expert_exchange(_comm(dev), _ptr(local_expert_count), _ptr(aec), _ptr(agec),
-                                       _ptr(gec), n_expert, n_workers, _stream()), "expert_exchange")
+        _run("expert_exchange", lib.fmoe_expert_exchange, _comm(dev), _ptr(local_expert_count), _ptr(aec), _ptr(agec),
+                                       _ptr(gec), n_expert, n_workers, _stream())
     return [aec, agec, gec]
 
 
@@ -251,8 +303,8 @@ def _global_move(fn, name, buf, local_expert_count, global_expert_count, stored_
     out = buf.new_empty((batch_size, buf.shape[1]))
     row_bytes = buf.shape[1] * buf.element_size()
     with torch.cuda.device(buf.device):
-        check(fn(_comm(buf.device), _ptr(buf), _ptr(out), _ptr(lec), _ptr(gec), _ptr(st), buf.shape[0],
-                 batch_size, row_bytes, n_expert, n_workers, _stream()), name)
+        _run(name, fn, _comm(buf.device), _ptr(buf), _ptr(out), _ptr(lec), _ptr(gec), _ptr(st), buf.shape[0],
+             batch_size, row_bytes, n_expert, n_workers, _stream())
     return out
 
 
@@ -276,8 +328,8 @@ def exchange_cache_info(sent_models, num_expert, world_size):
     assert sent_models.dtype == torch.bool and sent_models.numel() == num_expert
     stored = sent_models.new_zeros((world_size, num_expert))
     with torch.cuda.device(sent_models.device):
-        check(lib.fmoe_exchange_cache_info(_comm(sent_models.device), _ptr(sent_models), _ptr(stored),
-                                           num_expert, world_size, _stream()), "exchange_cache_info")
+        _run("exchange_cache_info", lib.fmoe_exchange_cache_info, _comm(sent_models.device), _ptr(sent_models), _ptr(stored),
+                                           num_expert, world_size, _stream())
     return [sent_models, stored]
 
 
@@ -298,8 +350,8 @@ def model_exchange(stored_models, local_params, params, num_expert, world_size):
                     continue
                 buf = local_params[i] if j == rank else params[j][i]
                 _check_cuda(buf)
-                check(lib.fmoe_model_broadcast(_comm(dev), _ptr(buf), buf.numel() * buf.element_size(),
-                                               j, _stream()), "model_exchange")
+                _run("model_exchange", lib.fmoe_model_broadcast, _comm(dev), _ptr(buf), buf.numel() * buf.element_size(),
+                                               j, _stream())
     return rank
 
 
@@ -313,8 +365,8 @@ def generate_cached_count(local_expert_count, global_expert_count, stored_models
     st = stored_models.reshape(-1).to(torch.uint8).contiguous()
     out = torch.empty_like(lec)
     with torch.cuda.device(dev):
-        check(lib.fmoe_generate_cached_count(_ptr(lec), _ptr(gec), _ptr(st), _ptr(out), rank, num_expert,
-                                             world_size, _stream()), "generate_cached_count")
+        _run("generate_cached_count", lib.fmoe_generate_cached_count, _ptr(lec), _ptr(gec), _ptr(st), _ptr(out), rank, num_expert,
+                                             world_size, _stream())
     return out
 
 
@@ -330,8 +382,8 @@ def gradient_exchange(stored_models, local_grads, grads, num_expert, world_size)
                     continue
                 buf = local_grads[i] if j == rank else grads[j][i]
                 _check_cuda(buf)
-                check(lib.fmoe_gradient_reduce(_comm(dev), _ptr(buf), buf.numel(), _dtype_code(buf), j,
-                                               _stream()), "gradient_exchange")
+                _run("gradient_exchange", lib.fmoe_gradient_reduce, _comm(dev), _ptr(buf), buf.numel(), _dtype_code(buf), j,
+                                               _stream())
 
 
 # ---------------------------------------------------------------------------
@@ -354,8 +406,8 @@ def count_and_pos(gate, n_expert_total, want_inv=True):
     inv = torch.empty(n, dtype=torch.int64, device=dev) if want_inv else None
     with torch.cuda.device(dev):
         scratch = _routing_scratch(n, n_expert_total, dev)
-        check(lib.fmoe_count_and_pos(_ptr(gate), n, n_expert_total, _ptr(lec), _ptr(off), _ptr(pos),
-                                     _ptr(inv), _ptr(scratch), _stream()), "count_and_pos")
+        _run("count_and_pos", lib.fmoe_count_and_pos, _ptr(gate), n, n_expert_total, _ptr(lec), _ptr(off), _ptr(pos),
+                                     _ptr(inv), _ptr(scratch), _stream())
     return lec, off, pos, inv
 
 
@@ -365,8 +417,8 @@ def local_scatter(inp, pos, pos_div=1, n_rows=None):
     n = pos.numel() if n_rows is None else n_rows
     out = inp.new_empty((n, inp.shape[1]))
     with torch.cuda.device(inp.device):
-        check(lib.fmoe_local_scatter(_ptr(inp), _ptr(pos), _ptr(out), n, inp.shape[0],
-                                     inp.shape[1] * inp.element_size(), pos_div, _stream()), "local_scatter")
+        _run("local_scatter", lib.fmoe_local_scatter, _ptr(inp), _ptr(pos), _ptr(out), n, inp.shape[0],
+                                     inp.shape[1] * inp.element_size(), pos_div, _stream())
     return out
 
 
@@ -376,8 +428,8 @@ def local_gather(buf, pos, out_rows):
     out = buf.new_empty((out_rows, buf.shape[1]))
     with torch.cuda.device(buf.device):
         inv = torch.empty(out_rows, dtype=torch.int64, device=buf.device)
-        check(lib.fmoe_local_gather(_ptr(buf), _ptr(pos), _ptr(out), pos.numel(), out_rows,
-                                    buf.shape[1] * buf.element_size(), _ptr(inv), _stream()), "local_gather")
+        _run("local_gather", lib.fmoe_local_gather, _ptr(buf), _ptr(pos), _ptr(out), pos.numel(), out_rows,
+                                    buf.shape[1] * buf.element_size(), _ptr(inv), _stream())
     return out
 
 
@@ -386,8 +438,8 @@ def local_gather_inv(buf, inv):
     _check_cuda(buf, inv)
     out = buf.new_empty((inv.numel(), buf.shape[1]))
     with torch.cuda.device(buf.device):
-        check(lib.fmoe_local_gather_inv(_ptr(buf), _ptr(inv), _ptr(out), inv.numel(),
-                                        buf.shape[1] * buf.element_size(), _stream()), "local_gather_inv")
+        _run("local_gather_inv", lib.fmoe_local_gather_inv, _ptr(buf), _ptr(inv), _ptr(out), inv.numel(),
+                                        buf.shape[1] * buf.element_size(), _stream())
     return out
 
 
@@ -396,8 +448,8 @@ def local_gather_sum(buf, inv, n_tokens, top_k):
     _check_cuda(buf, inv)
     out = buf.new_empty((n_tokens, buf.shape[1]))
     with torch.cuda.device(buf.device):
-        check(lib.fmoe_local_gather_sum(_ptr(buf), _ptr(inv), _ptr(out), n_tokens, top_k, buf.shape[1],
-                                        _dtype_code(buf), _stream()), "local_gather_sum")
+        _run("local_gather_sum", lib.fmoe_local_gather_sum, _ptr(buf), _ptr(inv), _ptr(out), n_tokens, top_k, buf.shape[1],
+                                        _dtype_code(buf), _stream())
     return out
 
 
@@ -408,8 +460,8 @@ def combine_forward(buf, inv, score):
     assert score.dtype == buf.dtype
     out = buf.new_empty((n_tokens, buf.shape[1]))
     with torch.cuda.device(buf.device):
-        check(lib.fmoe_combine_forward(_ptr(buf), _ptr(inv), _ptr(score), _ptr(out), n_tokens, top_k,
-                                       buf.shape[1], _dtype_code(buf), _stream()), "combine_forward")
+        _run("combine_forward", lib.fmoe_combine_forward, _ptr(buf), _ptr(inv), _ptr(score), _ptr(out), n_tokens, top_k,
+                                       buf.shape[1], _dtype_code(buf), _stream())
     return out
 
 
@@ -421,9 +473,9 @@ def combine_backward(grad_out, buf, inv, score, need_score_grad=True):
     grad_buf = torch.empty_like(buf)
     grad_score = torch.empty_like(score) if need_score_grad else None
     with torch.cuda.device(buf.device):
-        check(lib.fmoe_combine_backward(_ptr(grad_out), _ptr(buf), _ptr(inv), _ptr(score), _ptr(grad_buf),
+        _run("combine_backward", lib.fmoe_combine_backward, _ptr(grad_out), _ptr(buf), _ptr(inv), _ptr(score), _ptr(grad_buf),
                                         _ptr(grad_score), n_tokens, top_k, buf.shape[1], _dtype_code(buf),
-                                        _stream()), "combine_backward")
+                                        _stream())
     return grad_buf, grad_score
 
 
@@ -436,9 +488,9 @@ def linear_forward_act(x, seg_offsets, weight, bias, activation, want_pre=False)
     y = x.new_empty((x.shape[0], out_feat))
     pre = x.new_empty((x.shape[0], out_feat)) if want_pre else None
     with torch.cuda.device(x.device):
-        check(lib.fmoe_linear_forward(_ptr(x), _ptr(weight), _ptr(bias), _ptr(seg_offsets), _ptr(y),
+        _run("linear_forward", lib.fmoe_linear_forward, _ptr(x), _ptr(weight), _ptr(bias), _ptr(seg_offsets), _ptr(y),
                                       _ptr(pre), x.shape[0], in_feat, out_feat, n_expert, _dtype_code(x),
-                                      activation, _stream()), "linear_forward")
+                                      activation, _stream())
     return y, pre
 
 
@@ -455,8 +507,8 @@ def linear_backward_act(grad_y, x, seg_offsets, weight, act_pre, activation, nee
     with torch.cuda.device(x.device):
         nbytes = lib.fmoe_linear_scratch_bytes(n_rows, in_feat, out_feat, n_expert, _dtype_code(x))
         scratch = _scratch(nbytes, x.device)
-        check(lib.fmoe_linear_backward(_ptr(grad_y), _ptr(x), _ptr(weight), _ptr(seg_offsets),
+        _run("linear_backward", lib.fmoe_linear_backward, _ptr(grad_y), _ptr(x), _ptr(weight), _ptr(seg_offsets),
                                        _ptr(act_pre), _ptr(gx), _ptr(gw), _ptr(gb), n_rows, in_feat,
                                        out_feat, n_expert, _dtype_code(x), activation,
-                                       1 if accumulate else 0, _ptr(scratch), _stream()), "linear_backward")
+                                       1 if accumulate else 0, _ptr(scratch), _stream())
     return gx, gw, gb
