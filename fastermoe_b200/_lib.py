@@ -46,6 +46,7 @@ _SIGS = {
     "fmoe_last_error_string": (c_char_p, []),
     "fmoe_version": (c_int32, []),
     "fmoe_built_for_sm": (c_int32, []),
+    "fmoe_device_status": (I32, [POINTER(c_int32)]),
     "fmoe_routing_scratch_bytes": (c_size_t, [I64, I32]),
     "fmoe_expert_count": (I32, [P, P, I64, I32, P]),
     "fmoe_assign_pos": (I32, [P, P, P, I64, I32, P, P]),

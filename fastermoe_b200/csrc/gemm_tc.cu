@@ -1,10 +1,647 @@
-// tcgen05 grouped GEMM back end (placeholder until the tensor-core kernels land).
+// Grouped expert GEMM on the 5th-generation tensor cores (tcgen05 + TMEM + TMA).
+//
+// One persistent, warp-specialised kernel per product of the reference's
+// fmoe_linear (cuda/parallel_linear.cuh:55-161, where each is a loop of cuBLAS
+// calls, one per expert):
+//
+//   FWD    Y[m,n]     = sum_k X[m,k]  W_e[n,k]   (+bias, activation)   m ragged per expert
+//   DGRAD  dX[m,k]    = sum_n dY[m,n] W_e[n,k]   (* act'(pre))         m ragged per expert
+//   WGRAD  dW_e[n,k]  = sum_m dY[m,n] X[m,k]                           contraction ragged
+//
+// CTA = 6 warps: warp 0 issues TMA loads (one lane), warp 1 issues tcgen05.mma
+// (one lane; the whole warp helps to zero ragged tails for WGRAD), warps 2-5
+// drain the accumulator from TMEM (tcgen05.ld), apply the epilogue and store.
+// Tile 128 x 256 x 64 (bf16/fp16 in, fp32 accumulate), 4 shared-memory stages of
+// 48 KB, two 256-column TMEM accumulators so that the epilogue of a tile overlaps
+// the main loop of the next one.  Operands are staged with the 128-byte swizzle;
+// K-major operands use one 64x(128|256) box, MN-major operands (the transposed
+// reads of DGRAD/WGRAD) are fetched as 64x64 boxes laid 8 KB apart, which is the
+// canonical MN-major layout of the UMMA shared-memory descriptor.
+//
+// The work list is derived on the device from the expert segment offsets, so
+// the host never reads the counts.  Every mbarrier wait is bounded: on expiry
+// the kernel raises a status word, drains and exits (see fmoe_device_status).
 #include "common.cuh"
 #include "gemm.h"
+#include <cuda.h>
+#include <mutex>
+
 namespace fmoe {
-bool tc_forward_supported(const LinearArgs&) { return false; }
-bool tc_backward_supported(const LinearBwdArgs&) { return false; }
-int tc_linear_forward(const LinearArgs&, cudaStream_t) { return fail(FMOE_ERR_UNSUPPORTED, "tcgen05 path not built"); }
-int tc_linear_backward(const LinearBwdArgs&, cudaStream_t) { return fail(FMOE_ERR_UNSUPPORTED, "tcgen05 path not built"); }
+namespace {
+
+constexpr int BM = 128, BN = 256, BK = 64;
+constexpr int STAGES = 4;
+constexpr int A_BYTES = BM * BK * 2;  // 16 KB
+constexpr int B_BYTES = BN * BK * 2;  // 32 KB
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int SUB_BYTES = 64 * BK * 2;  // one 64x64 box: 8 KB
+constexpr int MAX_EXPERTS_TC = 256;
+constexpr int THREADS = 192;
+constexpr int TMEM_COLS = 512;
+constexpr unsigned long long WAIT_LIMIT_CYCLES = 4000000000ull;  // ~2 s at 1.9 GHz
+
+enum { MODE_FWD = 0, MODE_DGRAD = 1, MODE_WGRAD = 2 };
+
+struct Params {
+    const int64_t* seg;  // [n_expert + 1]
+    int n_expert;
+    int n_out;    // output columns (FWD: out_feat, DGRAD: in_feat, WGRAD: in_feat)
+    int n_contr;  // contraction length for FWD/DGRAD (WGRAD: ragged, from seg)
+    int w_rows;   // rows of one expert's weight matrix (out_feat): B row offset per expert
+    int out_rows_per_expert;  // WGRAD: out_feat
+    void* out;
+    void* pre_out;        // FWD only
+    const void* bias;     // FWD only
+    const void* act_pre;  // DGRAD only
+    int act;
+    int accumulate;  // WGRAD only
+    int is_bf16;
+    int* status;  // device status word
+};
+
+struct Shared {
+    unsigned long long full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2];
+    uint32_t tmem_base;
+    int abort;
+    int cum_tiles[MAX_EXPERTS_TC + 1];
+    int seg[MAX_EXPERTS_TC + 1];
+};
+
+__device__ int g_status = 0;
+
+// ---- PTX wrappers ------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(unsigned long long* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false (and raises the status word) when the barrier did
+// not complete within the limit or another role has already given up.
+__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, uint32_t parity, Shared* sh, int* status, int code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = clock64();
+    while (true) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (*(volatile int*)&sh->abort) return false;
+        if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+            *(volatile int*)&sh->abort = 1;
+            atomicCAS(status, 0, code);
+            return false;
+        }
+    }
+}
+__device__ __forceinline__ void tma_load_2d(const CUtensorMap* map, unsigned long long* bar, void* dst, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
+        : "memory");
+}
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(unsigned long long* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_mma(uint32_t tmem_c, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_c), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t* v) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+          "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+          "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor for tcgen05.mma (128-byte swizzle).
+//   bits [0,14)  start address >> 4      bits [16,30) leading byte offset >> 4
+//   bits [32,46) stride byte offset >> 4 bits [46,48) version = 1
+//   bits [61,64) layout type, 2 = SWIZZLE_128B
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr >> 4) & 0x3FFF);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+// Instruction descriptor, kind::f16: fp32 accumulate, A/B both bf16 or both fp16.
+//   [4,6) C format (1 = f32)  [7,10) A format  [10,13) B format (0 = f16, 1 = bf16)
+//   [15] A major (1 = MN)  [16] B major (1 = MN)  [17,23) N >> 3  [24,29) M >> 4
+__host__ __device__ constexpr uint32_t make_idesc(bool bf16, bool a_mn, bool b_mn) {
+    return (1u << 4) | ((bf16 ? 1u : 0u) << 7) | ((bf16 ? 1u : 0u) << 10) | ((a_mn ? 1u : 0u) << 15) |
+           ((b_mn ? 1u : 0u) << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+
+template <bool BF16> __device__ __forceinline__ float cvt_in(uint16_t raw) {
+    if (BF16) return __uint_as_float((uint32_t)raw << 16);
+    return __half2float(__ushort_as_half(raw));
+}
+template <bool BF16> __device__ __forceinline__ uint32_t cvt_pack(float lo, float hi) {
+    if (BF16) {
+        __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+        return *reinterpret_cast<uint32_t*>(&v);
+    }
+    __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+struct Tile {
+    int e, row0, rows, col0, chunks;  // rows/row0: output rows of the tile (FWD/DGRAD: tokens; WGRAD: weight rows)
+    int m_lo, m_hi;                   // WGRAD: contraction range
+};
+
+template <int MODE>
+__device__ __forceinline__ void locate(const Shared* sh, const Params& p, int tile, int& e_cursor, Tile& t) {
+    while (tile >= sh->cum_tiles[e_cursor + 1]) ++e_cursor;
+    const int local = tile - sh->cum_tiles[e_cursor];
+    const int nt = (p.n_out + BN - 1) / BN;
+    t.e = e_cursor;
+    const int lo = sh->seg[e_cursor], hi = sh->seg[e_cursor + 1];
+    if (MODE == MODE_WGRAD) {
+        t.row0 = (local / nt) * BM;
+        t.rows = min(BM, p.out_rows_per_expert - t.row0);
+        t.col0 = (local % nt) * BN;
+        t.m_lo = lo;
+        t.m_hi = hi;
+        t.chunks = (hi - lo + BK - 1) / BK;
+    } else {
+        t.row0 = lo + (local / nt) * BM;
+        t.rows = min(BM, hi - t.row0);
+        t.col0 = (local % nt) * BN;
+        t.chunks = (p.n_contr + BK - 1) / BK;
+        t.m_lo = t.m_hi = 0;
+    }
+}
+
+template <int MODE, bool BF16>
+__global__ void __launch_bounds__(THREADS, 1)
+grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                    const Params p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    Shared* sh = (Shared*)(tiles + STAGES * STAGE_BYTES);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    // ---- set-up ---------------------------------------------------------------
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&sh->full[s], 1);
+            mbar_init(&sh->empty[s], 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(&sh->tmem_full[a], 1);
+            mbar_init(&sh->tmem_empty[a], 4);
+        }
+        sh->abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    for (int e = threadIdx.x; e <= p.n_expert; e += THREADS) sh->seg[e] = (int)p.seg[e];
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const int nt = (p.n_out + BN - 1) / BN;
+        int acc = 0;
+        sh->cum_tiles[0] = 0;
+        for (int e = 0; e < p.n_expert; ++e) {
+            int mt;
+            if (MODE == MODE_WGRAD) mt = (p.out_rows_per_expert + BM - 1) / BM;
+            else mt = (sh->seg[e + 1] - sh->seg[e] + BM - 1) / BM;
+            acc += mt * nt;
+            sh->cum_tiles[e + 1] = acc;
+        }
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sh->tmem_base)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = sh->tmem_base;
+    const int total_tiles = sh->cum_tiles[p.n_expert];
+
+    if (warp == 0) {
+        // ---- TMA producer -----------------------------------------------------
+        if (lane == 0) {
+            int s = 0, e_cur = 0;
+            uint32_t ph = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                Tile t;
+                locate<MODE>(sh, p, tile, e_cur, t);
+                for (int ch = 0; ch < t.chunks; ++ch) {
+                    if (!(ok = mbar_wait(&sh->empty[s], ph ^ 1, sh, p.status, 1))) break;
+                    uint8_t* a_dst = tiles + s * STAGE_BYTES;
+                    uint8_t* b_dst = a_dst + A_BYTES;
+                    mbar_expect_tx(&sh->full[s], STAGE_BYTES);
+                    if (MODE == MODE_FWD) {
+                        tma_load_2d(&map_a, &sh->full[s], a_dst, ch * BK, t.row0);
+                        tma_load_2d(&map_b, &sh->full[s], b_dst, ch * BK, t.e * p.w_rows + t.col0);
+                    } else if (MODE == MODE_DGRAD) {
+                        tma_load_2d(&map_a, &sh->full[s], a_dst, ch * BK, t.row0);
+#pragma unroll
+                        for (int j = 0; j < BN / 64; ++j)
+                            tma_load_2d(&map_b, &sh->full[s], b_dst + j * SUB_BYTES, t.col0 + j * 64,
+                                        t.e * p.w_rows + ch * BK);
+                    } else {
+                        const int m0 = t.m_lo + ch * BK;
+#pragma unroll
+                        for (int j = 0; j < BM / 64; ++j)
+                            tma_load_2d(&map_a, &sh->full[s], a_dst + j * SUB_BYTES, t.row0 + j * 64, m0);
+#pragma unroll
+                        for (int j = 0; j < BN / 64; ++j)
+                            tma_load_2d(&map_b, &sh->full[s], b_dst + j * SUB_BYTES, t.col0 + j * 64, m0);
+                    }
+                    if (++s == STAGES) { s = 0; ph ^= 1; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---- MMA issuer -------------------------------------------------------
+        constexpr bool A_MN = MODE == MODE_WGRAD, B_MN = MODE != MODE_FWD;
+        constexpr uint32_t idesc = make_idesc(BF16, A_MN, B_MN);
+        // K-major: 8-row groups 1024 B apart, K advance 32 B per UMMA_K=16.
+        // MN-major: 64-element column blocks 8 KB apart (leading), 8-row K groups 1024 B apart (stride),
+        //           K advance 16 rows x 128 B = 2048 B.
+        constexpr uint32_t A_LBO = A_MN ? SUB_BYTES : 16, A_ADV = A_MN ? 2048 : 32;
+        constexpr uint32_t B_LBO = B_MN ? SUB_BYTES : 16, B_ADV = B_MN ? 2048 : 32;
+        int s = 0, e_cur = 0, acc = 0;
+        uint32_t ph = 0, acc_ph = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            Tile t;
+            locate<MODE>(sh, p, tile, e_cur, t);
+            if (t.chunks == 0) continue;
+            if (!(ok = mbar_wait(&sh->tmem_empty[acc], acc_ph ^ 1, sh, p.status, 2))) break;
+            tc_fence_after();
+            const uint32_t tmem_c = tmem_base + acc * BN;
+            for (int ch = 0; ch < t.chunks; ++ch) {
+                if (!(ok = mbar_wait(&sh->full[s], ph, sh, p.status, 3))) break;
+                tc_fence_after();
+                uint8_t* a_src = tiles + s * STAGE_BYTES;
+                uint8_t* b_src = a_src + A_BYTES;
+                if (MODE == MODE_WGRAD) {
+                    // Rows of the chunk past the end of the expert's segment belong to the
+                    // next expert (or are uninitialised): clear them in both operands.  A
+                    // row is one 128-byte line per 64-column block, whatever the swizzle.
+                    const int valid = t.m_hi - (t.m_lo + ch * BK);
+                    if (valid < BK) {
+                        const int lines = (BK - valid) * ((BM + BN) / 64);
+                        for (int i = lane; i < lines * 8; i += 32) {
+                            const int line = i >> 3, part = i & 7;
+                            const int blk = line / (BK - valid), r = valid + line % (BK - valid);
+                            uint8_t* base = a_src + blk * SUB_BYTES;  // blocks of A then B are contiguous
+                            *reinterpret_cast<uint4*>(base + r * 128 + part * 16) = make_uint4(0, 0, 0, 0);
+                        }
+                        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                        __syncwarp();
+                    }
+                }
+                if (lane == 0) {
+                    const uint64_t adesc = make_desc(smem_u32(a_src), A_LBO, 1024);
+                    const uint64_t bdesc = make_desc(smem_u32(b_src), B_LBO, 1024);
+#pragma unroll
+                    for (int k = 0; k < BK / 16; ++k)
+                        tc_mma(tmem_c, adesc + (uint64_t)((k * A_ADV) >> 4), bdesc + (uint64_t)((k * B_ADV) >> 4),
+                               idesc, (ch > 0 || k > 0) ? 1u : 0u);
+                    tc_commit(&sh->empty[s]);
+                }
+                __syncwarp();
+                if (++s == STAGES) { s = 0; ph ^= 1; }
+            }
+            if (!ok) break;
+            if (lane == 0) tc_commit(&sh->tmem_full[acc]);
+            __syncwarp();
+            if (++acc == 2) { acc = 0; acc_ph ^= 1; }
+        }
+    } else {
+        // ---- epilogue (warps 2..5) -------------------------------------------
+        const int quarter = warp & 3;  // TMEM lanes [32*quarter, +32) are readable by this warp
+        const int r = quarter * 32 + lane;
+        int e_cur = 0, acc = 0;
+        uint32_t acc_ph = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            Tile t;
+            locate<MODE>(sh, p, tile, e_cur, t);
+            const bool row_ok = r < t.rows;
+            uint16_t* out_row;
+            if (MODE == MODE_WGRAD)
+                out_row = (uint16_t*)p.out + ((size_t)t.e * p.out_rows_per_expert + t.row0 + r) * (size_t)p.n_out;
+            else
+                out_row = (uint16_t*)p.out + (size_t)(t.row0 + r) * (size_t)p.n_out;
+            if (t.chunks == 0) {
+                // WGRAD of an expert without rows: the gradient is zero.
+                if (!p.accumulate && row_ok)
+                    for (int c = 0; c < BN && t.col0 + c < p.n_out; c += 8)
+                        *reinterpret_cast<uint4*>(out_row + t.col0 + c) = make_uint4(0, 0, 0, 0);
+                continue;
+            }
+            if (!(ok = mbar_wait(&sh->tmem_full[acc], acc_ph, sh, p.status, 4))) break;
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                const int col = t.col0 + c0;
+                if (col >= p.n_out) break;
+                uint32_t raw[32];
+                tc_ld32(taddr + c0, raw);
+                tc_wait_ld();
+                if (!row_ok) continue;
+                float v[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(raw[i]);
+                if (MODE == MODE_FWD) {
+                    if (p.bias) {
+                        const uint4* bp = reinterpret_cast<const uint4*>((const uint16_t*)p.bias + (size_t)t.e * p.n_out + col);
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            const uint4 b = __ldg(bp + q);
+                            const uint32_t w[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                v[q * 8 + 2 * i] += cvt_in<BF16>((uint16_t)(w[i] & 0xffff));
+                                v[q * 8 + 2 * i + 1] += cvt_in<BF16>((uint16_t)(w[i] >> 16));
+                            }
+                        }
+                    }
+                    if (p.pre_out) {
+                        uint16_t* pr = (uint16_t*)p.pre_out + (size_t)(t.row0 + r) * (size_t)p.n_out + col;
+#pragma unroll
+                        for (int q = 0; q < 4; ++q)
+                            *reinterpret_cast<uint4*>(pr + q * 8) =
+                                make_uint4(cvt_pack<BF16>(v[q * 8], v[q * 8 + 1]), cvt_pack<BF16>(v[q * 8 + 2], v[q * 8 + 3]),
+                                           cvt_pack<BF16>(v[q * 8 + 4], v[q * 8 + 5]), cvt_pack<BF16>(v[q * 8 + 6], v[q * 8 + 7]));
+                    }
+                    if (p.act != FMOE_ACT_NONE) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) v[i] = apply_act(v[i], p.act);
+                    }
+                } else if (MODE == MODE_DGRAD) {
+                    if (p.act_pre) {
+                        const uint4* ap = reinterpret_cast<const uint4*>((const uint16_t*)p.act_pre + (size_t)(t.row0 + r) * (size_t)p.n_out + col);
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            const uint4 a = __ldg(ap + q);
+                            const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                v[q * 8 + 2 * i] *= act_grad(cvt_in<BF16>((uint16_t)(w[i] & 0xffff)), p.act);
+                                v[q * 8 + 2 * i + 1] *= act_grad(cvt_in<BF16>((uint16_t)(w[i] >> 16)), p.act);
+                            }
+                        }
+                    }
+                } else if (p.accumulate) {
+                    const uint4* op = reinterpret_cast<const uint4*>(out_row + col);
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const uint4 a = op[q];
+                        const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            v[q * 8 + 2 * i] += cvt_in<BF16>((uint16_t)(w[i] & 0xffff));
+                            v[q * 8 + 2 * i + 1] += cvt_in<BF16>((uint16_t)(w[i] >> 16));
+                        }
+                    }
+                }
+#pragma unroll
+                for (int q = 0; q < 4; ++q)
+                    *reinterpret_cast<uint4*>(out_row + col + q * 8) =
+                        make_uint4(cvt_pack<BF16>(v[q * 8], v[q * 8 + 1]), cvt_pack<BF16>(v[q * 8 + 2], v[q * 8 + 3]),
+                                   cvt_pack<BF16>(v[q * 8 + 4], v[q * 8 + 5]), cvt_pack<BF16>(v[q * 8 + 6], v[q * 8 + 7]));
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sh->tmem_empty[acc]);
+            if (++acc == 2) { acc = 0; acc_ph ^= 1; }
+        }
+    }
+
+    // ---- teardown -------------------------------------------------------------
+    if (*(volatile int*)&sh->abort) {
+        // Give copies that may still be in flight time to land before the CTA's
+        // shared memory is released.
+        const unsigned long long t0 = clock64();
+        while (clock64() - t0 < 2000000ull) { }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// ---- host side ---------------------------------------------------------------
+typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                             const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                             CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn get_encode() {
+    static EncodeFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeFn)p;
+    });
+    return fn;
+}
+
+// 2-D row-major tensor [rows, cols] of 16-bit elements, box [box_rows, 64 cols], 128-byte swizzle.
+int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int box_rows, bool bf16) {
+    EncodeFn enc = get_encode();
+    if (!enc) return fail(FMOE_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
+                     const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail(FMOE_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d) for a [%lld, %lld] tensor", (int)r,
+                    (long long)rows, (long long)cols);
+    return 0;
+}
+
+constexpr size_t SMEM_BYTES = 1024 + (size_t)STAGES * STAGE_BYTES + sizeof(Shared);
+
+// Device address of the status word on the current device (cached per device).
+int* status_ptr() {
+    static int* cache[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+    if (!cache[dev]) {
+        int* p = nullptr;
+        if (cudaGetSymbolAddress((void**)&p, g_status) == cudaSuccess) cache[dev] = p;
+    }
+    return cache[dev];
+}
+
+template <int MODE>
+int launch(const CUtensorMap& ma, const CUtensorMap& mb, const Params& p, int64_t max_tiles, cudaStream_t st) {
+    auto kern = p.is_bf16 ? grouped_gemm_kernel<MODE, true> : grouped_gemm_kernel<MODE, false>;
+    FMOE_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
+    const unsigned grid = (unsigned)std::max<int64_t>(1, std::min<int64_t>(max_tiles, sm_count()));
+    kern<<<grid, THREADS, SMEM_BYTES, st>>>(ma, mb, p);
+    FMOE_CHECK_LAUNCH();
+    return 0;
+}
+
+bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
+
+bool shape_ok(int64_t n_rows, int64_t in_feat, int64_t out_feat, int n_expert, int dtype) {
+    return (dtype == FMOE_BF16 || dtype == FMOE_F16) && n_expert <= MAX_EXPERTS_TC && in_feat % 64 == 0 &&
+           out_feat % 64 == 0 && in_feat >= 256 && out_feat >= 256 && n_rows > 0 && n_rows < ((int64_t)1 << 31) &&
+           (int64_t)n_expert * out_feat < ((int64_t)1 << 31);
+}
+
+// Column sums of dY per expert segment (bias gradient), fp32 accumulate.
+template <bool BF16>
+__global__ void __launch_bounds__(256)
+bias_grad_tc_kernel(const uint16_t* __restrict__ dy, const int64_t* __restrict__ seg, uint16_t* __restrict__ db,
+                    int out_feat, int accumulate) {
+    // block: 64 columns (as 32 pairs) x 8 row lanes
+    __shared__ float red[8][64];
+    const int e = blockIdx.y;
+    const int cp = threadIdx.x & 31, ry = threadIdx.x >> 5;
+    const int col = blockIdx.x * 64 + cp * 2;
+    const int64_t lo = seg[e], hi = seg[e + 1];
+    float s0 = 0.f, s1 = 0.f;
+    if (col < out_feat)
+        for (int64_t m = lo + ry; m < hi; m += 8) {
+            const uint32_t w = __ldg(reinterpret_cast<const uint32_t*>(dy + m * out_feat + col));
+            s0 += cvt_in<BF16>((uint16_t)(w & 0xffff));
+            s1 += cvt_in<BF16>((uint16_t)(w >> 16));
+        }
+    red[ry][cp * 2] = s0;
+    red[ry][cp * 2 + 1] = s1;
+    __syncthreads();
+    if (ry == 0 && col < out_feat) {
+        float t0 = 0.f, t1 = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { t0 += red[i][cp * 2]; t1 += red[i][cp * 2 + 1]; }
+        uint32_t* o = reinterpret_cast<uint32_t*>(db + (size_t)e * out_feat + col);
+        if (accumulate) {
+            const uint32_t w = *o;
+            t0 += cvt_in<BF16>((uint16_t)(w & 0xffff));
+            t1 += cvt_in<BF16>((uint16_t)(w >> 16));
+        }
+        *o = cvt_pack<BF16>(t0, t1);
+    }
+}
+
+}  // namespace
+
+bool tc_forward_supported(const LinearArgs& a) {
+    return shape_ok(a.n_rows, a.in_feat, a.out_feat, a.n_expert, a.dtype) && aligned16(a.x) && aligned16(a.weight) &&
+           aligned16(a.y) && (!a.bias || aligned16(a.bias)) && (!a.pre_act || aligned16(a.pre_act));
+}
+
+bool tc_backward_supported(const LinearBwdArgs& a) {
+    return shape_ok(a.n_rows, a.in_feat, a.out_feat, a.n_expert, a.dtype) && aligned16(a.grad_y) &&
+           aligned16(a.weight) && (!a.x || aligned16(a.x)) && (!a.grad_x || aligned16(a.grad_x)) &&
+           (!a.grad_w || aligned16(a.grad_w)) && (!a.act_pre || aligned16(a.act_pre)) &&
+           (!a.grad_b || ((uintptr_t)a.grad_b & 3) == 0);
+}
+
 size_t tc_backward_scratch_bytes(int64_t, int64_t, int64_t, int, int) { return 0; }
+
+int tc_linear_forward(const LinearArgs& a, cudaStream_t st) {
+    const bool bf16 = a.dtype == FMOE_BF16;
+    CUtensorMap ma, mb;
+    if (int rc = make_map(&ma, a.x, a.n_rows, a.in_feat, BM, bf16)) return rc;
+    if (int rc = make_map(&mb, a.weight, (int64_t)a.n_expert * a.out_feat, a.in_feat, BN, bf16)) return rc;
+    Params p{};
+    p.seg = a.seg_offsets; p.n_expert = a.n_expert; p.n_out = (int)a.out_feat; p.n_contr = (int)a.in_feat;
+    p.w_rows = (int)a.out_feat; p.out = a.y; p.pre_out = a.pre_act; p.bias = a.bias; p.act = a.activation;
+    p.is_bf16 = bf16; p.status = status_ptr();
+    const int64_t max_tiles = (ceil_div(a.n_rows, BM) + a.n_expert) * ceil_div(a.out_feat, BN);
+    return launch<MODE_FWD>(ma, mb, p, max_tiles, st);
+}
+
+int tc_linear_backward(const LinearBwdArgs& a, cudaStream_t st) {
+    const bool bf16 = a.dtype == FMOE_BF16;
+    if (a.grad_x && a.n_rows > 0) {
+        CUtensorMap ma, mb;
+        if (int rc = make_map(&ma, a.grad_y, a.n_rows, a.out_feat, BM, bf16)) return rc;
+        if (int rc = make_map(&mb, a.weight, (int64_t)a.n_expert * a.out_feat, a.in_feat, 64, bf16)) return rc;
+        Params p{};
+        p.seg = a.seg_offsets; p.n_expert = a.n_expert; p.n_out = (int)a.in_feat; p.n_contr = (int)a.out_feat;
+        p.w_rows = (int)a.out_feat; p.out = a.grad_x; p.act_pre = a.act_pre; p.act = a.activation;
+        p.is_bf16 = bf16; p.status = status_ptr();
+        const int64_t max_tiles = (ceil_div(a.n_rows, BM) + a.n_expert) * ceil_div(a.in_feat, BN);
+        if (int rc = launch<MODE_DGRAD>(ma, mb, p, max_tiles, st)) return rc;
+    }
+    if (a.grad_w) {
+        CUtensorMap ma, mb;
+        // Tensor maps need at least one row; with no rows at all every expert is empty
+        // and the kernel only writes zeros.
+        const int64_t rows = std::max<int64_t>(a.n_rows, 1);
+        if (int rc = make_map(&ma, a.grad_y, rows, a.out_feat, 64, bf16)) return rc;
+        if (int rc = make_map(&mb, a.x, rows, a.in_feat, 64, bf16)) return rc;
+        Params p{};
+        p.seg = a.seg_offsets; p.n_expert = a.n_expert; p.n_out = (int)a.in_feat; p.n_contr = 0;
+        p.out_rows_per_expert = (int)a.out_feat; p.out = a.grad_w; p.accumulate = a.accumulate;
+        p.is_bf16 = bf16; p.status = status_ptr();
+        const int64_t max_tiles = (int64_t)a.n_expert * ceil_div(a.out_feat, BM) * ceil_div(a.in_feat, BN);
+        if (int rc = launch<MODE_WGRAD>(ma, mb, p, max_tiles, st)) return rc;
+    }
+    if (a.grad_b) {
+        dim3 grid((unsigned)ceil_div(a.out_feat, 64), (unsigned)a.n_expert);
+        if (bf16)
+            bias_grad_tc_kernel<true><<<grid, 256, 0, st>>>((const uint16_t*)a.grad_y, a.seg_offsets, (uint16_t*)a.grad_b, (int)a.out_feat, a.accumulate);
+        else
+            bias_grad_tc_kernel<false><<<grid, 256, 0, st>>>((const uint16_t*)a.grad_y, a.seg_offsets, (uint16_t*)a.grad_b, (int)a.out_feat, a.accumulate);
+        FMOE_CHECK_LAUNCH();
+    }
+    return 0;
+}
+
+int read_device_status(int* out) {
+    int v = 0;
+    FMOE_CUDA_TRY(cudaMemcpyFromSymbol(&v, g_status, sizeof(int)));
+    *out = v;
+    return 0;
+}
+
 }  // namespace fmoe
+
+extern "C" int fmoe_device_status(int32_t* status_out) {
+    FMOE_REQUIRE(status_out, "device_status: null pointer");
+    int v = 0;
+    if (int rc = fmoe::read_device_status(&v)) return rc;
+    *status_out = v;
+    return 0;
+}

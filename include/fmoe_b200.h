@@ -47,6 +47,10 @@ const char* fmoe_last_error_string(void);
 /* Library version, and the compute capability it was built for (100). */
 int fmoe_version(void);
 int fmoe_built_for_sm(void);
+/* Reads the status word that the tensor-core kernels raise when one of their
+ * bounded waits expires (0 = none; 1..4 = which wait).  Copies from the device,
+ * so it waits for the work queued before it.  No counterpart in the reference. */
+int fmoe_device_status(int32_t* status_out);
 
 /* ------------------------------------------------------------------------
  * Routing: counting, bucketing, capacity            (integer work, bit-exact)

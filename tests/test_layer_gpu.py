@@ -66,11 +66,13 @@ def test_cpu_baseline_config_fp32():
     tol = dict(rtol=1e-5, atol=1e-4)
     torch.testing.assert_close(out.cpu(), want["out"], **tol)
     got = grads_of(m, x)
-    for name in ("x", "gate_w", "gate_b", "b1", "b2"):
+    for name in ("x", "b1", "b2"):
         torch.testing.assert_close(got[name].cpu(), want["grad_" + name], **tol, msg=lambda s, n=name: f"{n}: {s}")
-    # weight gradients sum ~1000 rows: floor scales with sqrt(rows)
-    for name in ("w1", "w2"):
-        torch.testing.assert_close(got[name].cpu(), want["grad_" + name], rtol=1e-5, atol=1e-3,
+    # gradients that sum over ~1000-4000 tokens: fp32 summation order differs, so the absolute
+    # floor scales with the size of the result (2e-5 of its largest entry)
+    for name in ("w1", "w2", "gate_w", "gate_b"):
+        w_ = want["grad_" + name]
+        torch.testing.assert_close(got[name].cpu(), w_, rtol=1e-5, atol=2e-5 * float(w_.abs().max()),
                                    msg=lambda s, n=name: f"{n}: {s}")
 
 
@@ -90,8 +92,7 @@ def test_bf16_layer_against_fp32_oracle(dtype, softmax_scores):
                                softmax_scores=softmax_scores, gate_idx=idx.cpu())
     out = m(x)
     out.sum().backward()
-    tol = dict(rtol=2e-2, atol=2e-2)
-    torch.testing.assert_close(out.float().cpu(), want["out"], **tol)
+    torch.testing.assert_close(out.float().cpu(), want["out"], rtol=2e-2, atol=5e-3)
     got = grads_of(m, x)
     for name in ("x", "b1", "b2"):
         torch.testing.assert_close(got[name].float().cpu(), want["grad_" + name], rtol=2e-2, atol=5e-2,
