@@ -22,6 +22,11 @@ class Move(ctypes.Structure):
                 ("rows", c_int64), ("local", c_int32), ("step", c_int32)]
 
 
+class FusedGeometry(ctypes.Structure):
+    """Mirror of fmoe_fused_geometry_t."""
+    _fields_ = [("n_steps", c_int32), ("gran", c_int32), ("global_rows", c_int64), ("shadow_rows", c_int64)]
+
+
 class MlpParams(ctypes.Structure):
     """Mirror of fmoe_mlp_params_t."""
     _fields_ = [(n, c_void_p) for n in ("w1", "w2", "b1", "b2", "gw1", "gw2", "gb1", "gb2")]
@@ -75,9 +80,9 @@ _SIGS = {
     "fmoe_gradient_reduce": (I32, [P, P, I64, I32, I32, P]),
     "fmoe_generate_cached_count": (I32, [P, P, P, P, I32, I32, I32, P]),
     "fmoe_fused_compute_ptrs": (I32, [P, P, P, I32, I32, I32, P, P, P]),
-    "fmoe_fused_scratch_bytes": (c_size_t, [I64, I64, I64, I64, I32, I32, I32]),
-    "fmoe_fused_forward": (I32, [P, P, P, P, P, P, P, P, P, P, I64, I64, I64, I64, I32, I32, I32, I32, I32, P, P, P]),
-    "fmoe_fused_backward": (I32, [P, P, P, P, P, P, P, P, P, P, P, P, P, I64, I64, I64, I64, I32, I32, I32, I32, I32, P, P, P]),
+    "fmoe_fused_geometry": (I32, [P, P, P, I32, I32, I32, I32, P]),
+    "fmoe_fused_forward": (I32, [P, P, P, P, P, P, P, P, P, P, P, I64, I64, I64, I32, I32, I32, I32, I32, P, P]),
+    "fmoe_fused_backward": (I32, [P, P, P, P, P, P, P, P, P, P, P, P, P, I64, I64, I64, I32, I32, I32, I32, I32, P, P]),
 }
 
 EXPORTS = tuple(_SIGS)

@@ -27,9 +27,11 @@ inline int fail(int code, const char* fmt, ...) {
 #define FMOE_CUDA_TRY(expr)                                                         \
     do {                                                                            \
         cudaError_t err__ = (expr);                                                 \
-        if (err__ != cudaSuccess)                                                   \
+        if (err__ != cudaSuccess) {                                                 \
+            (void)cudaGetLastError(); /* do not leave the error for the next call */\
             return ::fmoe::fail(FMOE_ERR_CUDA, "%s failed: %s (%s:%d)", #expr,      \
                                 cudaGetErrorString(err__), __FILE__, __LINE__);     \
+        }                                                                           \
     } while (0)
 
 #define FMOE_CHECK_LAUNCH() FMOE_CUDA_TRY(cudaGetLastError())

@@ -5,6 +5,15 @@
 
 namespace fmoe {
 
+// Expert row ranges known on the host (the smart schedule's per-step micro-batches):
+// expert e owns rows [lo[e], hi[e]).  Passed to the kernels by value.
+constexpr int kMaxHostSegs = 64;
+struct HostSegs {
+    int n;  // 0: unused, read the device offsets instead
+    int lo[kMaxHostSegs];
+    int hi[kMaxHostSegs];
+};
+
 struct LinearArgs {
     const void* x;       // [n_rows, in_feat]
     const void* weight;  // [n_expert, out_feat, in_feat]
@@ -14,6 +23,7 @@ struct LinearArgs {
     void* pre_act;       // [n_rows, out_feat] or null
     int64_t n_rows, in_feat, out_feat;
     int n_expert, dtype, activation;
+    const HostSegs* host_segs = nullptr;  // when set, replaces seg_offsets
 };
 
 struct LinearBwdArgs {
@@ -28,10 +38,15 @@ struct LinearBwdArgs {
     int64_t n_rows, in_feat, out_feat;
     int n_expert, dtype, activation, accumulate;
     void* scratch;
+    const HostSegs* host_segs = nullptr;
 };
 
 int simt_linear_forward(const LinearArgs& a, cudaStream_t st);
 int simt_linear_backward(const LinearBwdArgs& a, cudaStream_t st);
+
+// Picks the tensor-core kernels when the shapes allow it, else the FFMA kernels.
+int dispatch_linear_forward(const LinearArgs& a, cudaStream_t st);
+int dispatch_linear_backward(const LinearBwdArgs& a, cudaStream_t st);
 
 // tcgen05 back end.  *_supported() tells whether the shapes/dtype/alignment fit
 // its tiles; callers fall back to the FFMA kernels otherwise.

@@ -64,7 +64,7 @@ struct Shared {
     uint32_t tmem_base;
     int abort;
     int cum_tiles[MAX_EXPERTS_TC + 1];
-    int seg[MAX_EXPERTS_TC + 1];
+    int seg_lo[MAX_EXPERTS_TC], seg_hi[MAX_EXPERTS_TC];
 };
 
 __device__ int g_status = 0;
@@ -186,7 +186,7 @@ __device__ __forceinline__ void locate(const Shared* sh, const Params& p, int ti
     const int local = tile - sh->cum_tiles[e_cursor];
     const int nt = (p.n_out + BN - 1) / BN;
     t.e = e_cursor;
-    const int lo = sh->seg[e_cursor], hi = sh->seg[e_cursor + 1];
+    const int lo = sh->seg_lo[e_cursor], hi = sh->seg_hi[e_cursor];
     if (MODE == MODE_WGRAD) {
         t.row0 = (local / nt) * BM;
         t.rows = min(BM, p.out_rows_per_expert - t.row0);
@@ -206,7 +206,7 @@ __device__ __forceinline__ void locate(const Shared* sh, const Params& p, int ti
 template <int MODE, bool BF16>
 __global__ void __launch_bounds__(THREADS, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                    const Params p) {
+                    const __grid_constant__ HostSegs hs, const Params p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     Shared* sh = (Shared*)(tiles + STAGES * STAGE_BYTES);
@@ -225,7 +225,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         sh->abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    for (int e = threadIdx.x; e <= p.n_expert; e += THREADS) sh->seg[e] = (int)p.seg[e];
+    for (int e = threadIdx.x; e < p.n_expert; e += THREADS) {
+        sh->seg_lo[e] = hs.n ? hs.lo[e] : (int)p.seg[e];
+        sh->seg_hi[e] = hs.n ? hs.hi[e] : (int)p.seg[e + 1];
+    }
     __syncthreads();
     if (threadIdx.x == 0) {
         const int nt = (p.n_out + BN - 1) / BN;
@@ -234,7 +237,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         for (int e = 0; e < p.n_expert; ++e) {
             int mt;
             if (MODE == MODE_WGRAD) mt = (p.out_rows_per_expert + BM - 1) / BM;
-            else mt = (sh->seg[e + 1] - sh->seg[e] + BM - 1) / BM;
+            else mt = (sh->seg_hi[e] - sh->seg_lo[e] + BM - 1) / BM;
             acc += mt * nt;
             sh->cum_tiles[e + 1] = acc;
         }
@@ -509,12 +512,16 @@ int* status_ptr() {
     return cache[dev];
 }
 
+const HostSegs kNoSegs = {};
+
 template <int MODE>
-int launch(const CUtensorMap& ma, const CUtensorMap& mb, const Params& p, int64_t max_tiles, cudaStream_t st) {
+int launch(const CUtensorMap& ma, const CUtensorMap& mb, const HostSegs* hsp, const Params& p, int64_t max_tiles,
+           cudaStream_t st) {
+    const HostSegs& hs = hsp ? *hsp : kNoSegs;
     auto kern = p.is_bf16 ? grouped_gemm_kernel<MODE, true> : grouped_gemm_kernel<MODE, false>;
     FMOE_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
     const unsigned grid = (unsigned)std::max<int64_t>(1, std::min<int64_t>(max_tiles, sm_count()));
-    kern<<<grid, THREADS, SMEM_BYTES, st>>>(ma, mb, p);
+    kern<<<grid, THREADS, SMEM_BYTES, st>>>(ma, mb, hs, p);
     FMOE_CHECK_LAUNCH();
     return 0;
 }
@@ -530,14 +537,14 @@ bool shape_ok(int64_t n_rows, int64_t in_feat, int64_t out_feat, int n_expert, i
 // Column sums of dY per expert segment (bias gradient), fp32 accumulate.
 template <bool BF16>
 __global__ void __launch_bounds__(256)
-bias_grad_tc_kernel(const uint16_t* __restrict__ dy, const int64_t* __restrict__ seg, uint16_t* __restrict__ db,
-                    int out_feat, int accumulate) {
+bias_grad_tc_kernel(const uint16_t* __restrict__ dy, const int64_t* __restrict__ seg,
+                    const __grid_constant__ HostSegs hs, uint16_t* __restrict__ db, int out_feat, int accumulate) {
     // block: 64 columns (as 32 pairs) x 8 row lanes
     __shared__ float red[8][64];
     const int e = blockIdx.y;
     const int cp = threadIdx.x & 31, ry = threadIdx.x >> 5;
     const int col = blockIdx.x * 64 + cp * 2;
-    const int64_t lo = seg[e], hi = seg[e + 1];
+    const int64_t lo = hs.n ? (int64_t)hs.lo[e] : seg[e], hi = hs.n ? (int64_t)hs.hi[e] : seg[e + 1];
     float s0 = 0.f, s1 = 0.f;
     if (col < out_feat)
         for (int64_t m = lo + ry; m < hi; m += 8) {
@@ -588,7 +595,7 @@ int tc_linear_forward(const LinearArgs& a, cudaStream_t st) {
     p.w_rows = (int)a.out_feat; p.out = a.y; p.pre_out = a.pre_act; p.bias = a.bias; p.act = a.activation;
     p.is_bf16 = bf16; p.status = status_ptr();
     const int64_t max_tiles = (ceil_div(a.n_rows, BM) + a.n_expert) * ceil_div(a.out_feat, BN);
-    return launch<MODE_FWD>(ma, mb, p, max_tiles, st);
+    return launch<MODE_FWD>(ma, mb, a.host_segs, p, max_tiles, st);
 }
 
 int tc_linear_backward(const LinearBwdArgs& a, cudaStream_t st) {
@@ -602,7 +609,7 @@ int tc_linear_backward(const LinearBwdArgs& a, cudaStream_t st) {
         p.w_rows = (int)a.out_feat; p.out = a.grad_x; p.act_pre = a.act_pre; p.act = a.activation;
         p.is_bf16 = bf16; p.status = status_ptr();
         const int64_t max_tiles = (ceil_div(a.n_rows, BM) + a.n_expert) * ceil_div(a.in_feat, BN);
-        if (int rc = launch<MODE_DGRAD>(ma, mb, p, max_tiles, st)) return rc;
+        if (int rc = launch<MODE_DGRAD>(ma, mb, a.host_segs, p, max_tiles, st)) return rc;
     }
     if (a.grad_w) {
         CUtensorMap ma, mb;
@@ -616,14 +623,15 @@ int tc_linear_backward(const LinearBwdArgs& a, cudaStream_t st) {
         p.out_rows_per_expert = (int)a.out_feat; p.out = a.grad_w; p.accumulate = a.accumulate;
         p.is_bf16 = bf16; p.status = status_ptr();
         const int64_t max_tiles = (int64_t)a.n_expert * ceil_div(a.out_feat, BM) * ceil_div(a.in_feat, BN);
-        if (int rc = launch<MODE_WGRAD>(ma, mb, p, max_tiles, st)) return rc;
+        if (int rc = launch<MODE_WGRAD>(ma, mb, a.host_segs, p, max_tiles, st)) return rc;
     }
     if (a.grad_b) {
         dim3 grid((unsigned)ceil_div(a.out_feat, 64), (unsigned)a.n_expert);
+        const HostSegs& hs = a.host_segs ? *a.host_segs : kNoSegs;
         if (bf16)
-            bias_grad_tc_kernel<true><<<grid, 256, 0, st>>>((const uint16_t*)a.grad_y, a.seg_offsets, (uint16_t*)a.grad_b, (int)a.out_feat, a.accumulate);
+            bias_grad_tc_kernel<true><<<grid, 256, 0, st>>>((const uint16_t*)a.grad_y, a.seg_offsets, hs, (uint16_t*)a.grad_b, (int)a.out_feat, a.accumulate);
         else
-            bias_grad_tc_kernel<false><<<grid, 256, 0, st>>>((const uint16_t*)a.grad_y, a.seg_offsets, (uint16_t*)a.grad_b, (int)a.out_feat, a.accumulate);
+            bias_grad_tc_kernel<false><<<grid, 256, 0, st>>>((const uint16_t*)a.grad_y, a.seg_offsets, hs, (uint16_t*)a.grad_b, (int)a.out_feat, a.accumulate);
         FMOE_CHECK_LAUNCH();
     }
     return 0;

@@ -27,6 +27,18 @@ int check_common(int64_t n_rows, int64_t in_feat, int64_t out_feat, int n_expert
 
 }  // namespace
 
+namespace fmoe {
+int dispatch_linear_forward(const LinearArgs& a, cudaStream_t st) {
+    if (a.n_rows == 0) return 0;
+    if (!force_simt() && tc_forward_supported(a)) return tc_linear_forward(a, st);
+    return simt_linear_forward(a, st);
+}
+int dispatch_linear_backward(const LinearBwdArgs& a, cudaStream_t st) {
+    if (!force_simt() && tc_backward_supported(a)) return tc_linear_backward(a, st);
+    return simt_linear_backward(a, st);
+}
+}  // namespace fmoe
+
 extern "C" size_t fmoe_linear_scratch_bytes(int64_t n_rows, int64_t in_feat, int64_t out_feat,
                                             int32_t n_expert, int32_t dtype) {
     return tc_backward_scratch_bytes(n_rows, in_feat, out_feat, n_expert, dtype);
@@ -40,8 +52,7 @@ extern "C" int fmoe_linear_forward(const void* x, const void* weight, const void
     if (n_rows == 0) return 0;
     FMOE_REQUIRE(x && weight && y, "linear_forward: null pointer");
     LinearArgs a{x, weight, bias, seg_offsets, y, pre_act, n_rows, in_feat, out_feat, n_expert, dtype, activation};
-    if (!force_simt() && tc_forward_supported(a)) return tc_linear_forward(a, (cudaStream_t)stream);
-    return simt_linear_forward(a, (cudaStream_t)stream);
+    return dispatch_linear_forward(a, (cudaStream_t)stream);
 }
 
 extern "C" int fmoe_linear_backward(const void* grad_y, const void* x, const void* weight,
@@ -55,6 +66,5 @@ extern "C" int fmoe_linear_backward(const void* grad_y, const void* x, const voi
     FMOE_REQUIRE(!grad_w || x || n_rows == 0, "linear_backward: weight gradient needs the forward input");
     LinearBwdArgs a{grad_y, x, weight, seg_offsets, act_pre, grad_x, grad_w, grad_b, n_rows, in_feat,
                     out_feat, n_expert, dtype, activation, accumulate, scratch};
-    if (!force_simt() && tc_backward_supported(a)) return tc_linear_backward(a, (cudaStream_t)stream);
-    return simt_linear_backward(a, (cudaStream_t)stream);
+    return dispatch_linear_backward(a, (cudaStream_t)stream);
 }

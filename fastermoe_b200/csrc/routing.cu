@@ -207,7 +207,7 @@ finalize_kernel(int mode, int n_expert, const int32_t* __restrict__ totals,
 // Rank of this lane's entry among the lanes with the same expert, then advance
 // the warp's running counters.  Returns the rank within the expert's bucket
 // counted from the start of the whole array (or from seg_start).
-__device__ __forceinline__ int64_t rank_round(int e, int lane, int64_t* run) {
+__device__ __forceinline__ int64_t rank_round(int e, int lane, int32_t* run) {
     const unsigned m = __match_any_sync(kFull, e);
     int64_t r = -1;
     if (e >= 0) r = run[e] + __popc(m & ((1u << lane) - 1u));
@@ -223,13 +223,14 @@ apply_kernel(int mode, const int64_t* __restrict__ gate, int64_t n, int n_expert
              const int32_t* __restrict__ limit, const int64_t* __restrict__ total_ptr,
              int64_t* __restrict__ pos, int64_t* __restrict__ inv, int64_t* __restrict__ new_gate,
              bool vec) {
-    extern __shared__ int64_t shl[];
+    // Running position per expert and warp; positions fit 32 bits (n < 2^31 is checked on the host).
+    extern __shared__ int32_t shr[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    int64_t* run = shl + (size_t)warp * n_expert;
+    int32_t* run = shr + (size_t)warp * n_expert;
     const int64_t tile = (int64_t)blockIdx.x * kWarps + warp;
     if (tile >= n_tiles) return;
     const int32_t* b = base + tile * n_expert;
-    for (int e = lane; e < n_expert; e += 32) run[e] = seg_start[e] + b[e];
+    for (int e = lane; e < n_expert; e += 32) run[e] = (int32_t)seg_start[e] + b[e];
     __syncwarp();
     const int64_t total = (mode == MODE_COUNT_POS && total_ptr) ? *total_ptr : n;
     const int64_t tb = tile * (int64_t)chunks * 64;
@@ -326,7 +327,7 @@ int run_bucket(int mode, const int64_t* gate, int64_t n, int n_expert, void* scr
     const Geom g = make_geom(n, n_expert);
     const Scratch s = carve(scratch, n, n_expert);
     const bool vec = ((uintptr_t)gate & 15) == 0;
-    const size_t sm_hist = (size_t)kWarps * n_expert * 4, sm_apply = (size_t)kWarps * n_expert * 8;
+    const size_t sm_hist = (size_t)kWarps * n_expert * 4, sm_apply = sm_hist;
     if (int rc = set_smem((const void*)tile_hist_kernel, sm_hist)) return rc;
     if (int rc = set_smem((const void*)apply_kernel, sm_apply)) return rc;
     const unsigned blocks = (unsigned)ceil_div(g.n_tiles, kWarps);

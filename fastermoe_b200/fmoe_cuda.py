@@ -512,3 +512,154 @@ def linear_backward_act(grad_y, x, seg_offsets, weight, act_pre, activation, nee
                                        out_feat, n_expert, _dtype_code(x), activation,
                                        1 if accumulate else 0, _ptr(scratch), _stream())
     return gx, gw, gb
+
+
+# ---------------------------------------------------------------------------
+# fused_compute: cuda/fmoe_cuda.cpp:80-100 (smart schedule)
+# ---------------------------------------------------------------------------
+
+_comm_streams = {}
+
+
+def _comm_stream(device):
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    s = _comm_streams.get(idx)
+    if s is None:
+        s = torch.cuda.Stream(device=device)
+        _comm_streams[idx] = s
+    return s
+
+
+def fuse_gran():
+    """Peers per pipeline step: env FMOE_FUSE_GRAN, default 4 (cuda/fused_compute.cu:21-28).
+    Read on every call (the reference caches the first value in a process global)."""
+    try:
+        return max(1, int(os.environ.get("FMOE_FUSE_GRAN", "4")))
+    except ValueError:
+        return 4
+
+
+def fused_geometry(local_expert_count, global_expert_count, stored_models, n_workers, rank, gran=None):
+    """Returns (n_steps, gran, global_rows B, shadow_rows S) of a smart-schedule call."""
+    lec, gec, st = _host_i64(local_expert_count), _host_i64(global_expert_count), _host_flags(stored_models)
+    n_expert = lec.numel() // n_workers
+    geo = _lib.FusedGeometry()
+    check(lib.fmoe_fused_geometry(_ptr(lec), _ptr(gec), _ptr(st), rank, n_expert, n_workers,
+                                  fuse_gran() if gran is None else gran, ctypes.byref(geo)), "fused_geometry")
+    return geo.n_steps, geo.gran, geo.global_rows, geo.shadow_rows
+
+
+def _split_params(ps):
+    """(w1, b1, w2, b2) from a worker's parameter tuple: (w1, w2) or (w1, b1, w2, b2)."""
+    ps = tuple(ps)
+    if len(ps) == 2:
+        return ps[0], None, ps[1], None
+    if len(ps) == 4:
+        return ps
+    raise RuntimeError(f"fmoe_cuda: expected 2 or 4 expert parameter tensors per worker, got {len(ps)}")
+
+
+def _mlp_table(params, grads, n_workers):
+    table = (_lib.MlpParams * n_workers)()
+    keep = []
+    for j in range(n_workers):
+        if not params[j]:
+            continue
+        w1, b1, w2, b2 = _split_params(params[j][0])
+        _check_cuda(w1, b1, w2, b2)
+        table[j].w1, table[j].b1, table[j].w2, table[j].b2 = (t.data_ptr() if t is not None else None
+                                                              for t in (w1, b1, w2, b2))
+        if grads is not None and grads[j]:
+            g1, gb1, g2, gb2 = _split_params(grads[j][0])
+            _check_cuda(g1, gb1, g2, gb2)
+            table[j].gw1, table[j].gb1, table[j].gw2, table[j].gb2 = (t.data_ptr() if t is not None else None
+                                                                      for t in (g1, gb1, g2, gb2))
+        keep.append((w1, b1, w2, b2))
+    return table, keep
+
+
+def fused_forward(input_buf, params, local_expert_count, global_expert_count, stored_models,
+                  global_batch_size, n_workers, has_bias, activation=_lib.ACT_RELU):
+    """Smart-schedule forward (cuda/fused_compute.cu:12-62).
+
+    ``params[j]`` is ``[tuple_of_parameters]`` for the own worker and for shadowed
+    workers, else ``[]``.  Returns ``[out [A,d], global_in, middle, global_out]``
+    (+ the pre-activation buffer when ``activation`` is GELU); the expert-side
+    buffers have B+S rows (see fused_geometry) and are what fused_backward needs.
+    ``global_batch_size`` is accepted for signature compatibility and checked.
+    The reference hard-codes ReLU and ignores biases; here ``activation`` selects the
+    function and biases in the parameter tuples are applied.
+    """
+    _check_cuda(input_buf)
+    dev = input_buf.device
+    lec, gec, st = _host_i64(local_expert_count), _host_i64(global_expert_count), _host_flags(stored_models)
+    n_expert = lec.numel() // n_workers
+    rank = comm_rank(dev)[0] if n_workers > 1 else 0
+    w1 = _split_params(params[rank][0])[0]
+    d_hidden, d_model = w1.shape[1], w1.shape[2]
+    gran = fuse_gran()
+    _, _, B, S = fused_geometry(lec, gec, st, n_workers, rank, gran)
+    if global_batch_size is not None and int(global_batch_size) != B + S:
+        raise RuntimeError(f"fused_forward: global_batch_size={global_batch_size} but the counts give {B + S} rows")
+    A = input_buf.shape[0]
+    gib = input_buf.new_empty((B + S, d_model))
+    gmb = input_buf.new_empty((B + S, d_hidden))
+    pre = input_buf.new_empty((B + S, d_hidden)) if activation == _lib.ACT_GELU else None
+    gob = input_buf.new_empty((B + S, d_model))
+    out = input_buf.new_empty((A, d_model))
+    table, keep = _mlp_table(params, None, n_workers)
+    with torch.cuda.device(dev):
+        comm = _comm(dev) if n_workers > 1 else None
+        _run("fused_forward", lib.fmoe_fused_forward, comm, _ptr(input_buf), _ptr(out), _ptr(gib), _ptr(gmb),
+             _ptr(pre), _ptr(gob), table, _ptr(lec), _ptr(gec), _ptr(st), A, d_model, d_hidden, n_expert,
+             n_workers, _dtype_code(input_buf), activation, gran, _stream(),
+             ctypes.c_void_p(_comm_stream(dev).cuda_stream))
+    res = [out, gib, gmb, gob]
+    if pre is not None:
+        res.append(pre)
+    return res
+
+
+def fused_backward(input_buf, params, middle_buf, output_buf, grad_out, local_expert_count,
+                   global_expert_count, inp, stored_models, global_batch_size, buf_batch_size, n_workers,
+                   has_bias, activation=_lib.ACT_RELU, middle_pre=None, grads=None):
+    """Smart-schedule backward (cuda/fused_compute.cu:64-131).  Returns ``[grad_in [A,d]]``.
+
+    Weight gradients: with ``grads`` (same nesting as ``params``) they are written
+    there; otherwise into ``param.grad`` of every tensor in ``params``, created when
+    missing -- the own experts' gradients are OVERWRITTEN (first pipeline step) and
+    shadowed experts' accumulated, exactly as the reference does.
+    ``output_buf`` and ``inp`` are unused (kept for signature compatibility).
+    """
+    _check_cuda(input_buf, middle_buf, grad_out)
+    dev = input_buf.device
+    lec, gec, st = _host_i64(local_expert_count), _host_i64(global_expert_count), _host_flags(stored_models)
+    n_expert = lec.numel() // n_workers
+    rank = comm_rank(dev)[0] if n_workers > 1 else 0
+    d_hidden, d_model = middle_buf.shape[1], input_buf.shape[1]
+    if grads is None:
+        grads = []
+        for j in range(n_workers):
+            if not params[j]:
+                grads.append([])
+                continue
+            gs = []
+            for p in params[j][0]:
+                if p.grad is None:
+                    p.grad = torch.zeros_like(p)
+                gs.append(p.grad)
+            grads.append([tuple(gs)])
+    rows = input_buf.shape[0]
+    ggo = input_buf.new_empty((rows, d_model))
+    gmid = input_buf.new_empty((rows, d_hidden))
+    ggi = input_buf.new_empty((rows, d_model))
+    grad_in = input_buf.new_empty((grad_out.shape[0], d_model))
+    table, keep = _mlp_table(params, grads, n_workers)
+    gran = fuse_gran()
+    with torch.cuda.device(dev):
+        comm = _comm(dev) if n_workers > 1 else None
+        _run("fused_backward", lib.fmoe_fused_backward, comm, _ptr(grad_out), _ptr(grad_in), _ptr(input_buf),
+             _ptr(middle_buf), _ptr(middle_pre), _ptr(ggo), _ptr(gmid), _ptr(ggi), table, _ptr(lec), _ptr(gec),
+             _ptr(st), grad_out.shape[0], d_model, d_hidden, n_expert, n_workers, _dtype_code(input_buf),
+             activation, gran, _stream(), ctypes.c_void_p(_comm_stream(dev).cuda_stream))
+    return [grad_in]

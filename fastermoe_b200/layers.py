@@ -112,8 +112,9 @@ def _fmoe_general_global_forward(inp, gate, expert_fn, policy_fn, experts, num_e
         exch = Exchange(routing.lec, routing.gec, stored.reshape(-1), fwd_batch_size, world_size)
         n_rows = routing.n_rows
         if enable_fuse:
-            from .fused_functions import MOEForward
-            x = MOEForward.apply(inp, models, routing, top_k, exch, n_rows)
+            from .fused_functions import MOEForward, fused_activation
+            flat = [p for node in models if node for p in node[0].parameters()]
+            x = MOEForward.apply(inp, models, routing, top_k, exch, n_rows, fused_activation(experts), *flat)
             exch = None
         else:
             x = MOEScatterFused.apply(inp, routing.pos, routing.inv, top_k, n_rows, exch)

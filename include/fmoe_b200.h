@@ -320,46 +320,61 @@ int fmoe_fused_compute_ptrs(const int64_t* lec_host, const int64_t* gec_host,
                             int64_t* local_ptr, int64_t* global_ptr,
                             int64_t* local_global_ptr);
 
-/* Scratch bytes for fmoe_fused_forward / fmoe_fused_backward. */
-size_t fmoe_fused_scratch_bytes(int64_t global_rows, int64_t local_rows,
-                                int64_t d_model, int64_t d_hidden, int32_t n_expert,
-                                int32_t n_workers, int32_t dtype);
+/* Geometry of one smart-schedule call, computed on the host from the counts. */
+typedef struct {
+    int32_t n_steps;      /* pipeline steps = n_workers / gran */
+    int32_t gran;         /* peers exchanged per step: the largest divisor of n_workers
+                             that is <= the requested pipeline_gran (the reference silently
+                             drops ranks when n_workers is not a multiple,
+                             cuda/fused_compute.cuh:276-279) */
+    int64_t global_rows;  /* B: rows this rank receives for its own experts */
+    int64_t shadow_rows;  /* S: rows kept on this rank for shadowed experts */
+} fmoe_fused_geometry_t;
+
+int fmoe_fused_geometry(const int64_t* lec_host, const int64_t* gec_host,
+                        const uint8_t* stored_models_host, int32_t rank, int32_t n_expert,
+                        int32_t n_workers, int32_t pipeline_gran, fmoe_fused_geometry_t* out);
 
 /* fused_forward: cuda/fmoe_cuda.cpp:80-87, cuda/fused_compute.cu:12-62,
  * cuda/fused_compute.cuh:250-388.  params_host[w] is the parameter set of
- * worker w's experts (own experts at index rank; shadows where
- * stored_models says so; others ignored).  Buffers (caller-allocated):
- * local_in [A,d], local_out [A,d], global_in [B,d], middle [B+S,h] where S is
- * the number of rows kept local for shadowed experts, global_out [B,d].
- * The exchange runs per peer on comm_stream, the expert GEMMs on `stream`,
- * ordered with events; on return all work has been queued and `stream`
- * waits for comm_stream.  pipeline_gran: peers per step (FMOE_FUSE_GRAN). */
+ * worker w's experts (own experts at index rank; shadows where stored_models
+ * says so; other entries are ignored).  Buffers are allocated by the caller:
+ *   local_in, local_out [A, d_model]      token-side rows, ordered by (worker, expert)
+ *   global_in, global_out [B+S, d_model]  expert-side rows: [0,B) received, expert-major
+ *                                         then source; [B,B+S) rows of shadowed experts
+ *   middle [B+S, d_hidden]                activation output; middle_pre: value before the
+ *                                         activation (needed for GELU, else NULL)
+ * with B, S from fmoe_fused_geometry.  The exchange with the peers of step s is
+ * queued on comm_stream, the expert GEMMs of step s on `stream` once its rows have
+ * arrived, and the results travel back as each step finishes.  On return all work
+ * is queued and `stream` waits for comm_stream.  Unlike the reference (ReLU only,
+ * no bias) the activation is selectable and biases are applied when non-NULL.
+ * comm may be NULL when n_workers == 1. */
 int fmoe_fused_forward(fmoe_comm_t comm, const void* local_in, void* local_out,
-                       void* global_in, void* middle, void* global_out,
+                       void* global_in, void* middle, void* middle_pre, void* global_out,
                        const fmoe_mlp_params_t* params_host,
                        const int64_t* lec_host, const int64_t* gec_host,
-                       const uint8_t* stored_models_host,
-                       int64_t local_rows, int64_t global_rows,
+                       const uint8_t* stored_models_host, int64_t local_rows,
                        int64_t d_model, int64_t d_hidden, int32_t n_expert,
                        int32_t n_workers, int32_t dtype, int32_t activation,
-                       int32_t pipeline_gran, void* scratch,
-                       fmoe_stream_t stream, fmoe_stream_t comm_stream);
+                       int32_t pipeline_gran, fmoe_stream_t stream, fmoe_stream_t comm_stream);
 
 /* fused_backward: cuda/fmoe_cuda.cpp:88-100, cuda/fused_compute.cu:64-131,
- * cuda/fused_compute.cuh:391-542.  Weight gradients are written into
- * params_host[w].gw*: the own experts' are overwritten at the first pipeline
- * step and accumulated afterwards; shadowed experts' are accumulated. */
+ * cuda/fused_compute.cuh:391-542.  global_in, middle, middle_pre are the buffers
+ * the forward filled; global_grad_out [B+S,d], grad_middle [B+S,h] and
+ * global_grad_in [B+S,d] are work buffers.  Weight (and bias) gradients go to
+ * params_host[w].g*: the own experts' are overwritten by the first pipeline step
+ * and accumulated by the later ones; shadowed experts' are accumulated into
+ * (the caller zero-fills them), as in the reference. */
 int fmoe_fused_backward(fmoe_comm_t comm, const void* grad_out_local, void* grad_in_local,
-                        const void* local_in, const void* global_in, const void* middle,
+                        const void* global_in, const void* middle, const void* middle_pre,
                         void* global_grad_out, void* grad_middle, void* global_grad_in,
                         const fmoe_mlp_params_t* params_host,
                         const int64_t* lec_host, const int64_t* gec_host,
-                        const uint8_t* stored_models_host,
-                        int64_t local_rows, int64_t global_rows,
+                        const uint8_t* stored_models_host, int64_t local_rows,
                         int64_t d_model, int64_t d_hidden, int32_t n_expert,
                         int32_t n_workers, int32_t dtype, int32_t activation,
-                        int32_t pipeline_gran, void* scratch,
-                        fmoe_stream_t stream, fmoe_stream_t comm_stream);
+                        int32_t pipeline_gran, fmoe_stream_t stream, fmoe_stream_t comm_stream);
 
 #ifdef __cplusplus
 }

@@ -1,0 +1,286 @@
+"""Rank bodies of the multi-process tests (spawned by test_dist_gpu.py / test_dist_cpu.py)."""
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+from oracle import moe_oracle as O  # noqa: E402
+
+
+def init(rank, world, port, backend):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["RANK"], os.environ["WORLD_SIZE"], os.environ["LOCAL_RANK"] = str(rank), str(world), str(rank)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    if backend == "nccl":
+        torch.cuda.set_device(rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    else:
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+
+
+def finish(backend):
+    if backend == "nccl":
+        from fastermoe_b200 import fmoe_cuda
+        torch.cuda.synchronize()
+        fmoe_cuda.destroy_comms()
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def all_lecs(world, E, seed, lo=0, hi=9):
+    rng = np.random.default_rng(seed)
+    return [rng.integers(lo, hi, size=world * E) for _ in range(world)]
+
+
+# ------------------------------------------------------------------ GPU / NCCL
+
+def gpu_exchange(rank, world, port):
+    init(rank, world, port, "nccl")
+    from fastermoe_b200 import fmoe_cuda as fc
+    dev = torch.device("cuda", rank)
+    fc.ensure_nccl(None, torch.zeros(1, device=dev))
+    E, d = 3, 40
+    lecs = all_lecs(world, E, 5)
+    aec_w, agec_w, gecs = O.expert_exchange(lecs, E, world)
+    aec, agec, gec = fc.expert_exchange(torch.from_numpy(lecs[rank]).to(dev), E, world)
+    assert np.array_equal(aec.cpu().numpy(), aec_w) and np.array_equal(agec.cpu().numpy(), agec_w)
+    assert np.array_equal(gec.cpu().numpy(), gecs[rank])
+    for stored in (np.zeros(world * E, bool), np.repeat(np.arange(world) == 0, E), np.repeat(np.arange(world) == world - 1, E)):
+        rng = np.random.default_rng(9)
+        bufs = [rng.standard_normal((int(l.sum()), d)).astype(np.float32) for l in lecs]
+        want = O.global_scatter(bufs, lecs, stored, E, world)
+        for dtype in (torch.float32, torch.bfloat16):
+            mine = torch.from_numpy(bufs[rank]).to(dev).to(dtype)
+            out = fc.global_scatter(mine, torch.from_numpy(lecs[rank]), torch.from_numpy(gecs[rank]),
+                                    torch.from_numpy(stored), want[rank].shape[0], world)
+            assert torch.equal(out, torch.from_numpy(want[rank]).to(dev).to(dtype)), "global_scatter layout"
+            back = fc.global_gather(out, torch.from_numpy(lecs[rank]), torch.from_numpy(gecs[rank]),
+                                    torch.from_numpy(stored), mine.shape[0], world)
+            assert torch.equal(back, mine), "global_gather is not the inverse"
+        cc = fc.generate_cached_count(torch.from_numpy(lecs[rank]).to(dev).view(world, E),
+                                      torch.from_numpy(gecs[rank]).to(dev).view(world, E),
+                                      torch.from_numpy(stored).to(dev).view(world, E), E, world)
+        assert np.array_equal(cc.cpu().numpy(), O.generate_cached_count(lecs[rank], gecs[rank], stored, rank, E, world))
+    # mismatched buffer size is caught before anything is queued
+    try:
+        fc.global_scatter(torch.zeros(int(lecs[rank].sum()), d, device=dev), torch.from_numpy(lecs[rank]),
+                          torch.from_numpy(gecs[rank]), torch.zeros(world * E, dtype=torch.bool), 1, world)
+        raise AssertionError("size mismatch not detected")
+    except RuntimeError as e:
+        assert "rows" in str(e)
+    # capacity gate across ranks
+    from fastermoe_b200.gates.utils import limit_by_capacity
+    gates = [np.random.default_rng(100 + r).integers(0, world * E, size=(64, 2)) for r in range(world)]
+    for g in gates:
+        g[:40, 0] = 1
+    want = O.limit_by_capacity_gate(gates, E, world, 30)
+    new_lec, new_gec, pruned = limit_by_capacity(torch.from_numpy(gates[rank]).to(dev), E, world, 30)
+    assert np.array_equal(pruned.cpu().numpy(), want[rank][2])
+    assert np.array_equal(new_lec.cpu().numpy(), want[rank][0]) and np.array_equal(new_gec.cpu().numpy(), want[rank][1])
+    finish("nccl")
+
+
+def _make_layer(world, rank, E, d, h, k, act, bias, tens, dtype=torch.float32, gate=None):
+    from fastermoe_b200 import FMoETransformerMLP
+    fn = {"gelu": torch.nn.GELU(), "relu": torch.nn.ReLU()}[act]
+    kw = {} if gate is None else {"gate": gate}
+    m = FMoETransformerMLP(num_expert=E, d_model=d, d_hidden=h, world_size=world, activation=fn, top_k=k, bias=bias, **kw)
+    sl = slice(rank * E, (rank + 1) * E)
+    with torch.no_grad():
+        m.gate.gate.weight.copy_(tens["gate_w"]); m.gate.gate.bias.copy_(tens["gate_b"])
+        m.experts.htoh4.weight.copy_(tens["w1"][sl]); m.experts.h4toh.weight.copy_(tens["w2"][sl])
+        if bias:
+            m.experts.htoh4.bias.copy_(tens["b1"][sl]); m.experts.h4toh.bias.copy_(tens["b2"][sl])
+    return m.to(dtype).cuda()
+
+
+def _run_layer(m, x):
+    m.zero_grad(set_to_none=True)
+    x = x.detach().clone().requires_grad_(True)
+    out = m(x)
+    out.sum().backward()
+    g = {"out": out.detach(), "x": x.grad, "w1": m.experts.htoh4.weight.grad.clone(),
+         "w2": m.experts.h4toh.weight.grad.clone(), "gate_w": m.gate.gate.weight.grad.clone()}
+    if m.experts.htoh4.bias is not None:
+        g["b1"], g["b2"] = m.experts.htoh4.bias.grad.clone(), m.experts.h4toh.bias.grad.clone()
+    return g
+
+
+def gpu_layer(rank, world, port):
+    """Expert-parallel layer against the brute-force oracle; smart schedule == plain schedule;
+    shadowed == not shadowed (the reference's tests/test_fused.py and tests/test_cache.py)."""
+    init(rank, world, port, "nccl")
+    import fastermoe_b200.transformer as tr
+    T, d, h, E, k = 96, 64, 128, 2, 2
+    tens = O.make_layer_inputs(T * world, d, h, E * world, seed=3)
+    xs = tens["x"].view(world, T, d)
+    tol = dict(rtol=1e-5, atol=5e-5)
+    for act, bias in (("gelu", True), ("relu", False)):
+        m = _make_layer(world, rank, E, d, h, k, act, bias, tens)
+        got = _run_layer(m, xs[rank].cuda())
+        # oracle: every rank's tokens through all experts; expert grads summed over ranks
+        wants = [O.moe_layer_fwd_bwd(xs[r], tens["gate_w"], tens["gate_b"], tens["w1"], tens["b1"] if bias else None,
+                                     tens["w2"], tens["b2"] if bias else None, k, act=act) for r in range(world)]
+        sl = slice(rank * E, (rank + 1) * E)
+        torch.testing.assert_close(got["out"].cpu(), wants[rank]["out"], **tol)
+        torch.testing.assert_close(got["x"].cpu(), wants[rank]["grad_x"], **tol)
+        torch.testing.assert_close(got["gate_w"].cpu(), wants[rank]["grad_gate_w"], rtol=1e-5, atol=2e-4)
+        for name in ("w1", "w2") + (("b1", "b2") if bias else ()):
+            want = sum(w["grad_" + name][sl] for w in wants)
+            torch.testing.assert_close(got[name].cpu(), want, rtol=1e-5, atol=2e-4, msg=lambda s, n=name: f"{n}: {s}")
+        # smart schedule against the plain one, all pipeline granularities
+        for gran in ("1", "2", "4"):
+            os.environ["FMOE_FUSE_GRAN"] = gran
+            m.enable_fuse = True
+            fused = _run_layer(m, xs[rank].cuda())
+            m.enable_fuse = False
+            for name, v in got.items():
+                torch.testing.assert_close(fused[name], v, rtol=1e-5, atol=2e-5, msg=lambda s, n=name: f"fused {gran} {n}: {s}")
+        # dynamic shadowing: force worker 0 (then the last worker) to be shadowed everywhere
+        for hot in (0, world - 1):
+            def policy(aec, agec, num_expert, world_size, d_model, fused, hot=hot):
+                res = torch.zeros(world_size, num_expert, dtype=torch.bool)
+                res[hot] = True
+                return res
+            m.policy_fn = policy
+            for fuse in (False, True):
+                m.enable_fuse = fuse
+                shadow = _run_layer(m, xs[rank].cuda())
+                for name, v in got.items():
+                    torch.testing.assert_close(shadow[name], v, rtol=1e-5, atol=5e-5,
+                                               msg=lambda s, n=name: f"shadow hot={hot} fuse={fuse} {n}: {s}")
+            m.enable_fuse = False
+            m.policy_fn = tr._gen_policy(h / d)
+    finish("nccl")
+
+
+def gpu_layer_bf16(rank, world, port):
+    """bf16 shapes that take the tensor-core kernels, smart schedule and shadowing included."""
+    init(rank, world, port, "nccl")
+    T, d, h, E, k = 1024, 256, 512, 2, 2
+    tens = O.make_layer_inputs(T * world, d, h, E * world, seed=4, gate_std=0.02)
+    xs = tens["x"].view(world, T, d)
+    m = _make_layer(world, rank, E, d, h, k, "gelu", True, tens, dtype=torch.bfloat16)
+    x = xs[rank].bfloat16().cuda()
+    base = _run_layer(m, x)
+    with torch.no_grad():
+        idx, _ = m.gate(x)
+    idx_all = [torch.empty_like(idx) for _ in range(world)]
+    dist.all_gather(idx_all, idx)
+    r = {n: t.bfloat16().float() for n, t in tens.items()}
+    want = O.moe_layer_fwd_bwd(r["x"].view(world, T, d)[rank], r["gate_w"], r["gate_b"], r["w1"], r["b1"], r["w2"],
+                               r["b2"], k, gate_idx=idx.cpu())
+    torch.testing.assert_close(base["out"].float().cpu(), want["out"], rtol=2e-2, atol=5e-3)
+    torch.testing.assert_close(base["x"].float().cpu(), want["grad_x"], rtol=2e-2, atol=5e-2)
+    os.environ["FMOE_FUSE_GRAN"] = "1"
+    m.enable_fuse = True
+    fused = _run_layer(m, x)
+    m.enable_fuse = False
+    for name in ("out", "x"):
+        torch.testing.assert_close(fused[name].float(), base[name].float(), rtol=2e-2, atol=2e-2)
+    for name in ("w1", "w2", "b1", "b2"):
+        torch.testing.assert_close(fused[name].float(), base[name].float(), rtol=3e-2, atol=0.3)
+
+    def policy(aec, agec, num_expert, world_size, d_model, fused):
+        res = torch.zeros(world_size, num_expert, dtype=torch.bool)
+        res[0] = True
+        return res
+    m.policy_fn = policy
+    shadow = _run_layer(m, x)
+    for name in ("out", "x"):
+        torch.testing.assert_close(shadow[name].float(), base[name].float(), rtol=2e-2, atol=2e-2)
+    for name in ("w1", "w2", "b1", "b2"):
+        torch.testing.assert_close(shadow[name].float(), base[name].float(), rtol=3e-2, atol=0.3)
+    finish("nccl")
+
+
+# ------------------------------------------------------------------ CPU / gloo
+
+def cpu_plan_exchange(rank, world, port):
+    """Executes the library's exchange plan with gloo point-to-point on CPU tensors and
+    compares with the oracle: the host-side planning that the NCCL executor follows."""
+    import ctypes
+    init(rank, world, port, "gloo")
+    from fastermoe_b200 import _lib
+    E, d = 3, 8
+    lecs = all_lecs(world, E, 21)
+    _, _, gecs = O.expert_exchange(lecs, E, world)
+    # count exchange through the process group, as the layer does through NCCL
+    mine = torch.from_numpy(lecs[rank])
+    gathered = [torch.empty_like(mine) for _ in range(world)]
+    dist.all_gather(gathered, mine)
+    aec = torch.stack(gathered).view(world, world, E)
+    assert np.array_equal(aec.transpose(0, 1)[rank].reshape(-1).numpy(), gecs[rank])
+    for stored in (np.zeros(world * E, bool), np.repeat(np.arange(world) == 1, E)):
+        rng = np.random.default_rng(2)
+        bufs = [rng.standard_normal((int(l.sum()), d)).astype(np.float32) for l in lecs]
+        want = O.global_scatter(bufs, lecs, stored, E, world)
+        lec = np.ascontiguousarray(lecs[rank], dtype=np.int64)
+        gec = np.ascontiguousarray(gecs[rank], dtype=np.int64)
+        st = stored.astype(np.uint8)
+        moves = (_lib.Move * (4 * E * world + 8))()
+        n, rows = ctypes.c_int32(), ctypes.c_int64()
+        rc = _lib.lib.fmoe_plan_global_scatter(lec.ctypes.data, gec.ctypes.data, st.ctypes.data, rank, E, world,
+                                               ctypes.cast(moves, ctypes.c_void_p), len(moves), ctypes.byref(n),
+                                               ctypes.byref(rows))
+        assert rc == 0 and rows.value == want[rank].shape[0]
+        src = torch.from_numpy(bufs[rank])
+        dst = torch.zeros(rows.value, d)
+        ops = []
+        for i in range(n.value):
+            m = moves[i]
+            if m.local:
+                dst[m.dst_row:m.dst_row + m.rows] = src[m.src_row:m.src_row + m.rows]
+            elif m.is_send:
+                ops.append(dist.P2POp(dist.isend, src[m.src_row:m.src_row + m.rows].contiguous(), m.peer))
+            else:
+                ops.append(dist.P2POp(dist.irecv, dst[m.dst_row:m.dst_row + m.rows], m.peer))
+        if ops:
+            for w in dist.batch_isend_irecv(ops):
+                w.wait()
+        assert np.array_equal(dst.numpy(), want[rank]), f"rank {rank}: plan does not reproduce the reference layout"
+        # shadow bookkeeping on the host
+        from fastermoe_b200.functions import cached_count_host
+        cc = cached_count_host(torch.from_numpy(lec.copy()), torch.from_numpy(gec.copy()), torch.from_numpy(stored),
+                               rank, E, world)
+        assert np.array_equal(cc.numpy(), O.generate_cached_count(lec, gec, stored, rank, E, world))
+        assert int(cc.sum()) == rows.value
+        geo = _lib.FusedGeometry()
+        for gran in (1, 2, 3, 4):
+            assert _lib.lib.fmoe_fused_geometry(lec.ctypes.data, gec.ctypes.data, st.ctypes.data, rank, E, world, gran,
+                                                ctypes.byref(geo)) == 0
+            assert world % geo.gran == 0 and geo.n_steps * geo.gran == world and geo.gran <= max(gran, 1)
+            assert geo.global_rows + geo.shadow_rows == rows.value
+    finish("gloo")
+
+
+def cpu_grouped_ddp(rank, world, port):
+    """DistributedGroupedDataParallel: gradients are averaged per tag; 'none' is left alone."""
+    init(rank, world, port, "gloo")
+    from fastermoe_b200.distributed import DistributedGroupedDataParallel
+    torch.manual_seed(rank)
+    net = torch.nn.Sequential(torch.nn.Linear(4, 4), torch.nn.Linear(4, 2))
+    for p in net[0].parameters():
+        p.dp_comm = "moe"
+    for p in net[1].parameters():
+        p.dp_comm = "none"
+    ddp = DistributedGroupedDataParallel(net)
+    w0 = [torch.empty_like(net[0].weight) for _ in range(world)]
+    dist.all_gather(w0, net[0].weight.data)
+    assert all(torch.equal(w0[0], w) for w in w0), "tagged parameters were not broadcast"
+    ddp(torch.randn(3, 4)).sum().backward()
+    g_local = net[0].weight.grad.clone()
+    g_none = net[1].weight.grad.clone()
+    gs = [torch.empty_like(g_local) for _ in range(world)]
+    dist.all_gather(gs, g_local)
+    ddp.allreduce_params()
+    torch.testing.assert_close(net[0].weight.grad, sum(gs) / world)
+    assert torch.equal(net[1].weight.grad, g_none)
+    finish("gloo")
