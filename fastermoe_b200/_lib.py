@@ -56,6 +56,8 @@ _SIGS = {
     "fmoe_expert_count": (I32, [P, P, I64, I32, P]),
     "fmoe_assign_pos": (I32, [P, P, P, I64, I32, P, P]),
     "fmoe_count_and_pos": (I32, [P, I64, I32, P, P, P, P, P, P]),
+    "fmoe_static_scratch_capacity": (c_size_t, []),
+    "fmoe_count_and_pos_static": (I32, [P, I64, I32, P, P, P, P, P]),
     "fmoe_limit_by_capacity": (I32, [P, P, P, I32, I32, P]),
     "fmoe_prune_gate_by_capacity": (I32, [P, P, P, I64, I32, P, P]),
     "fmoe_local_scatter": (I32, [P, P, P, I64, I64, I64, I32, P]),

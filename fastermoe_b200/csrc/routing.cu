@@ -14,6 +14,7 @@
 // Gate entries are read with 16-byte loads; within an expert segment positions
 // ascend with the flat index, so results are identical from run to run.
 #include "common.cuh"
+#include <mutex>
 
 namespace fmoe {
 namespace {
@@ -415,4 +416,69 @@ extern "C" int fmoe_limit_by_capacity(const int64_t* ec, int32_t* cap, int64_t* 
         ec, cap, eca, n_expert, n_worker);
     FMOE_CHECK_LAUNCH();
     return 0;
+}
+
+
+// ---------------------------------------------------------------------------
+// Bucketing without caller-provided scratch
+// ---------------------------------------------------------------------------
+//
+// Some hosts of this library may not allocate device memory on the path that
+// routes tokens: a serving process that handed all free HBM to its own pool at
+// start-up, or a plugin host that bans the CUDA allocator from its request path
+// because cudaMalloc/cudaFree serialise with the work already on the device.
+// For them the per-tile histograms of the bucketing kernels live in a fixed
+// array inside the library image instead of a buffer the caller supplies.
+//
+// The array is part of the loaded module: every GPU that loads the library
+// keeps FMOE_STATIC_SCRATCH_BYTES of its memory for it until the process exits.
+namespace fmoe {
+namespace {
+
+static __device__ __align__(256) unsigned char g_static_scratch[FMOE_STATIC_SCRATCH_BYTES];
+
+// In host code `g_static_scratch` is only a handle for the runtime, not an address a
+// kernel may dereference.  The device address is looked up once per device, with
+// that device current, and cached.
+int static_scratch_ptr(void** out) {
+    static void* cache[64] = {};
+    static std::mutex mtx;
+    int dev = 0;
+    FMOE_CUDA_TRY(cudaGetDevice(&dev));
+    FMOE_REQUIRE(dev >= 0 && dev < 64, "static scratch: device index %d not supported", dev);
+    std::lock_guard<std::mutex> lk(mtx);
+    if (!cache[dev]) {
+        void* p = nullptr;
+        FMOE_CUDA_TRY(cudaGetSymbolAddress(&p, g_static_scratch));
+        FMOE_REQUIRE(p != nullptr, "static scratch: symbol has no device address");
+        cache[dev] = p;
+    }
+    *out = cache[dev];
+    return 0;
+}
+
+}  // namespace
+}  // namespace fmoe
+
+extern "C" size_t fmoe_static_scratch_capacity(void) { return FMOE_STATIC_SCRATCH_BYTES; }
+
+extern "C" int fmoe_count_and_pos_static(const int64_t* gate, int64_t n, int32_t n_expert_total,
+                                         int64_t* lec64, int64_t* offsets, int64_t* pos, int64_t* inv,
+                                         fmoe_stream_t stream) {
+    if (int rc = check_routing_args(gate, n, n_expert_total)) return rc;
+    FMOE_REQUIRE(n == 0 || pos != nullptr, "count_and_pos_static: pos pointer is null");
+    FMOE_REQUIRE(offsets != nullptr, "count_and_pos_static: offsets pointer is null");
+    const size_t need = scratch_bytes(n, n_expert_total);
+    if (need > (size_t)FMOE_STATIC_SCRATCH_BYTES)
+        return fail(FMOE_ERR_UNSUPPORTED,
+                    "count_and_pos_static: %lld entries x %d experts need %zu bytes of scratch, the built-in "
+                    "array holds %zu; use fmoe_count_and_pos with caller-provided scratch",
+                    (long long)n, n_expert_total, need, (size_t)FMOE_STATIC_SCRATCH_BYTES);
+    void* scratch = nullptr;
+    if (int rc = static_scratch_ptr(&scratch)) return rc;
+    // Nothing in the array has to start at zero: the histogram rows, the totals and the
+    // segment starts are each written in full by an earlier kernel of this call before
+    // a later one reads them, so whatever the previous call left behind is never read.
+    return run_bucket(MODE_COUNT_POS, gate, n, n_expert_total, scratch, lec64, offsets, nullptr, pos, inv, nullptr,
+                      (cudaStream_t)stream);
 }

@@ -94,6 +94,27 @@ int fmoe_count_and_pos(const int64_t* gate, int64_t n, int32_t n_expert_total,
                        int64_t* lec64, int64_t* offsets, int64_t* pos, int64_t* inv,
                        void* scratch, fmoe_stream_t stream);
 
+/* Same result as fmoe_count_and_pos, for callers that may not allocate device
+ * memory on this path and therefore have no scratch buffer to pass (a server
+ * whose memory pool owns all free HBM, a plugin host that keeps cudaMalloc off
+ * its request path).  Has no counterpart in the reference.  The scratch is a
+ * fixed array of FMOE_STATIC_SCRATCH_BYTES inside the library, resident on every
+ * GPU that loads the library until the process exits; the call allocates nothing.
+ *   - Limit: fmoe_routing_scratch_bytes(n, n_expert_total) must not exceed
+ *     fmoe_static_scratch_capacity() (e.g. 1 Mi entries x 256 experts, or
+ *     16 Mi entries x 16 experts); larger requests return FMOE_ERR_UNSUPPORTED.
+ *   - The first call on a device looks up the array's device address
+ *     (cudaGetSymbolAddress, with that device current); make that first call
+ *     before starting any stream capture.
+ *   - All calls on a device share the one array: two calls whose kernels can
+ *     overlap on the GPU (different streams, no ordering) race on it.  Calls
+ *     ordered on one stream are safe; nothing needs clearing between them. */
+#define FMOE_STATIC_SCRATCH_BYTES (4u * 1024u * 1024u + 64u * 1024u)
+size_t fmoe_static_scratch_capacity(void);
+int fmoe_count_and_pos_static(const int64_t* gate, int64_t n, int32_t n_expert_total,
+                              int64_t* lec64, int64_t* offsets, int64_t* pos, int64_t* inv,
+                              fmoe_stream_t stream);
+
 /* limit_by_capacity(expert_count, capacity, n_expert, n_worker):
  * cuda/fmoe_cuda.cpp:72-74, cuda/balancing.cu:7-20.  For each local expert e,
  * sources w are served in ascending order: eca[w*E+e] = min(ec[w*E+e], what is
