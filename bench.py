@@ -218,9 +218,11 @@ def run_ours(args):
     clocks = sampler.stop() if sampler else None
     launches = prof.launches
 
-    for _ in range(2):
-        step_e2e()
-    e2e_ms = timed(step_e2e, args.steps)
+    e2e_ms = None
+    if not args.skip_e2e:
+        for _ in range(2):
+            step_e2e()
+        e2e_ms = timed(step_e2e, args.steps)
 
     # Per-kernel timing pass: CUDA events around every library call on the launching stream.
     tprof = fmoe_cuda.Profile(timing=True)
@@ -235,7 +237,7 @@ def run_ours(args):
     ms_per_step = total_ms / args.steps
     tokens = T * world
     value = tokens / (ms_per_step / 1e3)
-    e2e_val = tokens / (e2e_ms / args.steps / 1e3)
+    e2e_val = tokens / (e2e_ms / args.steps / 1e3) if e2e_ms else None
 
     # Dominant kernel: the grouped expert GEMM forward (one launch per call).  Algorithmic
     # work per launch: 2 * rows * d_model * d_hidden flop with rows = tokens * top_k routed
@@ -261,14 +263,16 @@ def run_ours(args):
     layer_frac = layer_flops / (ms_per_step / 1e3) / 1e12 / peaks["bf16_tflops_sustained"]
 
     if rank == 0:
-        cpu_val, cpu_ms, threads = cpu_reference_run(3, 1, CPU_SAMPLE_TOKENS) if world == 1 else (None, None, None)
+        cpu_val, cpu_ms, threads = (cpu_reference_run(3, 1, CPU_SAMPLE_TOKENS)
+                                    if world == 1 and not args.skip_cpu else (None, None, None))
         line = {
             "metric": "moe_layer_fwd_bwd_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": workload_config(world),
-            "e2e": {"value": e2e_val, "unit": "tokens/s", "h2d_bytes_per_step": x_host.numel() * x_host.element_size(),
-                    "d2h_bytes_per_step": 4, "ms_per_step": e2e_ms / args.steps},
+            "e2e": ({"value": e2e_val, "unit": "tokens/s",
+                     "h2d_bytes_per_step": x_host.numel() * x_host.element_size(), "d2h_bytes_per_step": 4,
+                     "ms_per_step": e2e_ms / args.steps} if e2e_ms else None),
             "gpu_launches": launches, "clocks": clocks, "roofline": roofline,
             "layer_tensor_roofline_frac": layer_frac, "per_op_ms": per_op,
         }
@@ -289,6 +293,8 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--skip-e2e", action="store_true", help="omit the host-buffer (e2e) leg (profiling runs)")
+    ap.add_argument("--skip-cpu", action="store_true", help="omit the CPU baseline leg (profiling runs)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -83,4 +83,13 @@ __device__ __forceinline__ float act_grad(float v, int act) {
     return 1.f;
 }
 
+// Factor that the backward multiplies into the input gradient, from the buffer the
+// forward saved: for ReLU the buffer is the activation output (gradient is zero where
+// it is <= 0, cuda/fused_compute.cuh:36-44); for GELU it is the derivative itself.
+__device__ __forceinline__ float saved_act_grad(float saved, int act) {
+    if (act == FMOE_ACT_RELU) return saved > 0.f ? 1.f : 0.f;
+    if (act == FMOE_ACT_GELU) return saved;
+    return 1.f;
+}
+
 }  // namespace fmoe

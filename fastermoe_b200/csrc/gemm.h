@@ -20,7 +20,7 @@ struct LinearArgs {
     const void* bias;    // [n_expert, out_feat] or null
     const int64_t* seg_offsets;  // device, [n_expert + 1]
     void* y;             // [n_rows, out_feat]
-    void* pre_act;       // [n_rows, out_feat] or null
+    void* pre_act;       // [n_rows, out_feat] or null: receives activation'(pre-activation) (GELU)
     int64_t n_rows, in_feat, out_feat;
     int n_expert, dtype, activation;
     const HostSegs* host_segs = nullptr;  // when set, replaces seg_offsets
@@ -31,7 +31,7 @@ struct LinearBwdArgs {
     const void* x;       // [n_rows, in_feat]
     const void* weight;  // [n_expert, out_feat, in_feat]
     const int64_t* seg_offsets;
-    const void* act_pre;  // [n_rows, in_feat] or null: grad_x *= act'(act_pre)
+    const void* act_pre;  // [n_rows, in_feat] or null: ReLU: activation output; GELU: saved derivative
     void* grad_x;         // [n_rows, in_feat] or null
     void* grad_w;         // [n_expert, out_feat, in_feat] or null
     void* grad_b;         // [n_expert, out_feat] or null

@@ -74,7 +74,7 @@ __device__ __forceinline__ bool find_tile(const int64_t* __restrict__ off, const
 }
 
 // MODE 0: Y[m,n]  = sum_k X[m,k] W[e][n,k] (+bias, activation)      rows ragged
-// MODE 1: dX[m,k] = sum_n dY[m,n] W[e][n,k] (* act'(pre[m,k]))      rows ragged
+// MODE 1: dX[m,k] = sum_n dY[m,n] W[e][n,k] (* saved activation derivative)  rows ragged
 template <typename T, int MODE>
 __global__ void __launch_bounds__(TH)
 rows_gemm_kernel(const T* __restrict__ a, const T* __restrict__ w, const T* __restrict__ bias,
@@ -129,10 +129,10 @@ rows_gemm_kernel(const T* __restrict__ a, const T* __restrict__ w, const T* __re
             float v = acc[i][j];
             if (MODE == 0) {
                 if (bias) v += to_float<T>(bias[(int64_t)tm.expert * out_feat + col]);
-                if (pre_out) pre_out[row * ndim + col] = from_float<T>(v);
+                if (pre_out && act == FMOE_ACT_GELU) pre_out[row * ndim + col] = from_float<T>(act_grad(v, act));
                 v = apply_act(v, act);
             } else if (act_pre) {
-                v *= act_grad(to_float<T>(act_pre[row * ndim + col]), act);
+                v *= saved_act_grad(to_float<T>(act_pre[row * ndim + col]), act);
             }
             c[row * ndim + col] = from_float<T>(v);
         }

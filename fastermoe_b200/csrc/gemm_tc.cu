@@ -5,12 +5,14 @@
 // calls, one per expert):
 //
 //   FWD    Y[m,n]     = sum_k X[m,k]  W_e[n,k]   (+bias, activation)   m ragged per expert
-//   DGRAD  dX[m,k]    = sum_n dY[m,n] W_e[n,k]   (* act'(pre))         m ragged per expert
+//   DGRAD  dX[m,k]    = sum_n dY[m,n] W_e[n,k]   (* saved act. derivative) m ragged per expert
 //   WGRAD  dW_e[n,k]  = sum_m dY[m,n] X[m,k]                           contraction ragged
 //
-// CTA = 6 warps: warp 0 issues TMA loads (one lane), warp 1 issues tcgen05.mma
-// (one lane; the whole warp helps to zero ragged tails for WGRAD), warps 2-5
-// drain the accumulator from TMEM (tcgen05.ld), apply the epilogue and store.
+// CTA = 18 warps: warp 0 issues TMA loads (one lane), warp 1 issues tcgen05.mma
+// (one lane; the whole warp helps to zero ragged tails for WGRAD), warps 2-17
+// drain the accumulator from TMEM (tcgen05.ld; four warps per 32-lane quarter,
+// each taking 64 of the 256 columns), apply the epilogue and store through a
+// per-warp staging buffer so that rows are written in contiguous 64-byte pieces.
 // Tile 128 x 256 x 64 (bf16/fp16 in, fp32 accumulate), 4 shared-memory stages of
 // 48 KB, two 256-column TMEM accumulators so that the epilogue of a tile overlaps
 // the main loop of the next one.  Operands are staged with the 128-byte swizzle;
@@ -24,19 +26,34 @@
 #include "common.cuh"
 #include "gemm.h"
 #include <cuda.h>
+#include <cstdlib>
 #include <mutex>
 
 namespace fmoe {
 namespace {
 
 constexpr int BM = 128, BN = 256, BK = 64;
-constexpr int STAGES = 4;
-constexpr int A_BYTES = BM * BK * 2;  // 16 KB
-constexpr int B_BYTES = BN * BK * 2;  // 32 KB
-constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int A_BYTES = BM * BK * 2;    // 16 KB: the CTA's 128 rows of A
 constexpr int SUB_BYTES = 64 * BK * 2;  // one 64x64 box: 8 KB
-constexpr int MAX_EXPERTS_TC = 256;
-constexpr int THREADS = 192;
+constexpr int RING_BYTES = 192 * 1024;  // operand ring of one CTA
+constexpr int MAX_STAGES = 6;
+
+// One CTA per tile (128 x 256), or a pair of CTAs per tile (256 x 256, cta_group::2):
+// in a pair each CTA holds its own 128 rows of A and 128 of the 256 B columns, so
+// the bytes a CTA pulls from L2 per flop drop by a third.
+template <bool CTA2> struct Cfg {
+    static constexpr int B_COLS = CTA2 ? 128 : 256;          // B columns (tile N) staged by this CTA
+    static constexpr int B_BYTES = B_COLS * BK * 2;          // 16 or 32 KB
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;    // 32 or 48 KB
+    static constexpr int STAGES = RING_BYTES / STAGE_BYTES;  // 6 or 4
+    static constexpr int TILE_M = CTA2 ? 256 : 128;          // tile rows across the CTA group
+};
+constexpr int MAX_EXPERTS_TC = 128;
+constexpr int EPI_WARPS = 8;                 // EPI_WARPS/4 per TMEM lane quarter, splitting the 256 columns
+constexpr int CW = 64;                       // columns handled per epilogue iteration (32 or 64)
+constexpr int STAGING_BYTES = 32 * CW * 2;  // per epilogue warp: 32 rows x CW columns of 16-bit values
+constexpr int COLS_PER_WARP = BN / (EPI_WARPS / 4);
+constexpr int THREADS = 64 + EPI_WARPS * 32;
 constexpr int TMEM_COLS = 512;
 constexpr unsigned long long WAIT_LIMIT_CYCLES = 4000000000ull;  // ~2 s at 1.9 GHz
 
@@ -57,10 +74,13 @@ struct Params {
     int accumulate;  // WGRAD only
     int is_bf16;
     int* status;  // device status word
+    int debug;    // FMOE_B200_DEBUG bits (profiling experiments): 1 = no global stores, 2 = no TMEM loads
 };
 
 struct Shared {
-    unsigned long long full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2];
+    // full: this CTA's operands of a stage have landed (TMA).  peer_ready (pairs, in the
+    // leader): the other CTA's have.  empty: the MMAs reading the stage have completed.
+    unsigned long long full[MAX_STAGES], empty[MAX_STAGES], peer_ready[MAX_STAGES], tmem_full[2], tmem_empty[2];
     uint32_t tmem_base;
     int abort;
     int cum_tiles[MAX_EXPERTS_TC + 1];
@@ -107,6 +127,66 @@ __device__ __forceinline__ bool mbar_wait(unsigned long long* bar, uint32_t pari
         }
     }
 }
+// --- cluster (CTA pair) helpers ---
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Address of the same shared-memory object in CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t map_to_cta(const void* p, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_u32(p)), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster(unsigned long long* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait on a barrier that CTAs of the cluster arrive on.
+__device__ __forceinline__ bool mbar_wait_cluster(unsigned long long* bar, uint32_t parity, Shared* sh, int* status, int code) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    const unsigned long long t0 = clock64();
+    while (true) {
+        if (mbar_try_wait_cluster(bar, parity)) return true;
+        if (*(volatile int*)&sh->abort) return false;
+        if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+            *(volatile int*)&sh->abort = 1;
+            atomicCAS(status, 0, code);
+            return false;
+        }
+    }
+}
+// Completion of all MMAs issued so far by this thread -> arrive on the barrier at the
+// same shared-memory offset in both CTAs of the pair.
+__device__ __forceinline__ void tc_commit_pair(unsigned long long* bar) {
+    asm volatile(
+        "{\n\t.reg .b16 m;\n\tmov.b16 m, 3;\n\t"
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], m;\n\t}"
+        ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_mma_pair(uint32_t tmem_c, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_c), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
 __device__ __forceinline__ void tma_load_2d(const CUtensorMap* map, unsigned long long* bar, void* dst, int x, int y) {
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
@@ -157,11 +237,57 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes
 // Instruction descriptor, kind::f16: fp32 accumulate, A/B both bf16 or both fp16.
 //   [4,6) C format (1 = f32)  [7,10) A format  [10,13) B format (0 = f16, 1 = bf16)
 //   [15] A major (1 = MN)  [16] B major (1 = MN)  [17,23) N >> 3  [24,29) M >> 4
-__host__ __device__ constexpr uint32_t make_idesc(bool bf16, bool a_mn, bool b_mn) {
+__host__ __device__ constexpr uint32_t make_idesc(bool bf16, bool a_mn, bool b_mn, int m) {
     return (1u << 4) | ((bf16 ? 1u : 0u) << 7) | ((bf16 ? 1u : 0u) << 10) | ((a_mn ? 1u : 0u) << 15) |
-           ((b_mn ? 1u : 0u) << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+           ((b_mn ? 1u : 0u) << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
+// GELU and its derivative for the 16-bit epilogues.  Phi(x) = 1 - D(|x|/sqrt2)^-16 / 2
+// with the degree-6 polynomial D of Abramowitz-Stegun 7.1.28 (coefficients below are
+// already scaled to take |x|); the derivative of that form gives the density term.
+// One reciprocal per element, no exponential.  Absolute error: 7e-7 (value), 1.5e-6
+// (derivative), far below bf16/fp16 resolution.
+#define FMOE_D1 0.04986734616f
+#define FMOE_D2 0.02114100615f
+#define FMOE_D3 0.00327762621f
+#define FMOE_D4 0.0000380035750f
+#define FMOE_D5 0.0000488906318f
+#define FMOE_D6 0.0000053829750f
+__device__ __forceinline__ float rcp_approx(float d) {
+    float r;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(d));
+    return r;
+}
+__device__ __forceinline__ float gelu_fast(float x) {
+    const float ax = fabsf(x);
+    float d = fmaf(FMOE_D6, ax, FMOE_D5);
+    d = fmaf(d, ax, FMOE_D4); d = fmaf(d, ax, FMOE_D3); d = fmaf(d, ax, FMOE_D2); d = fmaf(d, ax, FMOE_D1);
+    d = fmaf(d, ax, 1.f);
+    float r = rcp_approx(d);
+    r *= r; r *= r; r *= r; r *= r;  // D^-16
+    return fmaf(-0.5f * ax, r, fmaxf(x, 0.f));
+}
+// Value and derivative together (they share the polynomial and the reciprocal).
+__device__ __forceinline__ void gelu_both_fast(float x, float& val, float& grad) {
+    const float ax = fabsf(x);
+    float d = fmaf(FMOE_D6, ax, FMOE_D5);
+    d = fmaf(d, ax, FMOE_D4); d = fmaf(d, ax, FMOE_D3); d = fmaf(d, ax, FMOE_D2); d = fmaf(d, ax, FMOE_D1);
+    d = fmaf(d, ax, 1.f);
+    float dp = fmaf(6.f * FMOE_D6, ax, 5.f * FMOE_D5);
+    dp = fmaf(dp, ax, 4.f * FMOE_D4); dp = fmaf(dp, ax, 3.f * FMOE_D3); dp = fmaf(dp, ax, 2.f * FMOE_D2);
+    dp = fmaf(dp, ax, FMOE_D1);
+    const float r = rcp_approx(d);
+    float r16 = r * r; r16 *= r16; r16 *= r16; r16 *= r16;
+    const float tail = 0.5f * r16;
+    val = fmaf(-ax, tail, fmaxf(x, 0.f));
+    const float cdf = x >= 0.f ? 1.f - tail : tail;
+    grad = fmaf(x, 8.f * r16 * r * dp, cdf);
+}
+__device__ __forceinline__ float act_fast(float v, int act) {
+    if (act == FMOE_ACT_RELU) return v > 0.f ? v : 0.f;
+    if (act == FMOE_ACT_GELU) return gelu_fast(v);
+    return v;
+}
 template <bool BF16> __device__ __forceinline__ float cvt_in(uint16_t raw) {
     if (BF16) return __uint_as_float((uint32_t)raw << 16);
     return __half2float(__ushort_as_half(raw));
@@ -175,12 +301,49 @@ template <bool BF16> __device__ __forceinline__ uint32_t cvt_pack(float lo, floa
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// ---- epilogue staging ----------------------------------------------------------
+// A warp's staging buffer holds 32 rows of CW 16-bit values (NCH = CW/8 chunks of 16
+// bytes).  Chunk j of row r sits at slot j ^ f(r), f chosen so that both access
+// patterns are free of bank conflicts: lane = row (register side) and NCH lanes per
+// row (global-memory side, CW*2 contiguous bytes per row).
+constexpr int NCH = CW / 8;
+__device__ __forceinline__ int stage_slot(int row, int j) {
+    return row * NCH + (NCH == 8 ? (j ^ (row & 7)) : (j ^ ((row >> 1) & 3)));
+}
+
+template <bool BF16>
+__device__ __forceinline__ void stage_put(uint4* stage, int lane, const float* v) {
+#pragma unroll
+    for (int q = 0; q < NCH; ++q)
+        stage[stage_slot(lane, q)] =
+            make_uint4(cvt_pack<BF16>(v[q * 8], v[q * 8 + 1]), cvt_pack<BF16>(v[q * 8 + 2], v[q * 8 + 3]),
+                       cvt_pack<BF16>(v[q * 8 + 4], v[q * 8 + 5]), cvt_pack<BF16>(v[q * 8 + 6], v[q * 8 + 7]));
+    __syncwarp();
+}
+// staging -> global: rows [0, rows) of the block, CW columns starting at dst.
+__device__ __forceinline__ void stage_store(const uint4* stage, int lane, uint16_t* dst, size_t ld, int rows) {
+    constexpr int RPI = 32 / NCH;  // rows per instruction
+    const int j = lane % NCH;
+#pragma unroll
+    for (int it = 0; it < 32 / RPI; ++it) {
+        const int row = it * RPI + lane / NCH;
+        if (row < rows) *reinterpret_cast<uint4*>(dst + (size_t)row * ld + j * 8) = stage[stage_slot(row, j)];
+    }
+    __syncwarp();
+}
+// CW values of this lane's own row (contiguous), or zeros when the row is absent.
+__device__ __forceinline__ void row_load(uint4* q, const uint16_t* src, bool valid) {
+#pragma unroll
+    for (int i = 0; i < NCH; ++i) q[i] = valid ? __ldg(reinterpret_cast<const uint4*>(src) + i) : make_uint4(0, 0, 0, 0);
+}
+
 struct Tile {
     int e, row0, rows, col0, chunks;  // rows/row0: output rows of the tile (FWD/DGRAD: tokens; WGRAD: weight rows)
     int m_lo, m_hi;                   // WGRAD: contraction range
 };
 
-template <int MODE>
+// Tile of the CTA group; row0/rows span TILE_M rows (a CTA of a pair takes 128 of them).
+template <int MODE, int TILE_M>
 __device__ __forceinline__ void locate(const Shared* sh, const Params& p, int tile, int& e_cursor, Tile& t) {
     while (tile >= sh->cum_tiles[e_cursor + 1]) ++e_cursor;
     const int local = tile - sh->cum_tiles[e_cursor];
@@ -188,39 +351,47 @@ __device__ __forceinline__ void locate(const Shared* sh, const Params& p, int ti
     t.e = e_cursor;
     const int lo = sh->seg_lo[e_cursor], hi = sh->seg_hi[e_cursor];
     if (MODE == MODE_WGRAD) {
-        t.row0 = (local / nt) * BM;
-        t.rows = min(BM, p.out_rows_per_expert - t.row0);
+        t.row0 = (local / nt) * TILE_M;
+        t.rows = min(TILE_M, p.out_rows_per_expert - t.row0);
         t.col0 = (local % nt) * BN;
         t.m_lo = lo;
         t.m_hi = hi;
         t.chunks = (hi - lo + BK - 1) / BK;
     } else {
-        t.row0 = lo + (local / nt) * BM;
-        t.rows = min(BM, hi - t.row0);
+        t.row0 = lo + (local / nt) * TILE_M;
+        t.rows = min(TILE_M, hi - t.row0);
         t.col0 = (local % nt) * BN;
         t.chunks = (p.n_contr + BK - 1) / BK;
         t.m_lo = t.m_hi = 0;
     }
 }
 
-template <int MODE, bool BF16>
+template <int MODE, bool BF16, bool CTA2>
 __global__ void __launch_bounds__(THREADS, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const __grid_constant__ HostSegs hs, const Params p) {
+    using C = Cfg<CTA2>;
+    constexpr int STAGES = C::STAGES, STAGE_BYTES = C::STAGE_BYTES, TILE_M = C::TILE_M, B_COLS = C::B_COLS;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    Shared* sh = (Shared*)(tiles + STAGES * STAGE_BYTES);
+    Shared* sh = (Shared*)(tiles + RING_BYTES + EPI_WARPS * STAGING_BYTES);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // In a pair, CTA 0 (the leader) issues the MMAs for both; each CTA loads its own
+    // operands and drains its own 128 accumulator rows.
+    const int cta = CTA2 ? (int)cluster_ctarank() : 0;
+    const int first_tile = CTA2 ? blockIdx.x / 2 : blockIdx.x;
+    const int tile_step = CTA2 ? gridDim.x / 2 : gridDim.x;
 
     // ---- set-up ---------------------------------------------------------------
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(&sh->full[s], 1);
             mbar_init(&sh->empty[s], 1);
+            mbar_init(&sh->peer_ready[s], 1);
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(&sh->tmem_full[a], 1);
-            mbar_init(&sh->tmem_empty[a], 4);
+            mbar_init(&sh->tmem_empty[a], CTA2 ? 2 * EPI_WARPS : EPI_WARPS);
         }
         sh->abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -236,18 +407,24 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         sh->cum_tiles[0] = 0;
         for (int e = 0; e < p.n_expert; ++e) {
             int mt;
-            if (MODE == MODE_WGRAD) mt = (p.out_rows_per_expert + BM - 1) / BM;
-            else mt = (sh->seg_hi[e] - sh->seg_lo[e] + BM - 1) / BM;
+            if (MODE == MODE_WGRAD) mt = (p.out_rows_per_expert + TILE_M - 1) / TILE_M;
+            else mt = (sh->seg_hi[e] - sh->seg_lo[e] + TILE_M - 1) / TILE_M;
             acc += mt * nt;
             sh->cum_tiles[e + 1] = acc;
         }
     }
     if (warp == 0) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sh->tmem_base)), "r"(TMEM_COLS) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        if (CTA2) {
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sh->tmem_base)), "r"(TMEM_COLS) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sh->tmem_base)), "r"(TMEM_COLS) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
     }
     tc_fence_before();
     __syncthreads();
+    if (CTA2) cluster_sync_all();  // both CTAs' barriers exist before anything arrives on them
     tc_fence_after();
     const uint32_t tmem_base = sh->tmem_base;
     const int total_tiles = sh->cum_tiles[p.n_expert];
@@ -258,31 +435,33 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             int s = 0, e_cur = 0;
             uint32_t ph = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            const int my_row = cta * BM;      // this CTA's rows inside the tile
+            const int my_col = cta * B_COLS;  // this CTA's share of the tile's B columns (pairs)
+            for (int tile = first_tile; tile < total_tiles && ok; tile += tile_step) {
                 Tile t;
-                locate<MODE>(sh, p, tile, e_cur, t);
+                locate<MODE, TILE_M>(sh, p, tile, e_cur, t);
                 for (int ch = 0; ch < t.chunks; ++ch) {
                     if (!(ok = mbar_wait(&sh->empty[s], ph ^ 1, sh, p.status, 1))) break;
                     uint8_t* a_dst = tiles + s * STAGE_BYTES;
                     uint8_t* b_dst = a_dst + A_BYTES;
                     mbar_expect_tx(&sh->full[s], STAGE_BYTES);
                     if (MODE == MODE_FWD) {
-                        tma_load_2d(&map_a, &sh->full[s], a_dst, ch * BK, t.row0);
-                        tma_load_2d(&map_b, &sh->full[s], b_dst, ch * BK, t.e * p.w_rows + t.col0);
+                        tma_load_2d(&map_a, &sh->full[s], a_dst, ch * BK, t.row0 + my_row);
+                        tma_load_2d(&map_b, &sh->full[s], b_dst, ch * BK, t.e * p.w_rows + t.col0 + my_col);
                     } else if (MODE == MODE_DGRAD) {
-                        tma_load_2d(&map_a, &sh->full[s], a_dst, ch * BK, t.row0);
+                        tma_load_2d(&map_a, &sh->full[s], a_dst, ch * BK, t.row0 + my_row);
 #pragma unroll
-                        for (int j = 0; j < BN / 64; ++j)
-                            tma_load_2d(&map_b, &sh->full[s], b_dst + j * SUB_BYTES, t.col0 + j * 64,
+                        for (int j = 0; j < B_COLS / 64; ++j)
+                            tma_load_2d(&map_b, &sh->full[s], b_dst + j * SUB_BYTES, t.col0 + my_col + j * 64,
                                         t.e * p.w_rows + ch * BK);
                     } else {
                         const int m0 = t.m_lo + ch * BK;
 #pragma unroll
                         for (int j = 0; j < BM / 64; ++j)
-                            tma_load_2d(&map_a, &sh->full[s], a_dst + j * SUB_BYTES, t.row0 + j * 64, m0);
+                            tma_load_2d(&map_a, &sh->full[s], a_dst + j * SUB_BYTES, t.row0 + my_row + j * 64, m0);
 #pragma unroll
-                        for (int j = 0; j < BN / 64; ++j)
-                            tma_load_2d(&map_b, &sh->full[s], b_dst + j * SUB_BYTES, t.col0 + j * 64, m0);
+                        for (int j = 0; j < B_COLS / 64; ++j)
+                            tma_load_2d(&map_b, &sh->full[s], b_dst + j * SUB_BYTES, t.col0 + my_col + j * 64, m0);
                     }
                     if (++s == STAGES) { s = 0; ph ^= 1; }
                 }
@@ -291,7 +470,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     } else if (warp == 1) {
         // ---- MMA issuer -------------------------------------------------------
         constexpr bool A_MN = MODE == MODE_WGRAD, B_MN = MODE != MODE_FWD;
-        constexpr uint32_t idesc = make_idesc(BF16, A_MN, B_MN);
+        constexpr uint32_t idesc = make_idesc(BF16, A_MN, B_MN, TILE_M);
         // K-major: 8-row groups 1024 B apart, K advance 32 B per UMMA_K=16.
         // MN-major: 64-element column blocks 8 KB apart (leading), 8-row K groups 1024 B apart (stride),
         //           K advance 16 rows x 128 B = 2048 B.
@@ -300,12 +479,15 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         int s = 0, e_cur = 0, acc = 0;
         uint32_t ph = 0, acc_ph = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        const bool leader = cta == 0;
+        for (int tile = first_tile; tile < total_tiles && ok; tile += tile_step) {
             Tile t;
-            locate<MODE>(sh, p, tile, e_cur, t);
+            locate<MODE, TILE_M>(sh, p, tile, e_cur, t);
             if (t.chunks == 0) continue;
-            if (!(ok = mbar_wait(&sh->tmem_empty[acc], acc_ph ^ 1, sh, p.status, 2))) break;
-            tc_fence_after();
+            if (leader) {
+                if (!(ok = mbar_wait_cluster(&sh->tmem_empty[acc], acc_ph ^ 1, sh, p.status, 2))) break;
+                tc_fence_after();
+            }
             const uint32_t tmem_c = tmem_base + acc * BN;
             for (int ch = 0; ch < t.chunks; ++ch) {
                 if (!(ok = mbar_wait(&sh->full[s], ph, sh, p.status, 3))) break;
@@ -318,7 +500,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     // row is one 128-byte line per 64-column block, whatever the swizzle.
                     const int valid = t.m_hi - (t.m_lo + ch * BK);
                     if (valid < BK) {
-                        const int lines = (BK - valid) * ((BM + BN) / 64);
+                        const int lines = (BK - valid) * ((BM + B_COLS) / 64);
                         for (int i = lane; i < lines * 8; i += 32) {
                             const int line = i >> 3, part = i & 7;
                             const int blk = line / (BK - valid), r = valid + line % (BK - valid);
@@ -329,66 +511,151 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         __syncwarp();
                     }
                 }
+                if (CTA2 && !leader) {
+                    // This CTA's operands of the stage are in place: tell the leader.
+                    if (lane == 0) mbar_arrive_remote(map_to_cta(&sh->peer_ready[s], 0));
+                    __syncwarp();
+                    if (++s == STAGES) { s = 0; ph ^= 1; }
+                    continue;
+                }
+                if (CTA2) {
+                    if (!(ok = mbar_wait_cluster(&sh->peer_ready[s], ph, sh, p.status, 5))) break;
+                    tc_fence_after();
+                }
                 if (lane == 0) {
                     const uint64_t adesc = make_desc(smem_u32(a_src), A_LBO, 1024);
                     const uint64_t bdesc = make_desc(smem_u32(b_src), B_LBO, 1024);
 #pragma unroll
-                    for (int k = 0; k < BK / 16; ++k)
-                        tc_mma(tmem_c, adesc + (uint64_t)((k * A_ADV) >> 4), bdesc + (uint64_t)((k * B_ADV) >> 4),
-                               idesc, (ch > 0 || k > 0) ? 1u : 0u);
-                    tc_commit(&sh->empty[s]);
+                    for (int k = 0; k < BK / 16; ++k) {
+                        const uint64_t ad = adesc + (uint64_t)((k * A_ADV) >> 4), bd = bdesc + (uint64_t)((k * B_ADV) >> 4);
+                        const uint32_t accum = (ch > 0 || k > 0) ? 1u : 0u;
+                        if (CTA2) tc_mma_pair(tmem_c, ad, bd, idesc, accum);
+                        else tc_mma(tmem_c, ad, bd, idesc, accum);
+                    }
+                    if (CTA2) tc_commit_pair(&sh->empty[s]);
+                    else tc_commit(&sh->empty[s]);
                 }
                 __syncwarp();
                 if (++s == STAGES) { s = 0; ph ^= 1; }
             }
             if (!ok) break;
-            if (lane == 0) tc_commit(&sh->tmem_full[acc]);
-            __syncwarp();
+            if (leader) {
+                if (lane == 0) {
+                    if (CTA2) tc_commit_pair(&sh->tmem_full[acc]);
+                    else tc_commit(&sh->tmem_full[acc]);
+                }
+                __syncwarp();
+            }
             if (++acc == 2) { acc = 0; acc_ph ^= 1; }
         }
     } else {
-        // ---- epilogue (warps 2..5) -------------------------------------------
-        const int quarter = warp & 3;  // TMEM lanes [32*quarter, +32) are readable by this warp
+        // ---- epilogue (warps 2..17) ------------------------------------------
+        const int quarter = warp & 3;    // TMEM lanes [32*quarter, +32) are readable by this warp
+        const int cgrp = (warp - 2) >> 2;  // which COLS_PER_WARP of the tile's 256 columns
         const int r = quarter * 32 + lane;
+        uint4* stage = reinterpret_cast<uint4*>(tiles + STAGES * STAGE_BYTES) + (warp - 2) * (STAGING_BYTES / 16);
         int e_cur = 0, acc = 0;
         uint32_t acc_ph = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        const uint32_t tmem_empty_addr[2] = {CTA2 ? map_to_cta(&sh->tmem_empty[0], 0) : 0u,
+                                             CTA2 ? map_to_cta(&sh->tmem_empty[1], 0) : 0u};
+        for (int tile = first_tile; tile < total_tiles && ok; tile += tile_step) {
             Tile t;
-            locate<MODE>(sh, p, tile, e_cur, t);
-            const bool row_ok = r < t.rows;
-            uint16_t* out_row;
-            if (MODE == MODE_WGRAD)
-                out_row = (uint16_t*)p.out + ((size_t)t.e * p.out_rows_per_expert + t.row0 + r) * (size_t)p.n_out;
-            else
-                out_row = (uint16_t*)p.out + (size_t)(t.row0 + r) * (size_t)p.n_out;
+            locate<MODE, TILE_M>(sh, p, tile, e_cur, t);
+            // this CTA's 128 rows of the tile
+            t.row0 += cta * BM;
+            t.rows = min(BM, t.rows - cta * BM);
+            const size_t ld = (size_t)p.n_out;
+            const int col_lo = t.col0 + cgrp * COLS_PER_WARP;  // this warp's first column
             if (t.chunks == 0) {
                 // WGRAD of an expert without rows: the gradient is zero.
-                if (!p.accumulate && row_ok)
-                    for (int c = 0; c < BN && t.col0 + c < p.n_out; c += 8)
-                        *reinterpret_cast<uint4*>(out_row + t.col0 + c) = make_uint4(0, 0, 0, 0);
+                if (!p.accumulate && r < t.rows && col_lo < p.n_out) {
+                    uint16_t* zrow = (uint16_t*)p.out + ((size_t)t.e * p.out_rows_per_expert + t.row0 + r) * ld + col_lo;
+#pragma unroll
+                    for (int c = 0; c < COLS_PER_WARP; c += 8)
+                        if (col_lo + c < p.n_out) *reinterpret_cast<uint4*>(zrow + c) = make_uint4(0, 0, 0, 0);
+                }
                 continue;
             }
+            // Rows of this warp: tile rows [32*quarter, +32).  Stores go through the warp's
+            // staging buffer so that 4 lanes write 64 contiguous bytes of a row.
+            const int rows_here = min(32, t.rows - quarter * 32);  // <= 0: nothing to store
+            const bool active = rows_here > 0 && col_lo < p.n_out;
+            const bool row_ok = r < t.rows;
+            const size_t row_off = (MODE == MODE_WGRAD ? (size_t)t.e * p.out_rows_per_expert : 0) + t.row0;
+            uint16_t* out_blk = (uint16_t*)p.out + (row_off + quarter * 32) * ld + col_lo;  // block origin
+            // Operands of the epilogue that do not depend on the accumulator are fetched
+            // before waiting for it: bias (FWD), pre-activation (DGRAD), old gradient (WGRAD).
+            const uint16_t* aux_src = nullptr;
+            bool aux_row = false;
+            if (MODE == MODE_FWD && p.bias) { aux_src = (const uint16_t*)p.bias + (size_t)t.e * ld + col_lo; aux_row = true; }
+            if (MODE == MODE_DGRAD && p.act_pre) { aux_src = (const uint16_t*)p.act_pre + (row_off + r) * ld + col_lo; aux_row = row_ok; }
+            if (MODE == MODE_WGRAD && p.accumulate) { aux_src = (const uint16_t*)p.out + (row_off + r) * ld + col_lo; aux_row = row_ok; }
+            uint4 aux[NCH];
+            if (aux_src && active) row_load(aux, aux_src, aux_row);
             if (!(ok = mbar_wait(&sh->tmem_full[acc], acc_ph, sh, p.status, 4))) break;
             tc_fence_after();
-            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
-            for (int c0 = 0; c0 < BN; c0 += 32) {
-                const int col = t.col0 + c0;
-                if (col >= p.n_out) break;
-                uint32_t raw[32];
-                tc_ld32(taddr + c0, raw);
-                tc_wait_ld();
-                if (!row_ok) continue;
-                float v[32];
+            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN + cgrp * COLS_PER_WARP;
+            if (active) {
+                for (int c = 0; c < COLS_PER_WARP / CW; ++c) {
+                    if (col_lo + c * CW >= p.n_out) break;
+                    uint32_t raw[CW];
+                    if (!(p.debug & 2)) {
+                        tc_ld32(taddr + c * CW, raw);
+                        if (CW == 64) tc_ld32(taddr + c * CW + 32, raw + 32);
+                    } else {
 #pragma unroll
-                for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(raw[i]);
-                if (MODE == MODE_FWD) {
-                    if (p.bias) {
-                        const uint4* bp = reinterpret_cast<const uint4*>((const uint16_t*)p.bias + (size_t)t.e * p.n_out + col);
+                        for (int i = 0; i < CW; ++i) raw[i] = 0;
+                    }
+                    if (c > 0 && aux_src) row_load(aux, aux_src + c * CW, aux_row);
+                    tc_wait_ld();
+                    float* v = reinterpret_cast<float*>(raw);
+                    const uint4* aq = aux;
+                    if (MODE == MODE_FWD) {
+                        if (p.bias) {
 #pragma unroll
-                        for (int q = 0; q < 4; ++q) {
-                            const uint4 b = __ldg(bp + q);
-                            const uint32_t w[4] = {b.x, b.y, b.z, b.w};
+                            for (int q = 0; q < NCH; ++q) {
+                                const uint32_t w[4] = {aq[q].x, aq[q].y, aq[q].z, aq[q].w};
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) {
+                                    v[q * 8 + 2 * i] += cvt_in<BF16>((uint16_t)(w[i] & 0xffff));
+                                    v[q * 8 + 2 * i + 1] += cvt_in<BF16>((uint16_t)(w[i] >> 16));
+                                }
+                            }
+                        }
+                        if (p.pre_out && p.act == FMOE_ACT_GELU) {
+                            // keep the derivative for the backward, then continue with the value
+#pragma unroll
+                            for (int q = 0; q < NCH; ++q) {
+                                float g[8];
+#pragma unroll
+                                for (int i = 0; i < 8; ++i) gelu_both_fast(v[q * 8 + i], v[q * 8 + i], g[i]);
+                                stage[stage_slot(lane, q)] =
+                                    make_uint4(cvt_pack<BF16>(g[0], g[1]), cvt_pack<BF16>(g[2], g[3]),
+                                               cvt_pack<BF16>(g[4], g[5]), cvt_pack<BF16>(g[6], g[7]));
+                            }
+                            __syncwarp();
+                            stage_store(stage, lane, (uint16_t*)p.pre_out + (row_off + quarter * 32) * ld + col_lo + c * CW, ld, rows_here);
+                        } else if (p.act != FMOE_ACT_NONE) {
+#pragma unroll
+                            for (int i = 0; i < CW; ++i) v[i] = act_fast(v[i], p.act);
+                        }
+                    } else if (MODE == MODE_DGRAD) {
+                        if (p.act_pre) {
+#pragma unroll
+                            for (int q = 0; q < NCH; ++q) {
+                                const uint32_t w[4] = {aq[q].x, aq[q].y, aq[q].z, aq[q].w};
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) {
+                                    v[q * 8 + 2 * i] *= saved_act_grad(cvt_in<BF16>((uint16_t)(w[i] & 0xffff)), p.act);
+                                    v[q * 8 + 2 * i + 1] *= saved_act_grad(cvt_in<BF16>((uint16_t)(w[i] >> 16)), p.act);
+                                }
+                            }
+                        }
+                    } else if (p.accumulate) {
+#pragma unroll
+                        for (int q = 0; q < NCH; ++q) {
+                            const uint32_t w[4] = {aq[q].x, aq[q].y, aq[q].z, aq[q].w};
 #pragma unroll
                             for (int i = 0; i < 4; ++i) {
                                 v[q * 8 + 2 * i] += cvt_in<BF16>((uint16_t)(w[i] & 0xffff));
@@ -396,54 +663,18 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                             }
                         }
                     }
-                    if (p.pre_out) {
-                        uint16_t* pr = (uint16_t*)p.pre_out + (size_t)(t.row0 + r) * (size_t)p.n_out + col;
-#pragma unroll
-                        for (int q = 0; q < 4; ++q)
-                            *reinterpret_cast<uint4*>(pr + q * 8) =
-                                make_uint4(cvt_pack<BF16>(v[q * 8], v[q * 8 + 1]), cvt_pack<BF16>(v[q * 8 + 2], v[q * 8 + 3]),
-                                           cvt_pack<BF16>(v[q * 8 + 4], v[q * 8 + 5]), cvt_pack<BF16>(v[q * 8 + 6], v[q * 8 + 7]));
-                    }
-                    if (p.act != FMOE_ACT_NONE) {
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) v[i] = apply_act(v[i], p.act);
-                    }
-                } else if (MODE == MODE_DGRAD) {
-                    if (p.act_pre) {
-                        const uint4* ap = reinterpret_cast<const uint4*>((const uint16_t*)p.act_pre + (size_t)(t.row0 + r) * (size_t)p.n_out + col);
-#pragma unroll
-                        for (int q = 0; q < 4; ++q) {
-                            const uint4 a = __ldg(ap + q);
-                            const uint32_t w[4] = {a.x, a.y, a.z, a.w};
-#pragma unroll
-                            for (int i = 0; i < 4; ++i) {
-                                v[q * 8 + 2 * i] *= act_grad(cvt_in<BF16>((uint16_t)(w[i] & 0xffff)), p.act);
-                                v[q * 8 + 2 * i + 1] *= act_grad(cvt_in<BF16>((uint16_t)(w[i] >> 16)), p.act);
-                            }
-                        }
-                    }
-                } else if (p.accumulate) {
-                    const uint4* op = reinterpret_cast<const uint4*>(out_row + col);
-#pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        const uint4 a = op[q];
-                        const uint32_t w[4] = {a.x, a.y, a.z, a.w};
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            v[q * 8 + 2 * i] += cvt_in<BF16>((uint16_t)(w[i] & 0xffff));
-                            v[q * 8 + 2 * i + 1] += cvt_in<BF16>((uint16_t)(w[i] >> 16));
-                        }
+                    if (!(p.debug & 1)) {
+                        stage_put<BF16>(stage, lane, v);
+                        stage_store(stage, lane, out_blk + c * CW, ld, rows_here);
                     }
                 }
-#pragma unroll
-                for (int q = 0; q < 4; ++q)
-                    *reinterpret_cast<uint4*>(out_row + col + q * 8) =
-                        make_uint4(cvt_pack<BF16>(v[q * 8], v[q * 8 + 1]), cvt_pack<BF16>(v[q * 8 + 2], v[q * 8 + 3]),
-                                   cvt_pack<BF16>(v[q * 8 + 4], v[q * 8 + 5]), cvt_pack<BF16>(v[q * 8 + 6], v[q * 8 + 7]));
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&sh->tmem_empty[acc]);
+            if (lane == 0) {
+                if (CTA2) mbar_arrive_remote(tmem_empty_addr[acc]);  // the leader's barrier (also from the leader)
+                else mbar_arrive(&sh->tmem_empty[acc]);
+            }
             if (++acc == 2) { acc = 0; acc_ph ^= 1; }
         }
     }
@@ -457,8 +688,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
     tc_fence_before();
     __syncthreads();
+    if (CTA2) cluster_sync_all();  // the peer may still arrive on this CTA's barriers until here
     if (warp == 0) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+        if (CTA2) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+        else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
     }
 }
 
@@ -498,7 +731,8 @@ int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int
     return 0;
 }
 
-constexpr size_t SMEM_BYTES = 1024 + (size_t)STAGES * STAGE_BYTES + sizeof(Shared);
+constexpr size_t SMEM_BYTES = 1024 + (size_t)RING_BYTES + (size_t)EPI_WARPS * STAGING_BYTES + sizeof(Shared);
+static_assert(SMEM_BYTES <= 232448, "shared memory budget of one CTA exceeded");
 
 // Device address of the status word on the current device (cached per device).
 int* status_ptr() {
@@ -514,15 +748,52 @@ int* status_ptr() {
 
 const HostSegs kNoSegs = {};
 
-template <int MODE>
-int launch(const CUtensorMap& ma, const CUtensorMap& mb, const HostSegs* hsp, const Params& p, int64_t max_tiles,
+// FMOE_B200_GEMM=pair selects the CTA-pair (cta_group::2) kernel.  It moves a third
+// fewer operand bytes per flop, but on ragged expert segments its 256-row tiles waste
+// more rows and it measured slightly slower than one CTA per tile, so it is opt-in.
+bool pair_kernel_enabled() {
+    const char* p = getenv("FMOE_B200_GEMM");
+    return p && p[0] == 'p';
+}
+
+template <int MODE, bool CTA2>
+int launch(const CUtensorMap& ma, const CUtensorMap& mb, const HostSegs* hsp, const Params& p_in, int64_t max_tiles,
            cudaStream_t st) {
     const HostSegs& hs = hsp ? *hsp : kNoSegs;
-    auto kern = p.is_bf16 ? grouped_gemm_kernel<MODE, true> : grouped_gemm_kernel<MODE, false>;
+    Params p = p_in;
+    if (const char* dbg = getenv("FMOE_B200_DEBUG")) p.debug = atoi(dbg);
+    auto kern = p.is_bf16 ? grouped_gemm_kernel<MODE, true, CTA2> : grouped_gemm_kernel<MODE, false, CTA2>;
     FMOE_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
-    const unsigned grid = (unsigned)std::max<int64_t>(1, std::min<int64_t>(max_tiles, sm_count()));
-    kern<<<grid, THREADS, SMEM_BYTES, st>>>(ma, mb, hs, p);
-    FMOE_CHECK_LAUNCH();
+    cudaLaunchConfig_t cfg = {};
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = SMEM_BYTES;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    if (CTA2) {
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        // one pair per two SMs, as many pairs as can be resident at once
+        static int max_pairs[64] = {};
+        int dev = 0;
+        FMOE_CUDA_TRY(cudaGetDevice(&dev));
+        if (dev < 0 || dev >= 64) dev = 0;
+        if (!max_pairs[dev]) {
+            cfg.gridDim = dim3((unsigned)(sm_count() / 2 * 2));
+            int n = 0;
+            FMOE_CUDA_TRY(cudaOccupancyMaxActiveClusters(&n, kern, &cfg));
+            max_pairs[dev] = n > 0 ? n : 1;
+            if (p.debug & 4) fprintf(stderr, "[fmoe] resident CTA pairs: %d (SMs: %d)\n", n, sm_count());
+        }
+        const int64_t pairs = std::max<int64_t>(1, std::min<int64_t>(max_tiles, max_pairs[dev]));
+        cfg.gridDim = dim3((unsigned)(2 * pairs));
+    } else {
+        cfg.gridDim = dim3((unsigned)std::max<int64_t>(1, std::min<int64_t>(max_tiles, sm_count())));
+    }
+    FMOE_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, ma, mb, hs, p));
     return 0;
 }
 
@@ -535,38 +806,78 @@ bool shape_ok(int64_t n_rows, int64_t in_feat, int64_t out_feat, int n_expert, i
 }
 
 // Column sums of dY per expert segment (bias gradient), fp32 accumulate.
-template <bool BF16>
+// Block = CL column lanes (8 columns each, one 16-byte load) x 256/CL row lanes;
+// every thread keeps four independent row loads in flight.  CL = 16 (128 columns per
+// block) for wide outputs, 8 (64 columns) when that gives too few blocks.
+template <bool BF16, int CL>
 __global__ void __launch_bounds__(256)
 bias_grad_tc_kernel(const uint16_t* __restrict__ dy, const int64_t* __restrict__ seg,
                     const __grid_constant__ HostSegs hs, uint16_t* __restrict__ db, int out_feat, int accumulate) {
-    // block: 64 columns (as 32 pairs) x 8 row lanes
-    __shared__ float red[8][64];
+    constexpr int RL = 256 / CL, COLS = CL * 8;
+    __shared__ float red[RL][COLS + 1];
     const int e = blockIdx.y;
-    const int cp = threadIdx.x & 31, ry = threadIdx.x >> 5;
-    const int col = blockIdx.x * 64 + cp * 2;
+    const int cl = threadIdx.x % CL, ry = threadIdx.x / CL;
+    const int col = blockIdx.x * COLS + cl * 8;
     const int64_t lo = hs.n ? (int64_t)hs.lo[e] : seg[e], hi = hs.n ? (int64_t)hs.hi[e] : seg[e + 1];
-    float s0 = 0.f, s1 = 0.f;
-    if (col < out_feat)
-        for (int64_t m = lo + ry; m < hi; m += 8) {
-            const uint32_t w = __ldg(reinterpret_cast<const uint32_t*>(dy + m * out_feat + col));
-            s0 += cvt_in<BF16>((uint16_t)(w & 0xffff));
-            s1 += cvt_in<BF16>((uint16_t)(w >> 16));
-        }
-    red[ry][cp * 2] = s0;
-    red[ry][cp * 2 + 1] = s1;
-    __syncthreads();
-    if (ry == 0 && col < out_feat) {
-        float t0 = 0.f, t1 = 0.f;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (col < out_feat) {
+        const uint16_t* base = dy + col;
+        int64_t m = lo + ry;
+        for (; m + 3 * RL < hi; m += 4 * RL) {
+            uint4 v[4];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) { t0 += red[i][cp * 2]; t1 += red[i][cp * 2 + 1]; }
-        uint32_t* o = reinterpret_cast<uint32_t*>(db + (size_t)e * out_feat + col);
-        if (accumulate) {
-            const uint32_t w = *o;
-            t0 += cvt_in<BF16>((uint16_t)(w & 0xffff));
-            t1 += cvt_in<BF16>((uint16_t)(w >> 16));
+            for (int u = 0; u < 4; ++u) v[u] = __ldg(reinterpret_cast<const uint4*>(base + (m + RL * u) * out_feat));
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const uint32_t w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    acc[2 * i] += cvt_in<BF16>((uint16_t)(w[i] & 0xffff));
+                    acc[2 * i + 1] += cvt_in<BF16>((uint16_t)(w[i] >> 16));
+                }
+            }
         }
-        *o = cvt_pack<BF16>(t0, t1);
+        for (; m < hi; m += RL) {
+            const uint4 v = __ldg(reinterpret_cast<const uint4*>(base + m * out_feat));
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                acc[2 * i] += cvt_in<BF16>((uint16_t)(w[i] & 0xffff));
+                acc[2 * i + 1] += cvt_in<BF16>((uint16_t)(w[i] >> 16));
+            }
+        }
     }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) red[ry][cl * 8 + i] = acc[i];
+    __syncthreads();
+    if (threadIdx.x < COLS) {
+        const int c = blockIdx.x * COLS + threadIdx.x;
+        if (c < out_feat) {
+            float t = 0.f;
+#pragma unroll
+            for (int i = 0; i < RL; ++i) t += red[i][threadIdx.x];
+            uint16_t* o = db + (size_t)e * out_feat + c;
+            if (accumulate) t += cvt_in<BF16>(*o);
+            const uint32_t packed = cvt_pack<BF16>(t, 0.f);
+            *o = (uint16_t)(packed & 0xffff);
+        }
+    }
+}
+
+template <bool BF16>
+int launch_bias_grad(const LinearBwdArgs& a, const HostSegs& hs, cudaStream_t st) {
+    const bool narrow = ceil_div(a.out_feat, 128) * a.n_expert < 2 * sm_count();
+    if (narrow) {
+        dim3 grid((unsigned)ceil_div(a.out_feat, 64), (unsigned)a.n_expert);
+        bias_grad_tc_kernel<BF16, 8><<<grid, 256, 0, st>>>((const uint16_t*)a.grad_y, a.seg_offsets, hs, (uint16_t*)a.grad_b,
+                                                            (int)a.out_feat, a.accumulate);
+    } else {
+        dim3 grid((unsigned)ceil_div(a.out_feat, 128), (unsigned)a.n_expert);
+        bias_grad_tc_kernel<BF16, 16><<<grid, 256, 0, st>>>((const uint16_t*)a.grad_y, a.seg_offsets, hs, (uint16_t*)a.grad_b,
+                                                             (int)a.out_feat, a.accumulate);
+    }
+    FMOE_CHECK_LAUNCH();
+    return 0;
 }
 
 }  // namespace
@@ -580,7 +891,7 @@ bool tc_backward_supported(const LinearBwdArgs& a) {
     return shape_ok(a.n_rows, a.in_feat, a.out_feat, a.n_expert, a.dtype) && aligned16(a.grad_y) &&
            aligned16(a.weight) && (!a.x || aligned16(a.x)) && (!a.grad_x || aligned16(a.grad_x)) &&
            (!a.grad_w || aligned16(a.grad_w)) && (!a.act_pre || aligned16(a.act_pre)) &&
-           (!a.grad_b || ((uintptr_t)a.grad_b & 3) == 0);
+           (!a.grad_b || ((uintptr_t)a.grad_b & 1) == 0);
 }
 
 size_t tc_backward_scratch_bytes(int64_t, int64_t, int64_t, int, int) { return 0; }
@@ -589,17 +900,24 @@ int tc_linear_forward(const LinearArgs& a, cudaStream_t st) {
     const bool bf16 = a.dtype == FMOE_BF16;
     CUtensorMap ma, mb;
     if (int rc = make_map(&ma, a.x, a.n_rows, a.in_feat, BM, bf16)) return rc;
-    if (int rc = make_map(&mb, a.weight, (int64_t)a.n_expert * a.out_feat, a.in_feat, BN, bf16)) return rc;
+    // Pairs of CTAs (256-row tiles) once there is enough work for them; each CTA of a
+    // pair stages 128 of the tile's 256 weight rows.
+    const bool pair = pair_kernel_enabled() && a.n_rows >= 2048;
+    if (int rc = make_map(&mb, a.weight, (int64_t)a.n_expert * a.out_feat, a.in_feat, pair ? 128 : BN, bf16)) return rc;
     Params p{};
     p.seg = a.seg_offsets; p.n_expert = a.n_expert; p.n_out = (int)a.out_feat; p.n_contr = (int)a.in_feat;
     p.w_rows = (int)a.out_feat; p.out = a.y; p.pre_out = a.pre_act; p.bias = a.bias; p.act = a.activation;
     p.is_bf16 = bf16; p.status = status_ptr();
-    const int64_t max_tiles = (ceil_div(a.n_rows, BM) + a.n_expert) * ceil_div(a.out_feat, BN);
-    return launch<MODE_FWD>(ma, mb, a.host_segs, p, max_tiles, st);
+    const int tile_m = pair ? 256 : BM;
+    const int64_t max_tiles = (ceil_div(a.n_rows, tile_m) + a.n_expert) * ceil_div(a.out_feat, BN);
+    return pair ? launch<MODE_FWD, true>(ma, mb, a.host_segs, p, max_tiles, st)
+                : launch<MODE_FWD, false>(ma, mb, a.host_segs, p, max_tiles, st);
 }
 
 int tc_linear_backward(const LinearBwdArgs& a, cudaStream_t st) {
     const bool bf16 = a.dtype == FMOE_BF16;
+    const bool pair = pair_kernel_enabled() && a.n_rows >= 2048;
+    const int tile_m = pair ? 256 : BM;
     if (a.grad_x && a.n_rows > 0) {
         CUtensorMap ma, mb;
         if (int rc = make_map(&ma, a.grad_y, a.n_rows, a.out_feat, BM, bf16)) return rc;
@@ -608,8 +926,10 @@ int tc_linear_backward(const LinearBwdArgs& a, cudaStream_t st) {
         p.seg = a.seg_offsets; p.n_expert = a.n_expert; p.n_out = (int)a.in_feat; p.n_contr = (int)a.out_feat;
         p.w_rows = (int)a.out_feat; p.out = a.grad_x; p.act_pre = a.act_pre; p.act = a.activation;
         p.is_bf16 = bf16; p.status = status_ptr();
-        const int64_t max_tiles = (ceil_div(a.n_rows, BM) + a.n_expert) * ceil_div(a.in_feat, BN);
-        if (int rc = launch<MODE_DGRAD>(ma, mb, a.host_segs, p, max_tiles, st)) return rc;
+        const int64_t max_tiles = (ceil_div(a.n_rows, tile_m) + a.n_expert) * ceil_div(a.in_feat, BN);
+        if (int rc = pair ? launch<MODE_DGRAD, true>(ma, mb, a.host_segs, p, max_tiles, st)
+                          : launch<MODE_DGRAD, false>(ma, mb, a.host_segs, p, max_tiles, st))
+            return rc;
     }
     if (a.grad_w) {
         CUtensorMap ma, mb;
@@ -622,17 +942,14 @@ int tc_linear_backward(const LinearBwdArgs& a, cudaStream_t st) {
         p.seg = a.seg_offsets; p.n_expert = a.n_expert; p.n_out = (int)a.in_feat; p.n_contr = 0;
         p.out_rows_per_expert = (int)a.out_feat; p.out = a.grad_w; p.accumulate = a.accumulate;
         p.is_bf16 = bf16; p.status = status_ptr();
-        const int64_t max_tiles = (int64_t)a.n_expert * ceil_div(a.out_feat, BM) * ceil_div(a.in_feat, BN);
-        if (int rc = launch<MODE_WGRAD>(ma, mb, a.host_segs, p, max_tiles, st)) return rc;
+        const int64_t max_tiles = (int64_t)a.n_expert * ceil_div(a.out_feat, tile_m) * ceil_div(a.in_feat, BN);
+        if (int rc = pair ? launch<MODE_WGRAD, true>(ma, mb, a.host_segs, p, max_tiles, st)
+                          : launch<MODE_WGRAD, false>(ma, mb, a.host_segs, p, max_tiles, st))
+            return rc;
     }
     if (a.grad_b) {
-        dim3 grid((unsigned)ceil_div(a.out_feat, 64), (unsigned)a.n_expert);
         const HostSegs& hs = a.host_segs ? *a.host_segs : kNoSegs;
-        if (bf16)
-            bias_grad_tc_kernel<true><<<grid, 256, 0, st>>>((const uint16_t*)a.grad_y, a.seg_offsets, hs, (uint16_t*)a.grad_b, (int)a.out_feat, a.accumulate);
-        else
-            bias_grad_tc_kernel<false><<<grid, 256, 0, st>>>((const uint16_t*)a.grad_y, a.seg_offsets, hs, (uint16_t*)a.grad_b, (int)a.out_feat, a.accumulate);
-        FMOE_CHECK_LAUNCH();
+        if (int rc = bf16 ? launch_bias_grad<true>(a, hs, st) : launch_bias_grad<false>(a, hs, st)) return rc;
     }
     return 0;
 }

@@ -480,7 +480,9 @@ def combine_backward(grad_out, buf, inv, score, need_score_grad=True):
 
 
 def linear_forward_act(x, seg_offsets, weight, bias, activation, want_pre=False):
-    """Grouped GEMM with fused bias and activation.  Returns (y, pre_act or None)."""
+    """Grouped GEMM with fused bias and activation.  Returns (y, act_deriv or None);
+    ``act_deriv`` (with ``want_pre`` and GELU) holds gelu'(pre-activation), the factor
+    that linear_backward_act multiplies into the input gradient."""
     _check_cuda(x, seg_offsets, weight, bias)
     n_expert, out_feat, in_feat = weight.shape
     assert x.shape[1] == in_feat and x.dtype == weight.dtype
@@ -497,7 +499,8 @@ def linear_forward_act(x, seg_offsets, weight, bias, activation, want_pre=False)
 def linear_backward_act(grad_y, x, seg_offsets, weight, act_pre, activation, need_bias=True,
                         need_input_grad=True, grad_w=None, grad_b=None, accumulate=False):
     """Grouped GEMM backward.  ``act_pre`` (shape of x) fuses the backward of the
-    activation that produced ``x`` into the input gradient.  Returns (dX, dW, db)."""
+    activation that produced ``x`` into the input gradient: for ReLU pass the activation
+    output, for GELU the derivative buffer of linear_forward_act.  Returns (dX, dW, db)."""
     _check_cuda(grad_y, x, seg_offsets, weight, act_pre)
     n_expert, out_feat, in_feat = weight.shape
     n_rows = grad_y.shape[0]

@@ -200,8 +200,10 @@ size_t fmoe_linear_scratch_bytes(int64_t n_rows, int64_t in_feat, int64_t out_fe
  * fmoe/transformer.py:28).  X [n_rows,in_feat], W [E,out_feat,in_feat],
  * bias [E,out_feat] or NULL, Y [n_rows,out_feat], all row-major, dtype as given;
  * accumulation is fp32.  seg_offsets: DEVICE int64[E+1], exclusive prefix sum
- * of the reference's expert_count.  pre_act (may be NULL): receives the value
- * before the activation, which the backward of GELU needs. */
+ * of the reference's expert_count.  pre_act (may be NULL; used with GELU):
+ * receives activation'(z) of the value z before the activation, in the tensor
+ * dtype -- the factor the backward of the activation multiplies by, computed
+ * here where z is still in registers. */
 int fmoe_linear_forward(const void* x, const void* weight, const void* bias,
                         const int64_t* seg_offsets, void* y, void* pre_act,
                         int64_t n_rows, int64_t in_feat, int64_t out_feat,
@@ -214,10 +216,12 @@ int fmoe_linear_forward(const void* x, const void* weight, const void* bias,
  *   dW_e      = dY[seg_e]^T * X[seg_e]    [E,out_feat,in_feat]  (zero if empty)
  *   db_e      = column sums of dY[seg_e]  [E,out_feat]          (NULL to skip)
  * Any of grad_x, grad_w, grad_b may be NULL to skip that product.
- * When act_pre [n_rows,in_feat] != NULL, dX is multiplied element-wise by
- * activation'(act_pre) before it is stored: the backward of the activation
- * that produced x, which the reference runs as a separate kernel
- * (cuda/fused_compute.cuh:155) or leaves to autograd.
+ * When act_pre [n_rows,in_feat] != NULL, dX is multiplied element-wise by the
+ * derivative of the activation that produced x before it is stored (the
+ * reference runs this as a separate kernel, cuda/fused_compute.cuh:155, or
+ * leaves it to autograd).  For FMOE_ACT_RELU act_pre is the activation OUTPUT
+ * (the factor is 1 where it is > 0); for FMOE_ACT_GELU it is the derivative
+ * buffer that fmoe_linear_forward wrote through pre_act.
  * accumulate != 0 adds into dW/db instead of overwriting them (what the smart
  * schedule's later pipeline steps do, cuda/fused_compute.cuh:120). */
 int fmoe_linear_backward(const void* grad_y, const void* x, const void* weight,
@@ -363,8 +367,8 @@ int fmoe_fused_geometry(const int64_t* lec_host, const int64_t* gec_host,
  *   local_in, local_out [A, d_model]      token-side rows, ordered by (worker, expert)
  *   global_in, global_out [B+S, d_model]  expert-side rows: [0,B) received, expert-major
  *                                         then source; [B,B+S) rows of shadowed experts
- *   middle [B+S, d_hidden]                activation output; middle_pre: value before the
- *                                         activation (needed for GELU, else NULL)
+ *   middle [B+S, d_hidden]                activation output; middle_pre: derivative of the
+ *                                         activation (written and needed for GELU, else NULL)
  * with B, S from fmoe_fused_geometry.  The exchange with the peers of step s is
  * queued on comm_stream, the expert GEMMs of step s on `stream` once its rows have
  * arrived, and the results travel back as each step finishes.  On return all work

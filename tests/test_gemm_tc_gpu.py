@@ -98,8 +98,12 @@ def test_tc_fused_epilogues_match_ffma(fc, act, monkeypatch):
     code = {"relu": _lib.ACT_RELU, "gelu": _lib.ACT_GELU}[act]
 
     def both():
-        y, pre = fc.linear_forward_act(x, off, w1, b1, code, want_pre=True)
-        # backward of a layer whose input was act(pre_in): here reuse x's shape with a fake pre
+        # the derivative buffer is only written for GELU (ReLU's backward reads the output)
+        y, pre = fc.linear_forward_act(x, off, w1, b1, code, want_pre=(act == "gelu"))
+        if pre is None:
+            pre = torch.zeros(1, device="cuda")
+        # backward of a layer whose input came from an activation: a saved buffer of x's shape
+        # (ReLU: the activation output, only its sign matters; GELU: the saved derivative)
         pre_in = torch.randn(B, d, device="cuda").bfloat16()
         torch.manual_seed(5)
         gx, gw, gb = fc.linear_backward_act(gh, x, off, w1, pre_in, code)
