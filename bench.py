@@ -180,9 +180,29 @@ def run_ours(args):
         out = layer(x_dev)
         out.sum().backward()
 
+    # End-to-end step: the batch starts in pinned host memory, the loss is read back.  The
+    # copy of the NEXT step's batch is issued on a copy stream before this step's loss is
+    # read, so it travels while this step computes (what an input pipeline does).
+    copy_stream = torch.cuda.Stream(device=dev)
+
+    def prefetch():
+        with torch.cuda.stream(copy_stream):
+            buf = x_host.to(dev, non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record(copy_stream)
+        return buf, ev
+
+    pending = {"next": None}
+
     def step_e2e():
         layer.zero_grad(set_to_none=True)
-        x = x_host.to(dev, non_blocking=True).requires_grad_(True)
+        if pending["next"] is None:
+            pending["next"] = prefetch()
+        x, ev = pending["next"]
+        torch.cuda.current_stream().wait_event(ev)
+        x.record_stream(torch.cuda.current_stream())
+        x.requires_grad_(True)
+        pending["next"] = prefetch()
         out = layer(x)
         loss = out.float().sum()
         loss.backward()

@@ -914,10 +914,45 @@ int tc_linear_forward(const LinearArgs& a, cudaStream_t st) {
                 : launch<MODE_FWD, false>(ma, mb, a.host_segs, p, max_tiles, st);
 }
 
+// A side stream and a pair of events per device, created on first use: the bias
+// gradient (an HBM-bound column sum with a small footprint) runs there, next to the
+// tensor-core kernels of the same call, instead of after them.
+struct SideStream {
+    cudaStream_t stream = nullptr;
+    cudaEvent_t fork = nullptr, join = nullptr;
+};
+int side_stream(SideStream** out) {
+    static SideStream pool[64];
+    static std::mutex mtx;
+    int dev = 0;
+    FMOE_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) dev = 0;
+    std::lock_guard<std::mutex> lk(mtx);
+    SideStream& s = pool[dev];
+    if (!s.stream) {
+        FMOE_CUDA_TRY(cudaStreamCreateWithFlags(&s.stream, cudaStreamNonBlocking));
+        FMOE_CUDA_TRY(cudaEventCreateWithFlags(&s.fork, cudaEventDisableTiming));
+        FMOE_CUDA_TRY(cudaEventCreateWithFlags(&s.join, cudaEventDisableTiming));
+    }
+    *out = &s;
+    return 0;
+}
+
 int tc_linear_backward(const LinearBwdArgs& a, cudaStream_t st) {
     const bool bf16 = a.dtype == FMOE_BF16;
     const bool pair = pair_kernel_enabled() && a.n_rows >= 2048;
     const int tile_m = pair ? 256 : BM;
+    SideStream* side = nullptr;
+    const bool overlap_bias = a.grad_b && (a.grad_x || a.grad_w) && a.n_rows > 0;
+    if (overlap_bias) {
+        if (int rc = side_stream(&side)) return rc;
+        const HostSegs& hs = a.host_segs ? *a.host_segs : kNoSegs;
+        FMOE_CUDA_TRY(cudaEventRecord(side->fork, st));
+        FMOE_CUDA_TRY(cudaStreamWaitEvent(side->stream, side->fork, 0));
+        if (int rc = bf16 ? launch_bias_grad<true>(a, hs, side->stream) : launch_bias_grad<false>(a, hs, side->stream))
+            return rc;
+        FMOE_CUDA_TRY(cudaEventRecord(side->join, side->stream));
+    }
     if (a.grad_x && a.n_rows > 0) {
         CUtensorMap ma, mb;
         if (int rc = make_map(&ma, a.grad_y, a.n_rows, a.out_feat, BM, bf16)) return rc;
@@ -947,7 +982,9 @@ int tc_linear_backward(const LinearBwdArgs& a, cudaStream_t st) {
                           : launch<MODE_WGRAD, false>(ma, mb, a.host_segs, p, max_tiles, st))
             return rc;
     }
-    if (a.grad_b) {
+    if (overlap_bias) {
+        FMOE_CUDA_TRY(cudaStreamWaitEvent(st, side->join, 0));
+    } else if (a.grad_b) {
         const HostSegs& hs = a.host_segs ? *a.host_segs : kNoSegs;
         if (int rc = bf16 ? launch_bias_grad<true>(a, hs, st) : launch_bias_grad<false>(a, hs, st)) return rc;
     }
