@@ -75,8 +75,8 @@ _SIGS = {
     "fmoe_comm_rank": (I32, [P, POINTER(c_int32), POINTER(c_int32)]),
     "fmoe_expert_exchange": (I32, [P, P, P, P, P, I32, I32, P]),
     "fmoe_plan_global_scatter": (I32, [P, P, P, I32, I32, I32, P, I32, POINTER(c_int32), POINTER(c_int64)]),
-    "fmoe_global_scatter": (I32, [P, P, P, P, P, P, I64, I64, I64, I32, I32, P]),
-    "fmoe_global_gather": (I32, [P, P, P, P, P, P, I64, I64, I64, I32, I32, P]),
+    "fmoe_global_scatter": (I32, [P, P, P, P, P, P, I64, I64, I64, I32, I32, P, P]),
+    "fmoe_global_gather": (I32, [P, P, P, P, P, P, I64, I64, I64, I32, I32, P, P]),
     "fmoe_exchange_cache_info": (I32, [P, P, P, I32, I32, P]),
     "fmoe_model_broadcast": (I32, [P, P, I64, I32, P]),
     "fmoe_gradient_reduce": (I32, [P, P, I64, I32, I32, P]),

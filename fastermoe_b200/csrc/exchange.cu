@@ -171,6 +171,162 @@ int run_exchange(Comm* c, const void* src, void* dst, const std::vector<fmoe_mov
     return 0;
 }
 
+// ---- merged exchange ---------------------------------------------------------------
+// With a staging buffer the exchange uses ONE send and ONE receive per peer: the rows a
+// rank sends to a peer are contiguous on the token side (all experts of that peer), and
+// the rows it receives from a peer land contiguously in the staging buffer; one copy
+// kernel then moves them (and the rows that never leave the GPU) to the expert-major
+// layout.  Large messages keep NVLink busy where many expert-sized ones do not.
+constexpr int kSegMax = 160;
+struct SegTable {
+    int n;
+    int prefix[kSegMax + 1];  // rows before segment k
+    int src_row[kSegMax], dst_row[kSegMax];
+    unsigned char src_sel[kSegMax], dst_sel[kSegMax];
+};
+
+__global__ void __launch_bounds__(256)
+segment_copy_kernel(const __grid_constant__ SegTable t, const uint4* __restrict__ src0, const uint4* __restrict__ src1,
+                    uint4* __restrict__ dst0, uint4* __restrict__ dst1, int64_t row_vecs) {
+    const int lane = threadIdx.x & 31;
+    const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (row >= t.prefix[t.n]) return;
+    int lo = 0, hi = t.n - 1;  // last segment whose prefix <= row
+    while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (t.prefix[mid] <= row) lo = mid; else hi = mid - 1;
+    }
+    const int k = lo, off = row - t.prefix[k];
+    const uint4* s = (t.src_sel[k] ? src1 : src0) + (int64_t)(t.src_row[k] + off) * row_vecs;
+    uint4* d = (t.dst_sel[k] ? dst1 : dst0) + (int64_t)(t.dst_row[k] + off) * row_vecs;
+    int64_t c = lane;
+    for (; c + 96 < row_vecs; c += 128) {
+        const uint4 v0 = __ldg(s + c), v1 = __ldg(s + c + 32), v2 = __ldg(s + c + 64), v3 = __ldg(s + c + 96);
+        d[c] = v0; d[c + 32] = v1; d[c + 64] = v2; d[c + 96] = v3;
+    }
+    for (; c < row_vecs; c += 32) d[c] = __ldg(s + c);
+}
+
+struct SegCopy { int src_sel, dst_sel; int64_t src_row, dst_row, rows; };
+struct P2P { int peer; int64_t row, rows; };
+
+int launch_segment_copies(const std::vector<SegCopy>& copies, const void* src0, const void* src1, void* dst0,
+                          void* dst1, int64_t row_bytes, cudaStream_t st) {
+    SegTable t;
+    size_t i = 0;
+    while (i < copies.size()) {
+        t.n = 0;
+        t.prefix[0] = 0;
+        for (; i < copies.size() && t.n < kSegMax; ++i) {
+            const SegCopy& c = copies[i];
+            if (c.rows == 0) continue;
+            t.src_sel[t.n] = (unsigned char)c.src_sel; t.dst_sel[t.n] = (unsigned char)c.dst_sel;
+            t.src_row[t.n] = (int)c.src_row; t.dst_row[t.n] = (int)c.dst_row;
+            t.prefix[t.n + 1] = t.prefix[t.n] + (int)c.rows;
+            ++t.n;
+        }
+        if (t.n == 0) break;
+        const unsigned blocks = (unsigned)ceil_div(t.prefix[t.n], 8);
+        segment_copy_kernel<<<blocks, 256, 0, st>>>(t, (const uint4*)src0, (const uint4*)src1, (uint4*)dst0, (uint4*)dst1,
+                                                    row_bytes / 16);
+        FMOE_CHECK_LAUNCH();
+    }
+    return 0;
+}
+
+// token: token-side buffer, expert: expert-side buffer, staging: >= rows received from
+// peers.  forward = global_scatter, otherwise global_gather.
+int run_exchange_merged(Comm* c, const void* token_c, const void* expert_c, void* staging, bool forward,
+                        const int64_t* lec, const int64_t* gec, const uint8_t* stored, int E, int W,
+                        int64_t row_bytes, cudaStream_t st) {
+    const int rank = c->rank;
+    char* token = (char*)token_c;
+    char* expert = (char*)expert_c;
+    std::vector<int64_t> eptr((size_t)E * W + 1, 0);
+    for (int i = 0; i < E * W; ++i) eptr[i + 1] = eptr[i] + lec[i];
+    std::vector<P2P> tok_runs, stg_runs;   // token-side runs (per peer) and staging runs (per peer)
+    std::vector<SegCopy> copies;            // sel 0: staging, sel 1: token buffer (source side, forward)
+    // token-side runs: experts of peer j that are not shadowed here, in maximal consecutive ranges
+    for (int j = 0; j < W; ++j) {
+        if (j == rank) continue;
+        int i = 0;
+        while (i < E) {
+            if (stored[j * E + i]) { ++i; continue; }
+            int i1 = i;
+            while (i1 < E && !stored[j * E + i1]) ++i1;
+            const int64_t rows = eptr[j * E + i1] - eptr[j * E + i];
+            if (rows) tok_runs.push_back({j, eptr[j * E + i], rows});
+            i = i1;
+        }
+    }
+    // expert-side layout, walked exactly as plan_scatter does
+    std::vector<int64_t> stg_off((size_t)E * W, -1);  // staging row of segment (i, j)
+    int64_t stg = 0;
+    for (int j = 0; j < W; ++j) {
+        if (j == rank) continue;
+        int i = 0;
+        while (i < E) {
+            if (stored[rank * E + i]) { ++i; continue; }
+            int i1 = i;
+            int64_t rows = 0;
+            while (i1 < E && !stored[rank * E + i1]) {
+                stg_off[i1 + j * E] = stg + rows;
+                rows += gec[i1 + j * E];
+                ++i1;
+            }
+            if (rows) stg_runs.push_back({j, stg, rows});
+            stg += rows;
+            i = i1;
+        }
+    }
+    int64_t rp = 0;
+    auto local_block = [&](int j) {
+        for (int i = 0; i < E; ++i) {
+            const int idx = i + j * E;
+            if (stored[idx]) {
+                copies.push_back({1, 0, eptr[idx], rp, lec[idx]});
+                rp += lec[idx];
+            }
+        }
+    };
+    for (int j = 0; j < rank; ++j) local_block(j);
+    for (int i = 0; i < E; ++i)
+        for (int j = 0; j < W; ++j) {
+            const int idx = i + j * E;
+            const bool do_recv = gec[idx] > 0 && (!stored[rank * E + i] || j == rank);
+            if (!do_recv) continue;
+            if (j == rank) copies.push_back({1, 0, eptr[idx], rp, gec[idx]});
+            else copies.push_back({0, 0, stg_off[idx], rp, gec[idx]});
+            rp += gec[idx];
+        }
+    for (int j = rank + 1; j < W; ++j) local_block(j);
+
+    auto group = [&](const std::vector<P2P>& sends, const char* sbuf, const std::vector<P2P>& recvs, char* rbuf) -> int {
+        if (sends.empty() && recvs.empty()) return 0;
+        FMOE_NCCL_TRY(g_nccl.GroupStart());
+        for (const auto& r : sends) {
+            ncclResult_t e = g_nccl.Send(sbuf + r.row * row_bytes, (size_t)r.rows * row_bytes, ncclChar, r.peer, c->comm, st);
+            if (e != ncclSuccess) { g_nccl.GroupEnd(); return fail(FMOE_ERR_NCCL, "ncclSend failed: %s", g_nccl.GetErrorString(e)); }
+        }
+        for (const auto& r : recvs) {
+            ncclResult_t e = g_nccl.Recv(rbuf + r.row * row_bytes, (size_t)r.rows * row_bytes, ncclChar, r.peer, c->comm, st);
+            if (e != ncclSuccess) { g_nccl.GroupEnd(); return fail(FMOE_ERR_NCCL, "ncclRecv failed: %s", g_nccl.GetErrorString(e)); }
+        }
+        FMOE_NCCL_TRY(g_nccl.GroupEnd());
+        return 0;
+    };
+    if (forward) {
+        if (int rc = group(tok_runs, token, stg_runs, (char*)staging)) return rc;
+        return launch_segment_copies(copies, staging, token, expert, nullptr, row_bytes, st);
+    }
+    // gather: expert-side rows go back: into the staging runs (remote) or straight to the token side (local)
+    std::vector<SegCopy> back;
+    back.reserve(copies.size());
+    for (const auto& cp : copies) back.push_back({0, cp.src_sel, cp.dst_row, cp.src_row, cp.rows});
+    if (int rc = launch_segment_copies(back, expert, nullptr, staging, token, row_bytes, st)) return rc;
+    return group(stg_runs, (const char*)staging, tok_runs, token);
+}
+
 }  // namespace
 }  // namespace fmoe
 
@@ -260,7 +416,7 @@ extern "C" int fmoe_plan_global_scatter(const int64_t* lec_host, const int64_t* 
 
 static int global_move(fmoe_comm_t comm, const void* in, void* out, const int64_t* lec, const int64_t* gec,
                        const uint8_t* stored, int64_t in_rows, int64_t out_rows, int64_t row_bytes,
-                       int n_expert, int n_workers, bool reverse, cudaStream_t st) {
+                       int n_expert, int n_workers, bool reverse, void* staging, cudaStream_t st) {
     FMOE_REQUIRE(comm, "global exchange: null communicator");
     Comm* c = (Comm*)comm;
     FMOE_REQUIRE(n_workers == c->world, "global exchange: n_workers=%d but communicator has %d ranks",
@@ -281,25 +437,30 @@ static int global_move(fmoe_comm_t comm, const void* in, void* out, const int64_
     if (reverse && out_rows > send_rows)
         FMOE_CUDA_TRY(cudaMemsetAsync((char*)out + send_rows * row_bytes, 0,
                                       (size_t)(out_rows - send_rows) * row_bytes, st));
+    const bool can_merge = staging && row_bytes % 16 == 0 && (((uintptr_t)in | (uintptr_t)out | (uintptr_t)staging) & 15) == 0 &&
+                           recv_rows < ((int64_t)1 << 31) && send_rows < ((int64_t)1 << 31);
+    if (can_merge)
+        return run_exchange_merged(c, reverse ? out : in, reverse ? in : out, staging, !reverse, lec, gec, stored,
+                                   n_expert, n_workers, row_bytes, st);
     return run_exchange(c, in, out, moves, reverse, row_bytes, st);
 }
 
 extern "C" int fmoe_global_scatter(fmoe_comm_t comm, const void* local_in, void* global_out,
                                    const int64_t* lec_host, const int64_t* gec_host,
                                    const uint8_t* stored_models_host, int64_t in_rows, int64_t out_rows,
-                                   int64_t row_bytes, int32_t n_expert, int32_t n_workers,
+                                   int64_t row_bytes, int32_t n_expert, int32_t n_workers, void* staging,
                                    fmoe_stream_t stream) {
     return global_move(comm, local_in, global_out, lec_host, gec_host, stored_models_host, in_rows, out_rows,
-                       row_bytes, n_expert, n_workers, false, (cudaStream_t)stream);
+                       row_bytes, n_expert, n_workers, false, staging, (cudaStream_t)stream);
 }
 
 extern "C" int fmoe_global_gather(fmoe_comm_t comm, const void* global_in, void* local_out,
                                   const int64_t* lec_host, const int64_t* gec_host,
                                   const uint8_t* stored_models_host, int64_t in_rows, int64_t out_rows,
-                                  int64_t row_bytes, int32_t n_expert, int32_t n_workers,
+                                  int64_t row_bytes, int32_t n_expert, int32_t n_workers, void* staging,
                                   fmoe_stream_t stream) {
     return global_move(comm, global_in, local_out, lec_host, gec_host, stored_models_host, in_rows, out_rows,
-                       row_bytes, n_expert, n_workers, true, (cudaStream_t)stream);
+                       row_bytes, n_expert, n_workers, true, staging, (cudaStream_t)stream);
 }
 
 extern "C" int fmoe_exchange_cache_info(fmoe_comm_t comm, const uint8_t* sent_models, uint8_t* stored_models,

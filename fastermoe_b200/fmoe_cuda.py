@@ -302,9 +302,12 @@ def _global_move(fn, name, buf, local_expert_count, global_expert_count, stored_
     n_expert = lec.numel() // n_workers
     out = buf.new_empty((batch_size, buf.shape[1]))
     row_bytes = buf.shape[1] * buf.element_size()
+    # staging of the expert-side size: one send/receive per peer instead of one per (expert, peer)
+    expert_rows = batch_size if name == "global_scatter" else buf.shape[0]
+    staging = buf.new_empty((expert_rows, buf.shape[1])) if os.environ.get("FMOE_B200_EXCHANGE") != "split" else None
     with torch.cuda.device(buf.device):
         _run(name, fn, _comm(buf.device), _ptr(buf), _ptr(out), _ptr(lec), _ptr(gec), _ptr(st), buf.shape[0],
-             batch_size, row_bytes, n_expert, n_workers, _stream())
+             batch_size, row_bytes, n_expert, n_workers, _ptr(staging), _stream())
     return out
 
 

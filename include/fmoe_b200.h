@@ -281,17 +281,23 @@ int fmoe_plan_global_scatter(const int64_t* lec_host, const int64_t* gec_host,
  * cuda/global_exchange.cu:26-80.  Counts and flags are HOST pointers, as in the
  * reference.  The whole exchange is one NCCL group.  out_rows is checked
  * against the plan (FMOE_ERR_MISMATCH) before anything is queued.
- * global_gather zero-fills local_out rows that receive nothing. */
+ * global_gather zero-fills local_out rows that receive nothing.
+ * staging (may be NULL): a device buffer of the expert-side size (out_rows rows
+ * for scatter, in_rows rows for gather).  With it each peer is served by one
+ * send and one receive (rows to a peer are contiguous on the token side; rows
+ * from a peer land contiguously in staging) and one copy kernel produces the
+ * expert-major layout; without it every (expert, peer) segment is its own
+ * send/receive, as in the reference. */
 int fmoe_global_scatter(fmoe_comm_t comm, const void* local_in, void* global_out,
                         const int64_t* lec_host, const int64_t* gec_host,
                         const uint8_t* stored_models_host, int64_t in_rows,
                         int64_t out_rows, int64_t row_bytes, int32_t n_expert,
-                        int32_t n_workers, fmoe_stream_t stream);
+                        int32_t n_workers, void* staging, fmoe_stream_t stream);
 int fmoe_global_gather(fmoe_comm_t comm, const void* global_in, void* local_out,
                        const int64_t* lec_host, const int64_t* gec_host,
                        const uint8_t* stored_models_host, int64_t in_rows,
                        int64_t out_rows, int64_t row_bytes, int32_t n_expert,
-                       int32_t n_workers, fmoe_stream_t stream);
+                       int32_t n_workers, void* staging, fmoe_stream_t stream);
 
 /* exchange_cache_info(sent_models, num_expert, world_size):
  * cuda/fmoe_cuda.cpp:24-27, cuda/global_exchange.cuh:232-249.  All-gather of

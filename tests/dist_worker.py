@@ -56,7 +56,9 @@ def gpu_exchange(rank, world, port):
         rng = np.random.default_rng(9)
         bufs = [rng.standard_normal((int(l.sum()), d)).astype(np.float32) for l in lecs]
         want = O.global_scatter(bufs, lecs, stored, E, world)
-        for dtype in (torch.float32, torch.bfloat16):
+        # "split": one send/receive per (expert, peer) as in the reference; default: one per peer + staging
+        for mode, dtype in (("", torch.float32), ("", torch.bfloat16), ("split", torch.float32)):
+            os.environ["FMOE_B200_EXCHANGE"] = mode
             mine = torch.from_numpy(bufs[rank]).to(dev).to(dtype)
             out = fc.global_scatter(mine, torch.from_numpy(lecs[rank]), torch.from_numpy(gecs[rank]),
                                     torch.from_numpy(stored), want[rank].shape[0], world)
@@ -64,6 +66,7 @@ def gpu_exchange(rank, world, port):
             back = fc.global_gather(out, torch.from_numpy(lecs[rank]), torch.from_numpy(gecs[rank]),
                                     torch.from_numpy(stored), mine.shape[0], world)
             assert torch.equal(back, mine), "global_gather is not the inverse"
+        os.environ["FMOE_B200_EXCHANGE"] = ""
         cc = fc.generate_cached_count(torch.from_numpy(lecs[rank]).to(dev).view(world, E),
                                       torch.from_numpy(gecs[rank]).to(dev).view(world, E),
                                       torch.from_numpy(stored).to(dev).view(world, E), E, world)
