@@ -2,7 +2,7 @@ r"""Records outputs of the reference's own CUDA routing kernels (needs a GPU).
 
 Run on the GPU box after oracle/build_ref.py has built oracle/_ref/fmoe_cuda_ref*.so:
 
-    python tests/golden/make_routing_golden.py        # writes tests/golden/routing_ref_gpu.npz
+    python tests/golden/make_routing_golden.py        # writes gpurun_out/routing_ref_gpu.npz; copy it to tests/golden/
 
 Recorded per case: the inputs and what the reference's kernels returned --
 ``expert_count`` (cuda/local_exchange.cuh:32-61), ``assign_pos`` (:5-16),
