@@ -6,7 +6,8 @@
 //   1. tile_hist:   every warp owns a contiguous tile of the flat gate array
 //                   and builds the tile's histogram in shared memory with
 //                   __match_any_sync (one add per distinct expert per 32 entries);
-//   2. scan_tiles:  per expert, exclusive prefix over tiles (in place);
+//   2. scan_tiles:  per expert, exclusive prefix over tiles (in place, blocks of 256
+//                   tiles in parallel; the block totals are scanned in step 3);
 //   3. finalize:    per-expert totals -> segment starts / limits, and the
 //                   in-place side effects the reference's operators have;
 //   4. apply:       every warp walks its tile again in order, ranks entries by
@@ -44,19 +45,23 @@ Geom make_geom(int64_t n, int n_expert) {
 }
 
 // Scratch layout (all offsets 16-byte aligned).
+constexpr int kScanRows = 256;  // tiles scanned by one block of the scan kernel
+
 struct Scratch {
     int32_t* totals;     // [E]
     int64_t* seg_start;  // [E]
     int32_t* limit;      // [E]
-    int32_t* hist;       // [n_tiles][E]
+    int32_t* blocksum;   // [ceil(n_tiles / kScanRows)][E]: per scan block totals, then their exclusive prefix
+    int32_t* hist;       // [n_tiles][E]: per tile counts, then exclusive prefix inside the scan block
 };
 
 size_t align16(size_t x) { return (x + 15) & ~(size_t)15; }
 
 size_t scratch_bytes(int64_t n, int n_expert) {
     Geom g = make_geom(n, n_expert);
-    return align16((size_t)n_expert * 4) + align16((size_t)n_expert * 8) +
-           align16((size_t)n_expert * 4) + align16((size_t)g.n_tiles * n_expert * 4) + 16;
+    return align16((size_t)n_expert * 4) + align16((size_t)n_expert * 8) + align16((size_t)n_expert * 4) +
+           align16((size_t)ceil_div(g.n_tiles, kScanRows) * n_expert * 4) +
+           align16((size_t)g.n_tiles * n_expert * 4) + 16;
 }
 
 Scratch carve(void* scratch, int64_t n, int n_expert) {
@@ -68,6 +73,8 @@ Scratch carve(void* scratch, int64_t n, int n_expert) {
     p += align16((size_t)n_expert * 8);
     s.limit = (int32_t*)p;
     p += align16((size_t)n_expert * 4);
+    s.blocksum = (int32_t*)p;
+    p += align16((size_t)ceil_div(make_geom(n, n_expert).n_tiles, kScanRows) * n_expert * 4);
     s.hist = (int32_t*)p;
     return s;
 }
@@ -115,56 +122,84 @@ tile_hist_kernel(const int64_t* __restrict__ gate, int64_t n, int n_expert, int 
     for (int e = lane; e < n_expert; e += 32) my[e] = 0;
     __syncwarp();
     const int64_t base = tile * (int64_t)chunks * 64;
-    for (int it = 0; it < chunks; ++it) {
-        const int64_t c = base + (int64_t)it * 64;
-        if (c >= n) break;
-        int ea, eb;
-        load_chunk(gate, n, c, lane, vec, n_expert, ea, eb);
-        hist_round(ea, lane, my);
-        hist_round(eb, lane, my);
+    // four chunks (256 entries) are fetched before any is processed, so that each warp
+    // keeps 2 KB of loads in flight
+    for (int it = 0; it < chunks; it += 4) {
+        int ea[4], eb[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int64_t c = base + (int64_t)(it + u) * 64;
+            if (it + u < chunks && c < n) load_chunk(gate, n, c, lane, vec, n_expert, ea[u], eb[u]);
+            else ea[u] = eb[u] = -1;
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            hist_round(ea[u], lane, my);
+            hist_round(eb[u], lane, my);
+        }
     }
     int32_t* out = hist + tile * n_expert;
     for (int e = lane; e < n_expert; e += 32) out[e] = my[e];
 }
 
-// Block e: exclusive prefix over tiles of hist[.][e], in place; totals[e] = sum.
+// Block b scans the rows [b*kScanRows, +kScanRows) of hist[tile][e] column by column:
+// each entry becomes the exclusive prefix inside the block, and blocksum[b][e] the
+// block's column total.  Consecutive threads take consecutive experts of a row, so
+// reads and writes are contiguous.
 __global__ void __launch_bounds__(256)
-scan_tiles_kernel(int32_t* __restrict__ hist, int64_t n_tiles, int n_expert,
-                  int32_t* __restrict__ totals) {
+scan_tiles_kernel(int32_t* __restrict__ hist, int64_t n_tiles, int n_expert, int32_t* __restrict__ blocksum) {
     __shared__ int32_t part[256];
-    const int e = blockIdx.x;
-    const int t = threadIdx.x;
-    const int64_t per = (n_tiles + 255) / 256;
-    const int64_t lo = t * per, hi = min(lo + per, n_tiles);
-    int32_t s = 0;
-    for (int64_t i = lo; i < hi; ++i) s += hist[i * n_expert + e];
-    part[t] = s;
-    __syncthreads();
-    // Hillis-Steele inclusive scan of 256 partial sums.
-    for (int off = 1; off < 256; off <<= 1) {
-        int32_t v = t >= off ? part[t - off] : 0;
+    const int64_t row0 = (int64_t)blockIdx.x * kScanRows;
+    const int rows = (int)min((int64_t)kScanRows, n_tiles - row0);
+    int cw = 1;  // columns per pass: power of two, at most 256
+    while (cw < n_expert && cw < 256) cw <<= 1;
+    const int rl = 256 / cw;  // row lanes per column
+    const int c = threadIdx.x % cw, lane_r = threadIdx.x / cw;
+    const int per = (rows + rl - 1) / rl;  // rows per thread
+    for (int e0 = 0; e0 < n_expert; e0 += cw) {
+        const int e = e0 + c;
+        const int lo = lane_r * per, hi = min(lo + per, rows);
+        int32_t sum = 0;
+        if (e < n_expert)
+            for (int r = lo; r < hi; ++r) sum += hist[(row0 + r) * n_expert + e];
+        part[threadIdx.x] = sum;
         __syncthreads();
-        part[t] += v;
+        // exclusive prefix over the row lanes of this column (serial: at most 256 lanes)
+        int32_t run = 0;
+        for (int l = 0; l < lane_r; ++l) run += part[l * cw + c];
+        if (e < n_expert) {
+            if (lane_r == rl - 1) blocksum[(int64_t)blockIdx.x * n_expert + e] = run + sum;
+            for (int r = lo; r < hi; ++r) {
+                const int64_t idx = (row0 + r) * n_expert + e;
+                const int32_t h = hist[idx];
+                hist[idx] = run;
+                run += h;
+            }
+        }
         __syncthreads();
     }
-    int32_t run = part[t] - s;  // exclusive prefix of this thread's chunk
-    for (int64_t i = lo; i < hi; ++i) {
-        const int32_t h = hist[i * n_expert + e];
-        hist[i * n_expert + e] = run;
-        run += h;
-    }
-    if (t == 255) totals[e] = part[255];
 }
 
 // Single block.  Turns totals into segment starts and applies the side effects
 // of the operator being emulated.
 __global__ void __launch_bounds__(1024)
-finalize_kernel(int mode, int n_expert, const int32_t* __restrict__ totals,
+finalize_kernel(int mode, int n_expert, int32_t* __restrict__ totals, int32_t* __restrict__ blocksum, int n_blocks,
                 int64_t* __restrict__ seg_start, int32_t* __restrict__ limit,
                 int64_t* __restrict__ lec64, int64_t* __restrict__ offsets,
                 int32_t* __restrict__ inout /* cum_count or ec */) {
     __shared__ int64_t part[1024];
     const int t = threadIdx.x;
+    // Block sums -> their exclusive prefix over scan blocks; column totals.
+    for (int e = t; e < n_expert; e += 1024) {
+        int32_t run = 0;
+        for (int b = 0; b < n_blocks; ++b) {
+            const int32_t v = blocksum[(int64_t)b * n_expert + e];
+            blocksum[(int64_t)b * n_expert + e] = run;
+            run += v;
+        }
+        totals[e] = run;
+    }
+    __syncthreads();
     if (mode == MODE_ASSIGN) {
         for (int e = t; e < n_expert; e += 1024) {
             const int32_t s = inout[e] - totals[e];
@@ -220,7 +255,8 @@ __device__ __forceinline__ int64_t rank_round(int e, int lane, int32_t* run) {
 
 __global__ void __launch_bounds__(kThreads)
 apply_kernel(int mode, const int64_t* __restrict__ gate, int64_t n, int n_expert, int chunks,
-             int64_t n_tiles, const int32_t* __restrict__ base, const int64_t* __restrict__ seg_start,
+             int64_t n_tiles, const int32_t* __restrict__ base, const int32_t* __restrict__ blockbase,
+             const int64_t* __restrict__ seg_start,
              const int32_t* __restrict__ limit, const int64_t* __restrict__ total_ptr,
              int64_t* __restrict__ pos, int64_t* __restrict__ inv, int64_t* __restrict__ new_gate,
              bool vec) {
@@ -231,57 +267,76 @@ apply_kernel(int mode, const int64_t* __restrict__ gate, int64_t n, int n_expert
     const int64_t tile = (int64_t)blockIdx.x * kWarps + warp;
     if (tile >= n_tiles) return;
     const int32_t* b = base + tile * n_expert;
-    for (int e = lane; e < n_expert; e += 32) run[e] = (int32_t)seg_start[e] + b[e];
+    const int32_t* bb = blockbase + (tile / kScanRows) * n_expert;
+    for (int e = lane; e < n_expert; e += 32) run[e] = (int32_t)seg_start[e] + b[e] + bb[e];
     __syncwarp();
     const int64_t total = (mode == MODE_COUNT_POS && total_ptr) ? *total_ptr : n;
     const int64_t tb = tile * (int64_t)chunks * 64;
-    for (int it = 0; it < chunks; ++it) {
-        const int64_t c = tb + (int64_t)it * 64;
-        if (c >= n) break;
-        int ea, eb;
-        load_chunk(gate, n, c, lane, vec, n_expert, ea, eb);
+    for (int it0 = 0; it0 < chunks; it0 += 4) {
+        int eas[4], ebs[4];
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-            const int e = half ? eb : ea;
-            const int64_t i = c + half * 32 + lane;
-            const int64_t r = rank_round(e, lane, run);
-            if (i < n) {
-                if (mode == MODE_PRUNE) {
-                    new_gate[i] = (e >= 0 && r < (int64_t)limit[e]) ? (int64_t)e : (int64_t)-1;
-                } else {
-                    if (e >= 0) pos[r] = i;
-                    if (inv) inv[i] = r;  // -1 for skipped entries
-                    // Slots past the number of kept entries are never a target
-                    // of the scatter above; mark them empty.
-                    if (mode == MODE_COUNT_POS && i >= total) pos[i] = -1;
+        for (int u = 0; u < 4; ++u) {
+            const int64_t c = tb + (int64_t)(it0 + u) * 64;
+            if (it0 + u < chunks && c < n) load_chunk(gate, n, c, lane, vec, n_expert, eas[u], ebs[u]);
+            else eas[u] = ebs[u] = -1;
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int64_t c = tb + (int64_t)(it0 + u) * 64;
+            if (it0 + u >= chunks || c >= n) break;
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                const int e = half ? ebs[u] : eas[u];
+                const int64_t i = c + half * 32 + lane;
+                const int64_t r = rank_round(e, lane, run);
+                if (i < n) {
+                    if (mode == MODE_PRUNE) {
+                        new_gate[i] = (e >= 0 && r < (int64_t)limit[e]) ? (int64_t)e : (int64_t)-1;
+                    } else {
+                        if (e >= 0) pos[r] = i;
+                        if (inv) inv[i] = r;  // -1 for skipped entries
+                        // Slots past the number of kept entries are never a target
+                        // of the scatter above; mark them empty.
+                        if (mode == MODE_COUNT_POS && i >= total) pos[i] = -1;
+                    }
                 }
             }
         }
     }
 }
 
-// Plain histogram: shared-memory counters per block, one global atomic per
-// non-empty counter per block.
+// Plain histogram: every warp counts into its own shared-memory row (no atomics
+// between warps), rows are summed at the end, and each block issues one global
+// atomic per non-empty counter.
 __global__ void __launch_bounds__(kThreads)
 expert_count_kernel(const int64_t* __restrict__ gate, int64_t n, int n_expert,
                     int32_t* __restrict__ expert_count, bool vec) {
     extern __shared__ int32_t sh[];
-    for (int e = threadIdx.x; e < n_expert; e += kThreads) sh[e] = 0;
+    for (int i = threadIdx.x; i < kWarps * n_expert; i += kThreads) sh[i] = 0;
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    int32_t* my = sh + (size_t)warp * n_expert;
     const int64_t n_chunks = (n + 63) / 64;
-    for (int64_t ch = (int64_t)blockIdx.x * kWarps + warp; ch < n_chunks;
-         ch += (int64_t)gridDim.x * kWarps) {
-        int ea, eb;
-        load_chunk(gate, n, ch * 64, lane, vec, n_expert, ea, eb);
-        unsigned m = __match_any_sync(kFull, ea);
-        if (ea >= 0 && lane == __ffs(m) - 1) atomicAdd(&sh[ea], __popc(m));
-        m = __match_any_sync(kFull, eb);
-        if (eb >= 0 && lane == __ffs(m) - 1) atomicAdd(&sh[eb], __popc(m));
+    const int64_t stride = (int64_t)gridDim.x * kWarps;
+    for (int64_t ch = (int64_t)blockIdx.x * kWarps + warp; ch < n_chunks; ch += 4 * stride) {
+        int ea[4], eb[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int64_t c = ch + u * stride;
+            if (c < n_chunks) load_chunk(gate, n, c * 64, lane, vec, n_expert, ea[u], eb[u]);
+            else ea[u] = eb[u] = -1;
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            hist_round(ea[u], lane, my);
+            hist_round(eb[u], lane, my);
+        }
     }
     __syncthreads();
     for (int e = threadIdx.x; e < n_expert; e += kThreads) {
-        const int32_t v = sh[e];
+        int32_t v = 0;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) v += sh[w * n_expert + e];
         if (v) atomicAdd(expert_count + e, v);
     }
 }
@@ -337,14 +392,17 @@ int run_bucket(int mode, const int64_t* gate, int64_t n, int n_expert, void* scr
                                                              s.hist, vec);
         FMOE_CHECK_LAUNCH();
     }
-    scan_tiles_kernel<<<n_expert, 256, 0, st>>>(s.hist, g.n_tiles, n_expert, s.totals);
-    FMOE_CHECK_LAUNCH();
-    finalize_kernel<<<1, 1024, 0, st>>>(mode, n_expert, s.totals, s.seg_start, s.limit, lec64,
-                                        offsets, inout);
+    const int scan_blocks = (int)ceil_div(g.n_tiles, kScanRows);
+    if (scan_blocks > 0) {
+        scan_tiles_kernel<<<scan_blocks, 256, 0, st>>>(s.hist, g.n_tiles, n_expert, s.blocksum);
+        FMOE_CHECK_LAUNCH();
+    }
+    finalize_kernel<<<1, 1024, 0, st>>>(mode, n_expert, s.totals, s.blocksum, scan_blocks, s.seg_start, s.limit,
+                                        lec64, offsets, inout);
     FMOE_CHECK_LAUNCH();
     if (g.n_tiles > 0) {
         apply_kernel<<<blocks, kThreads, sm_apply, st>>>(mode, gate, n, n_expert, g.chunks, g.n_tiles,
-                                                          s.hist, s.seg_start, s.limit,
+                                                          s.hist, s.blocksum, s.seg_start, s.limit,
                                                           offsets ? offsets + n_expert : nullptr, pos,
                                                           inv, new_gate, vec);
         FMOE_CHECK_LAUNCH();
@@ -370,7 +428,8 @@ extern "C" int fmoe_expert_count(const int64_t* gate_idx, int32_t* expert_count,
     const bool vec = ((uintptr_t)gate_idx & 15) == 0;
     const int64_t n_chunks = ceil_div(n, 64);
     const unsigned blocks = (unsigned)std::min<int64_t>(ceil_div(n_chunks, kWarps), (int64_t)sm_count() * 8);
-    const size_t smem = (size_t)n_expert_total * 4;
+    const size_t smem = (size_t)kWarps * n_expert_total * 4;
+    if (int rc = set_smem((const void*)expert_count_kernel, smem)) return rc;
     expert_count_kernel<<<blocks, kThreads, smem, (cudaStream_t)stream>>>(gate_idx, n, n_expert_total,
                                                                            expert_count, vec);
     FMOE_CHECK_LAUNCH();
