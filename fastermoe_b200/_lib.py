@@ -83,8 +83,8 @@ _SIGS = {
     "fmoe_generate_cached_count": (I32, [P, P, P, P, I32, I32, I32, P]),
     "fmoe_fused_compute_ptrs": (I32, [P, P, P, I32, I32, I32, P, P, P]),
     "fmoe_fused_geometry": (I32, [P, P, P, I32, I32, I32, I32, P]),
-    "fmoe_fused_forward": (I32, [P, P, P, P, P, P, P, P, P, P, P, I64, I64, I64, I32, I32, I32, I32, I32, P, P]),
-    "fmoe_fused_backward": (I32, [P, P, P, P, P, P, P, P, P, P, P, P, P, I64, I64, I64, I32, I32, I32, I32, I32, P, P]),
+    "fmoe_fused_forward": (I32, [P, P, P, P, P, P, P, P, P, P, P, I64, I64, I64, I32, I32, I32, I32, I32, P, P, P]),
+    "fmoe_fused_backward": (I32, [P, P, P, P, P, P, P, P, P, P, P, P, P, I64, I64, I64, I32, I32, I32, I32, I32, P, P, P]),
 }
 
 EXPORTS = tuple(_SIGS)

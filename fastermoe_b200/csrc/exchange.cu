@@ -207,8 +207,9 @@ segment_copy_kernel(const __grid_constant__ SegTable t, const uint4* __restrict_
     for (; c < row_vecs; c += 32) d[c] = __ldg(s + c);
 }
 
-struct SegCopy { int src_sel, dst_sel; int64_t src_row, dst_row, rows; };
 struct P2P { int peer; int64_t row, rows; };
+
+}  // namespace
 
 int launch_segment_copies(const std::vector<SegCopy>& copies, const void* src0, const void* src1, void* dst0,
                           void* dst1, int64_t row_bytes, cudaStream_t st) {
@@ -233,6 +234,8 @@ int launch_segment_copies(const std::vector<SegCopy>& copies, const void* src0, 
     }
     return 0;
 }
+
+namespace {
 
 // token: token-side buffer, expert: expert-side buffer, staging: >= rows received from
 // peers.  forward = global_scatter, otherwise global_gather.
@@ -437,8 +440,14 @@ static int global_move(fmoe_comm_t comm, const void* in, void* out, const int64_
     if (reverse && out_rows > send_rows)
         FMOE_CUDA_TRY(cudaMemsetAsync((char*)out + send_rows * row_bytes, 0,
                                       (size_t)(out_rows - send_rows) * row_bytes, st));
-    const bool can_merge = staging && row_bytes % 16 == 0 && (((uintptr_t)in | (uintptr_t)out | (uintptr_t)staging) & 15) == 0 &&
-                           recv_rows < ((int64_t)1 << 31) && send_rows < ((int64_t)1 << 31);
+    // The choice must be the same on every rank: it may only depend on arguments that are.
+    const bool can_merge = staging && row_bytes % 16 == 0;
+    if (can_merge) {
+        FMOE_REQUIRE((((uintptr_t)in | (uintptr_t)out | (uintptr_t)staging) & 15) == 0,
+                     "global exchange: buffers must be 16-byte aligned when a staging buffer is given");
+        FMOE_REQUIRE(recv_rows < ((int64_t)1 << 31) && send_rows < ((int64_t)1 << 31),
+                     "global exchange: row counts exceed the 32-bit range of the staged form");
+    }
     if (can_merge)
         return run_exchange_merged(c, reverse ? out : in, reverse ? in : out, staging, !reverse, lec, gec, stored,
                                    n_expert, n_workers, row_bytes, st);

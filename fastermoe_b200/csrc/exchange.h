@@ -41,6 +41,13 @@ struct Comm {
                                 ::fmoe::g_nccl.GetErrorString(r__));                     \
     } while (0)
 
+// Row-range copies between up to two source and two destination buffers in one
+// kernel launch per ~160 ranges (used to turn per-peer staging into the
+// expert-major layout and back).  sel picks buffer 0 or 1.
+struct SegCopy { int src_sel, dst_sel; int64_t src_row, dst_row, rows; };
+int launch_segment_copies(const std::vector<SegCopy>& copies, const void* src0, const void* src1, void* dst0,
+                          void* dst1, int64_t row_bytes, cudaStream_t st);
+
 // Row moves of global_scatter for this rank (see fmoe_plan_global_scatter).
 int plan_scatter(const int64_t* lec, const int64_t* gec, const uint8_t* stored, int rank, int E, int W,
                  std::vector<fmoe_move_t>& moves, int64_t* recv_rows, int64_t* send_rows);

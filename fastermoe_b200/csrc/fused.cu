@@ -134,6 +134,113 @@ int exchange_step(Comm* c, const Geometry& g, int step, bool forward_dir, const 
     return 0;
 }
 
+// Shadow flags that are all-or-none per worker (what the layer produces): the rows a
+// rank sends to a peer are then one contiguous token-side range.
+bool flags_uniform(const uint8_t* stored, int E, int W) {
+    for (int j = 0; j < W; ++j)
+        for (int i = 1; i < E; ++i)
+            if ((stored[j * E + i] != 0) != (stored[j * E] != 0)) return false;
+    return true;
+}
+
+// Same step with ONE send and ONE receive per peer: rows from a peer land contiguously in
+// `staging` (at a per-peer offset that is the same in every step) and one copy kernel moves
+// them to their expert-major positions; on the way back a copy kernel packs them first.
+int exchange_step_merged(Comm* c, const Geometry& g, int step, bool forward_dir, const void* token_c,
+                         const void* expert_c, void* staging, const int64_t* lec, const int64_t* gec,
+                         const uint8_t* stored, int64_t row_bytes, cudaStream_t st) {
+    const int to_base = (g.group_rank + step) % g.n_steps * g.gran;
+    const int from_base = (g.group_rank + g.n_steps - step) % g.n_steps * g.gran;
+    char* token = (char*)token_c;
+    char* expert = (char*)expert_c;
+    char* stg = (char*)staging;
+    const bool own_shadowed = stored[g.rank * g.E] != 0;
+    auto rows_from = [&](int q) -> int64_t {  // rows peer q routed to this rank's experts
+        if (own_shadowed) return 0;
+        int64_t r = 0;
+        for (int i = 0; i < g.E; ++i) r += gec[i + q * g.E];
+        return r;
+    };
+    auto staging_off = [&](int q) -> int64_t {
+        int64_t off = 0;
+        for (int q2 = 0; q2 < q; ++q2)
+            if (q2 != g.rank) off += rows_from(q2);
+        return off;
+    };
+    struct Xfer { int peer; int64_t off, rows; };
+    std::vector<Xfer> tok, exp;  // token-side ranges (per tok_peer), staging ranges (per exp_peer)
+    std::vector<SegCopy> copies;
+    for (int j = 0; j < g.gran; ++j) {
+        const int tp = j + to_base, ep = j + from_base;
+        if (tp == g.rank) {
+            // both sides of the pair are this GPU (step 0): token rows <-> expert rows directly
+            if (!own_shadowed)
+                for (int i = 0; i < g.E; ++i) {
+                    const int64_t n = lec[i + g.rank * g.E];
+                    if (!n) continue;
+                    if (forward_dir) copies.push_back({1, 0, g.local_ptr[i + g.rank * g.E], g.global_ptr[i * g.W + g.rank], n});
+                    else copies.push_back({0, 1, g.global_ptr[i * g.W + g.rank], g.local_ptr[i + g.rank * g.E], n});
+                }
+            continue;
+        }
+        if (!stored[tp * g.E]) {
+            const int64_t n = g.local_ptr[(tp + 1) * g.E] - g.local_ptr[tp * g.E];
+            if (n) tok.push_back({tp, g.local_ptr[tp * g.E], n});
+        }
+        const int64_t r = rows_from(ep);
+        if (r) {
+            const int64_t s0 = staging_off(ep);
+            exp.push_back({ep, s0, r});
+            int64_t pre = 0;
+            for (int i = 0; i < g.E; ++i) {
+                const int64_t n = gec[i + ep * g.E];
+                if (n) {
+                    if (forward_dir) copies.push_back({0, 0, s0 + pre, g.global_ptr[i * g.W + ep], n});
+                    else copies.push_back({0, 0, g.global_ptr[i * g.W + ep], s0 + pre, n});
+                }
+                pre += n;
+            }
+        }
+    }
+    auto group = [&](const std::vector<Xfer>& sends, const char* sbuf, const std::vector<Xfer>& recvs, char* rbuf) -> int {
+        if (sends.empty() && recvs.empty()) return 0;
+        FMOE_NCCL_TRY(g_nccl.GroupStart());
+        for (const auto& x : sends) {
+            ncclResult_t e = g_nccl.Send(sbuf + x.off * row_bytes, (size_t)x.rows * row_bytes, ncclChar, x.peer, c->comm, st);
+            if (e != ncclSuccess) { g_nccl.GroupEnd(); return fail(FMOE_ERR_NCCL, "ncclSend failed: %s", g_nccl.GetErrorString(e)); }
+        }
+        for (const auto& x : recvs) {
+            ncclResult_t e = g_nccl.Recv(rbuf + x.off * row_bytes, (size_t)x.rows * row_bytes, ncclChar, x.peer, c->comm, st);
+            if (e != ncclSuccess) { g_nccl.GroupEnd(); return fail(FMOE_ERR_NCCL, "ncclRecv failed: %s", g_nccl.GetErrorString(e)); }
+        }
+        FMOE_NCCL_TRY(g_nccl.GroupEnd());
+        return 0;
+    };
+    if (forward_dir) {
+        if (int rc = group(tok, token, exp, stg)) return rc;
+        // sources: 0 = staging, 1 = token buffer; destination 0 = expert buffer
+        return launch_segment_copies(copies, stg, token, expert, nullptr, row_bytes, st);
+    }
+    // sources: 0 = expert buffer; destinations: 0 = staging, 1 = token buffer
+    if (int rc = launch_segment_copies(copies, expert, nullptr, stg, token, row_bytes, st)) return rc;
+    return group(exp, stg, tok, token);
+}
+
+// Picks the merged form when a staging buffer is given and the layout allows it.
+int do_exchange_step(Comm* c, const Geometry& g, int step, bool forward_dir, const void* token, const void* expert,
+                     void* staging, const int64_t* lec, const int64_t* gec, const uint8_t* stored, int64_t row_bytes,
+                     cudaStream_t st) {
+    // The choice must come out the same on every rank (the two forms pair sends and receives
+    // differently), so it depends only on arguments that are identical everywhere.
+    const bool merged = staging && g.E > 1 && row_bytes % 16 == 0 && flags_uniform(stored, g.E, g.W);
+    if (merged)
+        FMOE_REQUIRE(((((uintptr_t)token) | ((uintptr_t)expert) | ((uintptr_t)staging)) & 15) == 0,
+                     "smart schedule: buffers must be 16-byte aligned when a staging buffer is given");
+    if (merged) return exchange_step_merged(c, g, step, forward_dir, token, expert, staging, lec, gec, stored, row_bytes, st);
+    if (forward_dir) return exchange_step(c, g, step, true, token, (void*)expert, lec, gec, stored, row_bytes, st);
+    return exchange_step(c, g, step, false, expert, (void*)token, lec, gec, stored, row_bytes, st);
+}
+
 // Row ranges of one pipeline step, per local expert, in expert-side coordinates.
 void step_segments(const Geometry& g, int step, HostSegs& hs) {
     const int from_base = (g.group_rank + g.n_steps - step) % g.n_steps * g.gran;
@@ -229,8 +336,8 @@ extern "C" int fmoe_fused_forward(fmoe_comm_t comm, const void* local_in, void* 
                                   void* middle, void* middle_pre, void* global_out,
                                   const fmoe_mlp_params_t* params, const int64_t* lec, const int64_t* gec,
                                   const uint8_t* stored, int64_t local_rows, int64_t d, int64_t h, int32_t E,
-                                  int32_t W, int32_t dtype, int32_t act, int32_t gran, fmoe_stream_t stream,
-                                  fmoe_stream_t comm_stream) {
+                                  int32_t W, int32_t dtype, int32_t act, int32_t gran, void* staging,
+                                  fmoe_stream_t stream, fmoe_stream_t comm_stream) {
     Comm* c;
     int rank;
     if (int rc = check_common(comm, params, W, E, dtype, act, d, h, &c, &rank)) return rc;
@@ -255,7 +362,7 @@ extern "C" int fmoe_fused_forward(fmoe_comm_t comm, const void* local_in, void* 
     FMOE_CUDA_TRY(cudaEventRecord(start, cs));
     FMOE_CUDA_TRY(cudaStreamWaitEvent(ms, start, 0));
     for (int step = 0; step < g.n_steps; ++step) {
-        if (int rc = exchange_step(c, g, step, true, local_in, global_in, lec, gec, stored, row_bytes, ms)) return rc;
+        if (int rc = do_exchange_step(c, g, step, true, local_in, global_in, staging, lec, gec, stored, row_bytes, ms)) return rc;
         FMOE_CUDA_TRY(cudaEventRecord(in_ready[step], ms));
     }
     // Rows of shadowed experts stay here: stage them behind the received rows.
@@ -277,7 +384,7 @@ extern "C" int fmoe_fused_forward(fmoe_comm_t comm, const void* local_in, void* 
     }
     for (int step = 0; step < g.n_steps; ++step) {
         FMOE_CUDA_TRY(cudaStreamWaitEvent(ms, out_ready[step], 0));
-        if (int rc = exchange_step(c, g, step, false, global_out, local_out, lec, gec, stored, row_bytes, ms)) return rc;
+        if (int rc = do_exchange_step(c, g, step, false, local_out, global_out, staging, lec, gec, stored, row_bytes, ms)) return rc;
     }
     // Shadowed experts: compute locally with the fetched parameters while results travel.
     for (int j = 0; j < W; ++j) {
@@ -302,8 +409,8 @@ extern "C" int fmoe_fused_backward(fmoe_comm_t comm, const void* grad_out_local,
                                    void* global_grad_out, void* grad_middle, void* global_grad_in,
                                    const fmoe_mlp_params_t* params, const int64_t* lec, const int64_t* gec,
                                    const uint8_t* stored, int64_t local_rows, int64_t d, int64_t h, int32_t E,
-                                   int32_t W, int32_t dtype, int32_t act, int32_t gran, fmoe_stream_t stream,
-                                   fmoe_stream_t comm_stream) {
+                                   int32_t W, int32_t dtype, int32_t act, int32_t gran, void* staging,
+                                   fmoe_stream_t stream, fmoe_stream_t comm_stream) {
     Comm* c;
     int rank;
     if (int rc = check_common(comm, params, W, E, dtype, act, d, h, &c, &rank)) return rc;
@@ -328,7 +435,7 @@ extern "C" int fmoe_fused_backward(fmoe_comm_t comm, const void* grad_out_local,
     FMOE_CUDA_TRY(cudaEventRecord(start, cs));
     FMOE_CUDA_TRY(cudaStreamWaitEvent(ms, start, 0));
     for (int step = 0; step < g.n_steps; ++step) {
-        if (int rc = exchange_step(c, g, step, true, grad_out_local, global_grad_out, lec, gec, stored, row_bytes, ms))
+        if (int rc = do_exchange_step(c, g, step, true, grad_out_local, global_grad_out, staging, lec, gec, stored, row_bytes, ms))
             return rc;
         FMOE_CUDA_TRY(cudaEventRecord(in_ready[step], ms));
     }
@@ -353,7 +460,7 @@ extern "C" int fmoe_fused_backward(fmoe_comm_t comm, const void* grad_out_local,
     }
     for (int step = 0; step < g.n_steps; ++step) {
         FMOE_CUDA_TRY(cudaStreamWaitEvent(ms, out_ready[step], 0));
-        if (int rc = exchange_step(c, g, step, false, global_grad_in, grad_in_local, lec, gec, stored, row_bytes, ms))
+        if (int rc = do_exchange_step(c, g, step, false, grad_in_local, global_grad_in, staging, lec, gec, stored, row_bytes, ms))
             return rc;
     }
     for (int j = 0; j < W; ++j) {

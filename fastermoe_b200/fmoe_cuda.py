@@ -304,7 +304,9 @@ def _global_move(fn, name, buf, local_expert_count, global_expert_count, stored_
     row_bytes = buf.shape[1] * buf.element_size()
     # staging of the expert-side size: one send/receive per peer instead of one per (expert, peer)
     expert_rows = batch_size if name == "global_scatter" else buf.shape[0]
-    staging = buf.new_empty((expert_rows, buf.shape[1])) if os.environ.get("FMOE_B200_EXCHANGE") != "split" else None
+    # (allocated on every rank, also one that receives nothing: all ranks must use the same form)
+    staging = (buf.new_empty((max(int(expert_rows), 1), buf.shape[1]))
+               if os.environ.get("FMOE_B200_EXCHANGE") != "split" else None)
     with torch.cuda.device(buf.device):
         _run(name, fn, _comm(buf.device), _ptr(buf), _ptr(out), _ptr(lec), _ptr(gec), _ptr(st), buf.shape[0],
              batch_size, row_bytes, n_expert, n_workers, _ptr(staging), _stream())
@@ -536,6 +538,15 @@ def _comm_stream(device):
     return s
 
 
+def _fused_staging(like, rows, d_model):
+    """Staging for the one-send-per-peer exchange of the smart schedule (None: per-expert sends)."""
+    # Every rank must make the same choice (the two forms pair sends and receives
+    # differently), so the buffer exists even on a rank that receives nothing.
+    if os.environ.get("FMOE_B200_EXCHANGE") == "split":
+        return None
+    return like.new_empty((max(int(rows), 1), d_model))
+
+
 def fuse_gran():
     """Peers per pipeline step: env FMOE_FUSE_GRAN, default 4 (cuda/fused_compute.cu:21-28).
     Read on every call (the reference caches the first value in a process global)."""
@@ -618,7 +629,7 @@ def fused_forward(input_buf, params, local_expert_count, global_expert_count, st
         comm = _comm(dev) if n_workers > 1 else None
         _run("fused_forward", lib.fmoe_fused_forward, comm, _ptr(input_buf), _ptr(out), _ptr(gib), _ptr(gmb),
              _ptr(pre), _ptr(gob), table, _ptr(lec), _ptr(gec), _ptr(st), A, d_model, d_hidden, n_expert,
-             n_workers, _dtype_code(input_buf), activation, gran, _stream(),
+             n_workers, _dtype_code(input_buf), activation, gran, _ptr(_fused_staging(input_buf, B, d_model)), _stream(),
              ctypes.c_void_p(_comm_stream(dev).cuda_stream))
     res = [out, gib, gmb, gob]
     if pre is not None:
@@ -667,5 +678,5 @@ def fused_backward(input_buf, params, middle_buf, output_buf, grad_out, local_ex
         _run("fused_backward", lib.fmoe_fused_backward, comm, _ptr(grad_out), _ptr(grad_in), _ptr(input_buf),
              _ptr(middle_buf), _ptr(middle_pre), _ptr(ggo), _ptr(gmid), _ptr(ggi), table, _ptr(lec), _ptr(gec),
              _ptr(st), grad_out.shape[0], d_model, d_hidden, n_expert, n_workers, _dtype_code(input_buf),
-             activation, gran, _stream(), ctypes.c_void_p(_comm_stream(dev).cuda_stream))
+             activation, gran, _ptr(_fused_staging(input_buf, rows, d_model)), _stream(), ctypes.c_void_p(_comm_stream(dev).cuda_stream))
     return [grad_in]

@@ -287,7 +287,8 @@ int fmoe_plan_global_scatter(const int64_t* lec_host, const int64_t* gec_host,
  * send and one receive (rows to a peer are contiguous on the token side; rows
  * from a peer land contiguously in staging) and one copy kernel produces the
  * expert-major layout; without it every (expert, peer) segment is its own
- * send/receive, as in the reference. */
+ * send/receive, as in the reference.  All ranks must make the same choice
+ * (pass a buffer, of at least one row, on every rank or on none). */
 int fmoe_global_scatter(fmoe_comm_t comm, const void* local_in, void* global_out,
                         const int64_t* lec_host, const int64_t* gec_host,
                         const uint8_t* stored_models_host, int64_t in_rows,
@@ -378,7 +379,11 @@ int fmoe_fused_geometry(const int64_t* lec_host, const int64_t* gec_host,
  * with B, S from fmoe_fused_geometry.  The exchange with the peers of step s is
  * queued on comm_stream, the expert GEMMs of step s on `stream` once its rows have
  * arrived, and the results travel back as each step finishes.  On return all work
- * is queued and `stream` waits for comm_stream.  Unlike the reference (ReLU only,
+ * is queued and `stream` waits for comm_stream.  staging (may be NULL): B rows of
+ * d_model; with it and more than one expert per worker every peer is served by one
+ * send and one receive per step plus a copy kernel, instead of one per expert
+ * (pass it on every rank or on none, also on a rank with B = 0).
+ * Unlike the reference (ReLU only,
  * no bias) the activation is selectable and biases are applied when non-NULL.
  * comm may be NULL when n_workers == 1. */
 int fmoe_fused_forward(fmoe_comm_t comm, const void* local_in, void* local_out,
@@ -388,7 +393,8 @@ int fmoe_fused_forward(fmoe_comm_t comm, const void* local_in, void* local_out,
                        const uint8_t* stored_models_host, int64_t local_rows,
                        int64_t d_model, int64_t d_hidden, int32_t n_expert,
                        int32_t n_workers, int32_t dtype, int32_t activation,
-                       int32_t pipeline_gran, fmoe_stream_t stream, fmoe_stream_t comm_stream);
+                       int32_t pipeline_gran, void* staging, fmoe_stream_t stream,
+                       fmoe_stream_t comm_stream);
 
 /* fused_backward: cuda/fmoe_cuda.cpp:88-100, cuda/fused_compute.cu:64-131,
  * cuda/fused_compute.cuh:391-542.  global_in, middle, middle_pre are the buffers
@@ -405,7 +411,8 @@ int fmoe_fused_backward(fmoe_comm_t comm, const void* grad_out_local, void* grad
                         const uint8_t* stored_models_host, int64_t local_rows,
                         int64_t d_model, int64_t d_hidden, int32_t n_expert,
                         int32_t n_workers, int32_t dtype, int32_t activation,
-                        int32_t pipeline_gran, fmoe_stream_t stream, fmoe_stream_t comm_stream);
+                        int32_t pipeline_gran, void* staging, fmoe_stream_t stream,
+                        fmoe_stream_t comm_stream);
 
 #ifdef __cplusplus
 }

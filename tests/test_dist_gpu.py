@@ -26,8 +26,24 @@ def needs_gpus():
         pytest.skip("needs at least 2 GPUs")
 
 
+def run_ranks(fn, world, limit_s=240):
+    """Spawns the ranks and ends them if they do not finish in time (a mismatched exchange
+    would otherwise wait for ever)."""
+    import time
+    ctx = mp.spawn(fn, args=(world, free_port()), nprocs=world, join=False)
+    deadline = time.time() + limit_s
+    try:
+        while not ctx.join(timeout=5):
+            if time.time() > deadline:
+                raise TimeoutError(f"{fn.__name__} on {world} ranks did not finish within {limit_s} s")
+    finally:
+        for p in ctx.processes:
+            if p.is_alive():
+                p.terminate()
+
+
 @pytest.mark.parametrize("fn", ["gpu_exchange", "gpu_layer", "gpu_layer_bf16"])
 def test_expert_parallel(fn):
     needs_gpus()
     for world in world_sizes():
-        mp.spawn(getattr(dist_worker, fn), args=(world, free_port()), nprocs=world, join=True)
+        run_ranks(getattr(dist_worker, fn), world)
