@@ -494,19 +494,22 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 tc_fence_after();
                 uint8_t* a_src = tiles + s * STAGE_BYTES;
                 uint8_t* b_src = a_src + A_BYTES;
+                int k_steps = BK / 16;  // UMMA_K = 16 rows of the chunk per instruction
                 if (MODE == MODE_WGRAD) {
-                    // Rows of the chunk past the end of the expert's segment belong to the
-                    // next expert (or are uninitialised): clear them in both operands.  A
-                    // row is one 128-byte line per 64-column block, whatever the swizzle.
+                    // Rows of the chunk past the end of the expert's segment belong to the next
+                    // expert (or are uninitialised).  K steps that lie entirely past the end are
+                    // not issued; in the one step that straddles it the rows past the end are
+                    // cleared in both operands (a row is one 128-byte line per 64-column block,
+                    // whatever the swizzle).
                     const int valid = t.m_hi - (t.m_lo + ch * BK);
                     if (valid < BK) {
-                        const int lines = (BK - valid) * ((BM + B_COLS) / 64);
-                        for (int i = lane; i < lines * 8; i += 32) {
-                            const int line = i >> 3, part = i & 7;
-                            const int blk = line / (BK - valid), r = valid + line % (BK - valid);
-                            uint8_t* base = a_src + blk * SUB_BYTES;  // blocks of A then B are contiguous
-                            *reinterpret_cast<uint4*>(base + r * 128 + part * 16) = make_uint4(0, 0, 0, 0);
-                        }
+                        k_steps = (valid + 15) >> 4;
+                        const int row_end = k_steps << 4;
+                        constexpr int BLOCKS = (BM + B_COLS) / 64;  // blocks of A then B are contiguous
+                        for (int blk = 0; blk < BLOCKS; ++blk)
+                            for (int r = valid + (lane >> 3); r < row_end; r += 4)
+                                *reinterpret_cast<uint4*>(a_src + blk * SUB_BYTES + r * 128 + (lane & 7) * 16) =
+                                    make_uint4(0, 0, 0, 0);
                         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                         __syncwarp();
                     }
@@ -527,6 +530,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     const uint64_t bdesc = make_desc(smem_u32(b_src), B_LBO, 1024);
 #pragma unroll
                     for (int k = 0; k < BK / 16; ++k) {
+                        if (k >= k_steps) break;
                         const uint64_t ad = adesc + (uint64_t)((k * A_ADV) >> 4), bd = bdesc + (uint64_t)((k * B_ADV) >> 4);
                         const uint32_t accum = (ch > 0 || k > 0) ? 1u : 0u;
                         if (CTA2) tc_mma_pair(tmem_c, ad, bd, idesc, accum);
