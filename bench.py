@@ -21,6 +21,7 @@ All data is synthetic (seeded); working set per step is several hundred MB,
 larger than the 126 MB L2, so no explicit L2 flush is needed between steps.
 """
 import argparse
+import ctypes
 import json
 import os
 import statistics
@@ -253,6 +254,14 @@ def run_ours(args):
     dur = tprof.durations_ms()
     fmoe_cuda.set_profile(None)
 
+    exchange_form = None
+    if world > 1:
+        exchange_form = ("smart schedule (NCCL, pipelined with the expert GEMMs)" if layer.enable_fuse else
+                         "direct stores into peer memory over NVLink" if fmoe_cuda.peer_slot_bytes(dev) > 0 else
+                         "NCCL send/receive, one pair per peer")
+        st = ctypes.c_int32(0)
+        fmoe_cuda.lib.fmoe_device_status(ctypes.byref(st))
+        assert st.value == 0, f"device status word {st.value}: a bounded wait expired"
     peaks = measured_peaks()
     ms_per_step = total_ms / args.steps
     tokens = T * world
@@ -293,7 +302,7 @@ def run_ours(args):
             "metric": "moe_layer_fwd_bwd_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": workload_config(world),
+            "config": dict(workload_config(world), **({"exchange": exchange_form} if world > 1 else {})),
             "e2e": ({"value": e2e_val, "unit": "tokens/s",
                      "h2d_bytes_per_step": x_host.numel() * x_host.element_size(), "d2h_bytes_per_step": 4,
                      "ms_per_step": e2e_ms / args.steps} if e2e_ms else None),

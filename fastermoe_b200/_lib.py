@@ -46,6 +46,7 @@ lib = _load()
 
 P = c_void_p
 I32, I64 = c_int32, c_int64
+PEER_UNAVAILABLE = 1      # FMOE_PEER_UNAVAILABLE
 
 _SIGS = {
     "fmoe_last_error_string": (c_char_p, []),
@@ -77,6 +78,10 @@ _SIGS = {
     "fmoe_plan_global_scatter": (I32, [P, P, P, I32, I32, I32, P, I32, POINTER(c_int32), POINTER(c_int64)]),
     "fmoe_global_scatter": (I32, [P, P, P, P, P, P, I64, I64, I64, I32, I32, P, P]),
     "fmoe_global_gather": (I32, [P, P, P, P, P, P, I64, I64, I64, I32, I32, P, P]),
+    "fmoe_peer_enable": (I32, [P, I64, P]),
+    "fmoe_peer_slot_bytes": (I64, [P]),
+    "fmoe_peer_global_scatter": (I32, [P, P, P, P, P, I64, I64, I64, I32, I32, P]),
+    "fmoe_peer_global_gather": (I32, [P, P, P, P, P, I64, I64, I64, I32, I32, P]),
     "fmoe_exchange_cache_info": (I32, [P, P, P, I32, I32, P]),
     "fmoe_model_broadcast": (I32, [P, P, I64, I32, P]),
     "fmoe_gradient_reduce": (I32, [P, P, I64, I32, I32, P]),
@@ -101,6 +106,6 @@ def last_error():
 
 
 def check(status, what):
-    """Raise RuntimeError for a negative status returned by the library."""
+    """Raise RuntimeError for a non-zero status returned by the library."""
     if status != 0:
         raise RuntimeError(f"{what} failed (status {status}): {last_error()}")

@@ -368,6 +368,7 @@ extern "C" int fmoe_comm_init(const void* id128_host, int32_t rank, int32_t worl
 extern "C" int fmoe_comm_destroy(fmoe_comm_t comm) {
     if (!comm) return 0;
     Comm* c = (Comm*)comm;
+    peer_release(c);
     if (c->comm) g_nccl.CommDestroy(c->comm);
     for (auto& ev : c->events) cudaEventDestroy(ev);
     delete c;

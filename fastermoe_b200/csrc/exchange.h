@@ -27,11 +27,27 @@ struct NcclApi {
 extern NcclApi g_nccl;
 int ensure_nccl_loaded();
 
+// Peer-memory exchange state (see peer.cu).  `base[p]` is rank p's landing allocation
+// as mapped into this process (own allocation at p == rank); slot_bytes == 0: off.
+constexpr int kMaxPeers = 64;
+struct PeerState {
+    int64_t slot_bytes = 0;
+    char* base[kMaxPeers] = {};
+    unsigned int* counter = nullptr;   // device word for last-block detection
+    unsigned long long epoch = 0;      // exchanges done over peer memory (same on every rank)
+    unsigned long long timeout_ns = 0;
+};
+
 struct Comm {
     ncclComm_t comm = nullptr;
     int rank = 0, world = 1, device = 0;
     std::vector<cudaEvent_t> events;  // pool reused by the smart schedule
+    PeerState peer;
 };
+
+// Device address of the status word that bounded waits raise (per device).
+int* device_status_ptr();
+void peer_release(Comm* c);
 
 #define FMOE_NCCL_TRY(expr)                                                              \
     do {                                                                                 \

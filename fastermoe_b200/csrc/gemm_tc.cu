@@ -995,6 +995,8 @@ int tc_linear_backward(const LinearBwdArgs& a, cudaStream_t st) {
     return 0;
 }
 
+int* device_status_ptr() { return status_ptr(); }
+
 int read_device_status(int* out) {
     int v = 0;
     FMOE_CUDA_TRY(cudaMemcpyFromSymbol(&v, g_status, sizeof(int)));

@@ -1,0 +1,423 @@
+// Token all-to-all-v over NVLink peer memory: the rows of global_scatter /
+// global_gather are stored straight into the destination GPU's memory by a copy
+// kernel, with no NCCL send/receive pairs and no staging pass on the sender.
+//
+// Same data movement as cuda/global_exchange.cuh:75-124 of the reference (which
+// issues one ncclSend/ncclRecv per expert and peer); the row layout on both sides
+// is the one plan_scatter describes.
+//
+// Every rank owns a "landing" allocation that its peers map through CUDA IPC:
+//
+//     [ header 4 KiB | slot 0 | slot 1 ]
+//
+// One exchange, numbered by an epoch that advances in step on all ranks, uses slot
+// (epoch & 1):
+//   1. push kernel: waits until every peer has released the slot it used two epochs
+//      ago (freed flags, in this rank's header), stores its outgoing rows into the
+//      peers' slots at their final row offsets (rows that stay on this GPU go
+//      straight to the output), then the last block to finish publishes
+//      arrived[slot][rank] = epoch in every peer's header;
+//   2. consume kernel: waits for arrived == epoch from every peer, copies the rows
+//      that came from peers out of the slot into the caller's buffer, and its last
+//      block publishes freed[slot][rank] = epoch in every peer's header.
+// The two slots let a rank push epoch n while a slow peer still reads epoch n-1.
+//
+// All waits are bounded (wall-clock limit, FMOE_B200_PEER_TIMEOUT_MS, default
+// 20000): when one expires the kernel raises bit 16 (slot not released) or 32 (rows
+// not arrived) in the device status word and carries on, so that the stream drains.
+//
+// Whether an exchange goes over peer memory must be decided identically on all
+// ranks; the entry points therefore take the all-gathered count table, from which
+// every rank derives every other rank's layout and the largest slot any rank needs.
+#include "common.cuh"
+#include "exchange.h"
+#include <cstdlib>
+#include <cstring>
+#include <vector>
+
+namespace fmoe {
+namespace {
+
+constexpr int kHeaderBytes = 4096;
+constexpr int kFreedOffset = 1024;          // arrived[2][kMaxPeers] u64 at 0, freed[2][kMaxPeers] u64 at 1024
+constexpr int kPeerSegMax = 128;
+constexpr int kLocal = 255;                 // dst_sel of rows that stay on this GPU
+static_assert(2 * 2 * kMaxPeers * 8 <= kHeaderBytes, "flags fit the header");
+
+struct PeerSegs {
+    int n;
+    int prefix[kPeerSegMax + 1];            // rows before segment k
+    int src_row[kPeerSegMax], dst_row[kPeerSegMax];
+    unsigned char dst_sel[kPeerSegMax];     // destination rank, or kLocal
+};
+struct PeerBases { char* base[kMaxPeers]; };
+
+__device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long long* p) {
+    unsigned long long v;
+    asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_sys(unsigned long long* p, unsigned long long v) {
+    asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long now_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Waits until *flag + slack >= want; gives up after timeout_ns (or 2^28 polls).
+__device__ bool wait_flag(const unsigned long long* flag, unsigned long long want, unsigned long long slack,
+                          unsigned long long timeout_ns) {
+    if (ld_acquire_sys(flag) + slack >= want) return true;
+    const unsigned long long t0 = now_ns();
+    for (unsigned it = 0; it < (1u << 28); ++it) {
+        if (ld_acquire_sys(flag) + slack >= want) return true;
+        if (now_ns() - t0 > timeout_ns) return false;
+        __nanosleep(256);
+    }
+    return false;
+}
+
+struct PeerLaunch {
+    int rank, world, slot;
+    int wait_first, signal_last;            // this launch opens / closes the phase
+    unsigned long long epoch, timeout_ns;
+    int64_t row_vecs, slot_off;             // 16-byte units per row; byte offset of the slot in an allocation
+    unsigned int* counter;
+    int* status;
+};
+
+template <bool kPush>
+__global__ void __launch_bounds__(256)
+peer_rows_kernel(const __grid_constant__ PeerSegs t, const __grid_constant__ PeerBases b,
+                 const __grid_constant__ PeerLaunch a, const uint4* __restrict__ src, uint4* __restrict__ out) {
+    __shared__ int s_last;
+    unsigned long long* hdr = (unsigned long long*)b.base[a.rank];
+    if (a.wait_first) {
+        const int p = threadIdx.x;
+        if (p < a.world && p != a.rank) {
+            if (kPush) {       // the slot must have been read out by everyone who got rows in it two epochs ago
+                if (!wait_flag(hdr + kFreedOffset / 8 + a.slot * kMaxPeers + p, a.epoch, 2, a.timeout_ns))
+                    atomicOr(a.status, 16);
+            } else {           // everyone's rows of this epoch must have landed
+                if (!wait_flag(hdr + a.slot * kMaxPeers + p, a.epoch, 0, a.timeout_ns)) atomicOr(a.status, 32);
+            }
+        }
+        __syncthreads();
+    }
+    const int lane = threadIdx.x & 31;
+    const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (row < t.prefix[t.n]) {
+        int lo = 0, hi = t.n - 1;  // last segment whose prefix <= row
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (t.prefix[mid] <= row) lo = mid; else hi = mid - 1;
+        }
+        const int k = lo, off = row - t.prefix[k];
+        const uint4* s;
+        uint4* d;
+        if (kPush) {
+            s = src + (int64_t)(t.src_row[k] + off) * a.row_vecs;
+            const int sel = t.dst_sel[k];
+            d = (sel == kLocal ? out : (uint4*)(b.base[sel] + a.slot_off)) + (int64_t)(t.dst_row[k] + off) * a.row_vecs;
+        } else {
+            s = (const uint4*)(b.base[a.rank] + a.slot_off) + (int64_t)(t.src_row[k] + off) * a.row_vecs;
+            d = out + (int64_t)(t.dst_row[k] + off) * a.row_vecs;
+        }
+        // Rows in the slot were written by other GPUs while this kernel may already have
+        // been running: read them through L2 (ld.cg), never through the non-coherent path.
+        int64_t c = lane;
+        for (; c + 96 < a.row_vecs; c += 128) {
+            const uint4 v0 = __ldcg(s + c), v1 = __ldcg(s + c + 32), v2 = __ldcg(s + c + 64), v3 = __ldcg(s + c + 96);
+            d[c] = v0; d[c + 32] = v1; d[c + 64] = v2; d[c + 96] = v3;
+        }
+        for (; c < a.row_vecs; c += 32) d[c] = __ldcg(s + c);
+    }
+    if (a.signal_last) {
+        // All of this block's stores are ordered before thread 0's fence by the barrier,
+        // and the fence is cumulative: one fence per block publishes them.
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            __threadfence_system();
+            s_last = atomicAdd(a.counter, 1u) == gridDim.x - 1;
+        }
+        __syncthreads();
+        if (s_last) {
+            __threadfence_system();
+            const int p = threadIdx.x;
+            if (p < a.world && p != a.rank) {
+                unsigned long long* peer_hdr = (unsigned long long*)b.base[p];
+                st_release_sys(peer_hdr + (kPush ? 0 : kFreedOffset / 8) + a.slot * kMaxPeers + a.rank, a.epoch);
+            }
+            if (threadIdx.x == 0) *a.counter = 0;
+        }
+    }
+}
+
+struct Seg { int sel; int64_t src_row, dst_row, rows; };
+
+template <bool kPush>
+int launch_phase(Comm* c, const std::vector<Seg>& segs, const void* src, void* out, int64_t row_bytes, int slot,
+                 cudaStream_t st) {
+    PeerBases b;
+    for (int p = 0; p < kMaxPeers; ++p) b.base[p] = c->peer.base[p];
+    PeerLaunch a;
+    a.rank = c->rank; a.world = c->world; a.slot = slot;
+    a.epoch = c->peer.epoch; a.timeout_ns = c->peer.timeout_ns;
+    a.row_vecs = row_bytes / 16;
+    a.slot_off = kHeaderBytes + (int64_t)slot * c->peer.slot_bytes;
+    a.counter = c->peer.counter + (kPush ? 0 : 1);
+    a.status = device_status_ptr();
+    FMOE_REQUIRE(a.status, "peer exchange: no device status word");
+    PeerSegs t;
+    size_t i = 0;
+    bool first = true;
+    do {
+        t.n = 0;
+        t.prefix[0] = 0;
+        for (; i < segs.size() && t.n < kPeerSegMax; ++i) {
+            const Seg& s = segs[i];
+            if (s.rows == 0) continue;
+            t.dst_sel[t.n] = (unsigned char)s.sel;
+            t.src_row[t.n] = (int)s.src_row; t.dst_row[t.n] = (int)s.dst_row;
+            t.prefix[t.n + 1] = t.prefix[t.n] + (int)s.rows;
+            ++t.n;
+        }
+        if (t.n == 0) t.prefix[1] = 0;
+        a.wait_first = first;
+        a.signal_last = i >= segs.size();
+        const unsigned blocks = (unsigned)std::max<int64_t>(1, ceil_div(t.n ? t.prefix[t.n] : 0, 8));
+        peer_rows_kernel<kPush><<<blocks, 256, 0, st>>>(t, b, a, (const uint4*)src, (uint4*)out);
+        FMOE_CHECK_LAUNCH();
+        first = false;
+    } while (i < segs.size());
+    return 0;
+}
+
+// Expert-side row of segment (expert i of rank p, source rank j), as plan_scatter lays
+// rank p's buffer out; -1 for segments that are not exchanged.  table is [W][W][E]:
+// rows that rank `src` routes to expert e of rank `dst`.
+struct Layout {
+    std::vector<int64_t> off;     // [i + j * E]
+    std::vector<int64_t> shadow;  // [j * E + i]: row of the block of rank p's own rows for shadowed expert (j, i)
+    int64_t total = 0;
+};
+
+void expert_layout(const int64_t* table, const uint8_t* stored, int p, int E, int W, Layout& L) {
+    const int64_t* lec = table + (int64_t)p * W * E;
+    L.off.assign((size_t)E * W, -1);
+    L.shadow.assign((size_t)E * W, -1);
+    int64_t rp = 0;
+    auto local_block = [&](int j) {
+        for (int i = 0; i < E; ++i) {
+            const int idx = i + j * E;
+            if (stored[idx]) { L.shadow[idx] = rp; rp += lec[idx]; }
+        }
+    };
+    for (int j = 0; j < p; ++j) local_block(j);
+    for (int i = 0; i < E; ++i)
+        for (int j = 0; j < W; ++j) {
+            const int64_t g = table[((int64_t)j * W + p) * E + i];
+            if (g > 0 && (!stored[p * E + i] || j == p)) { L.off[i + j * E] = rp; rp += g; }
+        }
+    for (int j = p + 1; j < W; ++j) local_block(j);
+    L.total = rp;
+}
+
+int peer_move(fmoe_comm_t comm, const void* in, void* out, const int64_t* table, const uint8_t* stored,
+              int64_t in_rows, int64_t out_rows, int64_t row_bytes, int E, int W, bool reverse, cudaStream_t st) {
+    FMOE_REQUIRE(comm, "peer exchange: null communicator");
+    Comm* c = (Comm*)comm;
+    FMOE_REQUIRE(W == c->world, "peer exchange: n_workers=%d but communicator has %d ranks", W, c->world);
+    FMOE_REQUIRE(table && stored && E > 0 && row_bytes > 0, "peer exchange: bad argument");
+    if (c->peer.slot_bytes == 0 || row_bytes % 16 != 0) return FMOE_PEER_UNAVAILABLE;
+    const int r = c->rank;
+    const size_t n = (size_t)W * E;
+    for (size_t i = 0; i < n * W; ++i) FMOE_REQUIRE(table[i] >= 0, "peer exchange: negative count at %zu", i);
+
+    // token-side offsets of every rank, expert-side layout of every rank
+    std::vector<std::vector<int64_t>> eptr(W, std::vector<int64_t>(n + 1, 0));
+    std::vector<Layout> lay(W);
+    int64_t max_token = 0, max_expert = 0;
+    for (int p = 0; p < W; ++p) {
+        for (size_t i = 0; i < n; ++i) eptr[p][i + 1] = eptr[p][i] + table[(size_t)p * n + i];
+        expert_layout(table, stored, p, E, W, lay[p]);
+        max_token = std::max(max_token, eptr[p][n]);
+        max_expert = std::max(max_expert, lay[p].total);
+    }
+    const int64_t need_rows = reverse ? max_token : max_expert;
+    if (need_rows * row_bytes > c->peer.slot_bytes || max_token >= ((int64_t)1 << 31) || max_expert >= ((int64_t)1 << 31))
+        return FMOE_PEER_UNAVAILABLE;     // same verdict on every rank: it depends on the shared table only
+
+    const int64_t token_rows = reverse ? out_rows : in_rows, expert_rows = reverse ? in_rows : out_rows;
+    if (expert_rows != lay[r].total)
+        return fail(FMOE_ERR_MISMATCH, "peer exchange: expert-side buffer has %lld rows, counts say %lld",
+                    (long long)expert_rows, (long long)lay[r].total);
+    if (token_rows < eptr[r][n])
+        return fail(FMOE_ERR_MISMATCH, "peer exchange: token-side buffer has %lld rows, counts say %lld",
+                    (long long)token_rows, (long long)eptr[r][n]);
+    FMOE_REQUIRE((in || in_rows == 0) && (out || out_rows == 0), "peer exchange: null buffer");
+    FMOE_REQUIRE((((uintptr_t)in | (uintptr_t)out) & 15) == 0, "peer exchange: buffers must be 16-byte aligned");
+    if (reverse && out_rows > eptr[r][n])
+        FMOE_CUDA_TRY(cudaMemsetAsync((char*)out + eptr[r][n] * row_bytes, 0,
+                                      (size_t)(out_rows - eptr[r][n]) * row_bytes, st));
+
+    std::vector<Seg> push, pull;
+    const int64_t* mine = table + (size_t)r * n;
+    // rows that stay here: own rows of shadowed experts, and rows for this rank's own experts
+    for (size_t idx = 0; idx < n; ++idx)
+        if ((int)(idx / E) != r && stored[idx] && mine[idx] > 0) {
+            const int64_t tok = eptr[r][idx], ex = lay[r].shadow[idx];
+            push.push_back(reverse ? Seg{kLocal, ex, tok, mine[idx]} : Seg{kLocal, tok, ex, mine[idx]});
+        }
+    for (int i = 0; i < E; ++i) {
+        const int64_t ex = lay[r].off[i + r * E];
+        if (ex < 0) continue;
+        const int64_t tok = eptr[r][r * E + i], rows = mine[r * E + i];
+        push.push_back(reverse ? Seg{kLocal, ex, tok, rows} : Seg{kLocal, tok, ex, rows});
+    }
+    for (int p = 0; p < W; ++p) {
+        if (p == r) continue;
+        for (int i = 0; i < E; ++i) {
+            // rows this rank routes to expert i of rank p
+            const int64_t out_rows_pi = mine[p * E + i];
+            if (out_rows_pi > 0 && !stored[p * E + i]) {
+                const int64_t tok = eptr[r][p * E + i], ex = lay[p].off[i + r * E];
+                if (!reverse) push.push_back({p, tok, ex, out_rows_pi});   // to p's expert-side layout
+                else pull.push_back({kLocal, tok, tok, out_rows_pi});      // back, into this rank's token-side layout
+            }
+            // rows rank p routes to expert i of this rank
+            const int64_t in_rows_pi = table[((size_t)p * W + r) * E + i];
+            if (in_rows_pi > 0 && !stored[r * E + i]) {
+                const int64_t ex = lay[r].off[i + p * E], tok = eptr[p][r * E + i];
+                if (!reverse) pull.push_back({kLocal, ex, ex, in_rows_pi});
+                else push.push_back({p, ex, tok, in_rows_pi});             // to p's token-side layout
+            }
+        }
+    }
+    c->peer.epoch += 1;
+    const int slot = (int)(c->peer.epoch & 1);
+    if (int rc = launch_phase<true>(c, push, in, out, row_bytes, slot, st)) return rc;
+    return launch_phase<false>(c, pull, nullptr, out, row_bytes, slot, st);
+}
+
+}  // namespace
+
+void peer_release(Comm* c) {
+    PeerState& ps = c->peer;
+    if (ps.slot_bytes == 0) return;
+    cudaDeviceSynchronize();
+    for (int p = 0; p < c->world && p < kMaxPeers; ++p) {
+        if (!ps.base[p]) continue;
+        if (p == c->rank) cudaFree(ps.base[p]);
+        else cudaIpcCloseMemHandle(ps.base[p]);
+        ps.base[p] = nullptr;
+    }
+    if (ps.counter) cudaFree(ps.counter);
+    ps.counter = nullptr;
+    ps.slot_bytes = 0;
+    (void)cudaGetLastError();
+}
+
+}  // namespace fmoe
+
+using namespace fmoe;
+
+extern "C" int fmoe_peer_enable(fmoe_comm_t comm, int64_t slot_bytes, fmoe_stream_t stream) {
+    FMOE_REQUIRE(comm, "peer_enable: null communicator");
+    Comm* c = (Comm*)comm;
+    FMOE_REQUIRE(slot_bytes >= 0, "peer_enable: slot_bytes=%lld", (long long)slot_bytes);
+    if (c->peer.slot_bytes) return 0;          // already on
+    if (c->world < 2 || c->world > kMaxPeers || slot_bytes == 0) return 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    const int W = c->world;
+    slot_bytes = (slot_bytes + 255) & ~(int64_t)255;
+
+    // Every step below is taken by all ranks, whatever happened before, so that the
+    // collectives match; `ok` carries this rank's verdict to the final agreement.
+    int ok = 1;
+    char* own = nullptr;
+    cudaIpcMemHandle_t handle;
+    memset(&handle, 0, sizeof(handle));
+    if (cudaMalloc((void**)&own, (size_t)kHeaderBytes + 2 * (size_t)slot_bytes) != cudaSuccess) { ok = 0; own = nullptr; }
+    if (ok && (cudaMemset(own, 0, kHeaderBytes) != cudaSuccess || cudaDeviceSynchronize() != cudaSuccess)) ok = 0;
+    if (ok && cudaIpcGetMemHandle(&handle, own) != cudaSuccess) ok = 0;
+    (void)cudaGetLastError();
+
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle is 64 bytes");
+    const size_t rec = sizeof(cudaIpcMemHandle_t) + 8;     // handle + verdict
+    char* dev_buf = nullptr;
+    FMOE_CUDA_TRY(cudaMalloc((void**)&dev_buf, rec * (W + 1)));
+    std::vector<char> host(rec * (W + 1), 0);
+    auto gather = [&](int verdict) -> int {
+        memcpy(host.data(), &handle, sizeof(handle));
+        memcpy(host.data() + sizeof(handle), &verdict, sizeof(int));
+        FMOE_CUDA_TRY(cudaMemcpyAsync(dev_buf, host.data(), rec, cudaMemcpyHostToDevice, st));
+        FMOE_NCCL_TRY(g_nccl.AllGather(dev_buf, dev_buf + rec, rec, ncclChar, c->comm, st));
+        FMOE_CUDA_TRY(cudaMemcpyAsync(host.data() + rec, dev_buf + rec, rec * W, cudaMemcpyDeviceToHost, st));
+        FMOE_CUDA_TRY(cudaStreamSynchronize(st));
+        return 0;
+    };
+    auto verdict_of = [&](int p) { int v; memcpy(&v, host.data() + rec * (p + 1) + sizeof(handle), sizeof(int)); return v; };
+    if (int rc = gather(ok)) { cudaFree(dev_buf); if (own) cudaFree(own); return rc; }
+    for (int p = 0; p < W; ++p) ok &= verdict_of(p);
+
+    char* base[kMaxPeers] = {};
+    if (ok) {
+        base[c->rank] = own;
+        for (int p = 0; p < W; ++p) {
+            if (p == c->rank) continue;
+            cudaIpcMemHandle_t h;
+            memcpy(&h, host.data() + rec * (p + 1), sizeof(h));
+            void* mapped = nullptr;
+            if (cudaIpcOpenMemHandle(&mapped, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) { ok = 0; break; }
+            base[p] = (char*)mapped;
+        }
+        (void)cudaGetLastError();
+    }
+    // second agreement: everybody mapped everybody
+    if (int rc = gather(ok)) { cudaFree(dev_buf); return rc; }
+    int all = 1;
+    for (int p = 0; p < W; ++p) all &= verdict_of(p);
+    cudaFree(dev_buf);
+    if (!all) {
+        for (int p = 0; p < W; ++p)
+            if (base[p] && p != c->rank) cudaIpcCloseMemHandle(base[p]);
+        if (own) cudaFree(own);
+        (void)cudaGetLastError();
+        return 0;                                // stays off, on every rank
+    }
+    unsigned int* counter = nullptr;
+    FMOE_CUDA_TRY(cudaMalloc((void**)&counter, 2 * sizeof(unsigned int)));
+    FMOE_CUDA_TRY(cudaMemset(counter, 0, 2 * sizeof(unsigned int)));
+    for (int p = 0; p < W; ++p) c->peer.base[p] = base[p];
+    c->peer.counter = counter;
+    c->peer.epoch = 0;
+    const char* env = getenv("FMOE_B200_PEER_TIMEOUT_MS");
+    long ms = env ? atol(env) : 20000;
+    if (ms < 1) ms = 1;
+    c->peer.timeout_ns = (unsigned long long)ms * 1000000ull;
+    c->peer.slot_bytes = slot_bytes;
+    return 0;
+}
+
+extern "C" int64_t fmoe_peer_slot_bytes(fmoe_comm_t comm) {
+    return comm ? ((Comm*)comm)->peer.slot_bytes : 0;
+}
+
+extern "C" int fmoe_peer_global_scatter(fmoe_comm_t comm, const void* local_in, void* global_out,
+                                        const int64_t* all_expert_count_host, const uint8_t* stored_models_host,
+                                        int64_t in_rows, int64_t out_rows, int64_t row_bytes, int32_t n_expert,
+                                        int32_t n_workers, fmoe_stream_t stream) {
+    return peer_move(comm, local_in, global_out, all_expert_count_host, stored_models_host, in_rows, out_rows,
+                     row_bytes, n_expert, n_workers, false, (cudaStream_t)stream);
+}
+
+extern "C" int fmoe_peer_global_gather(fmoe_comm_t comm, const void* global_in, void* local_out,
+                                       const int64_t* all_expert_count_host, const uint8_t* stored_models_host,
+                                       int64_t in_rows, int64_t out_rows, int64_t row_bytes, int32_t n_expert,
+                                       int32_t n_workers, fmoe_stream_t stream) {
+    return peer_move(comm, global_in, local_out, all_expert_count_host, stored_models_host, in_rows, out_rows,
+                     row_bytes, n_expert, n_workers, true, (cudaStream_t)stream);
+}

@@ -32,7 +32,8 @@ _DT = {torch.float32: _lib.F32, torch.float16: _lib.F16, torch.bfloat16: _lib.BF
 _KERNELS = {"expert_count": 1, "assign_pos": 4, "count_and_pos": 4, "limit_by_capacity": 1,
             "prune_gate_by_capacity": 4, "local_scatter": 1, "local_gather": 3, "local_gather_inv": 1,
             "local_gather_sum": 1, "combine_forward": 1, "combine_backward": 1, "linear_forward": 1,
-            "linear_backward": 3, "expert_exchange": 2, "generate_cached_count": 1}
+            "linear_backward": 3, "expert_exchange": 2, "generate_cached_count": 1,
+            "peer_scatter": 2, "peer_gather": 2}
 
 
 class Profile:
@@ -63,21 +64,29 @@ def set_profile(p):
     _profile = p
 
 
-def _run(name, fn, *args):
+def _check_or_unavailable(status, name):
+    if status == _lib.PEER_UNAVAILABLE:
+        return False
+    check(status, name)
+    return True
+
+
+def _run(name, fn, *args, soft=False):
+    """Calls the library; with ``soft`` a positive FMOE_PEER_UNAVAILABLE is returned as False."""
+    chk = _check_or_unavailable if soft else check
     p = _profile
     if p is None:
-        check(fn(*args), name)
-        return
+        return chk(fn(*args), name)
     p.calls[name] = p.calls.get(name, 0) + 1
     p.launches += _KERNELS.get(name, 1)
     if p.timing:
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
-        check(fn(*args), name)
+        ok = chk(fn(*args), name)
         b.record()
         p.events.append((name, a, b))
-    else:
-        check(fn(*args), name)
+        return ok
+    return chk(fn(*args), name)
 
 
 def _dtype_code(t):
@@ -251,6 +260,18 @@ def ensure_nccl(group, t):
         handle = ctypes.c_void_p()
         _run("comm_init", lib.fmoe_comm_init, ident, rank, world, dev, ctypes.byref(handle))
         _comms[dev] = handle
+        # Token rows travel by direct stores into the peers' memory where the GPUs allow it
+        # (FMOE_B200_PEER=0 keeps NCCL send/receive; FMOE_B200_PEER_SLOT_MB sizes the landing slots).
+        if world > 1 and os.environ.get("FMOE_B200_PEER", "1") != "0":
+            slot = int(os.environ.get("FMOE_B200_PEER_SLOT_MB", "256")) << 20
+            with torch.cuda.device(dev):
+                _run("peer_enable", lib.fmoe_peer_enable, handle, slot, _stream())
+
+
+def peer_slot_bytes(device):
+    """Bytes of one landing slot of the peer-memory exchange on ``device`` (0: the form is off)."""
+    c = _comms.get(device.index if device.index is not None else torch.cuda.current_device())
+    return int(lib.fmoe_peer_slot_bytes(c)) if c is not None else 0
 
 
 def comm_rank(device):
@@ -282,6 +303,8 @@ def expert_exchange(local_expert_count, n_expert, n_workers):
 
 
 def _host_i64(t):
+    if t.dtype == torch.int64 and not t.is_cuda and t.dim() == 1 and t.is_contiguous():
+        return t
     t = t.detach()
     if t.is_cuda:
         t = t.cpu()
@@ -289,6 +312,9 @@ def _host_i64(t):
 
 
 def _host_flags(t):
+    if t.dtype == torch.bool and not t.is_cuda and t.is_contiguous():
+        # same bytes as uint8
+        return t.view(torch.uint8).reshape(-1)
     t = t.detach()
     if t.is_cuda:
         t = t.cpu()
@@ -325,6 +351,31 @@ def global_gather(output_buf, local_expert_count, global_expert_count, stored_mo
     """Inverse of global_scatter (cuda/global_exchange.cu:54-80)."""
     return _global_move(lib.fmoe_global_gather, "global_gather", output_buf, local_expert_count,
                         global_expert_count, stored_models, batch_size, n_workers)
+
+
+def _peer_move(fn, name, buf, table, stored_models, batch_size, n_expert, n_workers):
+    _check_cuda(buf)
+    tab, st = _host_i64(table.reshape(-1)), _host_flags(stored_models)
+    assert tab.numel() == n_workers * n_workers * n_expert
+    out = buf.new_empty((batch_size, buf.shape[1]))
+    with torch.cuda.device(buf.device):
+        ok = _run(name, fn, _comm(buf.device), _ptr(buf), _ptr(out), _ptr(tab), _ptr(st), buf.shape[0], batch_size,
+                  buf.shape[1] * buf.element_size(), n_expert, n_workers, _stream(), soft=True)
+    return out if ok else None
+
+
+def peer_global_scatter(input_buf, all_expert_count, stored_models, batch_size, n_expert, n_workers):
+    """global_scatter by direct stores into the peers' memory; ``all_expert_count`` is the host table
+    [W, W, E] of expert_exchange.  Returns None (nothing queued, on every rank alike) when that form
+    cannot serve the call; the caller then uses global_scatter."""
+    return _peer_move(lib.fmoe_peer_global_scatter, "peer_scatter", input_buf, all_expert_count, stored_models,
+                      batch_size, n_expert, n_workers)
+
+
+def peer_global_gather(output_buf, all_expert_count, stored_models, batch_size, n_expert, n_workers):
+    """Inverse of peer_global_scatter; same contract."""
+    return _peer_move(lib.fmoe_peer_global_gather, "peer_gather", output_buf, all_expert_count, stored_models,
+                      batch_size, n_expert, n_workers)
 
 
 def exchange_cache_info(sent_models, num_expert, world_size):

@@ -8,6 +8,7 @@ Where the reference copies five count vectors to the host per forward
 (fmoe/functions.py:64-68), this module needs none at world_size 1 and one
 (the all-gathered count table, a few KB) otherwise.
 """
+import numpy as np
 import torch
 from torch.autograd import Function
 
@@ -80,28 +81,55 @@ def count_by_gate(gate, num_expert, world_size, require_pos=True):
 
 class Routing:
     """Everything the layer derives from the gate indices for one forward."""
-    __slots__ = ("pos", "inv", "lec_dev", "offsets_dev", "n_rows", "lec", "gec", "aec", "agec", "rank")
+    __slots__ = ("pos", "inv", "lec_dev", "offsets_dev", "own_offsets_dev", "n_rows", "n_recv", "lec", "gec",
+                 "own_counts", "_aec", "_agec", "rank")
+
+    @property
+    def aec(self):
+        """all_expert_count [W, W, E] on the host: [source worker, destination worker, expert]."""
+        return self._aec
+
+    @property
+    def agec(self):
+        """all_global_expert_count [W, W, E] on the host (built on first use: only a shadowing policy reads it)."""
+        if self._agec is None and self._aec is not None:
+            self._agec = self._aec.transpose(0, 1).contiguous()
+        return self._agec
 
 
 def route(gate, num_expert, world_size):
-    """Bucketing + count exchange with at most one device-to-host copy."""
+    """Bucketing + count exchange with at most one device-to-host copy.
+
+    Everything that needs only device data (the positions, the offsets of this
+    worker's experts in the received buffer) is queued before the host waits for
+    the count table, and the host-side slicing after the wait is a few numpy
+    views, so the GPU idles as briefly as possible around the one sync."""
     r = Routing()
+    r._aec = r._agec = None
     with torch.no_grad():
         flat = gate.reshape(-1)
         n_tot = num_expert * world_size
         r.lec_dev, r.offsets_dev, r.pos, r.inv = fmoe_cuda.count_and_pos(flat, n_tot)
         if world_size == 1:
             r.n_rows = flat.numel()
-            r.lec = r.gec = r.aec = r.agec = None
+            r.lec = r.gec = r.own_offsets_dev = r.own_counts = None
             r.rank = 0
             return r
         aec, _, _ = fmoe_cuda.expert_exchange(r.lec_dev, num_expert, world_size)
         r.rank, _ = fmoe_cuda.comm_rank(gate.device)
-        r.aec = aec.cpu()
-        r.agec = r.aec.transpose(0, 1).contiguous()
-        r.lec = r.aec[r.rank].reshape(-1).contiguous()
-        r.gec = r.agec[r.rank].reshape(-1).contiguous()
-        r.n_rows = int(r.lec.sum())
+        # rows of this worker's expert e sit together in the received buffer (all sources)
+        own = aec[:, r.rank, :].sum(dim=0)
+        r.own_offsets_dev = torch.zeros(num_expert + 1, dtype=torch.int64, device=gate.device)
+        torch.cumsum(own, 0, out=r.own_offsets_dev[1:])
+        r._aec = aec.cpu()                      # the one sync of the forward pass
+        table = r._aec.numpy()
+        lec = table[r.rank].reshape(-1)
+        gec = np.ascontiguousarray(table[:, r.rank, :]).reshape(-1)
+        r.n_rows = int(lec.sum())
+        r.n_recv = int(gec.sum())
+        r.lec = torch.from_numpy(lec)
+        r.gec = torch.from_numpy(gec)
+        r.own_counts = torch.from_numpy(gec.reshape(world_size, num_expert).sum(axis=0))
     return r
 
 
@@ -293,8 +321,7 @@ class MOEScatterFused(Function):
         ctx.exch, ctx.top_k, ctx.n_tokens, ctx.n_rows = exch, top_k, inp.shape[0], n_rows
         ctx.save_for_backward(inv)
         if exch is not None:
-            buf = fmoe_cuda.global_scatter(buf, exch.lec, exch.gec, exch.stored, exch.fwd_batch_size,
-                                           exch.world_size)
+            buf = exch.scatter(buf, exch.fwd_batch_size)
         return buf
 
     @staticmethod
@@ -303,8 +330,7 @@ class MOEScatterFused(Function):
         grad_buf = grad_buf.contiguous()
         exch = ctx.exch
         if exch is not None:
-            grad_buf = fmoe_cuda.global_gather(grad_buf, exch.lec, exch.gec, exch.stored, ctx.n_rows,
-                                               exch.world_size)
+            grad_buf = exch.gather(grad_buf, ctx.n_rows)
         grad_inp = fmoe_cuda.local_gather_sum(grad_buf, inv, ctx.n_tokens, ctx.top_k)
         return grad_inp, None, None, None, None, None
 
@@ -319,7 +345,7 @@ class MOEGatherCombine(Function):
         buf = buf.contiguous()
         ctx.exch, ctx.global_rows = exch, buf.shape[0]
         if exch is not None:
-            buf = fmoe_cuda.global_gather(buf, exch.lec, exch.gec, exch.stored, n_rows, exch.world_size)
+            buf = exch.gather(buf, n_rows)
         score_c = score.contiguous().to(buf.dtype)
         ctx.save_for_backward(buf, inv, score_c)
         ctx.score_dtype = score.dtype
@@ -332,20 +358,43 @@ class MOEGatherCombine(Function):
                                                           need_score_grad=ctx.needs_input_grad[2])
         exch = ctx.exch
         if exch is not None:
-            grad_buf = fmoe_cuda.global_scatter(grad_buf, exch.lec, exch.gec, exch.stored, ctx.global_rows,
-                                                exch.world_size)
+            grad_buf = exch.scatter(grad_buf, ctx.global_rows)
         if grad_score is not None:
             grad_score = grad_score.to(ctx.score_dtype)
         return grad_buf, None, grad_score, None, None
 
 
 class Exchange:
-    """Host-side description of one layer call's all-to-all-v."""
-    __slots__ = ("lec", "gec", "stored", "fwd_batch_size", "world_size")
+    """Host-side description of one layer call's all-to-all-v.
 
-    def __init__(self, lec, gec, stored, fwd_batch_size, world_size):
+    ``table`` is the all-gathered count table [W, W, E] on the host (or None); with
+    it the rows travel by direct stores into the peers' memory when the library
+    has that form enabled, else over NCCL."""
+    __slots__ = ("lec", "gec", "stored", "fwd_batch_size", "world_size", "table", "num_expert")
+
+    def __init__(self, lec, gec, stored, fwd_batch_size, world_size, table=None):
         self.lec, self.gec, self.stored = lec, gec, stored
         self.fwd_batch_size, self.world_size = fwd_batch_size, world_size
+        self.table = table.reshape(-1) if table is not None else None
+        self.num_expert = lec.numel() // world_size
+
+    def scatter(self, buf, out_rows):
+        """Token-side rows -> expert-side rows on the experts' owners."""
+        if self.table is not None:
+            out = fmoe_cuda.peer_global_scatter(buf, self.table, self.stored, out_rows, self.num_expert,
+                                                self.world_size)
+            if out is not None:
+                return out
+        return fmoe_cuda.global_scatter(buf, self.lec, self.gec, self.stored, out_rows, self.world_size)
+
+    def gather(self, buf, out_rows):
+        """Expert-side rows -> token-side rows on the tokens' owners."""
+        if self.table is not None:
+            out = fmoe_cuda.peer_global_gather(buf, self.table, self.stored, out_rows, self.num_expert,
+                                               self.world_size)
+            if out is not None:
+                return out
+        return fmoe_cuda.global_gather(buf, self.lec, self.gec, self.stored, out_rows, self.world_size)
 
 
 _ACT_CODES = {"none": _lib.ACT_NONE, "relu": _lib.ACT_RELU, "gelu": _lib.ACT_GELU}

@@ -48,6 +48,16 @@ def mark_module_parallel_comm(module, comm):
         setattr(p, "dp_comm", comm)
 
 
+_no_shadow = {}
+
+
+def _no_shadow_flags(world_size, num_expert):
+    key = (world_size, num_expert)
+    if key not in _no_shadow:
+        _no_shadow[key] = torch.zeros(world_size, num_expert, dtype=torch.bool)
+    return _no_shadow[key]
+
+
 def _shadow_plan(policy_fn, routing, experts, num_expert, world_size, d_model, fused, shadows):
     """Runs the shadowing policy on the count tables and makes sure a module exists
     for every shadowed worker.  Returns (stored [W,E] bool CPU, stored_workers [W])."""
@@ -96,20 +106,35 @@ def _fmoe_general_global_forward(inp, gate, expert_fn, policy_fn, experts, num_e
         n_rows = routing.n_rows
     else:
         shadows = {} if shadows is None else shadows
-        stored, workers = _shadow_plan(policy_fn, routing, experts, num_expert, world_size,
-                                       inp.shape[1], fused, shadows)
-        fwd_count = cached_count_host(routing.lec.clone(), routing.gec.clone(), stored, routing.rank,
-                                      num_expert, world_size)
-        fwd_batch_size = int(fwd_count.sum())
-        models = [[] for _ in range(world_size)]
-        for j in range(world_size):
-            if j == routing.rank:
-                models[j] = [experts] if fused else experts
-            elif bool(workers[j]):
-                models[j] = [shadows[j]] if fused else shadows[j]
-        if bool(workers.any()):
+        if policy_fn is None or getattr(policy_fn, "never_shadows", False):
+            # No shadowing: every row goes to its expert's owner; nothing else to plan on the host.
+            stored, any_shadow = _no_shadow_flags(world_size, num_expert), False
+            if fused:
+                fwd_count = ExpertCounts(routing.own_offsets_dev, routing.own_counts)
+            else:
+                fwd_count = torch.zeros(world_size, num_expert, dtype=torch.int64)
+                fwd_count[routing.rank] = routing.own_counts
+                fwd_count = fwd_count.reshape(-1)
+            fwd_batch_size = routing.n_recv
+            models = [[] for _ in range(world_size)]
+            models[routing.rank] = [experts] if fused else experts
+        else:
+            stored, workers = _shadow_plan(policy_fn, routing, experts, num_expert, world_size,
+                                           inp.shape[1], fused, shadows)
+            any_shadow = bool(workers.any())
+            fwd_count = cached_count_host(routing.lec.clone(), routing.gec.clone(), stored, routing.rank,
+                                          num_expert, world_size)
+            fwd_batch_size = int(fwd_count.sum())
+            models = [[] for _ in range(world_size)]
+            for j in range(world_size):
+                if j == routing.rank:
+                    models[j] = [experts] if fused else experts
+                elif bool(workers[j]):
+                    models[j] = [shadows[j]] if fused else shadows[j]
+        if any_shadow:
             inp = MOECache.apply(inp, workers, experts, shadows, world_size, routing.rank)
-        exch = Exchange(routing.lec, routing.gec, stored.reshape(-1), fwd_batch_size, world_size)
+        exch = Exchange(routing.lec, routing.gec, stored.reshape(-1), fwd_batch_size, world_size,
+                        table=routing.aec)
         n_rows = routing.n_rows
         if enable_fuse:
             from .fused_functions import MOEForward, fused_activation
@@ -178,8 +203,10 @@ class FMoE(nn.Module):
         r"""Runs the experts over a buffer laid out worker by worker, expert by expert
         (fmoe/layers.py:222-255).  ``models[j]`` holds worker j's experts (own or
         shadowed) or is empty."""
-        if isinstance(fwd_expert_count, ExpertCounts) and self.experts_fused and len(models) == 1:
-            return models[0][0](inp, fwd_expert_count)
+        if isinstance(fwd_expert_count, ExpertCounts) and self.experts_fused:
+            present = [m for m in models if m]
+            if len(present) == 1:
+                return present[0][0](inp, fwd_expert_count)
         counts_all = (fwd_expert_count.host_counts() if isinstance(fwd_expert_count, ExpertCounts)
                       else fwd_expert_count.cpu()).view(-1, num_expert)
         res, ptr = [], 0

@@ -86,6 +86,7 @@ def _gen_policy(alpha, constants=None):
 
     if os.environ.get("FMOE_ENABLE_DYNREP", "0") == "1":
         return _global_policy
+    _no_policy.never_shadows = True      # lets the layer skip the shadowing plan altogether
     return _no_policy
 
 

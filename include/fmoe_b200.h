@@ -48,7 +48,8 @@ const char* fmoe_last_error_string(void);
 int fmoe_version(void);
 int fmoe_built_for_sm(void);
 /* Reads the status word that the tensor-core kernels raise when one of their
- * bounded waits expires (0 = none; 1..4 = which wait).  Copies from the device,
+ * bounded waits expires (0 = none; 1..4 = which wait; bits 16 and 32: waits of
+ * the peer-memory exchange).  Copies from the device,
  * so it waits for the work queued before it.  No counterpart in the reference. */
 int fmoe_device_status(int32_t* status_out);
 
@@ -299,6 +300,41 @@ int fmoe_global_gather(fmoe_comm_t comm, const void* global_in, void* local_out,
                        const uint8_t* stored_models_host, int64_t in_rows,
                        int64_t out_rows, int64_t row_bytes, int32_t n_expert,
                        int32_t n_workers, void* staging, fmoe_stream_t stream);
+
+/* Peer-memory form of the two exchanges above (no counterpart in the reference,
+ * which always goes through ncclSend/ncclRecv, cuda/global_exchange.cuh:75-124):
+ * rows are stored straight into the destination GPU's memory over NVLink by a copy
+ * kernel and published with flags; no NCCL call is made.
+ *
+ * fmoe_peer_enable is collective over the communicator: every rank allocates a
+ * landing area of 2 slots of slot_bytes (+4 KiB of flags), the ranks swap CUDA IPC
+ * handles and map each other's areas.  If any rank cannot (no peer access, IPC
+ * closed to the process), the form stays off on every rank and FMOE_OK is
+ * returned; fmoe_peer_slot_bytes then reports 0.
+ *
+ * fmoe_peer_global_scatter / _gather take all_expert_count_host[W][W][E] (rows that
+ * rank s routes to expert e of rank d at [s][d][e]; the table fmoe_expert_exchange
+ * gathers), because each rank needs the layout of every other rank's buffer, and
+ * because the decision to use this form must be the same everywhere: they return
+ * FMOE_PEER_UNAVAILABLE, having queued nothing, when the form is off, row_bytes is
+ * not a multiple of 16 or some rank would need more than one slot; the caller then
+ * uses fmoe_global_scatter / _gather.  Buffers, row counts and stored_models_host
+ * mean what they mean there.  Waits on other ranks are bounded
+ * (FMOE_B200_PEER_TIMEOUT_MS, default 20000): an expired wait raises bit 16 or 32
+ * of fmoe_device_status. */
+#define FMOE_PEER_UNAVAILABLE 1
+int fmoe_peer_enable(fmoe_comm_t comm, int64_t slot_bytes, fmoe_stream_t stream);
+int64_t fmoe_peer_slot_bytes(fmoe_comm_t comm);
+int fmoe_peer_global_scatter(fmoe_comm_t comm, const void* local_in, void* global_out,
+                             const int64_t* all_expert_count_host,
+                             const uint8_t* stored_models_host, int64_t in_rows,
+                             int64_t out_rows, int64_t row_bytes, int32_t n_expert,
+                             int32_t n_workers, fmoe_stream_t stream);
+int fmoe_peer_global_gather(fmoe_comm_t comm, const void* global_in, void* local_out,
+                            const int64_t* all_expert_count_host,
+                            const uint8_t* stored_models_host, int64_t in_rows,
+                            int64_t out_rows, int64_t row_bytes, int32_t n_expert,
+                            int32_t n_workers, fmoe_stream_t stream);
 
 /* exchange_cache_info(sent_models, num_expert, world_size):
  * cuda/fmoe_cuda.cpp:24-27, cuda/global_exchange.cuh:232-249.  All-gather of

@@ -1,4 +1,5 @@
 """Rank bodies of the multi-process tests (spawned by test_dist_gpu.py / test_dist_cpu.py)."""
+import ctypes
 import os
 import sys
 
@@ -45,6 +46,7 @@ def gpu_exchange(rank, world, port):
     init(rank, world, port, "nccl")
     from fastermoe_b200 import fmoe_cuda as fc
     dev = torch.device("cuda", rank)
+    os.environ.setdefault("FMOE_B200_PEER_TIMEOUT_MS", "4000")    # a protocol error should fail fast here
     fc.ensure_nccl(None, torch.zeros(1, device=dev))
     E, d = 3, 40
     lecs = all_lecs(world, E, 5)
@@ -67,6 +69,23 @@ def gpu_exchange(rank, world, port):
                                     torch.from_numpy(stored), mine.shape[0], world)
             assert torch.equal(back, mine), "global_gather is not the inverse"
         os.environ["FMOE_B200_EXCHANGE"] = ""
+        # the same exchange by direct stores into the peers' memory; several rounds reuse both landing slots
+        if fc.peer_slot_bytes(dev) > 0:
+            table = torch.from_numpy(aec_w.copy())
+            for rnd in range(5):
+                for dtype in (torch.float32, torch.bfloat16):
+                    mine = (torch.from_numpy(bufs[rank]).to(dev) + rnd).to(dtype)
+                    out = fc.peer_global_scatter(mine, table, torch.from_numpy(stored), want[rank].shape[0], E, world)
+                    assert out is not None, "peer form refused a call it can serve"
+                    assert torch.equal(out, (torch.from_numpy(want[rank]).to(dev) + rnd).to(dtype)), "peer scatter layout"
+                    back = fc.peer_global_gather(out, table, torch.from_numpy(stored), mine.shape[0] + 2, E, world)
+                    assert torch.equal(back[:-2], mine) and not back[-2:].any(), "peer gather is not the inverse"
+            odd = torch.zeros(int(lecs[rank].sum()), 3, device=dev)        # 12-byte rows: not served, on any rank
+            assert fc.peer_global_scatter(odd, table, torch.from_numpy(stored), want[rank].shape[0], E, world) is None
+            st = ctypes.c_int32(-1)
+            assert fc.lib.fmoe_device_status(ctypes.byref(st)) == 0 and st.value == 0, f"device status {st.value}"
+        else:
+            print(f"[rank {rank}] peer-memory exchange is off on this machine; NCCL form only", flush=True)
         cc = fc.generate_cached_count(torch.from_numpy(lecs[rank]).to(dev).view(world, E),
                                       torch.from_numpy(gecs[rank]).to(dev).view(world, E),
                                       torch.from_numpy(stored).to(dev).view(world, E), E, world)
