@@ -242,51 +242,90 @@ __host__ __device__ constexpr uint32_t make_idesc(bool bf16, bool a_mn, bool b_m
            ((b_mn ? 1u : 0u) << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
-// GELU and its derivative for the 16-bit epilogues.  Phi(x) = 1 - D(|x|/sqrt2)^-16 / 2
-// with the degree-6 polynomial D of Abramowitz-Stegun 7.1.28 (coefficients below are
-// already scaled to take |x|); the derivative of that form gives the density term.
-// One reciprocal per element, no exponential.  Absolute error: 7e-7 (value), 1.5e-6
-// (derivative), far below bf16/fp16 resolution.
-#define FMOE_D1 0.04986734616f
-#define FMOE_D2 0.02114100615f
-#define FMOE_D3 0.00327762621f
-#define FMOE_D4 0.0000380035750f
-#define FMOE_D5 0.0000488906318f
-#define FMOE_D6 0.0000053829750f
+// ---- packed fp32 arithmetic ----------------------------------------------------
+// sm_100 executes add/mul/fma on two fp32 values held in one 64-bit register pair
+// (fma.rn.f32x2 ...).  The epilogues are bound by instruction issue (two epilogue warps
+// per scheduler), so they do their per-element math on column pairs.
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 pk(float lo, float hi) {
+    f32x2 r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ f32x2 pk1(float c) { return pk(c, c); }
+__device__ __forceinline__ void unpk(f32x2 v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
+    f32x2 d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
+    f32x2 d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) {
+    f32x2 d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
 __device__ __forceinline__ float rcp_approx(float d) {
     float r;
     asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(d));
     return r;
 }
-__device__ __forceinline__ float gelu_fast(float x) {
-    const float ax = fabsf(x);
-    float d = fmaf(FMOE_D6, ax, FMOE_D5);
-    d = fmaf(d, ax, FMOE_D4); d = fmaf(d, ax, FMOE_D3); d = fmaf(d, ax, FMOE_D2); d = fmaf(d, ax, FMOE_D1);
-    d = fmaf(d, ax, 1.f);
-    float r = rcp_approx(d);
-    r *= r; r *= r; r *= r; r *= r;  // D^-16
-    return fmaf(-0.5f * ax, r, fmaxf(x, 0.f));
+__device__ __forceinline__ float ex2_approx(float d) {
+    float r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(d));
+    return r;
 }
-// Value and derivative together (they share the polynomial and the reciprocal).
-__device__ __forceinline__ void gelu_both_fast(float x, float& val, float& grad) {
-    const float ax = fabsf(x);
-    float d = fmaf(FMOE_D6, ax, FMOE_D5);
-    d = fmaf(d, ax, FMOE_D4); d = fmaf(d, ax, FMOE_D3); d = fmaf(d, ax, FMOE_D2); d = fmaf(d, ax, FMOE_D1);
-    d = fmaf(d, ax, 1.f);
-    float dp = fmaf(6.f * FMOE_D6, ax, 5.f * FMOE_D5);
-    dp = fmaf(dp, ax, 4.f * FMOE_D4); dp = fmaf(dp, ax, 3.f * FMOE_D3); dp = fmaf(dp, ax, 2.f * FMOE_D2);
-    dp = fmaf(dp, ax, FMOE_D1);
-    const float r = rcp_approx(d);
-    float r16 = r * r; r16 *= r16; r16 *= r16; r16 *= r16;
-    const float tail = 0.5f * r16;
-    val = fmaf(-ax, tail, fmaxf(x, 0.f));
-    const float cdf = x >= 0.f ? 1.f - tail : tail;
-    grad = fmaf(x, 8.f * r16 * r * dp, cdf);
+
+// GELU (exact, erf form) and its derivative for the 16-bit epilogues, on a column pair.
+//   Phi(x)  = 1/2 + sign(x) (1/2 - T(|x|)),   T(a) = erfc(a / sqrt 2) / 2
+//   T(a)    = (b1 t + ... + b5 t^5) exp(-a^2 / 2),   t = 1 / (1 + p a / sqrt 2)
+// is Abramowitz-Stegun 7.1.26 (|error| of erf <= 1.5e-7) with the halving folded into
+// the coefficients.  The exponential is the one the density needs, so value and
+// derivative  gelu'(x) = Phi(x) + x exp(-x^2/2) / sqrt(2 pi)  share everything:
+// two special-function instructions and ~10 packed operations per pair.  Absolute
+// error 5e-7 (value), 3e-7 (derivative): far below bf16/fp16 resolution.
+template <bool GRAD>
+__device__ __forceinline__ void gelu_pair(f32x2 x, f32x2& val, f32x2& grad) {
+    const f32x2 ax = x & 0x7fffffff7fffffffull;
+    float d0, d1, u0, u1;
+    unpk(fma2(ax, pk1(0.23164189f), pk1(1.f)), d0, d1);
+    const f32x2 t = pk(rcp_approx(d0), rcp_approx(d1));
+    unpk(mul2(mul2(x, pk1(-0.72134752f)), x), u0, u1);          // -x^2/2 in base 2
+    const f32x2 e = pk(ex2_approx(u0), ex2_approx(u1));
+    f32x2 q = fma2(pk1(0.5307027145f), t, pk1(-0.7265760135f));
+    q = fma2(q, t, pk1(0.7107068705f));
+    q = fma2(q, t, pk1(-0.142248368f));
+    q = fma2(q, t, pk1(0.127414796f));
+    const f32x2 tail = mul2(mul2(q, t), e);
+    const f32x2 inner = fma2(tail, pk1(-1.f), pk1(0.5f));         // 1/2 - T >= 0
+    const f32x2 cdf = add2(inner | (x & 0x8000000080000000ull), pk1(0.5f));
+    val = mul2(x, cdf);
+    if (GRAD) grad = fma2(mul2(x, pk1(0.39894228f)), e, cdf);
+}
+__device__ __forceinline__ float gelu_fast(float x) {
+    f32x2 v, g;
+    gelu_pair<false>(pk(x, x), v, g);
+    float lo, hi;
+    unpk(v, lo, hi);
+    return lo;
 }
 __device__ __forceinline__ float act_fast(float v, int act) {
     if (act == FMOE_ACT_RELU) return v > 0.f ? v : 0.f;
     if (act == FMOE_ACT_GELU) return gelu_fast(v);
     return v;
+}
+// Two 16-bit values of one 32-bit word as a packed fp32 pair.
+template <bool BF16> __device__ __forceinline__ f32x2 cvt_in2(uint32_t w) {
+    if (BF16) return pk(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+    const __half2 h = *reinterpret_cast<const __half2*>(&w);
+    const float2 f = __half22float2(h);
+    return pk(f.x, f.y);
 }
 template <bool BF16> __device__ __forceinline__ float cvt_in(uint16_t raw) {
     if (BF16) return __uint_as_float((uint32_t)raw << 16);
@@ -622,8 +661,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                                 const uint32_t w[4] = {aq[q].x, aq[q].y, aq[q].z, aq[q].w};
 #pragma unroll
                                 for (int i = 0; i < 4; ++i) {
-                                    v[q * 8 + 2 * i] += cvt_in<BF16>((uint16_t)(w[i] & 0xffff));
-                                    v[q * 8 + 2 * i + 1] += cvt_in<BF16>((uint16_t)(w[i] >> 16));
+                                    const f32x2 sum = add2(pk(v[q * 8 + 2 * i], v[q * 8 + 2 * i + 1]), cvt_in2<BF16>(w[i]));
+                                    unpk(sum, v[q * 8 + 2 * i], v[q * 8 + 2 * i + 1]);
                                 }
                             }
                         }
@@ -633,19 +672,42 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                             for (int q = 0; q < NCH; ++q) {
                                 float g[8];
 #pragma unroll
-                                for (int i = 0; i < 8; ++i) gelu_both_fast(v[q * 8 + i], v[q * 8 + i], g[i]);
+                                for (int i = 0; i < 4; ++i) {
+                                    f32x2 val, grad;
+                                    gelu_pair<true>(pk(v[q * 8 + 2 * i], v[q * 8 + 2 * i + 1]), val, grad);
+                                    unpk(val, v[q * 8 + 2 * i], v[q * 8 + 2 * i + 1]);
+                                    unpk(grad, g[2 * i], g[2 * i + 1]);
+                                }
                                 stage[stage_slot(lane, q)] =
                                     make_uint4(cvt_pack<BF16>(g[0], g[1]), cvt_pack<BF16>(g[2], g[3]),
                                                cvt_pack<BF16>(g[4], g[5]), cvt_pack<BF16>(g[6], g[7]));
                             }
                             __syncwarp();
                             stage_store(stage, lane, (uint16_t*)p.pre_out + (row_off + quarter * 32) * ld + col_lo + c * CW, ld, rows_here);
+                        } else if (p.act == FMOE_ACT_GELU) {
+#pragma unroll
+                            for (int i = 0; i < CW / 2; ++i) {
+                                f32x2 val, grad;
+                                gelu_pair<false>(pk(v[2 * i], v[2 * i + 1]), val, grad);
+                                unpk(val, v[2 * i], v[2 * i + 1]);
+                            }
                         } else if (p.act != FMOE_ACT_NONE) {
 #pragma unroll
                             for (int i = 0; i < CW; ++i) v[i] = act_fast(v[i], p.act);
                         }
                     } else if (MODE == MODE_DGRAD) {
-                        if (p.act_pre) {
+                        if (p.act_pre && p.act == FMOE_ACT_GELU) {
+                            // the forward saved gelu'(pre-activation)
+#pragma unroll
+                            for (int q = 0; q < NCH; ++q) {
+                                const uint32_t w[4] = {aq[q].x, aq[q].y, aq[q].z, aq[q].w};
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) {
+                                    const f32x2 prod = mul2(pk(v[q * 8 + 2 * i], v[q * 8 + 2 * i + 1]), cvt_in2<BF16>(w[i]));
+                                    unpk(prod, v[q * 8 + 2 * i], v[q * 8 + 2 * i + 1]);
+                                }
+                            }
+                        } else if (p.act_pre) {
 #pragma unroll
                             for (int q = 0; q < NCH; ++q) {
                                 const uint32_t w[4] = {aq[q].x, aq[q].y, aq[q].z, aq[q].w};
@@ -662,8 +724,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                             const uint32_t w[4] = {aq[q].x, aq[q].y, aq[q].z, aq[q].w};
 #pragma unroll
                             for (int i = 0; i < 4; ++i) {
-                                v[q * 8 + 2 * i] += cvt_in<BF16>((uint16_t)(w[i] & 0xffff));
-                                v[q * 8 + 2 * i + 1] += cvt_in<BF16>((uint16_t)(w[i] >> 16));
+                                const f32x2 sum = add2(pk(v[q * 8 + 2 * i], v[q * 8 + 2 * i + 1]), cvt_in2<BF16>(w[i]));
+                                unpk(sum, v[q * 8 + 2 * i], v[q * 8 + 2 * i + 1]);
                             }
                         }
                     }
