@@ -193,6 +193,14 @@ __device__ __forceinline__ void tma_load_2d(const CUtensorMap* map, unsigned lon
         ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
         : "memory");
 }
+// Pair form: the bytes land in this CTA's shared memory, the completion is counted on a
+// barrier that may live in the other CTA of the pair (bar_cluster: shared::cluster address).
+__device__ __forceinline__ void tma_load_2d_pair(const CUtensorMap* map, uint32_t bar_cluster, void* dst, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(bar_cluster), "r"(x), "r"(y)
+        : "memory");
+}
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_commit(unsigned long long* bar) {
@@ -411,6 +419,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     const __grid_constant__ HostSegs hs, const Params p) {
     using C = Cfg<CTA2>;
     constexpr int STAGES = C::STAGES, STAGE_BYTES = C::STAGE_BYTES, TILE_M = C::TILE_M, B_COLS = C::B_COLS;
+    // Pairs, forward and input gradient: TMA completions of both CTAs go straight to the
+    // leader's barriers.  The weight gradient keeps the relay (each CTA patches the ragged
+    // tail of its own operands after they land, so it must see its own completions).
+    constexpr bool DIRECT = CTA2 && MODE != MODE_WGRAD;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     Shared* sh = (Shared*)(tiles + RING_BYTES + EPI_WARPS * STAGING_BYTES);
@@ -483,6 +495,23 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     if (!(ok = mbar_wait(&sh->empty[s], ph ^ 1, sh, p.status, 1))) break;
                     uint8_t* a_dst = tiles + s * STAGE_BYTES;
                     uint8_t* b_dst = a_dst + A_BYTES;
+                    if (DIRECT) {
+                        // Both CTAs' bytes are counted on the leader's barrier, which the MMA
+                        // issuer waits on: no relay through the other CTA's warps.
+                        const uint32_t bar = map_to_cta(&sh->full[s], 0);
+                        if (cta == 0) mbar_expect_tx(&sh->full[s], 2 * STAGE_BYTES);
+                        tma_load_2d_pair(&map_a, bar, a_dst, ch * BK, t.row0 + my_row);
+                        if (MODE == MODE_FWD) {
+                            tma_load_2d_pair(&map_b, bar, b_dst, ch * BK, t.e * p.w_rows + t.col0 + my_col);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < B_COLS / 64; ++j)
+                                tma_load_2d_pair(&map_b, bar, b_dst + j * SUB_BYTES, t.col0 + my_col + j * 64,
+                                                 t.e * p.w_rows + ch * BK);
+                        }
+                        if (++s == STAGES) { s = 0; ph ^= 1; }
+                        continue;
+                    }
                     mbar_expect_tx(&sh->full[s], STAGE_BYTES);
                     if (MODE == MODE_FWD) {
                         tma_load_2d(&map_a, &sh->full[s], a_dst, ch * BK, t.row0 + my_row);
@@ -523,6 +552,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             Tile t;
             locate<MODE, TILE_M>(sh, p, tile, e_cur, t);
             if (t.chunks == 0) continue;
+            if (DIRECT && !leader) continue;
             if (leader) {
                 if (!(ok = mbar_wait_cluster(&sh->tmem_empty[acc], acc_ph ^ 1, sh, p.status, 2))) break;
                 tc_fence_after();
@@ -560,7 +590,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     if (++s == STAGES) { s = 0; ph ^= 1; }
                     continue;
                 }
-                if (CTA2) {
+                if (CTA2 && !DIRECT) {
                     if (!(ok = mbar_wait_cluster(&sh->peer_ready[s], ph, sh, p.status, 5))) break;
                     tc_fence_after();
                 }
@@ -814,12 +844,26 @@ int* status_ptr() {
 
 const HostSegs kNoSegs = {};
 
-// FMOE_B200_GEMM=pair selects the CTA-pair (cta_group::2) kernel.  It moves a third
-// fewer operand bytes per flop, but on ragged expert segments its 256-row tiles waste
-// more rows and it measured slightly slower than one CTA per tile, so it is opt-in.
-bool pair_kernel_enabled() {
+// One CTA per 128x256 tile, or a pair of CTAs (cta_group::2) per 256x256 tile.  A pair
+// pulls a third fewer operand bytes per flop through each SM's L2 port, which is what
+// bounds the one-CTA kernel once the epilogue's stores share that port; on the other hand
+// its 256-row tiles waste more rows at the ragged end of each expert's segment and its
+// weight-gradient form still relays operand arrival through the second CTA.  Default:
+// pairs for the forward and input-gradient products when segments are long and there is
+// work for every pair; FMOE_B200_GEMM=pair / tc1 forces one form for all products.
+enum { FORM_AUTO = 0, FORM_PAIR = 1, FORM_SINGLE = 2 };
+int forced_form() {
     const char* p = getenv("FMOE_B200_GEMM");
-    return p && p[0] == 'p';
+    if (p && p[0] == 'p') return FORM_PAIR;
+    if (p && p[0] == 't') return FORM_SINGLE;
+    return FORM_AUTO;
+}
+bool use_pairs(int mode, int64_t n_rows, int n_expert, int64_t n_out) {
+    const int form = forced_form();
+    if (form == FORM_PAIR) return n_rows >= 2048;
+    if (form == FORM_SINGLE || mode == MODE_WGRAD) return false;
+    const int64_t pair_tiles = ceil_div(n_rows, 256) * ceil_div(n_out, BN);
+    return n_rows >= (int64_t)512 * n_expert && pair_tiles >= 2 * (sm_count() / 2);
 }
 
 template <int MODE, bool CTA2>
@@ -968,7 +1012,7 @@ int tc_linear_forward(const LinearArgs& a, cudaStream_t st) {
     if (int rc = make_map(&ma, a.x, a.n_rows, a.in_feat, BM, bf16)) return rc;
     // Pairs of CTAs (256-row tiles) once there is enough work for them; each CTA of a
     // pair stages 128 of the tile's 256 weight rows.
-    const bool pair = pair_kernel_enabled() && a.n_rows >= 2048;
+    const bool pair = use_pairs(MODE_FWD, a.n_rows, a.n_expert, a.out_feat);
     if (int rc = make_map(&mb, a.weight, (int64_t)a.n_expert * a.out_feat, a.in_feat, pair ? 128 : BN, bf16)) return rc;
     Params p{};
     p.seg = a.seg_offsets; p.n_expert = a.n_expert; p.n_out = (int)a.out_feat; p.n_contr = (int)a.in_feat;
@@ -1006,8 +1050,6 @@ int side_stream(SideStream** out) {
 
 int tc_linear_backward(const LinearBwdArgs& a, cudaStream_t st) {
     const bool bf16 = a.dtype == FMOE_BF16;
-    const bool pair = pair_kernel_enabled() && a.n_rows >= 2048;
-    const int tile_m = pair ? 256 : BM;
     SideStream* side = nullptr;
     const bool overlap_bias = a.grad_b && (a.grad_x || a.grad_w) && a.n_rows > 0;
     if (overlap_bias) {
@@ -1027,7 +1069,8 @@ int tc_linear_backward(const LinearBwdArgs& a, cudaStream_t st) {
         p.seg = a.seg_offsets; p.n_expert = a.n_expert; p.n_out = (int)a.in_feat; p.n_contr = (int)a.out_feat;
         p.w_rows = (int)a.out_feat; p.out = a.grad_x; p.act_pre = a.act_pre; p.act = a.activation;
         p.is_bf16 = bf16; p.status = status_ptr();
-        const int64_t max_tiles = (ceil_div(a.n_rows, tile_m) + a.n_expert) * ceil_div(a.in_feat, BN);
+        const bool pair = use_pairs(MODE_DGRAD, a.n_rows, a.n_expert, a.in_feat);
+        const int64_t max_tiles = (ceil_div(a.n_rows, pair ? 256 : BM) + a.n_expert) * ceil_div(a.in_feat, BN);
         if (int rc = pair ? launch<MODE_DGRAD, true>(ma, mb, a.host_segs, p, max_tiles, st)
                           : launch<MODE_DGRAD, false>(ma, mb, a.host_segs, p, max_tiles, st))
             return rc;
@@ -1043,7 +1086,8 @@ int tc_linear_backward(const LinearBwdArgs& a, cudaStream_t st) {
         p.seg = a.seg_offsets; p.n_expert = a.n_expert; p.n_out = (int)a.in_feat; p.n_contr = 0;
         p.out_rows_per_expert = (int)a.out_feat; p.out = a.grad_w; p.accumulate = a.accumulate;
         p.is_bf16 = bf16; p.status = status_ptr();
-        const int64_t max_tiles = (int64_t)a.n_expert * ceil_div(a.out_feat, tile_m) * ceil_div(a.in_feat, BN);
+        const bool pair = use_pairs(MODE_WGRAD, a.n_rows, a.n_expert, a.in_feat);
+        const int64_t max_tiles = (int64_t)a.n_expert * ceil_div(a.out_feat, pair ? 256 : BM) * ceil_div(a.in_feat, BN);
         if (int rc = pair ? launch<MODE_WGRAD, true>(ma, mb, a.host_segs, p, max_tiles, st)
                           : launch<MODE_WGRAD, false>(ma, mb, a.host_segs, p, max_tiles, st))
             return rc;

@@ -159,3 +159,45 @@ def test_full_size_layer_shapes_properties(fc):
     mid = (gx.float() * x.float()).sum()
     assert abs(float(mid - rhs)) <= 2e-2 * abs(float(rhs)) + 50.0
     assert device_status() == 0
+
+
+@pytest.mark.parametrize("form", ["pair", "auto"])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_cta_pair_kernels(fc, form, dtype, monkeypatch):
+    """The cta_group::2 kernels (256-row tiles, one CTA pair per tile) against fp32 matmuls and,
+    bit for bit, against the one-CTA kernels: both accumulate the same products in the same order.
+    'pair' forces them for all three products; 'auto' is the default choice at a size where it
+    picks pairs for the forward and input-gradient products."""
+    from fastermoe_b200 import _lib
+    torch.manual_seed(11)
+    if form == "pair":
+        counts, fin, fout = [2048 + 77, 300, 2600, 0, 1500, 255, 257], 512, 768
+        monkeypatch.setenv("FMOE_B200_GEMM", "pair")
+    else:
+        counts, fin, fout = [9000, 12001, 8191, 10808], 256, 1024      # >= 512 rows per expert, >= 148 pair tiles
+        monkeypatch.delenv("FMOE_B200_GEMM", raising=False)
+    E, B = len(counts), sum(counts)
+    off = torch.tensor(np.concatenate([[0], np.cumsum(counts)]), dtype=torch.int64, device="cuda")
+    x = torch.randn(B, fin, device="cuda").to(dtype)
+    gy = torch.randn(B, fout, device="cuda").to(dtype)
+    w = ((torch.rand(E, fout, fin, device="cuda") * 2 - 1) / np.sqrt(fin)).to(dtype)
+    b = ((torch.rand(E, fout, device="cuda") * 2 - 1) / np.sqrt(fin)).to(dtype)
+
+    def run():
+        y, pre = fc.linear_forward_act(x, off, w, b, _lib.ACT_GELU, want_pre=True)
+        y0, _ = fc.linear_forward_act(x, off, w, b, _lib.ACT_NONE)
+        gx, gw, gb = fc.linear_backward_act(gy, x, off, w, None, _lib.ACT_NONE)
+        return y, pre, y0, gx, gw, gb
+
+    got = run()
+    monkeypatch.setenv("FMOE_B200_GEMM", "tc1")
+    single = run()
+    monkeypatch.delenv("FMOE_B200_GEMM")
+    assert device_status() == 0
+    for name, a_, b_ in zip(["y", "pre", "y0", "gx", "gw", "gb"], got, single):
+        assert torch.equal(a_, b_), f"{name}: CTA-pair and one-CTA kernels differ"
+    wy, wgx, wgw, wgb = reference(x, counts, w, b, gy)
+    close(got[2], wy, fin)
+    close(got[3], wgx, fout)
+    close(got[4], wgw, max(counts))
+    close(got[5], wgb, max(counts))
