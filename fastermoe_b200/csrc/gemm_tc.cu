@@ -49,11 +49,17 @@ template <bool CTA2> struct Cfg {
     static constexpr int TILE_M = CTA2 ? 256 : 128;          // tile rows across the CTA group
 };
 constexpr int MAX_EXPERTS_TC = 128;
-constexpr int EPI_WARPS = 8;                 // EPI_WARPS/4 per TMEM lane quarter, splitting the 256 columns
-constexpr int CW = 64;                       // columns handled per epilogue iteration (32 or 64)
+// Warp roles.  Warps 0..3: 0 = TMA producer, 1 = MMA issuer, 2-3 idle (they keep the
+// epilogue warps aligned to the TMEM lane quarters); warps 4..19 drain the accumulators.
+// The epilogues are bound by instruction issue (a warp issues at most every other cycle
+// on dependent code), so there are four epilogue warps per scheduler, each handling 32
+// columns at a time so that 640 threads x 96 registers fit the register file without spills.
+constexpr int EPI_WARPS = 16;                // EPI_WARPS/4 per TMEM lane quarter, splitting the 256 columns
+constexpr int FIRST_EPI_WARP = 4;
+constexpr int CW = 32;                       // columns handled per epilogue iteration (32 or 64)
 constexpr int STAGING_BYTES = 32 * CW * 2;  // per epilogue warp: 32 rows x CW columns of 16-bit values
 constexpr int COLS_PER_WARP = BN / (EPI_WARPS / 4);
-constexpr int THREADS = 64 + EPI_WARPS * 32;
+constexpr int THREADS = (FIRST_EPI_WARP + EPI_WARPS) * 32;
 constexpr int TMEM_COLS = 512;
 constexpr unsigned long long WAIT_LIMIT_CYCLES = 4000000000ull;  // ~2 s at 1.9 GHz
 
@@ -621,12 +627,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             }
             if (++acc == 2) { acc = 0; acc_ph ^= 1; }
         }
-    } else {
-        // ---- epilogue (warps 2..17) ------------------------------------------
+    } else if (warp >= FIRST_EPI_WARP) {
+        // ---- epilogue ----------------------------------------------------------
         const int quarter = warp & 3;    // TMEM lanes [32*quarter, +32) are readable by this warp
-        const int cgrp = (warp - 2) >> 2;  // which COLS_PER_WARP of the tile's 256 columns
+        const int cgrp = (warp - FIRST_EPI_WARP) >> 2;  // which COLS_PER_WARP of the tile's 256 columns
         const int r = quarter * 32 + lane;
-        uint4* stage = reinterpret_cast<uint4*>(tiles + STAGES * STAGE_BYTES) + (warp - 2) * (STAGING_BYTES / 16);
+        uint4* stage = reinterpret_cast<uint4*>(tiles + STAGES * STAGE_BYTES) + (warp - FIRST_EPI_WARP) * (STAGING_BYTES / 16);
         int e_cur = 0, acc = 0;
         uint32_t acc_ph = 0;
         bool ok = true;
