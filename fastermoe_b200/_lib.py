@@ -78,6 +78,8 @@ _SIGS = {
     "fmoe_plan_global_scatter": (I32, [P, P, P, I32, I32, I32, P, I32, POINTER(c_int32), POINTER(c_int64)]),
     "fmoe_global_scatter": (I32, [P, P, P, P, P, P, I64, I64, I64, I32, I32, P, P]),
     "fmoe_global_gather": (I32, [P, P, P, P, P, P, I64, I64, I64, I32, I32, P, P]),
+    "fmoe_gate_topk": (I32, [P, I64, I32, I32, I32, P, P, P]),
+    "fmoe_gate_topk_backward": (I32, [P, P, I64, I32, I32, I32, P, P]),
     "fmoe_peer_enable": (I32, [P, I64, P]),
     "fmoe_peer_slot_bytes": (I64, [P]),
     "fmoe_peer_global_scatter": (I32, [P, P, P, P, P, I64, I64, I64, I32, I32, P]),

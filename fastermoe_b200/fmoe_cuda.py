@@ -446,6 +446,32 @@ def gradient_exchange(stored_models, local_grads, grads, num_expert, world_size)
 # Extended operators (no counterpart in the reference's extension)
 # ---------------------------------------------------------------------------
 
+def gate_topk(logits, k):
+    """(values [T,k], indices [T,k] int64): the k largest logits per row (torch.topk, largest=True), in
+    descending order, ties by ascending index (fmoe/gates/naive_gate.py:31-34)."""
+    _check_cuda(logits)
+    logits = logits.contiguous()
+    n_tok, n_exp = logits.shape
+    val = logits.new_empty((n_tok, k))
+    idx = torch.empty((n_tok, k), dtype=torch.int64, device=logits.device)
+    with torch.cuda.device(logits.device):
+        _run("gate_topk", lib.fmoe_gate_topk, _ptr(logits), n_tok, n_exp, k, _dtype_code(logits), _ptr(val), _ptr(idx),
+             _stream())
+    return val, idx
+
+
+def gate_topk_backward(grad_values, indices, n_expert_total):
+    """Gradient of gate_topk with respect to the logits ([T, n_expert_total])."""
+    _check_cuda(grad_values, indices)
+    grad_values = grad_values.contiguous()
+    n_tok, k = indices.shape
+    out = grad_values.new_empty((n_tok, n_expert_total))
+    with torch.cuda.device(grad_values.device):
+        _run("gate_topk_backward", lib.fmoe_gate_topk_backward, _ptr(grad_values), _ptr(indices), n_tok, n_expert_total, k,
+             _dtype_code(grad_values), _ptr(out), _stream())
+    return out
+
+
 def count_and_pos(gate, n_expert_total, want_inv=True):
     """One-call form of count_by_gate's bucketing (fmoe/functions.py:19-41).
 

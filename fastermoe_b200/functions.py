@@ -464,6 +464,34 @@ class AllGather(Function):
         return grad_out[rank * dim0: (rank + 1) * dim0], None, None, None
 
 
+class GateTopK(Function):
+    """torch.topk(logits, k, largest=True) on the last dimension of a 2-D CUDA tensor with the
+    library's kernels (fmoe/gates/naive_gate.py:31-34): returns (values, indices), descending."""
+
+    @staticmethod
+    def forward(ctx, logits, k):
+        val, idx = fmoe_cuda.gate_topk(logits, k)
+        ctx.n_expert = logits.shape[1]
+        ctx.save_for_backward(idx)
+        ctx.mark_non_differentiable(idx)
+        return val, idx
+
+    @staticmethod
+    def backward(ctx, grad_val, _grad_idx):
+        (idx,) = ctx.saved_tensors
+        return fmoe_cuda.gate_topk_backward(grad_val, idx, ctx.n_expert), None
+
+
+def gate_topk(logits, k):
+    """Top-k over the last dimension: the library's kernel for CUDA float tensors with k <= 8,
+    torch.topk otherwise (CPU tensors, other dtypes).  Returns (values, indices)."""
+    if logits.is_cuda and k <= 8 and logits.dtype in (torch.float32, torch.float16, torch.bfloat16):
+        lead = logits.shape[:-1]
+        val, idx = GateTopK.apply(logits.reshape(-1, logits.shape[-1]), k)
+        return val.reshape(*lead, k), idx.reshape(*lead, k)
+    return torch.topk(logits, k=k, dim=-1, largest=True, sorted=False)
+
+
 class Slice(Function):
     """Keeps this rank's slice of dim 0; backward all-gathers (fmoe/functions.py:355-375)."""
 

@@ -4,6 +4,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from .base_gate import BaseGate
+from ..functions import gate_topk
 
 
 class NaiveGate(BaseGate):
@@ -23,7 +24,7 @@ class NaiveGate(BaseGate):
 
     def forward(self, inp, return_all_scores=False):
         gate = self.gate(inp)
-        top_val, top_idx = torch.topk(gate, k=self.top_k, dim=-1, largest=True, sorted=False)
+        top_val, top_idx = gate_topk(gate, self.top_k)
         top_val = top_val.view(-1, self.top_k)
         if self.softmax_scores:
             top_val = F.softmax(top_val, dim=-1)

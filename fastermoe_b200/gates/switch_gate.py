@@ -5,6 +5,7 @@ import torch
 import torch.nn.functional as F
 
 from .naive_gate import NaiveGate
+from ..functions import gate_topk
 from .utils import limit_by_capacity
 
 
@@ -21,7 +22,7 @@ class SwitchGate(NaiveGate):
             noise = torch.rand_like(score)
             score = score + (noise * 2 * self.switch_eps + 1.0 - self.switch_eps)
         score = F.softmax(score.float(), dim=-1)
-        top1_score, top1_idx = torch.topk(score, k=1, dim=-1, largest=True)
+        top1_score, top1_idx = gate_topk(score, 1)
         top1_score = top1_score.to(dtype=inp.dtype)
 
         cap_rate = self.capacity[0 if self.training else 1]

@@ -54,6 +54,25 @@ int fmoe_built_for_sm(void);
 int fmoe_device_status(int32_t* status_out);
 
 /* ------------------------------------------------------------------------
+ * Gate top-k                                         (selection: bit-exact)
+ * ---------------------------------------------------------------------- */
+
+/* The torch.topk(gate, k, largest=True, sorted=False) call of the reference's
+ * gates (fmoe/gates/naive_gate.py:31-34) and its backward.
+ *   logits  [n_tokens, n_expert_total] of dtype (FMOE_F32/F16/BF16), device
+ *   values  [n_tokens, k] same dtype: the k largest logits of each token, copied
+ *   indices [n_tokens, k] int64: their expert indices
+ * Order inside a token: descending value; equal values by ascending index; NaN
+ * ranks above every number (as torch.topk does).  1 <= k <= 8.
+ * Backward: grad_logits [n_tokens, n_expert_total] = zeros with grad_values
+ * scattered to the selected columns (every element is written). */
+int fmoe_gate_topk(const void* logits, int64_t n_tokens, int32_t n_expert_total, int32_t k,
+                   int32_t dtype, void* values, int64_t* indices, fmoe_stream_t stream);
+int fmoe_gate_topk_backward(const void* grad_values, const int64_t* indices, int64_t n_tokens,
+                            int32_t n_expert_total, int32_t k, int32_t dtype, void* grad_logits,
+                            fmoe_stream_t stream);
+
+/* ------------------------------------------------------------------------
  * Routing: counting, bucketing, capacity            (integer work, bit-exact)
  * ---------------------------------------------------------------------- */
 
