@@ -1,0 +1,75 @@
+r"""CUDA-graph capture of a training step of an MoE layer.
+
+At ``world_size == 1`` the layer's forward and backward never read anything back
+to the host (bucket sizes stay on the device; the grouped GEMMs take their tile
+list from the device-resident offsets), so a whole step is a fixed sequence of
+kernel launches and can be replayed as one CUDA graph.  What remains on the host
+per step is one graph launch, which removes the launch gaps at the start of a
+step that follows a synchronising read of the loss.
+
+With ``world_size > 1`` the forward waits for the count table on the host (buffer
+sizes depend on it), so it cannot be captured; ``GraphedStep`` refuses such modules.
+"""
+import torch
+
+
+class GraphedStep:
+    """``loss = loss_fn(module(x)); loss.backward()`` captured once, replayed per call.
+
+    ``module``: a ``FMoE`` / ``FMoETransformerMLP`` with ``world_size == 1`` (any
+    module whose forward+backward is free of host synchronisation works).
+    ``example_input``: a CUDA tensor with the shape and dtype of every later input.
+    ``loss_fn``: maps the module output to a scalar (default: sum in fp32).
+    ``input_grad``: also keep the gradient with respect to the input (``.input_grad``).
+
+    Calling the object copies ``x`` (CUDA or pinned host tensor) into the captured
+    input buffer on the current stream, replays the graph and returns the loss
+    tensor (device-resident, valid until the next call).  Parameter gradients are
+    written to ``param.grad`` (the same tensors at every replay: they are
+    overwritten, not accumulated); ``output`` holds the module output.
+    """
+
+    def __init__(self, module, example_input, loss_fn=None, warmup=3, input_grad=False):
+        if getattr(module, "world_size", 1) != 1:
+            raise ValueError("GraphedStep: the expert-parallel forward (world_size > 1) waits on the host for the "
+                             "count table and cannot be captured in a CUDA graph")
+        if not example_input.is_cuda:
+            raise ValueError("GraphedStep: example_input must be a CUDA tensor")
+        self.module = module
+        self.loss_fn = loss_fn if loss_fn is not None else (lambda out: out.float().sum())
+        self.static_input = example_input.detach().clone().requires_grad_(input_grad)
+        # Parameters that already took part in a backward pass on another stream make autograd
+        # warn about the stream of their accumulation nodes; the warm-up below is meant to run
+        # on a side stream, so the warning is switched off around it.
+        quiet = getattr(torch.autograd.graph, "set_warn_on_accumulate_grad_stream_mismatch", None)
+        if quiet is not None:
+            quiet(False)
+        try:
+            side = torch.cuda.Stream(device=example_input.device)
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):       # warm-up off the default stream, as graph capture requires
+                for _ in range(max(int(warmup), 1)):
+                    self._step()
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize(example_input.device)
+            # gradients must be allocated inside the capture, from the graph's own memory pool
+            module.zero_grad(set_to_none=True)
+            self.static_input.grad = None
+            self.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph):
+                self.output, self.loss = self._step()
+        finally:
+            if quiet is not None:
+                quiet(True)
+        self.input_grad = self.static_input.grad
+
+    def _step(self):
+        out = self.module(self.static_input)
+        loss = self.loss_fn(out)
+        loss.backward()
+        return out, loss
+
+    def __call__(self, x):
+        self.static_input.detach().copy_(x, non_blocking=True)
+        self.graph.replay()
+        return self.loss
