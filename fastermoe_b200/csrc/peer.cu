@@ -277,8 +277,10 @@ int peer_move(fmoe_comm_t comm, const void* in, void* out, const int64_t* table,
         const int64_t tok = eptr[r][r * E + i], rows = mine[r * E + i];
         push.push_back(reverse ? Seg{kLocal, ex, tok, rows} : Seg{kLocal, tok, ex, rows});
     }
-    for (int p = 0; p < W; ++p) {
-        if (p == r) continue;
+    // Peers are visited in the order r+1, r+2, ...: at any moment every rank stores into a
+    // different peer, so no GPU's NVLink ingress is shared by several senders.
+    for (int dlt = 1; dlt < W; ++dlt) {
+        const int p = (r + dlt) % W;
         for (int i = 0; i < E; ++i) {
             // rows this rank routes to expert i of rank p
             const int64_t out_rows_pi = mine[p * E + i];
