@@ -304,9 +304,9 @@ def run_ours(args):
                     "frac": ach / peaks["bf16_tflops"], "peak_source": peaks["source"] + " burst cuBLAS bf16",
                     "avg_launch_ms": avg, "launches_timed": len(fwd),
                     # dram__bytes_read.sum + dram__bytes_write.sum per forward launch, mean of the two
-                    # forward products of a step (687.5 MB and 478.0 MB), from the ncu capture summarised in
+                    # forward products of a step (690.0 MB and 490.9 MB), from the ncu capture summarised in
                     # profiles/grouped_gemm_config2_ncu_full.md; algorithmic bytes: 738 MB and 470 MB
-                    "traffic": 582.7e6 if world == 1 else None, "traffic_unit": "bytes per launch"}
+                    "traffic": 590.5e6 if world == 1 else None, "traffic_unit": "bytes per launch"}
         if bwd:
             avg_b = sum(bwd) / len(bwd)
             roofline["backward_call"] = {"avg_ms": avg_b, "achieved": 2 * flops_per_launch / (avg_b / 1e3) / 1e12,

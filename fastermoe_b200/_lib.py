@@ -16,6 +16,11 @@ ACT_NONE, ACT_RELU, ACT_GELU = 0, 1, 2
 MAX_EXPERTS = 4096
 
 
+class PeerSeg(ctypes.Structure):
+    _fields_ = [("dst_rank", c_int32), ("reserved", c_int32), ("src_row", c_int64), ("dst_row", c_int64),
+                ("rows", c_int64)]
+
+
 class Move(ctypes.Structure):
     """Mirror of fmoe_move_t."""
     _fields_ = [("peer", c_int32), ("is_send", c_int32), ("src_row", c_int64), ("dst_row", c_int64),
@@ -80,6 +85,7 @@ _SIGS = {
     "fmoe_global_gather": (I32, [P, P, P, P, P, P, I64, I64, I64, I32, I32, P, P]),
     "fmoe_gate_topk": (I32, [P, I64, I32, I32, I32, P, P, P]),
     "fmoe_gate_topk_backward": (I32, [P, P, I64, I32, I32, I32, P, P]),
+    "fmoe_peer_plan": (I32, [P, P, I32, I32, I32, I32, P, POINTER(c_int32), P, POINTER(c_int32), I32, POINTER(c_int64)]),
     "fmoe_peer_enable": (I32, [P, I64, P]),
     "fmoe_peer_slot_bytes": (I64, [P]),
     "fmoe_peer_global_scatter": (I32, [P, P, P, P, P, I64, I64, I64, I32, I32, P]),

@@ -225,17 +225,19 @@ void expert_layout(const int64_t* table, const uint8_t* stored, int p, int E, in
     L.total = rp;
 }
 
-int peer_move(fmoe_comm_t comm, const void* in, void* out, const int64_t* table, const uint8_t* stored,
-              int64_t in_rows, int64_t out_rows, int64_t row_bytes, int E, int W, bool reverse, cudaStream_t st) {
-    FMOE_REQUIRE(comm, "peer exchange: null communicator");
-    Comm* c = (Comm*)comm;
-    FMOE_REQUIRE(W == c->world, "peer exchange: n_workers=%d but communicator has %d ranks", W, c->world);
-    FMOE_REQUIRE(table && stored && E > 0 && row_bytes > 0, "peer exchange: bad argument");
-    if (c->peer.slot_bytes == 0 || row_bytes % 16 != 0) return FMOE_PEER_UNAVAILABLE;
-    const int r = c->rank;
+// Row segments of one exchange for rank r: `push` = what its push kernel stores (sel = kLocal:
+// the rows stay on this GPU and go straight to the output), `pull` = what its consume kernel
+// copies out of its own landing slot.  slot_rows = rows of the largest slot any rank needs (the
+// same on every rank, because it depends on the shared table only).
+struct Plan {
+    std::vector<Seg> push, pull;
+    int64_t slot_rows = 0, expert_rows = 0, token_rows = 0, max_rows = 0;
+};
+
+int plan_peer(const int64_t* table, const uint8_t* stored, int r, int E, int W, bool reverse, Plan& plan) {
+    FMOE_REQUIRE(table && stored && E > 0 && W > 0 && r >= 0 && r < W, "peer exchange: bad argument");
     const size_t n = (size_t)W * E;
     for (size_t i = 0; i < n * W; ++i) FMOE_REQUIRE(table[i] >= 0, "peer exchange: negative count at %zu", i);
-
     // token-side offsets of every rank, expert-side layout of every rank
     std::vector<std::vector<int64_t>> eptr(W, std::vector<int64_t>(n + 1, 0));
     std::vector<Layout> lay(W);
@@ -246,24 +248,12 @@ int peer_move(fmoe_comm_t comm, const void* in, void* out, const int64_t* table,
         max_token = std::max(max_token, eptr[p][n]);
         max_expert = std::max(max_expert, lay[p].total);
     }
-    const int64_t need_rows = reverse ? max_token : max_expert;
-    if (need_rows * row_bytes > c->peer.slot_bytes || max_token >= ((int64_t)1 << 31) || max_expert >= ((int64_t)1 << 31))
-        return FMOE_PEER_UNAVAILABLE;     // same verdict on every rank: it depends on the shared table only
-
-    const int64_t token_rows = reverse ? out_rows : in_rows, expert_rows = reverse ? in_rows : out_rows;
-    if (expert_rows != lay[r].total)
-        return fail(FMOE_ERR_MISMATCH, "peer exchange: expert-side buffer has %lld rows, counts say %lld",
-                    (long long)expert_rows, (long long)lay[r].total);
-    if (token_rows < eptr[r][n])
-        return fail(FMOE_ERR_MISMATCH, "peer exchange: token-side buffer has %lld rows, counts say %lld",
-                    (long long)token_rows, (long long)eptr[r][n]);
-    FMOE_REQUIRE((in || in_rows == 0) && (out || out_rows == 0), "peer exchange: null buffer");
-    FMOE_REQUIRE((((uintptr_t)in | (uintptr_t)out) & 15) == 0, "peer exchange: buffers must be 16-byte aligned");
-    if (reverse && out_rows > eptr[r][n])
-        FMOE_CUDA_TRY(cudaMemsetAsync((char*)out + eptr[r][n] * row_bytes, 0,
-                                      (size_t)(out_rows - eptr[r][n]) * row_bytes, st));
-
-    std::vector<Seg> push, pull;
+    plan.slot_rows = reverse ? max_token : max_expert;
+    plan.max_rows = std::max(max_token, max_expert);
+    plan.expert_rows = lay[r].total;
+    plan.token_rows = eptr[r][n];
+    std::vector<Seg>& push = plan.push;
+    std::vector<Seg>& pull = plan.pull;
     const int64_t* mine = table + (size_t)r * n;
     // rows that stay here: own rows of shadowed experts, and rows for this rank's own experts
     for (size_t idx = 0; idx < n; ++idx)
@@ -298,10 +288,37 @@ int peer_move(fmoe_comm_t comm, const void* in, void* out, const int64_t* table,
             }
         }
     }
+    return 0;
+}
+
+int peer_move(fmoe_comm_t comm, const void* in, void* out, const int64_t* table, const uint8_t* stored,
+              int64_t in_rows, int64_t out_rows, int64_t row_bytes, int E, int W, bool reverse, cudaStream_t st) {
+    FMOE_REQUIRE(comm, "peer exchange: null communicator");
+    Comm* c = (Comm*)comm;
+    FMOE_REQUIRE(W == c->world, "peer exchange: n_workers=%d but communicator has %d ranks", W, c->world);
+    FMOE_REQUIRE(row_bytes > 0, "peer exchange: row_bytes=%lld", (long long)row_bytes);
+    if (c->peer.slot_bytes == 0 || row_bytes % 16 != 0) return FMOE_PEER_UNAVAILABLE;
+    Plan plan;
+    if (int rc = plan_peer(table, stored, c->rank, E, W, reverse, plan)) return rc;
+    if (plan.slot_rows * row_bytes > c->peer.slot_bytes || plan.max_rows >= ((int64_t)1 << 31))
+        return FMOE_PEER_UNAVAILABLE;     // same verdict on every rank: it depends on the shared table only
+
+    const int64_t token_rows = reverse ? out_rows : in_rows, expert_rows = reverse ? in_rows : out_rows;
+    if (expert_rows != plan.expert_rows)
+        return fail(FMOE_ERR_MISMATCH, "peer exchange: expert-side buffer has %lld rows, counts say %lld",
+                    (long long)expert_rows, (long long)plan.expert_rows);
+    if (token_rows < plan.token_rows)
+        return fail(FMOE_ERR_MISMATCH, "peer exchange: token-side buffer has %lld rows, counts say %lld",
+                    (long long)token_rows, (long long)plan.token_rows);
+    FMOE_REQUIRE((in || in_rows == 0) && (out || out_rows == 0), "peer exchange: null buffer");
+    FMOE_REQUIRE((((uintptr_t)in | (uintptr_t)out) & 15) == 0, "peer exchange: buffers must be 16-byte aligned");
+    if (reverse && out_rows > plan.token_rows)
+        FMOE_CUDA_TRY(cudaMemsetAsync((char*)out + plan.token_rows * row_bytes, 0,
+                                      (size_t)(out_rows - plan.token_rows) * row_bytes, st));
     c->peer.epoch += 1;
     const int slot = (int)(c->peer.epoch & 1);
-    if (int rc = launch_phase<true>(c, push, in, out, row_bytes, slot, st)) return rc;
-    return launch_phase<false>(c, pull, nullptr, out, row_bytes, slot, st);
+    if (int rc = launch_phase<true>(c, plan.push, in, out, row_bytes, slot, st)) return rc;
+    return launch_phase<false>(c, plan.pull, nullptr, out, row_bytes, slot, st);
 }
 
 }  // namespace
@@ -422,4 +439,31 @@ extern "C" int fmoe_peer_global_gather(fmoe_comm_t comm, const void* global_in, 
                                        int32_t n_workers, fmoe_stream_t stream) {
     return peer_move(comm, global_in, local_out, all_expert_count_host, stored_models_host, in_rows, out_rows,
                      row_bytes, n_expert, n_workers, true, (cudaStream_t)stream);
+}
+
+extern "C" int fmoe_peer_plan(const int64_t* all_expert_count_host, const uint8_t* stored_models_host, int32_t rank,
+                              int32_t n_expert, int32_t n_workers, int32_t reverse, fmoe_peer_seg_t* push,
+                              int32_t* n_push, fmoe_peer_seg_t* pull, int32_t* n_pull, int32_t max_segs,
+                              int64_t* slot_rows) {
+    FMOE_REQUIRE(n_push && n_pull && slot_rows, "peer_plan: null output pointer");
+    Plan plan;
+    if (int rc = plan_peer(all_expert_count_host, stored_models_host, rank, n_expert, n_workers, reverse != 0, plan))
+        return rc;
+    auto emit = [&](const std::vector<Seg>& v, fmoe_peer_seg_t* out, int32_t* n) -> int {
+        int k = 0;
+        for (const Seg& sg : v) {
+            if (sg.rows == 0) continue;
+            if (out) {
+                FMOE_REQUIRE(k < max_segs, "peer_plan: more than max_segs=%d segments", max_segs);
+                out[k] = {sg.sel == kLocal ? n_workers : sg.sel, 0, sg.src_row, sg.dst_row, sg.rows};
+            }
+            ++k;
+        }
+        *n = k;
+        return 0;
+    };
+    if (int rc = emit(plan.push, push, n_push)) return rc;
+    if (int rc = emit(plan.pull, pull, n_pull)) return rc;
+    *slot_rows = plan.slot_rows;
+    return 0;
 }

@@ -342,6 +342,20 @@ int fmoe_global_gather(fmoe_comm_t comm, const void* global_in, void* local_out,
  * (FMOE_B200_PEER_TIMEOUT_MS, default 20000): an expired wait raises bit 16 or 32
  * of fmoe_device_status. */
 #define FMOE_PEER_UNAVAILABLE 1
+/* The row segments of one such exchange for `rank` (host only, no GPU needed; for inspection and
+ * tests).  push: rows its push kernel stores, dst_rank == n_workers meaning "stays on this GPU,
+ * written to the output buffer", else rows src_row.. of its input go to rows dst_row.. of dst_rank's
+ * landing slot.  pull: rows its consume kernel copies from its own slot (src_row) to its output
+ * (dst_row).  reverse = 0: global_scatter, 1: global_gather.  slot_rows: rows of the largest slot
+ * any rank needs.  Pass push = pull = NULL to get the counts only. */
+typedef struct {
+    int32_t dst_rank, reserved;
+    int64_t src_row, dst_row, rows;
+} fmoe_peer_seg_t;
+int fmoe_peer_plan(const int64_t* all_expert_count_host, const uint8_t* stored_models_host,
+                   int32_t rank, int32_t n_expert, int32_t n_workers, int32_t reverse,
+                   fmoe_peer_seg_t* push, int32_t* n_push, fmoe_peer_seg_t* pull, int32_t* n_pull,
+                   int32_t max_segs, int64_t* slot_rows);
 int fmoe_peer_enable(fmoe_comm_t comm, int64_t slot_bytes, fmoe_stream_t stream);
 int64_t fmoe_peer_slot_bytes(fmoe_comm_t comm);
 int fmoe_peer_global_scatter(fmoe_comm_t comm, const void* local_in, void* global_out,
