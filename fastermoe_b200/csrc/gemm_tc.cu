@@ -1118,6 +1118,12 @@ int read_device_status(int* out) {
 
 }  // namespace fmoe
 
+extern "C" int fmoe_device_status_clear(void) {
+    const int zero = 0;
+    FMOE_CUDA_TRY(cudaMemcpyToSymbol(fmoe::g_status, &zero, sizeof(int)));
+    return 0;
+}
+
 extern "C" int fmoe_device_status(int32_t* status_out) {
     FMOE_REQUIRE(status_out, "device_status: null pointer");
     int v = 0;

@@ -421,6 +421,34 @@ extern "C" int fmoe_peer_enable(fmoe_comm_t comm, int64_t slot_bytes, fmoe_strea
     return 0;
 }
 
+extern "C" int fmoe_peer_wait_probe(fmoe_comm_t comm, int32_t timeout_ms, fmoe_stream_t stream) {
+    FMOE_REQUIRE(comm, "peer_wait_probe: null communicator");
+    Comm* c = (Comm*)comm;
+    FMOE_REQUIRE(c->peer.slot_bytes > 0, "peer_wait_probe: the peer-memory exchange is off");
+    FMOE_REQUIRE(timeout_ms >= 1 && timeout_ms <= 10000, "peer_wait_probe: timeout_ms=%d (1..10000)", timeout_ms);
+    // A consume phase without rows that waits for an epoch no peer will ever publish.
+    const unsigned long long epoch = c->peer.epoch, limit = c->peer.timeout_ns;
+    c->peer.epoch = epoch + (1ull << 40);
+    c->peer.timeout_ns = (unsigned long long)timeout_ms * 1000000ull;
+    PeerBases b;
+    for (int p = 0; p < kMaxPeers; ++p) b.base[p] = c->peer.base[p];
+    PeerSegs t;
+    t.n = 0; t.prefix[0] = 0; t.prefix[1] = 0;
+    PeerLaunch a;
+    a.rank = c->rank; a.world = c->world; a.slot = 0;
+    a.wait_first = 1; a.signal_last = 0;
+    a.epoch = c->peer.epoch; a.timeout_ns = c->peer.timeout_ns;
+    a.row_vecs = 1; a.slot_off = kHeaderBytes;
+    a.counter = c->peer.counter + 1;
+    a.status = device_status_ptr();
+    c->peer.epoch = epoch;
+    c->peer.timeout_ns = limit;
+    FMOE_REQUIRE(a.status, "peer_wait_probe: no device status word");
+    peer_rows_kernel<false><<<1, 256, 0, (cudaStream_t)stream>>>(t, b, a, nullptr, nullptr);
+    FMOE_CHECK_LAUNCH();
+    return 0;
+}
+
 extern "C" int64_t fmoe_peer_slot_bytes(fmoe_comm_t comm) {
     return comm ? ((Comm*)comm)->peer.slot_bytes : 0;
 }

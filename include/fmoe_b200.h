@@ -52,6 +52,8 @@ int fmoe_built_for_sm(void);
  * the peer-memory exchange).  Copies from the device,
  * so it waits for the work queued before it.  No counterpart in the reference. */
 int fmoe_device_status(int32_t* status_out);
+/* Sets the status word back to 0 (after the caller has dealt with an expired wait). */
+int fmoe_device_status_clear(void);
 
 /* ------------------------------------------------------------------------
  * Gate top-k                                         (selection: bit-exact)
@@ -357,6 +359,11 @@ int fmoe_peer_plan(const int64_t* all_expert_count_host, const uint8_t* stored_m
                    fmoe_peer_seg_t* push, int32_t* n_push, fmoe_peer_seg_t* pull, int32_t* n_pull,
                    int32_t max_segs, int64_t* slot_rows);
 int fmoe_peer_enable(fmoe_comm_t comm, int64_t slot_bytes, fmoe_stream_t stream);
+/* Queues a wait of the exchange's consume step for rows that no peer will ever announce, bounded by
+ * timeout_ms: when it expires the kernel raises bit 32 of fmoe_device_status and returns; the
+ * exchange state is untouched.  Lets a host check that its handling of an expired wait works
+ * without a peer having to fail. */
+int fmoe_peer_wait_probe(fmoe_comm_t comm, int32_t timeout_ms, fmoe_stream_t stream);
 int64_t fmoe_peer_slot_bytes(fmoe_comm_t comm);
 int fmoe_peer_global_scatter(fmoe_comm_t comm, const void* local_in, void* global_out,
                              const int64_t* all_expert_count_host,

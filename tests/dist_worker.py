@@ -84,6 +84,20 @@ def gpu_exchange(rank, world, port):
             assert fc.peer_global_scatter(odd, table, torch.from_numpy(stored), want[rank].shape[0], E, world) is None
             st = ctypes.c_int32(-1)
             assert fc.lib.fmoe_device_status(ctypes.byref(st)) == 0 and st.value == 0, f"device status {st.value}"
+            if True:
+                # a wait for rows that nobody sends ends by itself, raises the status bit and leaves the
+                # exchange usable
+                import time
+                t0 = time.time()
+                with torch.cuda.device(dev):
+                    assert fc.lib.fmoe_peer_wait_probe(fc._comm(dev), 150, fc._stream()) == 0, fc._lib.last_error()
+                assert fc.lib.fmoe_device_status(ctypes.byref(st)) == 0 and st.value & 32, f"status {st.value}"
+                assert 0.1 < time.time() - t0 < 5.0
+                assert fc.lib.fmoe_device_status_clear() == 0
+                assert fc.lib.fmoe_device_status(ctypes.byref(st)) == 0 and st.value == 0
+                mine = torch.from_numpy(bufs[rank]).to(dev)
+                out = fc.peer_global_scatter(mine, table, torch.from_numpy(stored), want[rank].shape[0], E, world)
+                assert torch.equal(out, torch.from_numpy(want[rank]).to(dev)), "exchange after an expired wait"
         else:
             print(f"[rank {rank}] peer-memory exchange is off on this machine; NCCL form only", flush=True)
         cc = fc.generate_cached_count(torch.from_numpy(lecs[rank]).to(dev).view(world, E),
