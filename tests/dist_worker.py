@@ -239,6 +239,74 @@ def gpu_layer_bf16(rank, world, port):
 
 # ------------------------------------------------------------------ CPU / gloo
 
+def gpu_full_size(rank, world, port):
+    """BASELINE configurations 3 and 4 at their per-GPU sizes (the 8-GPU runs shard the same work per
+    GPU), checked through properties that need no CPU oracle of that size: the exchange over peer
+    memory and over NCCL give bit-identical layers; the smart schedule equals the plain schedule
+    within bf16 rounding; gradients are finite; no bounded wait expired."""
+    init(rank, world, port, "nccl")
+    from fastermoe_b200 import FMoETransformerMLP, fmoe_cuda as fc
+    import fastermoe_b200.functions as F
+    dev = torch.device("cuda", rank)
+
+    def build(E, d, h, seed, zipf):
+        g = torch.Generator().manual_seed(seed)
+        m = FMoETransformerMLP(num_expert=E, d_model=d, d_hidden=h, world_size=world, top_k=2, activation=torch.nn.GELU())
+        with torch.no_grad():
+            m.gate.gate.weight.copy_(torch.randn(E * world, d, generator=g) * 0.02)
+            m.gate.gate.bias.zero_()
+            if zipf:      # expert popularity ~ rank^-1.2
+                m.gate.gate.bias.copy_(-1.2 * torch.log(torch.arange(1, E * world + 1).float()))
+            ge = torch.Generator().manual_seed(seed * 1000 + rank)
+            for lin, fan in ((m.experts.htoh4, d), (m.experts.h4toh, h)):
+                lin.weight.copy_((torch.rand(lin.weight.shape, generator=ge) * 2 - 1) / fan ** 0.5)
+                lin.bias.copy_((torch.rand(lin.bias.shape, generator=ge) * 2 - 1) / fan ** 0.5)
+        return m.bfloat16().to(dev)
+
+    def status():
+        st = ctypes.c_int32(-1)
+        assert fc.lib.fmoe_device_status(ctypes.byref(st)) == 0
+        return st.value
+
+    # configuration 3: 4 experts per GPU, d_model 2048, d_hidden 8192, 8192 tokens per GPU, Zipf routing
+    m = build(4, 2048, 8192, 2, zipf=True)
+    x = torch.randn(8192, 2048, generator=torch.Generator().manual_seed(20 + rank)).bfloat16().to(dev)
+    peer = _run_layer(m, x)
+    if fc.peer_slot_bytes(dev) > 0:
+        plain_exchange = F.Exchange.__init__
+
+        def without_table(self, lec, gec, stored, fwd_batch_size, world_size, table=None):
+            plain_exchange(self, lec, gec, stored, fwd_batch_size, world_size, table=None)
+        F.Exchange.__init__ = without_table
+        try:
+            nccl = _run_layer(m, x)
+        finally:
+            F.Exchange.__init__ = plain_exchange
+        for name, v in peer.items():
+            assert torch.equal(nccl[name], v), f"config 3: peer-memory and NCCL exchange differ in {name}"
+    for name, v in peer.items():
+        assert torch.isfinite(v.float()).all(), f"config 3: {name} not finite"
+    assert status() == 0
+    del m, peer
+    torch.cuda.empty_cache()
+
+    # configuration 4: smart schedule, 1 expert per GPU, d_model 4096, d_hidden 16384, 16384 tokens per GPU
+    m = build(1, 4096, 16384, 3, zipf=False)
+    x = torch.randn(16384, 4096, generator=torch.Generator().manual_seed(30 + rank)).bfloat16().to(dev)
+    plain = _run_layer(m, x)
+    os.environ["FMOE_FUSE_GRAN"] = "1"
+    m.enable_fuse = True
+    fused = _run_layer(m, x)
+    m.enable_fuse = False
+    for name, v in plain.items():
+        assert torch.isfinite(v.float()).all(), f"config 4: {name} not finite"
+        scale = float(v.float().abs().mean()) + 1e-6
+        torch.testing.assert_close(fused[name].float(), v.float(), rtol=2e-2, atol=2e-2 * scale * 8,
+                                   msg=lambda s_, n=name: f"config 4 smart schedule vs plain, {n}: {s_}")
+    assert status() == 0
+    finish("nccl")
+
+
 def cpu_plan_exchange(rank, world, port):
     """Executes the library's exchange plan with gloo point-to-point on CPU tensors and
     compares with the oracle: the host-side planning that the NCCL executor follows."""

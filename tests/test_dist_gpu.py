@@ -47,3 +47,10 @@ def test_expert_parallel(fn):
     needs_gpus()
     for world in world_sizes():
         run_ranks(getattr(dist_worker, fn), world)
+
+
+def test_full_size_configs():
+    """Per-GPU sizes of BASELINE configurations 3 and 4, on 2 GPUs (property checks)."""
+    needs_gpus()
+    run_ranks(dist_worker.gpu_full_size, 2, limit_s=400)
+
