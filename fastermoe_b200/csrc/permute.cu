@@ -129,6 +129,117 @@ gather_sum_kernel(const T* __restrict__ buf, const int64_t* __restrict__ inv, co
     }
 }
 
+// Same result for the common case (16-byte packets, top_k = K known at compile time):
+// the K row indices and weights are read once, and each pass issues the loads of CH
+// column chunks of all K source rows before it uses any of them, so that a warp keeps
+// K*CH 16-byte loads per lane in flight instead of K.
+template <typename T, int K, bool WEIGHTED>
+__global__ void __launch_bounds__(kRowThreads)
+gather_sum_fast_kernel(const T* __restrict__ buf, const int64_t* __restrict__ inv, const T* __restrict__ score,
+                       T* __restrict__ out, int64_t n_tokens, int64_t d) {
+    constexpr int N = Pack<T>::N, CH = 4;
+    const int lane = threadIdx.x & 31;
+    const int64_t t = (int64_t)blockIdx.x * kRowWarps + (threadIdx.x >> 5);
+    if (t >= n_tokens) return;
+    const T* rows[K];
+    float w[K];
+#pragma unroll
+    for (int j = 0; j < K; ++j) {
+        const int64_t r = t * K + j;
+        const int64_t s = inv ? __ldg(inv + r) : r;
+        rows[j] = s >= 0 ? buf + s * d : nullptr;
+        w[j] = WEIGHTED ? to_float<T>(score[r]) : 1.f;
+    }
+    const int64_t step = 32 * N;
+    for (int64_t c0 = lane * N; c0 < d; c0 += CH * step) {
+        uint4 v[CH][K];
+#pragma unroll
+        for (int ch = 0; ch < CH; ++ch)
+#pragma unroll
+            for (int j = 0; j < K; ++j)
+                v[ch][j] = (rows[j] && c0 + ch * step < d) ? __ldg(reinterpret_cast<const uint4*>(rows[j] + c0 + ch * step))
+                                                           : make_uint4(0, 0, 0, 0);
+#pragma unroll
+        for (int ch = 0; ch < CH; ++ch) {
+            if (c0 + ch * step >= d) break;
+            float acc[N];
+#pragma unroll
+            for (int i = 0; i < N; ++i) acc[i] = 0.f;
+#pragma unroll
+            for (int j = 0; j < K; ++j) {
+                float f[N];
+                unpack<T>(v[ch][j], f);
+#pragma unroll
+                for (int i = 0; i < N; ++i) acc[i] = WEIGHTED ? fmaf(w[j], f[i], acc[i]) : acc[i] + f[i];
+            }
+            *reinterpret_cast<uint4*>(out + t * d + c0 + ch * step) = pack<T>(acc);
+        }
+    }
+}
+
+// Backward of the combine, same case: grad_out's row is read once per pass for all K slots.
+template <typename T, int K>
+__global__ void __launch_bounds__(kRowThreads)
+combine_bwd_fast_kernel(const T* __restrict__ grad_out, const T* __restrict__ buf, const int64_t* __restrict__ inv,
+                        const T* __restrict__ score, T* __restrict__ grad_buf, T* __restrict__ grad_score,
+                        int64_t n_tokens, int64_t d) {
+    constexpr int N = Pack<T>::N, CH = 2;
+    const int lane = threadIdx.x & 31;
+    const int64_t t = (int64_t)blockIdx.x * kRowWarps + (threadIdx.x >> 5);
+    if (t >= n_tokens) return;
+    int64_t src[K];
+    float w[K], dot[K];
+#pragma unroll
+    for (int j = 0; j < K; ++j) {
+        const int64_t r = t * K + j;
+        src[j] = inv ? __ldg(inv + r) : r;
+        w[j] = to_float<T>(score[r]);
+        dot[j] = 0.f;
+    }
+    const int64_t step = 32 * N;
+    const T* grow = grad_out + t * d;
+    for (int64_t c0 = lane * N; c0 < d; c0 += CH * step) {
+        uint4 g[CH], x[CH][K];
+#pragma unroll
+        for (int ch = 0; ch < CH; ++ch) {
+            const bool in = c0 + ch * step < d;
+            g[ch] = in ? __ldg(reinterpret_cast<const uint4*>(grow + c0 + ch * step)) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+            for (int j = 0; j < K; ++j)
+                x[ch][j] = (in && grad_score && src[j] >= 0)
+                               ? __ldg(reinterpret_cast<const uint4*>(buf + src[j] * d + c0 + ch * step))
+                               : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int ch = 0; ch < CH; ++ch) {
+            if (c0 + ch * step >= d) break;
+            float gf[N];
+            unpack<T>(g[ch], gf);
+#pragma unroll
+            for (int j = 0; j < K; ++j) {
+                if (src[j] < 0) continue;
+                float xf[N], o[N];
+                unpack<T>(x[ch][j], xf);
+#pragma unroll
+                for (int i = 0; i < N; ++i) {
+                    dot[j] = fmaf(gf[i], xf[i], dot[j]);
+                    o[i] = w[j] * gf[i];
+                }
+                *reinterpret_cast<uint4*>(grad_buf + src[j] * d + c0 + ch * step) = pack<T>(o);
+            }
+        }
+    }
+    if (grad_score) {
+#pragma unroll
+        for (int j = 0; j < K; ++j) {
+            float v = dot[j];
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+            if (lane == 0) grad_score[t * K + j] = from_float<T>(src[j] >= 0 ? v : 0.f);
+        }
+    }
+}
+
 // Backward of the combine.  One warp per token: reads grad_out[t,:] once, and for
 // each of the k slots writes score*grad_out into the slot's buffer row and
 // reduces dot(grad_out, src_row) into grad_score.
@@ -190,6 +301,15 @@ int gather_sum_t(const void* buf, const int64_t* inv, const void* score, void* o
     const bool v = vec_ok<T>(d, {buf, out});
     const T *b = (const T*)buf, *s = (const T*)score;
     T* o = (T*)out;
+    if (v && (top_k == 1 || top_k == 2 || top_k == 4)) {
+#define FMOE_GS(K_)                                                                                                 \
+        if (score) gather_sum_fast_kernel<T, K_, true><<<blocks, kRowThreads, 0, st>>>(b, inv, s, o, n_tokens, d);   \
+        else gather_sum_fast_kernel<T, K_, false><<<blocks, kRowThreads, 0, st>>>(b, inv, s, o, n_tokens, d)
+        if (top_k == 1) { FMOE_GS(1); } else if (top_k == 2) { FMOE_GS(2); } else { FMOE_GS(4); }
+#undef FMOE_GS
+        FMOE_CHECK_LAUNCH();
+        return 0;
+    }
     if (score) {
         if (v) gather_sum_kernel<T, true, true><<<blocks, kRowThreads, 0, st>>>(b, inv, s, o, n_tokens, top_k, d);
         else gather_sum_kernel<T, false, true><<<blocks, kRowThreads, 0, st>>>(b, inv, s, o, n_tokens, top_k, d);
@@ -207,6 +327,15 @@ int combine_bwd_t(const void* grad_out, const void* buf, const int64_t* inv, con
                   cudaStream_t st) {
     const unsigned blocks = (unsigned)ceil_div(n_tokens, kRowWarps);
     const bool v = vec_ok<T>(d, {grad_out, buf, grad_buf});
+    if (v && (top_k == 1 || top_k == 2 || top_k == 4)) {
+#define FMOE_CB(K_)                                                                                           \
+        combine_bwd_fast_kernel<T, K_><<<blocks, kRowThreads, 0, st>>>((const T*)grad_out, (const T*)buf, inv,  \
+            (const T*)score, (T*)grad_buf, (T*)grad_score, n_tokens, d)
+        if (top_k == 1) { FMOE_CB(1); } else if (top_k == 2) { FMOE_CB(2); } else { FMOE_CB(4); }
+#undef FMOE_CB
+        FMOE_CHECK_LAUNCH();
+        return 0;
+    }
     if (v)
         combine_bwd_kernel<T, true><<<blocks, kRowThreads, 0, st>>>((const T*)grad_out, (const T*)buf, inv,
             (const T*)score, (T*)grad_buf, (T*)grad_score, n_tokens, top_k, d);
