@@ -82,7 +82,7 @@ def count_by_gate(gate, num_expert, world_size, require_pos=True):
 class Routing:
     """Everything the layer derives from the gate indices for one forward."""
     __slots__ = ("pos", "inv", "lec_dev", "offsets_dev", "own_offsets_dev", "n_rows", "n_recv", "lec", "gec",
-                 "own_counts", "_aec", "_agec", "rank")
+                 "own_counts", "_aec", "_agec", "rank", "early")
 
     @property
     def aec(self):
@@ -97,15 +97,20 @@ class Routing:
         return self._agec
 
 
-def route(gate, num_expert, world_size):
+def route(gate, num_expert, world_size, before_wait=None):
     """Bucketing + count exchange with at most one device-to-host copy.
+
+    ``before_wait(routing)``, if given, is called right before the host waits for
+    the count table (world_size > 1 only) with ``pos``/``inv`` already queued; what
+    it returns is kept in ``routing.early``.  The layer uses it to queue the local
+    scatter, which needs no counts, so that the GPU works through the wait.
 
     Everything that needs only device data (the positions, the offsets of this
     worker's experts in the received buffer) is queued before the host waits for
     the count table, and the host-side slicing after the wait is a few numpy
     views, so the GPU idles as briefly as possible around the one sync."""
     r = Routing()
-    r._aec = r._agec = None
+    r._aec = r._agec = r.early = None
     with torch.no_grad():
         flat = gate.reshape(-1)
         n_tot = num_expert * world_size
@@ -121,6 +126,8 @@ def route(gate, num_expert, world_size):
         own = aec[:, r.rank, :].sum(dim=0)
         r.own_offsets_dev = torch.zeros(num_expert + 1, dtype=torch.int64, device=gate.device)
         torch.cumsum(own, 0, out=r.own_offsets_dev[1:])
+        if before_wait is not None:
+            r.early = before_wait(r)
         r._aec = aec.cpu()                      # the one sync of the forward pass
         table = r._aec.numpy()
         lec = table[r.rank].reshape(-1)
@@ -315,9 +322,10 @@ class MOEScatterFused(Function):
     world_size > 1 the all-to-all-v follows / precedes."""
 
     @staticmethod
-    def forward(ctx, inp, pos, inv, top_k, n_rows, exch):
+    def forward(ctx, inp, pos, inv, top_k, n_rows, exch, scattered=None):
         inp = inp.contiguous()
-        buf = fmoe_cuda.local_scatter(inp, pos, pos_div=top_k, n_rows=n_rows)
+        # `scattered`: the same local scatter, queued earlier by the caller (at least n_rows rows)
+        buf = scattered if scattered is not None else fmoe_cuda.local_scatter(inp, pos, pos_div=top_k, n_rows=n_rows)
         ctx.exch, ctx.top_k, ctx.n_tokens, ctx.n_rows = exch, top_k, inp.shape[0], n_rows
         ctx.save_for_backward(inv)
         if exch is not None:
@@ -332,7 +340,7 @@ class MOEScatterFused(Function):
         if exch is not None:
             grad_buf = exch.gather(grad_buf, ctx.n_rows)
         grad_inp = fmoe_cuda.local_gather_sum(grad_buf, inv, ctx.n_tokens, ctx.top_k)
-        return grad_inp, None, None, None, None, None
+        return grad_inp, None, None, None, None, None, None
 
 
 class MOEGatherCombine(Function):

@@ -93,7 +93,13 @@ def _fmoe_general_global_forward(inp, gate, expert_fn, policy_fn, experts, num_e
     """
     top_k = gate.shape[1] if gate.dim() == 2 else 1
     n_tokens = inp.shape[0]
-    routing = route(gate, num_expert, world_size)
+    early = None
+    if world_size > 1 and not enable_fuse:
+        # the local scatter needs the positions only: queue it before the host waits for the counts
+        def early(r, inp=inp):
+            with torch.no_grad():
+                return fmoe_cuda.local_scatter(inp.detach().contiguous(), r.pos, pos_div=top_k, n_rows=r.pos.numel())
+    routing = route(gate, num_expert, world_size, before_wait=early)
 
     if world_size == 1:
         # No exchange, no host copies: buffers have one row per gate entry; rows past
@@ -142,7 +148,7 @@ def _fmoe_general_global_forward(inp, gate, expert_fn, policy_fn, experts, num_e
             x = MOEForward.apply(inp, models, routing, top_k, exch, n_rows, fused_activation(experts), *flat)
             exch = None
         else:
-            x = MOEScatterFused.apply(inp, routing.pos, routing.inv, top_k, n_rows, exch)
+            x = MOEScatterFused.apply(inp, routing.pos, routing.inv, top_k, n_rows, exch, routing.early)
             x = expert_fn(x, models, fwd_count, num_expert)
 
     if gate_score is not None:
