@@ -84,9 +84,9 @@ struct Params {
 };
 
 struct Shared {
-    // full: this CTA's operands of a stage have landed (TMA).  peer_ready (pairs, in the
-    // leader): the other CTA's have.  empty: the MMAs reading the stage have completed.
-    unsigned long long full[MAX_STAGES], empty[MAX_STAGES], peer_ready[MAX_STAGES], tmem_full[2], tmem_empty[2];
+    // full: the operands of a stage have landed (TMA; in a pair, both CTAs' operands, counted on
+    // the leader's barrier).  empty: the MMAs reading the stage have completed.
+    unsigned long long full[MAX_STAGES], empty[MAX_STAGES], tmem_full[2], tmem_empty[2];
     uint32_t tmem_base;
     int abort;
     int cum_tiles[MAX_EXPERTS_TC + 1];
@@ -147,6 +147,9 @@ __device__ __forceinline__ uint32_t map_to_cta(const void* p, uint32_t rank) {
     uint32_t r;
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_u32(p)), "r"(rank));
     return r;
+}
+__device__ __forceinline__ void st_cluster_zero16(uint32_t cluster_addr) {
+    asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(cluster_addr), "r"(0) : "memory");
 }
 __device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
     asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
@@ -425,10 +428,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     const __grid_constant__ HostSegs hs, const Params p) {
     using C = Cfg<CTA2>;
     constexpr int STAGES = C::STAGES, STAGE_BYTES = C::STAGE_BYTES, TILE_M = C::TILE_M, B_COLS = C::B_COLS;
-    // Pairs, forward and input gradient: TMA completions of both CTAs go straight to the
-    // leader's barriers.  The weight gradient keeps the relay (each CTA patches the ragged
-    // tail of its own operands after they land, so it must see its own completions).
-    constexpr bool DIRECT = CTA2 && MODE != MODE_WGRAD;
+    // Pairs: TMA completions of both CTAs go straight to the leader's barriers, so the MMA
+    // issuer waits on one barrier and no warp of the second CTA sits in the critical path.
+    // (The weight gradient's ragged contraction tail is then patched by the leader in both
+    // CTAs' shared memory, see below.)
+    constexpr bool DIRECT = CTA2;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     Shared* sh = (Shared*)(tiles + RING_BYTES + EPI_WARPS * STAGING_BYTES);
@@ -444,7 +448,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(&sh->full[s], 1);
             mbar_init(&sh->empty[s], 1);
-            mbar_init(&sh->peer_ready[s], 1);
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(&sh->tmem_full[a], 1);
@@ -506,14 +509,23 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         // issuer waits on: no relay through the other CTA's warps.
                         const uint32_t bar = map_to_cta(&sh->full[s], 0);
                         if (cta == 0) mbar_expect_tx(&sh->full[s], 2 * STAGE_BYTES);
-                        tma_load_2d_pair(&map_a, bar, a_dst, ch * BK, t.row0 + my_row);
                         if (MODE == MODE_FWD) {
+                            tma_load_2d_pair(&map_a, bar, a_dst, ch * BK, t.row0 + my_row);
                             tma_load_2d_pair(&map_b, bar, b_dst, ch * BK, t.e * p.w_rows + t.col0 + my_col);
-                        } else {
+                        } else if (MODE == MODE_DGRAD) {
+                            tma_load_2d_pair(&map_a, bar, a_dst, ch * BK, t.row0 + my_row);
 #pragma unroll
                             for (int j = 0; j < B_COLS / 64; ++j)
                                 tma_load_2d_pair(&map_b, bar, b_dst + j * SUB_BYTES, t.col0 + my_col + j * 64,
                                                  t.e * p.w_rows + ch * BK);
+                        } else {
+                            const int m0 = t.m_lo + ch * BK;
+#pragma unroll
+                            for (int j = 0; j < BM / 64; ++j)
+                                tma_load_2d_pair(&map_a, bar, a_dst + j * SUB_BYTES, t.row0 + my_row + j * 64, m0);
+#pragma unroll
+                            for (int j = 0; j < B_COLS / 64; ++j)
+                                tma_load_2d_pair(&map_b, bar, b_dst + j * SUB_BYTES, t.col0 + my_col + j * 64, m0);
                         }
                         if (++s == STAGES) { s = 0; ph ^= 1; }
                         continue;
@@ -582,23 +594,16 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         const int row_end = k_steps << 4;
                         constexpr int BLOCKS = (BM + B_COLS) / 64;  // blocks of A then B are contiguous
                         for (int blk = 0; blk < BLOCKS; ++blk)
-                            for (int r = valid + (lane >> 3); r < row_end; r += 4)
-                                *reinterpret_cast<uint4*>(a_src + blk * SUB_BYTES + r * 128 + (lane & 7) * 16) =
-                                    make_uint4(0, 0, 0, 0);
-                        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                            for (int r = valid + (lane >> 3); r < row_end; r += 4) {
+                                uint8_t* dst = a_src + blk * SUB_BYTES + r * 128 + (lane & 7) * 16;
+                                *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+                                // pairs: the same rows of the other CTA's operands, through distributed shared memory
+                                if (CTA2) st_cluster_zero16(map_to_cta(dst, 1));
+                            }
+                        if (CTA2) asm volatile("fence.proxy.async;" ::: "memory");
+                        else asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                         __syncwarp();
                     }
-                }
-                if (CTA2 && !leader) {
-                    // This CTA's operands of the stage are in place: tell the leader.
-                    if (lane == 0) mbar_arrive_remote(map_to_cta(&sh->peer_ready[s], 0));
-                    __syncwarp();
-                    if (++s == STAGES) { s = 0; ph ^= 1; }
-                    continue;
-                }
-                if (CTA2 && !DIRECT) {
-                    if (!(ok = mbar_wait_cluster(&sh->peer_ready[s], ph, sh, p.status, 5))) break;
-                    tc_fence_after();
                 }
                 if (lane == 0) {
                     const uint64_t adesc = make_desc(smem_u32(a_src), A_LBO, 1024);
@@ -853,10 +858,11 @@ const HostSegs kNoSegs = {};
 // One CTA per 128x256 tile, or a pair of CTAs (cta_group::2) per 256x256 tile.  A pair
 // pulls a third fewer operand bytes per flop through each SM's L2 port, which is what
 // bounds the one-CTA kernel once the epilogue's stores share that port; on the other hand
-// its 256-row tiles waste more rows at the ragged end of each expert's segment and its
-// weight-gradient form still relays operand arrival through the second CTA.  Default:
-// pairs for the forward and input-gradient products when segments are long and there is
-// work for every pair; FMOE_B200_GEMM=pair / tc1 forces one form for all products.
+// its 256-row tiles waste more rows at the ragged end of each expert's segment.  The
+// weight gradient (MN-major operands, long contraction, small epilogue) does not gain
+// from pairs: measured 1.16 vs 1.36 PFLOP/s on dense input.  Default: pairs for the
+// forward and input-gradient products when segments are long and there is work for every
+// pair; FMOE_B200_GEMM=pair / tc1 forces one form for all products.
 enum { FORM_AUTO = 0, FORM_PAIR = 1, FORM_SINGLE = 2 };
 int forced_form() {
     const char* p = getenv("FMOE_B200_GEMM");
