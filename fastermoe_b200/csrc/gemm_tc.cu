@@ -79,8 +79,10 @@ struct Params {
     int act;
     int accumulate;  // WGRAD only
     int is_bf16;
+    int tma_store;  // outputs have tensor maps: full 32-row blocks leave through TMA stores
     int* status;  // device status word
-    int debug;    // FMOE_B200_DEBUG bits (profiling experiments): 1 = no global stores, 2 = no TMEM loads
+    int debug;    // FMOE_B200_DEBUG bits (profiling experiments): 1 = no global stores, 2 = no TMEM loads,
+                  // 8 = per-row stores instead of TMA stores
 };
 
 struct Shared {
@@ -94,6 +96,10 @@ struct Shared {
 };
 
 __device__ int g_status = 0;
+
+// Tensor maps of the outputs (box: 32 rows x 32 columns, 64-byte swizzle = the layout of the
+// epilogue's staging buffers): `out`, and the forward's second output (saved derivative).
+struct OutMaps { CUtensorMap out, out2; };
 
 // ---- PTX wrappers ------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -210,6 +216,15 @@ __device__ __forceinline__ void tma_load_2d_pair(const CUtensorMap* map, uint32_
         ::"r"(smem_u32(dst)), "l"(map), "r"(bar_cluster), "r"(x), "r"(y)
         : "memory");
 }
+// Bulk store of one staging buffer (smem, written by this warp) to the tile of `map` at (x, y).
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* src, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(map), "r"(smem_u32(src)), "r"(x), "r"(y) : "memory");
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+// The bulk stores issued by this thread have finished READING shared memory.
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_commit(unsigned long long* bar) {
@@ -425,7 +440,7 @@ __device__ __forceinline__ void locate(const Shared* sh, const Params& p, int ti
 template <int MODE, bool BF16, bool CTA2>
 __global__ void __launch_bounds__(THREADS, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                    const __grid_constant__ HostSegs hs, const Params p) {
+                    const __grid_constant__ HostSegs hs, const __grid_constant__ OutMaps om, const Params p) {
     using C = Cfg<CTA2>;
     constexpr int STAGES = C::STAGES, STAGE_BYTES = C::STAGE_BYTES, TILE_M = C::TILE_M, B_COLS = C::B_COLS;
     // Pairs: TMA completions of both CTAs go straight to the leader's barriers, so the MMA
@@ -665,6 +680,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             // staging buffer so that 4 lanes write 64 contiguous bytes of a row.
             const int rows_here = min(32, t.rows - quarter * 32);  // <= 0: nothing to store
             const bool active = rows_here > 0 && col_lo < p.n_out;
+            // Full 32-row blocks leave through TMA stores; ragged ones (the end of an expert's
+            // segment: the rows below belong to the next expert) through per-row stores.
+            const bool bulk = p.tma_store && rows_here == 32;
             const bool row_ok = r < t.rows;
             const size_t row_off = (MODE == MODE_WGRAD ? (size_t)t.e * p.out_rows_per_expert : 0) + t.row0;
             uint16_t* out_blk = (uint16_t*)p.out + (row_off + quarter * 32) * ld + col_lo;  // block origin
@@ -709,6 +727,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         }
                         if (p.pre_out && p.act == FMOE_ACT_GELU) {
                             // keep the derivative for the backward, then continue with the value
+                            if (p.tma_store) {   // an earlier bulk store may still be reading the buffer
+                                if (lane == 0) tma_store_wait_read();
+                                __syncwarp();
+                            }
 #pragma unroll
                             for (int q = 0; q < NCH; ++q) {
                                 float g[8];
@@ -724,7 +746,17 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                                                cvt_pack<BF16>(g[4], g[5]), cvt_pack<BF16>(g[6], g[7]));
                             }
                             __syncwarp();
-                            stage_store(stage, lane, (uint16_t*)p.pre_out + (row_off + quarter * 32) * ld + col_lo + c * CW, ld, rows_here);
+                            if (bulk) {
+                                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                                __syncwarp();
+                                if (lane == 0) {
+                                    tma_store_2d(&om.out2, stage, col_lo + c * CW, (int)row_off + quarter * 32);
+                                    tma_store_wait_read();      // the staging buffer is reused right away
+                                }
+                                __syncwarp();
+                            } else {
+                                stage_store(stage, lane, (uint16_t*)p.pre_out + (row_off + quarter * 32) * ld + col_lo + c * CW, ld, rows_here);
+                            }
                         } else if (p.act == FMOE_ACT_GELU) {
 #pragma unroll
                             for (int i = 0; i < CW / 2; ++i) {
@@ -771,8 +803,19 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         }
                     }
                     if (!(p.debug & 1)) {
-                        stage_put<BF16>(stage, lane, v);
-                        stage_store(stage, lane, out_blk + c * CW, ld, rows_here);
+                        if (p.tma_store) {   // an earlier bulk store may still be reading the buffer
+                            if (lane == 0) tma_store_wait_read();
+                            __syncwarp();
+                        }
+                        if (bulk) {
+                            stage_put<BF16>(stage, lane, v);
+                            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                            __syncwarp();
+                            if (lane == 0) tma_store_2d(&om.out, stage, col_lo + c * CW, (int)row_off + quarter * 32);
+                        } else {
+                            stage_put<BF16>(stage, lane, v);
+                            stage_store(stage, lane, out_blk + c * CW, ld, rows_here);
+                        }
                     }
                 }
             }
@@ -784,6 +827,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             }
             if (++acc == 2) { acc = 0; acc_ph ^= 1; }
         }
+        if (p.tma_store && lane == 0) tma_store_wait_all();
     }
 
     // ---- teardown -------------------------------------------------------------
@@ -834,6 +878,23 @@ int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS)
         return fail(FMOE_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d) for a [%lld, %lld] tensor", (int)r,
+                    (long long)rows, (long long)cols);
+    return 0;
+}
+
+// Output tensor [rows, cols] of 16-bit elements, box 32 x 32, 64-byte swizzle.
+int make_out_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, bool bf16) {
+    EncodeFn enc = get_encode();
+    if (!enc) return fail(FMOE_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+    cuuint32_t box[2] = {(cuuint32_t)CW, 32u};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
+                     const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail(FMOE_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d) for a [%lld, %lld] output", (int)r,
                     (long long)rows, (long long)cols);
     return 0;
 }
@@ -892,10 +953,21 @@ int cta_cap() {
 
 template <int MODE, bool CTA2>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, const HostSegs* hsp, const Params& p_in, int64_t max_tiles,
-           cudaStream_t st) {
+           int64_t out_rows, cudaStream_t st) {
     const HostSegs& hs = hsp ? *hsp : kNoSegs;
     Params p = p_in;
     if (const char* dbg = getenv("FMOE_B200_DEBUG")) p.debug = atoi(dbg);
+    static_assert(CW == 32, "the output tensor maps assume 32-column staging buffers");
+    OutMaps om;
+    memset(&om, 0, sizeof(om));
+    p.tma_store = 0;
+    if (!(p.debug & 8) && out_rows > 0 && p.out) {
+        if (int rc = make_out_map(&om.out, p.out, out_rows, p.n_out, p.is_bf16 != 0)) return rc;
+        if (p.pre_out) {
+            if (int rc = make_out_map(&om.out2, p.pre_out, out_rows, p.n_out, p.is_bf16 != 0)) return rc;
+        }
+        p.tma_store = 1;
+    }
     auto kern = p.is_bf16 ? grouped_gemm_kernel<MODE, true, CTA2> : grouped_gemm_kernel<MODE, false, CTA2>;
     FMOE_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
     cudaLaunchConfig_t cfg = {};
@@ -927,7 +999,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const HostSegs* hsp, co
     } else {
         cfg.gridDim = dim3((unsigned)std::max<int64_t>(1, std::min<int64_t>(max_tiles, cta_cap())));
     }
-    FMOE_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, ma, mb, hs, p));
+    FMOE_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, ma, mb, hs, om, p));
     return 0;
 }
 
@@ -1044,8 +1116,8 @@ int tc_linear_forward(const LinearArgs& a, cudaStream_t st) {
     p.is_bf16 = bf16; p.status = status_ptr();
     const int tile_m = pair ? 256 : BM;
     const int64_t max_tiles = (ceil_div(a.n_rows, tile_m) + a.n_expert) * ceil_div(a.out_feat, BN);
-    return pair ? launch<MODE_FWD, true>(ma, mb, a.host_segs, p, max_tiles, st)
-                : launch<MODE_FWD, false>(ma, mb, a.host_segs, p, max_tiles, st);
+    return pair ? launch<MODE_FWD, true>(ma, mb, a.host_segs, p, max_tiles, a.n_rows, st)
+                : launch<MODE_FWD, false>(ma, mb, a.host_segs, p, max_tiles, a.n_rows, st);
 }
 
 // A side stream and a pair of events per device, created on first use: the bias
@@ -1095,8 +1167,8 @@ int tc_linear_backward(const LinearBwdArgs& a, cudaStream_t st) {
         p.is_bf16 = bf16; p.status = status_ptr();
         const bool pair = use_pairs(MODE_DGRAD, a.n_rows, a.n_expert, a.in_feat);
         const int64_t max_tiles = (ceil_div(a.n_rows, pair ? 256 : BM) + a.n_expert) * ceil_div(a.in_feat, BN);
-        if (int rc = pair ? launch<MODE_DGRAD, true>(ma, mb, a.host_segs, p, max_tiles, st)
-                          : launch<MODE_DGRAD, false>(ma, mb, a.host_segs, p, max_tiles, st))
+        if (int rc = pair ? launch<MODE_DGRAD, true>(ma, mb, a.host_segs, p, max_tiles, a.n_rows, st)
+                          : launch<MODE_DGRAD, false>(ma, mb, a.host_segs, p, max_tiles, a.n_rows, st))
             return rc;
     }
     if (a.grad_w) {
@@ -1112,8 +1184,8 @@ int tc_linear_backward(const LinearBwdArgs& a, cudaStream_t st) {
         p.is_bf16 = bf16; p.status = status_ptr();
         const bool pair = use_pairs(MODE_WGRAD, a.n_rows, a.n_expert, a.in_feat);
         const int64_t max_tiles = (int64_t)a.n_expert * ceil_div(a.out_feat, pair ? 256 : BM) * ceil_div(a.in_feat, BN);
-        if (int rc = pair ? launch<MODE_WGRAD, true>(ma, mb, a.host_segs, p, max_tiles, st)
-                          : launch<MODE_WGRAD, false>(ma, mb, a.host_segs, p, max_tiles, st))
+        if (int rc = pair ? launch<MODE_WGRAD, true>(ma, mb, a.host_segs, p, max_tiles, (int64_t)a.n_expert * a.out_feat, st)
+                          : launch<MODE_WGRAD, false>(ma, mb, a.host_segs, p, max_tiles, (int64_t)a.n_expert * a.out_feat, st))
             return rc;
     }
     if (overlap_bias) {
