@@ -75,6 +75,7 @@ _SIGS = {
     "fmoe_linear_scratch_bytes": (c_size_t, [I64, I64, I64, I32, I32]),
     "fmoe_linear_forward": (I32, [P, P, P, P, P, P, I64, I64, I64, I32, I32, I32, P]),
     "fmoe_linear_backward": (I32, [P, P, P, P, P, P, P, P, I64, I64, I64, I32, I32, I32, I32, P, P]),
+    "fmoe_linear_backward_colsum": (I32, [P, P, P, P, P, P, P, P, P, I64, I64, I64, I32, I32, I32, I32, P, P]),
     "fmoe_comm_unique_id": (I32, [P]),
     "fmoe_comm_init": (I32, [P, I32, I32, I32, POINTER(c_void_p)]),
     "fmoe_comm_destroy": (I32, [P]),

@@ -39,6 +39,9 @@ struct LinearBwdArgs {
     int n_expert, dtype, activation, accumulate;
     void* scratch;
     const HostSegs* host_segs = nullptr;
+    // [n_expert, in_feat] or null: per-expert column sums of grad_x (what the bias gradient of
+    // the layer that produced x is, when grad_x is the gradient of its output)
+    void* grad_x_colsum = nullptr;
 };
 
 int simt_linear_forward(const LinearArgs& a, cudaStream_t st);

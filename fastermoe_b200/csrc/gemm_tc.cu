@@ -79,6 +79,7 @@ struct Params {
     int act;
     int accumulate;  // WGRAD only
     int is_bf16;
+    float* colsum;  // DGRAD: fp32 partial column sums of the output, one row per 32-row block, or null
     int tma_store;  // outputs have tensor maps: full 32-row blocks leave through TMA stores
     int* status;  // device status word
     int debug;    // FMOE_B200_DEBUG bits (profiling experiments): 1 = no global stores, 2 = no TMEM loads,
@@ -92,6 +93,7 @@ struct Shared {
     uint32_t tmem_base;
     int abort;
     int cum_tiles[MAX_EXPERTS_TC + 1];
+    int blk_base[MAX_EXPERTS_TC + 1];  // DGRAD with column sums: 32-row blocks before each expert
     int seg_lo[MAX_EXPERTS_TC], seg_hi[MAX_EXPERTS_TC];
 };
 
@@ -448,8 +450,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     // (The weight gradient's ragged contraction tail is then patched by the leader in both
     // CTAs' shared memory, see below.)
     constexpr bool DIRECT = CTA2;
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    // The operand ring needs 1024-byte alignment (128-byte swizzle atoms).  The dynamic shared
+    // memory of a kernel without static shared memory starts on such a boundary; no slack is
+    // spent on it, the address is checked below.
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* tiles = smem_raw;
     Shared* sh = (Shared*)(tiles + RING_BYTES + EPI_WARPS * STAGING_BYTES);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // In a pair, CTA 0 (the leader) issues the MMAs for both; each CTA loads its own
@@ -469,6 +474,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             mbar_init(&sh->tmem_empty[a], CTA2 ? 2 * EPI_WARPS : EPI_WARPS);
         }
         sh->abort = 0;
+        if (smem_u32(smem_raw) & 1023u) {   // never seen; every wait below then ends at once
+            sh->abort = 1;
+            atomicCAS(p.status, 0, 7);
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     for (int e = threadIdx.x; e < p.n_expert; e += THREADS) {
@@ -478,14 +487,17 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     __syncthreads();
     if (threadIdx.x == 0) {
         const int nt = (p.n_out + BN - 1) / BN;
-        int acc = 0;
+        int acc = 0, blk = 0;
         sh->cum_tiles[0] = 0;
+        sh->blk_base[0] = 0;
         for (int e = 0; e < p.n_expert; ++e) {
             int mt;
             if (MODE == MODE_WGRAD) mt = (p.out_rows_per_expert + TILE_M - 1) / TILE_M;
             else mt = (sh->seg_hi[e] - sh->seg_lo[e] + TILE_M - 1) / TILE_M;
             acc += mt * nt;
             sh->cum_tiles[e + 1] = acc;
+            blk += (sh->seg_hi[e] - sh->seg_lo[e] + 31) >> 5;
+            sh->blk_base[e + 1] = blk;
         }
     }
     if (warp == 0) {
@@ -807,13 +819,32 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                             if (lane == 0) tma_store_wait_read();
                             __syncwarp();
                         }
+                        stage_put<BF16>(stage, lane, v);
+                        if (MODE == MODE_DGRAD && p.colsum) {
+                            // Column sums of this 32x32 block of the (rounded) output, read back from
+                            // the staging buffer: lane = (row parity, column pair), 16 rows each.
+                            const uint32_t* st32 = reinterpret_cast<const uint32_t*>(stage);
+                            const int half = lane >> 4, cp = lane & 15;
+                            f32x2 sum = 0ull;
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) {
+                                const int row = 2 * i + half;
+                                const uint32_t w = st32[row * 16 + (((cp >> 2) ^ (i & 3)) << 2) + (cp & 3)];
+                                if (row < rows_here) sum = add2(sum, cvt_in2<BF16>(w));
+                            }
+                            float lo, hi;
+                            unpk(sum, lo, hi);
+                            lo += __shfl_xor_sync(0xffffffffu, lo, 16);
+                            hi += __shfl_xor_sync(0xffffffffu, hi, 16);
+                            const int blk = sh->blk_base[t.e] + ((t.row0 - sh->seg_lo[t.e]) >> 5) + quarter;
+                            if (lane < 16)
+                                *reinterpret_cast<float2*>(p.colsum + (size_t)blk * ld + col_lo + c * CW + cp * 2) = make_float2(lo, hi);
+                        }
                         if (bulk) {
-                            stage_put<BF16>(stage, lane, v);
                             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                             __syncwarp();
                             if (lane == 0) tma_store_2d(&om.out, stage, col_lo + c * CW, (int)row_off + quarter * 32);
                         } else {
-                            stage_put<BF16>(stage, lane, v);
                             stage_store(stage, lane, out_blk + c * CW, ld, rows_here);
                         }
                     }
@@ -899,7 +930,7 @@ int make_out_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols,
     return 0;
 }
 
-constexpr size_t SMEM_BYTES = 1024 + (size_t)RING_BYTES + (size_t)EPI_WARPS * STAGING_BYTES + sizeof(Shared);
+constexpr size_t SMEM_BYTES = (size_t)RING_BYTES + (size_t)EPI_WARPS * STAGING_BYTES + sizeof(Shared);
 static_assert(SMEM_BYTES <= 232448, "shared memory budget of one CTA exceeded");
 
 // Device address of the status word on the current device (cached per device).
@@ -1070,6 +1101,45 @@ bias_grad_tc_kernel(const uint16_t* __restrict__ dy, const int64_t* __restrict__
     }
 }
 
+// Adds up the per-block partial column sums that the input-gradient kernel left in the
+// scratch buffer: out[e, col] = sum over the 32-row blocks of expert e, in block order.
+template <bool BF16>
+__global__ void __launch_bounds__(128)
+colsum_finish_kernel(const float* __restrict__ partial, const int64_t* __restrict__ seg, const __grid_constant__ HostSegs hs,
+                     uint16_t* __restrict__ out, int n_cols, int accumulate) {
+    const int e = blockIdx.y;
+    const int col = (blockIdx.x * 128 + threadIdx.x) * 2;
+    if (col >= n_cols) return;
+    int base = 0;
+    for (int j = 0; j < e; ++j) {
+        const int64_t lo = hs.n ? (int64_t)hs.lo[j] : seg[j], hi = hs.n ? (int64_t)hs.hi[j] : seg[j + 1];
+        base += (int)((hi - lo + 31) >> 5);
+    }
+    const int64_t lo = hs.n ? (int64_t)hs.lo[e] : seg[e], hi = hs.n ? (int64_t)hs.hi[e] : seg[e + 1];
+    const int nb = (int)((hi - lo + 31) >> 5);
+    float t0 = 0.f, t1 = 0.f;
+    const float* src = partial + (size_t)base * n_cols + col;
+    int b = 0;
+    for (; b + 3 < nb; b += 4) {
+        const float2 v0 = *reinterpret_cast<const float2*>(src + (size_t)b * n_cols);
+        const float2 v1 = *reinterpret_cast<const float2*>(src + (size_t)(b + 1) * n_cols);
+        const float2 v2 = *reinterpret_cast<const float2*>(src + (size_t)(b + 2) * n_cols);
+        const float2 v3 = *reinterpret_cast<const float2*>(src + (size_t)(b + 3) * n_cols);
+        t0 += v0.x; t1 += v0.y; t0 += v1.x; t1 += v1.y; t0 += v2.x; t1 += v2.y; t0 += v3.x; t1 += v3.y;
+    }
+    for (; b < nb; ++b) {
+        const float2 v = *reinterpret_cast<const float2*>(src + (size_t)b * n_cols);
+        t0 += v.x; t1 += v.y;
+    }
+    uint32_t* o = reinterpret_cast<uint32_t*>(out + (size_t)e * n_cols + col);
+    if (accumulate) {
+        float x0, x1;
+        unpk(cvt_in2<BF16>(*o), x0, x1);
+        t0 += x0; t1 += x1;
+    }
+    *o = cvt_pack<BF16>(t0, t1);
+}
+
 template <bool BF16>
 int launch_bias_grad(const LinearBwdArgs& a, const HostSegs& hs, cudaStream_t st) {
     const bool narrow = ceil_div(a.out_feat, 128) * a.n_expert < 2 * sm_count();
@@ -1100,7 +1170,10 @@ bool tc_backward_supported(const LinearBwdArgs& a) {
            (!a.grad_b || ((uintptr_t)a.grad_b & 1) == 0);
 }
 
-size_t tc_backward_scratch_bytes(int64_t, int64_t, int64_t, int, int) { return 0; }
+// fp32 partial column sums of the input gradient: one row of in_feat values per 32-row block
+size_t tc_backward_scratch_bytes(int64_t n_rows, int64_t in_feat, int64_t, int n_expert, int) {
+    return (size_t)(n_rows / 32 + n_expert + 1) * (size_t)in_feat * sizeof(float);
+}
 
 int tc_linear_forward(const LinearArgs& a, cudaStream_t st) {
     const bool bf16 = a.dtype == FMOE_BF16;
@@ -1165,11 +1238,25 @@ int tc_linear_backward(const LinearBwdArgs& a, cudaStream_t st) {
         p.seg = a.seg_offsets; p.n_expert = a.n_expert; p.n_out = (int)a.in_feat; p.n_contr = (int)a.out_feat;
         p.w_rows = (int)a.out_feat; p.out = a.grad_x; p.act_pre = a.act_pre; p.act = a.activation;
         p.is_bf16 = bf16; p.status = status_ptr();
+        if (a.grad_x_colsum) {
+            FMOE_REQUIRE(a.scratch && aligned16(a.scratch) && ((uintptr_t)a.grad_x_colsum & 3) == 0,
+                         "linear_backward: column sums of grad_x need the scratch buffer of fmoe_linear_scratch_bytes");
+            p.colsum = (float*)a.scratch;
+        }
         const bool pair = use_pairs(MODE_DGRAD, a.n_rows, a.n_expert, a.in_feat);
         const int64_t max_tiles = (ceil_div(a.n_rows, pair ? 256 : BM) + a.n_expert) * ceil_div(a.in_feat, BN);
         if (int rc = pair ? launch<MODE_DGRAD, true>(ma, mb, a.host_segs, p, max_tiles, a.n_rows, st)
                           : launch<MODE_DGRAD, false>(ma, mb, a.host_segs, p, max_tiles, a.n_rows, st))
             return rc;
+        if (a.grad_x_colsum) {
+            const HostSegs& hs = a.host_segs ? *a.host_segs : kNoSegs;
+            dim3 grid((unsigned)ceil_div(a.in_feat, 256), (unsigned)a.n_expert);
+            if (bf16) colsum_finish_kernel<true><<<grid, 128, 0, st>>>((const float*)a.scratch, a.seg_offsets, hs,
+                                                                       (uint16_t*)a.grad_x_colsum, (int)a.in_feat, 0);
+            else colsum_finish_kernel<false><<<grid, 128, 0, st>>>((const float*)a.scratch, a.seg_offsets, hs,
+                                                                   (uint16_t*)a.grad_x_colsum, (int)a.in_feat, 0);
+            FMOE_CHECK_LAUNCH();
+        }
     }
     if (a.grad_w) {
         CUtensorMap ma, mb;

@@ -25,6 +25,32 @@ int check_common(int64_t n_rows, int64_t in_feat, int64_t out_feat, int n_expert
     return 0;
 }
 
+// out[e, c] = sum of grad_x[r, c] over the rows of expert e (plain kernel for the FFMA path).
+template <typename T>
+__global__ void colsum_rows_kernel(const T* __restrict__ gx, const int64_t* __restrict__ seg, const HostSegs hs,
+                                   T* __restrict__ out, int64_t n_cols) {
+    const int e = blockIdx.y;
+    const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= n_cols) return;
+    const int64_t lo = hs.n ? (int64_t)hs.lo[e] : seg[e], hi = hs.n ? (int64_t)hs.hi[e] : seg[e + 1];
+    float s = 0.f;
+    for (int64_t r = lo; r < hi; ++r) s += to_float<T>(gx[r * n_cols + c]);
+    out[(int64_t)e * n_cols + c] = from_float<T>(s);
+}
+
+int colsum_rows(const LinearBwdArgs& a, cudaStream_t st) {
+    static const HostSegs none = {};
+    const HostSegs& hs = a.host_segs ? *a.host_segs : none;
+    dim3 grid((unsigned)ceil_div(a.in_feat, 128), (unsigned)a.n_expert);
+    switch (a.dtype) {
+        case FMOE_F32: colsum_rows_kernel<float><<<grid, 128, 0, st>>>((const float*)a.grad_x, a.seg_offsets, hs, (float*)a.grad_x_colsum, a.in_feat); break;
+        case FMOE_F16: colsum_rows_kernel<__half><<<grid, 128, 0, st>>>((const __half*)a.grad_x, a.seg_offsets, hs, (__half*)a.grad_x_colsum, a.in_feat); break;
+        default: colsum_rows_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>((const __nv_bfloat16*)a.grad_x, a.seg_offsets, hs, (__nv_bfloat16*)a.grad_x_colsum, a.in_feat); break;
+    }
+    FMOE_CHECK_LAUNCH();
+    return 0;
+}
+
 }  // namespace
 
 namespace fmoe {
@@ -34,8 +60,11 @@ int dispatch_linear_forward(const LinearArgs& a, cudaStream_t st) {
     return simt_linear_forward(a, st);
 }
 int dispatch_linear_backward(const LinearBwdArgs& a, cudaStream_t st) {
-    if (!force_simt() && tc_backward_supported(a)) return tc_linear_backward(a, st);
-    return simt_linear_backward(a, st);
+    if (a.grad_x_colsum) FMOE_REQUIRE(a.grad_x, "linear_backward: column sums of grad_x requested without grad_x");
+    if (!force_simt() && tc_backward_supported(a) && a.n_rows > 0) return tc_linear_backward(a, st);
+    if (int rc = simt_linear_backward(a, st)) return rc;
+    if (a.grad_x_colsum) return colsum_rows(a, st);   // the tensor-core kernel produces them itself
+    return 0;
 }
 }  // namespace fmoe
 
@@ -68,3 +97,19 @@ extern "C" int fmoe_linear_backward(const void* grad_y, const void* x, const voi
                     out_feat, n_expert, dtype, activation, accumulate, scratch};
     return dispatch_linear_backward(a, (cudaStream_t)stream);
 }
+
+extern "C" int fmoe_linear_backward_colsum(const void* grad_y, const void* x, const void* weight,
+                                           const int64_t* seg_offsets, const void* act_pre, void* grad_x,
+                                           void* grad_w, void* grad_b, void* grad_x_colsum, int64_t n_rows,
+                                           int64_t in_feat, int64_t out_feat, int32_t n_expert, int32_t dtype,
+                                           int32_t activation, int32_t accumulate, void* scratch,
+                                           fmoe_stream_t stream) {
+    if (int rc = check_common(n_rows, in_feat, out_feat, n_expert, dtype, activation, seg_offsets)) return rc;
+    FMOE_REQUIRE(n_rows == 0 || (grad_y && weight), "linear_backward: null pointer");
+    FMOE_REQUIRE(!grad_w || x || n_rows == 0, "linear_backward: weight gradient needs the forward input");
+    LinearBwdArgs a{grad_y, x, weight, seg_offsets, act_pre, grad_x, grad_w, grad_b, n_rows, in_feat,
+                    out_feat, n_expert, dtype, activation, accumulate, scratch};
+    a.grad_x_colsum = grad_x_colsum;
+    return dispatch_linear_backward(a, (cudaStream_t)stream);
+}
+

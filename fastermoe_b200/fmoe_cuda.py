@@ -579,10 +579,12 @@ def linear_forward_act(x, seg_offsets, weight, bias, activation, want_pre=False)
 
 
 def linear_backward_act(grad_y, x, seg_offsets, weight, act_pre, activation, need_bias=True,
-                        need_input_grad=True, grad_w=None, grad_b=None, accumulate=False):
+                        need_input_grad=True, grad_w=None, grad_b=None, accumulate=False, want_gx_colsum=False):
     """Grouped GEMM backward.  ``act_pre`` (shape of x) fuses the backward of the
     activation that produced ``x`` into the input gradient: for ReLU pass the activation
-    output, for GELU the derivative buffer of linear_forward_act.  Returns (dX, dW, db)."""
+    output, for GELU the derivative buffer of linear_forward_act.  Returns (dX, dW, db), and with
+    ``want_gx_colsum`` a fourth tensor [E, in_feat]: the per-expert column sums of dX (the bias
+    gradient of the layer that produced ``x``), which the input-gradient kernel computes on the way."""
     _check_cuda(grad_y, x, seg_offsets, weight, act_pre)
     n_expert, out_feat, in_feat = weight.shape
     n_rows = grad_y.shape[0]
@@ -592,6 +594,13 @@ def linear_backward_act(grad_y, x, seg_offsets, weight, act_pre, activation, nee
     with torch.cuda.device(x.device):
         nbytes = lib.fmoe_linear_scratch_bytes(n_rows, in_feat, out_feat, n_expert, _dtype_code(x))
         scratch = _scratch(nbytes, x.device)
+        if want_gx_colsum:
+            assert need_input_grad
+            cs = weight.new_empty((n_expert, in_feat))
+            _run("linear_backward", lib.fmoe_linear_backward_colsum, _ptr(grad_y), _ptr(x), _ptr(weight),
+                 _ptr(seg_offsets), _ptr(act_pre), _ptr(gx), _ptr(gw), _ptr(gb), _ptr(cs), n_rows, in_feat,
+                 out_feat, n_expert, _dtype_code(x), activation, 1 if accumulate else 0, _ptr(scratch), _stream())
+            return gx, gw, gb, cs
         _run("linear_backward", lib.fmoe_linear_backward, _ptr(grad_y), _ptr(x), _ptr(weight), _ptr(seg_offsets),
                                        _ptr(act_pre), _ptr(gx), _ptr(gw), _ptr(gb), n_rows, in_feat,
                                        out_feat, n_expert, _dtype_code(x), activation,

@@ -448,11 +448,17 @@ class FusedExpertMLP(Function):
             act_pre = h
         elif act == _lib.ACT_GELU:
             act_pre = pre
-        gh, gw2, gb2 = fmoe_cuda.linear_backward_act(grad_y.contiguous(), h, offsets, w2, act_pre, act,
-                                                     need_bias=ctx.has_bias[1])
-        gx, gw1, gb1 = fmoe_cuda.linear_backward_act(gh, x, offsets, w1, None, _lib.ACT_NONE,
-                                                     need_bias=ctx.has_bias[0],
-                                                     need_input_grad=ctx.needs_input_grad[0])
+        # The first layer's bias gradient is the column sum of gh: the input-gradient kernel of the
+        # second layer returns it, so the first layer's backward does not read gh once more for it.
+        if ctx.has_bias[0]:
+            gh, gw2, gb2, gb1 = fmoe_cuda.linear_backward_act(grad_y.contiguous(), h, offsets, w2, act_pre, act,
+                                                              need_bias=ctx.has_bias[1], want_gx_colsum=True)
+        else:
+            gh, gw2, gb2 = fmoe_cuda.linear_backward_act(grad_y.contiguous(), h, offsets, w2, act_pre, act,
+                                                         need_bias=ctx.has_bias[1])
+            gb1 = None
+        gx, gw1, _ = fmoe_cuda.linear_backward_act(gh, x, offsets, w1, None, _lib.ACT_NONE, need_bias=False,
+                                                   need_input_grad=ctx.needs_input_grad[0])
         return gx, None, gw1, gb1, gw2, gb2, None
 
 

@@ -210,8 +210,9 @@ int fmoe_combine_backward(const void* grad_out, const void* buf, const int64_t* 
  * Grouped expert GEMM (fmoe_linear)
  * ---------------------------------------------------------------------- */
 
-/* Bytes of scratch needed by fmoe_linear_backward (split accumulation of the
- * weight gradient). */
+/* Bytes of scratch that fmoe_linear_backward_colsum needs (fp32 partial column sums of the
+ * input gradient, one row per 32-row block); fmoe_linear_backward accepts the same buffer
+ * or NULL. */
 size_t fmoe_linear_scratch_bytes(int64_t n_rows, int64_t in_feat, int64_t out_feat,
                                  int32_t n_expert, int32_t dtype);
 
@@ -252,6 +253,20 @@ int fmoe_linear_backward(const void* grad_y, const void* x, const void* weight,
                          int64_t n_rows, int64_t in_feat, int64_t out_feat,
                          int32_t n_expert, int32_t dtype, int32_t activation,
                          int32_t accumulate, void* scratch, fmoe_stream_t stream);
+
+/* fmoe_linear_backward that also returns the per-expert column sums of grad_x
+ * (grad_x_colsum [n_expert, in_feat], same dtype; needs grad_x): when x is the output of
+ * another expert layer, that is that layer's bias gradient, and the tensor-core
+ * input-gradient kernel produces it from the output blocks it stages anyway (fp32 partial
+ * sums per 32-row block in `scratch`, added in block order: deterministic), which saves
+ * the separate pass over grad_x that the reference makes (cuda/parallel_linear.cuh:
+ * column_reduce).  No counterpart in the reference. */
+int fmoe_linear_backward_colsum(const void* grad_y, const void* x, const void* weight,
+                                const int64_t* seg_offsets, const void* act_pre, void* grad_x,
+                                void* grad_w, void* grad_b, void* grad_x_colsum, int64_t n_rows,
+                                int64_t in_feat, int64_t out_feat, int32_t n_expert, int32_t dtype,
+                                int32_t activation, int32_t accumulate, void* scratch,
+                                fmoe_stream_t stream);
 
 /* ------------------------------------------------------------------------
  * Expert-parallel exchange over NCCL

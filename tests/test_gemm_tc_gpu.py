@@ -201,3 +201,37 @@ def test_cta_pair_kernels(fc, form, dtype, monkeypatch):
     close(got[3], wgx, fout)
     close(got[4], wgw, max(counts))
     close(got[5], wgb, max(counts))
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("form", ["auto", "pair"])
+def test_input_gradient_column_sums(fc, dtype, form, monkeypatch):
+    """linear_backward_act(want_gx_colsum=True): per-expert column sums of the returned dX (the bias
+    gradient of the layer below), from the tensor-core epilogue (16-bit) or the plain kernel (fp32)."""
+    from fastermoe_b200 import _lib
+    if form == "pair":
+        if dtype == torch.float32:
+            pytest.skip("fp32 takes the FFMA kernels")
+        monkeypatch.setenv("FMOE_B200_GEMM", "pair")
+        counts, fin, fout = [2048 + 77, 300, 2600, 0, 1500, 31, 33], 512, 256
+    else:
+        counts, fin, fout = [100, 0, 0, 29, 257, 32, 1, 511], 320, 256
+    torch.manual_seed(5)
+    E, B = len(counts), sum(counts)
+    off = torch.tensor(np.concatenate([[0], np.cumsum(counts)]), dtype=torch.int64, device="cuda")
+    x = torch.randn(B, fin, device="cuda").to(dtype)
+    gy = torch.randn(B, fout, device="cuda").to(dtype)
+    w = ((torch.rand(E, fout, fin, device="cuda") * 2 - 1) / np.sqrt(fin)).to(dtype)
+    saved = torch.rand(B, fin, device="cuda").to(dtype)          # stands for a saved GELU derivative
+    for act_pre, act in ((None, _lib.ACT_NONE), (saved, _lib.ACT_GELU)):
+        gx, gw, gb, cs = fc.linear_backward_act(gy, x, off, w, act_pre, act, want_gx_colsum=True)
+        gx0, gw0, gb0 = fc.linear_backward_act(gy, x, off, w, act_pre, act)
+        assert torch.equal(gx, gx0) and torch.equal(gw, gw0) and torch.equal(gb, gb0)
+        want = torch.zeros(E, fin, device="cuda")
+        p = 0
+        for e, c in enumerate(counts):
+            want[e] = gx[p:p + c].float().sum(0)
+            p += c
+        tol = 1e-5 if dtype == torch.float32 else 1e-2
+        torch.testing.assert_close(cs.float(), want, rtol=tol, atol=tol * float(want.abs().max() + 1))
+    assert device_status() == 0
