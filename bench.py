@@ -205,7 +205,7 @@ def run_ours(args):
         x.requires_grad_(True)
         pending["next"] = prefetch()
         out = layer(x)
-        loss = out.float().sum()
+        loss = out.sum(dtype=torch.float32)      # fp32 accumulation without an fp32 copy of the output
         loss.backward()
         return loss.item()
 

@@ -19,7 +19,7 @@ class GraphedStep:
     ``module``: a ``FMoE`` / ``FMoETransformerMLP`` with ``world_size == 1`` (any
     module whose forward+backward is free of host synchronisation works).
     ``example_input``: a CUDA tensor with the shape and dtype of every later input.
-    ``loss_fn``: maps the module output to a scalar (default: sum in fp32).
+    ``loss_fn``: maps the module output to a scalar (default: sum accumulated in fp32).
     ``input_grad``: also keep the gradient with respect to the input (``.input_grad``).
 
     Calling the object copies ``x`` (CUDA or pinned host tensor) into the captured
@@ -36,7 +36,7 @@ class GraphedStep:
         if not example_input.is_cuda:
             raise ValueError("GraphedStep: example_input must be a CUDA tensor")
         self.module = module
-        self.loss_fn = loss_fn if loss_fn is not None else (lambda out: out.float().sum())
+        self.loss_fn = loss_fn if loss_fn is not None else (lambda out: out.sum(dtype=torch.float32))
         self.static_input = example_input.detach().clone().requires_grad_(input_grad)
         # Parameters that already took part in a backward pass on another stream make autograd
         # warn about the stream of their accumulation nodes; the warm-up below is meant to run

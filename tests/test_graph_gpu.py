@@ -22,7 +22,7 @@ def eager_step(m, x):
     m.zero_grad(set_to_none=True)
     xi = x.clone().requires_grad_(True)
     out = m(xi)
-    loss = out.float().sum()
+    loss = out.sum(dtype=torch.float32)
     loss.backward()
     return out.detach().clone(), loss.detach().clone(), xi.grad.clone(), {n: p.grad.clone() for n, p in m.named_parameters()}
 
