@@ -22,12 +22,19 @@ SOURCES = ["fmoe_cuda.cpp", "stream_manager.cpp", "balanced_assignment.cpp", "lo
            "parallel_linear.cu"]
 
 
+def default_reference():
+    """The reference checkout: $FASTERMOE_REFERENCE, else the directory `reference` beside this repository."""
+    here = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    return os.environ.get("FASTERMOE_REFERENCE") or os.path.join(os.path.dirname(here), "reference")
+
+
 def built_path():
     hits = glob.glob(os.path.join(OUT, NAME + "*.so"))
     return hits[0] if hits else None
 
 
-def build(reference="/root/reference", verbose=False):
+def build(reference=None, verbose=False):
+    reference = reference or default_reference()
     from torch.utils import cpp_extension
     cuda_dir = os.path.join(reference, "cuda")
     os.makedirs(OUT, exist_ok=True)
@@ -40,8 +47,9 @@ def build(reference="/root/reference", verbose=False):
     return built_path()
 
 
-def build_if_possible(reference="/root/reference"):
+def build_if_possible(reference=None):
     """Builds when the reference checkout is mounted and nothing is built yet."""
+    reference = reference or default_reference()
     if built_path() or not os.path.isdir(os.path.join(reference, "cuda")):
         return built_path()
     try:

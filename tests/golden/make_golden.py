@@ -24,8 +24,9 @@ import types
 import numpy as np
 import torch
 
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
 HERE = os.path.dirname(os.path.abspath(__file__))
+# the reference checkout: first argument, else the directory `reference` beside this repository
+REF = sys.argv[1] if len(sys.argv) > 1 else os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(HERE))), "reference")
 
 stub = types.ModuleType("fmoe_cuda")
 _fake_world = {}

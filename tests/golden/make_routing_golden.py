@@ -2,7 +2,9 @@ r"""Records outputs of the reference's own CUDA routing kernels (needs a GPU).
 
 Run on the GPU box after oracle/build_ref.py has built oracle/_ref/fmoe_cuda_ref*.so:
 
-    python tests/golden/make_routing_golden.py        # writes gpurun_out/routing_ref_gpu.npz; copy it to tests/golden/
+    python tests/golden/make_routing_golden.py [output directory]
+
+writes routing_ref_gpu.npz into the given directory (default: tests/golden/).
 
 Recorded per case: the inputs and what the reference's kernels returned --
 ``expert_count`` (cuda/local_exchange.cuh:32-61), ``assign_pos`` (:5-16),
@@ -66,7 +68,7 @@ for name, t in dict(x=x, w=w, b=b, gy=gy, y=y, gx=gx, gw=gw, gb=gb).items():
     out["linear/" + name] = t.cpu().numpy()
 out["linear/counts"] = np.array(counts)
 torch.cuda.synchronize()
-dst = os.path.join(ROOT, "gpurun_out", "routing_ref_gpu.npz")
+dst = os.path.join(sys.argv[1] if len(sys.argv) > 1 else os.path.join(ROOT, "tests", "golden"), "routing_ref_gpu.npz")
 os.makedirs(os.path.dirname(dst), exist_ok=True)
 np.savez_compressed(dst, **out)
 print("wrote", dst, len(out), "arrays")
