@@ -87,7 +87,10 @@ _SIGS = {
     "fmoe_gate_topk": (I32, [P, I64, I32, I32, I32, P, P, P]),
     "fmoe_gate_topk_backward": (I32, [P, P, I64, I32, I32, I32, P, P]),
     "fmoe_peer_plan": (I32, [P, P, I32, I32, I32, I32, P, POINTER(c_int32), P, POINTER(c_int32), I32, POINTER(c_int64)]),
-    "fmoe_peer_enable": (I32, [P, I64, P]),
+    "fmoe_peer_enable": (I32, [P, I64, I64, P]),
+    "fmoe_peer_pool_bytes": (I64, [P]),
+    "fmoe_pool_alloc": (P, [c_size_t, I32, P]),
+    "fmoe_pool_free": (None, [P, c_size_t, I32, P]),
     "fmoe_peer_wait_probe": (I32, [P, I32, P]),
     "fmoe_device_status_clear": (I32, []),
     "fmoe_peer_slot_bytes": (I64, [P]),

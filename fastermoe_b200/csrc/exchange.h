@@ -32,6 +32,7 @@ int ensure_nccl_loaded();
 constexpr int kMaxPeers = 64;
 struct PeerState {
     int64_t slot_bytes = 0;
+    int64_t pool_bytes = 0;            // receive pool behind the two slots (0: none)
     char* base[kMaxPeers] = {};
     unsigned int* counter = nullptr;   // device word for last-block detection
     unsigned long long epoch = 0;      // exchanges done over peer memory (same on every rank)

@@ -6,24 +6,30 @@
 // issues one ncclSend/ncclRecv per expert and peer); the row layout on both sides
 // is the one plan_scatter describes.
 //
-// Every rank owns a "landing" allocation that its peers map through CUDA IPC:
+// Every rank owns an allocation that its peers map through CUDA IPC:
 //
-//     [ header 4 KiB | slot 0 | slot 1 ]
+//     [ header 4 KiB | slot 0 | slot 1 | receive pool ]
 //
-// One exchange, numbered by an epoch that advances in step on all ranks, uses slot
-// (epoch & 1):
-//   1. push kernel: waits until every peer has released the slot it used two epochs
-//      ago (freed flags, in this rank's header), stores its outgoing rows into the
-//      peers' slots at their final row offsets (rows that stay on this GPU go
-//      straight to the output), then the last block to finish publishes
-//      arrived[slot][rank] = epoch in every peer's header;
-//   2. consume kernel: waits for arrived == epoch from every peer, copies the rows
-//      that came from peers out of the slot into the caller's buffer, and its last
-//      block publishes freed[slot][rank] = epoch in every peer's header.
-// The two slots let a rank push epoch n while a slow peer still reads epoch n-1.
+// One exchange, numbered by an epoch that advances in step on all ranks (parity = epoch & 1):
+//   1. push kernel: its first block ANNOUNCES where this rank wants its incoming rows (a byte
+//      offset into its allocation, dest[parity][rank], then ann[parity][rank] = epoch, in every
+//      peer's header); every block then waits for the announcements of all peers, stores this
+//      rank's outgoing rows at the announced places at their final row offsets (rows that stay
+//      on this GPU go straight to the output), and the last block to finish publishes
+//      arrived[parity][rank] = epoch in every peer's header;
+//   2. consume kernel: waits for arrived == epoch from every peer; nothing else when the
+//      announced place was the output buffer itself, else it copies the rows that came from
+//      peers out of the slot into the output.
+// The output buffer can be announced directly when it lies in the receive pool: the Python
+// layer allocates exchange outputs there through a torch memory pool whose allocator is
+// fmoe_pool_alloc/fmoe_pool_free below, so tensor lifetimes stay with torch's caching
+// allocator.  Otherwise rows land in slot `parity` and are copied once more.  An announcement
+// is made by a kernel that is stream-ordered after every earlier use of the announced memory
+// on its GPU, and entry `parity` is rewritten two epochs later, after the peers have arrived
+// for the epoch in between, so neither the memory nor the entry is overwritten while in use.
 //
 // All waits are bounded (wall-clock limit, FMOE_B200_PEER_TIMEOUT_MS, default
-// 20000): when one expires the kernel raises bit 16 (slot not released) or 32 (rows
+// 20000): when one expires the kernel raises bit 16 (no announcement) or 32 (rows
 // not arrived) in the device status word and carries on, so that the stream drains.
 //
 // Whether an exchange goes over peer memory must be decided identically on all
@@ -33,16 +39,23 @@
 #include "exchange.h"
 #include <cstdlib>
 #include <cstring>
+#include <iterator>
+#include <map>
+#include <mutex>
 #include <vector>
 
 namespace fmoe {
+void pool_register(int device, char* base, size_t size);
+void* pool_take(int device, size_t bytes);
+void pool_give(int device, void* ptr, size_t bytes);
 namespace {
 
 constexpr int kHeaderBytes = 4096;
-constexpr int kFreedOffset = 1024;          // arrived[2][kMaxPeers] u64 at 0, freed[2][kMaxPeers] u64 at 1024
+// header words (u64): arrived[2][kMaxPeers] at byte 0, ann[2][kMaxPeers] at 1024, dest[2][kMaxPeers] at 2048
+constexpr int kAnnWord = 1024 / 8, kDestWord = 2048 / 8;
 constexpr int kPeerSegMax = 128;
 constexpr int kLocal = 255;                 // dst_sel of rows that stay on this GPU
-static_assert(2 * 2 * kMaxPeers * 8 <= kHeaderBytes, "flags fit the header");
+static_assert(3 * 2 * kMaxPeers * 8 <= kHeaderBytes, "flags fit the header");
 
 struct PeerSegs {
     int n;
@@ -80,10 +93,11 @@ __device__ bool wait_flag(const unsigned long long* flag, unsigned long long wan
 }
 
 struct PeerLaunch {
-    int rank, world, slot;
-    int wait_first, signal_last;            // this launch opens / closes the phase
+    int rank, world, parity;
+    int announce, signal_last;              // this launch opens / closes the push phase
     unsigned long long epoch, timeout_ns;
-    int64_t row_vecs, slot_off;             // 16-byte units per row; byte offset of the slot in an allocation
+    unsigned long long my_dest;             // push: byte offset in this rank's allocation where its rows shall land
+    int64_t row_vecs, slot_off;             // 16-byte units per row; consume: byte offset of the slot
     unsigned int* counter;
     int* status;
 };
@@ -93,15 +107,22 @@ __global__ void __launch_bounds__(256)
 peer_rows_kernel(const __grid_constant__ PeerSegs t, const __grid_constant__ PeerBases b,
                  const __grid_constant__ PeerLaunch a, const uint4* __restrict__ src, uint4* __restrict__ out) {
     __shared__ int s_last;
+    __shared__ unsigned long long s_dest[kMaxPeers];
     unsigned long long* hdr = (unsigned long long*)b.base[a.rank];
-    if (a.wait_first) {
+    {
         const int p = threadIdx.x;
         if (p < a.world && p != a.rank) {
-            if (kPush) {       // the slot must have been read out by everyone who got rows in it two epochs ago
-                if (!wait_flag(hdr + kFreedOffset / 8 + a.slot * kMaxPeers + p, a.epoch, 2, a.timeout_ns))
-                    atomicOr(a.status, 16);
+            if (kPush) {
+                if (a.announce && blockIdx.x == 0) {
+                    unsigned long long* peer_hdr = (unsigned long long*)b.base[p];
+                    peer_hdr[kDestWord + a.parity * kMaxPeers + a.rank] = a.my_dest;
+                    st_release_sys(peer_hdr + kAnnWord + a.parity * kMaxPeers + a.rank, a.epoch);
+                }
+                // where peer p wants its rows
+                if (!wait_flag(hdr + kAnnWord + a.parity * kMaxPeers + p, a.epoch, 0, a.timeout_ns)) atomicOr(a.status, 16);
+                s_dest[p] = hdr[kDestWord + a.parity * kMaxPeers + p];
             } else {           // everyone's rows of this epoch must have landed
-                if (!wait_flag(hdr + a.slot * kMaxPeers + p, a.epoch, 0, a.timeout_ns)) atomicOr(a.status, 32);
+                if (!wait_flag(hdr + a.parity * kMaxPeers + p, a.epoch, 0, a.timeout_ns)) atomicOr(a.status, 32);
             }
         }
         __syncthreads();
@@ -120,7 +141,7 @@ peer_rows_kernel(const __grid_constant__ PeerSegs t, const __grid_constant__ Pee
         if (kPush) {
             s = src + (int64_t)(t.src_row[k] + off) * a.row_vecs;
             const int sel = t.dst_sel[k];
-            d = (sel == kLocal ? out : (uint4*)(b.base[sel] + a.slot_off)) + (int64_t)(t.dst_row[k] + off) * a.row_vecs;
+            d = (sel == kLocal ? out : (uint4*)(b.base[sel] + s_dest[sel])) + (int64_t)(t.dst_row[k] + off) * a.row_vecs;
         } else {
             s = (const uint4*)(b.base[a.rank] + a.slot_off) + (int64_t)(t.src_row[k] + off) * a.row_vecs;
             d = out + (int64_t)(t.dst_row[k] + off) * a.row_vecs;
@@ -134,7 +155,7 @@ peer_rows_kernel(const __grid_constant__ PeerSegs t, const __grid_constant__ Pee
         }
         for (; c < a.row_vecs; c += 32) d[c] = __ldcg(s + c);
     }
-    if (a.signal_last) {
+    if (kPush && a.signal_last) {
         // All of this block's stores are ordered before thread 0's fence by the barrier,
         // and the fence is cumulative: one fence per block publishes them.
         __syncthreads();
@@ -148,7 +169,7 @@ peer_rows_kernel(const __grid_constant__ PeerSegs t, const __grid_constant__ Pee
             const int p = threadIdx.x;
             if (p < a.world && p != a.rank) {
                 unsigned long long* peer_hdr = (unsigned long long*)b.base[p];
-                st_release_sys(peer_hdr + (kPush ? 0 : kFreedOffset / 8) + a.slot * kMaxPeers + a.rank, a.epoch);
+                st_release_sys(peer_hdr + a.parity * kMaxPeers + a.rank, a.epoch);
             }
             if (threadIdx.x == 0) *a.counter = 0;
         }
@@ -158,16 +179,17 @@ peer_rows_kernel(const __grid_constant__ PeerSegs t, const __grid_constant__ Pee
 struct Seg { int sel; int64_t src_row, dst_row, rows; };
 
 template <bool kPush>
-int launch_phase(Comm* c, const std::vector<Seg>& segs, const void* src, void* out, int64_t row_bytes, int slot,
-                 cudaStream_t st) {
+int launch_phase(Comm* c, const std::vector<Seg>& segs, const void* src, void* out, int64_t row_bytes, int parity,
+                 unsigned long long my_dest, cudaStream_t st) {
     PeerBases b;
     for (int p = 0; p < kMaxPeers; ++p) b.base[p] = c->peer.base[p];
     PeerLaunch a;
-    a.rank = c->rank; a.world = c->world; a.slot = slot;
+    a.rank = c->rank; a.world = c->world; a.parity = parity;
     a.epoch = c->peer.epoch; a.timeout_ns = c->peer.timeout_ns;
+    a.my_dest = my_dest;
     a.row_vecs = row_bytes / 16;
-    a.slot_off = kHeaderBytes + (int64_t)slot * c->peer.slot_bytes;
-    a.counter = c->peer.counter + (kPush ? 0 : 1);
+    a.slot_off = kHeaderBytes + (int64_t)parity * c->peer.slot_bytes;
+    a.counter = c->peer.counter;
     a.status = device_status_ptr();
     FMOE_REQUIRE(a.status, "peer exchange: no device status word");
     PeerSegs t;
@@ -185,7 +207,7 @@ int launch_phase(Comm* c, const std::vector<Seg>& segs, const void* src, void* o
             ++t.n;
         }
         if (t.n == 0) t.prefix[1] = 0;
-        a.wait_first = first;
+        a.announce = first;
         a.signal_last = i >= segs.size();
         const unsigned blocks = (unsigned)std::max<int64_t>(1, ceil_div(t.n ? t.prefix[t.n] : 0, 8));
         peer_rows_kernel<kPush><<<blocks, 256, 0, st>>>(t, b, a, (const uint4*)src, (uint4*)out);
@@ -316,17 +338,79 @@ int peer_move(fmoe_comm_t comm, const void* in, void* out, const int64_t* table,
         FMOE_CUDA_TRY(cudaMemsetAsync((char*)out + plan.token_rows * row_bytes, 0,
                                       (size_t)(out_rows - plan.token_rows) * row_bytes, st));
     c->peer.epoch += 1;
-    const int slot = (int)(c->peer.epoch & 1);
-    if (int rc = launch_phase<true>(c, plan.push, in, out, row_bytes, slot, st)) return rc;
-    return launch_phase<false>(c, plan.pull, nullptr, out, row_bytes, slot, st);
+    const int parity = (int)(c->peer.epoch & 1);
+    // Rows can land in the output itself when it lies in this rank's receive pool.
+    char* pool = c->peer.base[c->rank] + kHeaderBytes + 2 * c->peer.slot_bytes;
+    const int64_t recv_bytes = (reverse ? out_rows : plan.expert_rows) * row_bytes;
+    const bool direct = c->peer.pool_bytes > 0 && (char*)out >= pool && (char*)out + recv_bytes <= pool + c->peer.pool_bytes;
+    const unsigned long long my_dest = direct ? (unsigned long long)((char*)out - c->peer.base[c->rank])
+                                              : (unsigned long long)(kHeaderBytes + (int64_t)parity * c->peer.slot_bytes);
+    if (int rc = launch_phase<true>(c, plan.push, in, out, row_bytes, parity, my_dest, st)) return rc;
+    static const std::vector<Seg> nothing;
+    return launch_phase<false>(c, direct ? nothing : plan.pull, nullptr, out, row_bytes, parity, 0, st);
 }
 
 }  // namespace
+
+// ---- receive pool: first-fit free list over one region per device ------------------------
+namespace {
+struct Pool {
+    char* base = nullptr;
+    size_t size = 0;
+    std::map<size_t, size_t> free_;   // offset -> length, coalesced
+};
+Pool g_pool[64];
+std::mutex g_pool_mtx;
+constexpr size_t kPoolAlign = 512;
+}  // namespace
+
+void pool_register(int device, char* base, size_t size) {
+    if (device < 0 || device >= 64) return;
+    std::lock_guard<std::mutex> lk(g_pool_mtx);
+    Pool& p = g_pool[device];
+    p.base = base;
+    p.size = size;
+    p.free_.clear();
+    if (base && size) p.free_[0] = size;
+}
+
+void* pool_take(int device, size_t bytes) {
+    if (device < 0 || device >= 64) return nullptr;
+    bytes = (bytes + kPoolAlign - 1) & ~(kPoolAlign - 1);
+    std::lock_guard<std::mutex> lk(g_pool_mtx);
+    Pool& p = g_pool[device];
+    for (auto it = p.free_.begin(); it != p.free_.end(); ++it) {
+        if (it->second < bytes) continue;
+        const size_t off = it->first, len = it->second;
+        p.free_.erase(it);
+        if (len > bytes) p.free_[off + bytes] = len - bytes;
+        return p.base + off;
+    }
+    return nullptr;
+}
+
+void pool_give(int device, void* ptr, size_t bytes) {
+    if (device < 0 || device >= 64 || !ptr) return;
+    bytes = (bytes + kPoolAlign - 1) & ~(kPoolAlign - 1);
+    std::lock_guard<std::mutex> lk(g_pool_mtx);
+    Pool& p = g_pool[device];
+    if (!p.base || (char*)ptr < p.base || (char*)ptr + bytes > p.base + p.size) return;   // region already gone
+    size_t off = (size_t)((char*)ptr - p.base), len = bytes;
+    auto next = p.free_.lower_bound(off);
+    if (next != p.free_.begin()) {
+        auto prev = std::prev(next);
+        if (prev->first + prev->second == off) { off = prev->first; len += prev->second; p.free_.erase(prev); }
+    }
+    if (next != p.free_.end() && off + len == next->first) { len += next->second; p.free_.erase(next); }
+    p.free_[off] = len;
+}
 
 void peer_release(Comm* c) {
     PeerState& ps = c->peer;
     if (ps.slot_bytes == 0) return;
     cudaDeviceSynchronize();
+    if (ps.pool_bytes) pool_register(c->device, nullptr, 0);
+    ps.pool_bytes = 0;
     for (int p = 0; p < c->world && p < kMaxPeers; ++p) {
         if (!ps.base[p]) continue;
         if (p == c->rank) cudaFree(ps.base[p]);
@@ -343,10 +427,12 @@ void peer_release(Comm* c) {
 
 using namespace fmoe;
 
-extern "C" int fmoe_peer_enable(fmoe_comm_t comm, int64_t slot_bytes, fmoe_stream_t stream) {
+extern "C" int fmoe_peer_enable(fmoe_comm_t comm, int64_t slot_bytes, int64_t pool_bytes, fmoe_stream_t stream) {
     FMOE_REQUIRE(comm, "peer_enable: null communicator");
     Comm* c = (Comm*)comm;
-    FMOE_REQUIRE(slot_bytes >= 0, "peer_enable: slot_bytes=%lld", (long long)slot_bytes);
+    FMOE_REQUIRE(slot_bytes >= 0 && pool_bytes >= 0, "peer_enable: slot_bytes=%lld pool_bytes=%lld", (long long)slot_bytes,
+                 (long long)pool_bytes);
+    pool_bytes = (pool_bytes + 511) & ~(int64_t)511;
     if (c->peer.slot_bytes) return 0;          // already on
     if (c->world < 2 || c->world > kMaxPeers || slot_bytes == 0) return 0;
     cudaStream_t st = (cudaStream_t)stream;
@@ -359,7 +445,7 @@ extern "C" int fmoe_peer_enable(fmoe_comm_t comm, int64_t slot_bytes, fmoe_strea
     char* own = nullptr;
     cudaIpcMemHandle_t handle;
     memset(&handle, 0, sizeof(handle));
-    if (cudaMalloc((void**)&own, (size_t)kHeaderBytes + 2 * (size_t)slot_bytes) != cudaSuccess) { ok = 0; own = nullptr; }
+    if (cudaMalloc((void**)&own, (size_t)kHeaderBytes + 2 * (size_t)slot_bytes + (size_t)pool_bytes) != cudaSuccess) { ok = 0; own = nullptr; }
     if (ok && (cudaMemset(own, 0, kHeaderBytes) != cudaSuccess || cudaDeviceSynchronize() != cudaSuccess)) ok = 0;
     if (ok && cudaIpcGetMemHandle(&handle, own) != cudaSuccess) ok = 0;
     (void)cudaGetLastError();
@@ -418,8 +504,17 @@ extern "C" int fmoe_peer_enable(fmoe_comm_t comm, int64_t slot_bytes, fmoe_strea
     if (ms < 1) ms = 1;
     c->peer.timeout_ns = (unsigned long long)ms * 1000000ull;
     c->peer.slot_bytes = slot_bytes;
+    c->peer.pool_bytes = pool_bytes;
+    if (pool_bytes > 0) pool_register(c->device, own + kHeaderBytes + 2 * slot_bytes, (size_t)pool_bytes);
     return 0;
 }
+
+extern "C" int64_t fmoe_peer_pool_bytes(fmoe_comm_t comm) { return comm ? ((Comm*)comm)->peer.pool_bytes : 0; }
+
+// Allocator functions for torch.cuda.memory.CUDAPluggableAllocator: sub-allocate this device's
+// receive pool.  A NULL result makes torch report an out-of-memory condition for the request.
+extern "C" void* fmoe_pool_alloc(ptrdiff_t size, int device, void*) { return pool_take(device, size > 0 ? (size_t)size : 1); }
+extern "C" void fmoe_pool_free(void* ptr, ptrdiff_t size, int device, void*) { pool_give(device, ptr, size > 0 ? (size_t)size : 1); }
 
 extern "C" int fmoe_peer_wait_probe(fmoe_comm_t comm, int32_t timeout_ms, fmoe_stream_t stream) {
     FMOE_REQUIRE(comm, "peer_wait_probe: null communicator");
@@ -435,11 +530,11 @@ extern "C" int fmoe_peer_wait_probe(fmoe_comm_t comm, int32_t timeout_ms, fmoe_s
     PeerSegs t;
     t.n = 0; t.prefix[0] = 0; t.prefix[1] = 0;
     PeerLaunch a;
-    a.rank = c->rank; a.world = c->world; a.slot = 0;
-    a.wait_first = 1; a.signal_last = 0;
+    a.rank = c->rank; a.world = c->world; a.parity = 0;
+    a.announce = 0; a.signal_last = 0; a.my_dest = 0;
     a.epoch = c->peer.epoch; a.timeout_ns = c->peer.timeout_ns;
     a.row_vecs = 1; a.slot_off = kHeaderBytes;
-    a.counter = c->peer.counter + 1;
+    a.counter = c->peer.counter;
     a.status = device_status_ptr();
     c->peer.epoch = epoch;
     c->peer.timeout_ns = limit;

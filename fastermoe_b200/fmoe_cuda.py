@@ -264,8 +264,9 @@ def ensure_nccl(group, t):
         # (FMOE_B200_PEER=0 keeps NCCL send/receive; FMOE_B200_PEER_SLOT_MB sizes the landing slots).
         if world > 1 and os.environ.get("FMOE_B200_PEER", "1") != "0":
             slot = int(os.environ.get("FMOE_B200_PEER_SLOT_MB", "256")) << 20
+            pool = int(os.environ.get("FMOE_B200_PEER_POOL_MB", "2048")) << 20
             with torch.cuda.device(dev):
-                _run("peer_enable", lib.fmoe_peer_enable, handle, slot, _stream())
+                _run("peer_enable", lib.fmoe_peer_enable, handle, slot, pool, _stream())
 
 
 def peer_slot_bytes(device):
@@ -281,7 +282,9 @@ def comm_rank(device):
 
 
 def destroy_comms():
-    """Destroys every communicator created by ensure_nccl (for orderly shutdown)."""
+    """Destroys every communicator created by ensure_nccl (for orderly shutdown).  Tensors that were
+    allocated from a receive pool must not be used afterwards: the pool's memory goes with it."""
+    _recv_pools.clear()
     with _comm_lock:
         for h in _comms.values():
             lib.fmoe_comm_destroy(h)
@@ -353,11 +356,41 @@ def global_gather(output_buf, local_expert_count, global_expert_count, stored_mo
                         global_expert_count, stored_models, batch_size, n_workers)
 
 
+_recv_pools = {}
+
+
+def _recv_pool(device):
+    """torch memory pool over this device's peer-mapped receive pool (None: there is none).  Exchange
+    outputs allocated from it are written by the peers directly; torch's caching allocator keeps
+    managing their lifetime (it obtains its segments from fmoe_pool_alloc)."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    if idx not in _recv_pools:
+        pool = None
+        c = _comms.get(idx)
+        if c is not None and int(lib.fmoe_peer_pool_bytes(c)) > 0 and hasattr(torch.cuda, "MemPool"):
+            alloc = torch.cuda.memory.CUDAPluggableAllocator(_lib.LIB_PATH, "fmoe_pool_alloc", "fmoe_pool_free")
+            pool = (torch.cuda.MemPool(alloc.allocator()), alloc)      # the allocator object must stay alive
+        _recv_pools[idx] = pool
+    return _recv_pools[idx]
+
+
+def _recv_empty(like, rows):
+    """Output buffer of a peer exchange: from the receive pool when there is one and it has room."""
+    pool = _recv_pool(like.device)
+    if pool is not None:
+        try:
+            with torch.cuda.use_mem_pool(pool[0], device=like.device):
+                return like.new_empty((rows, like.shape[1]))
+        except torch.OutOfMemoryError:
+            pass
+    return like.new_empty((rows, like.shape[1]))
+
+
 def _peer_move(fn, name, buf, table, stored_models, batch_size, n_expert, n_workers):
     _check_cuda(buf)
     tab, st = _host_i64(table.reshape(-1)), _host_flags(stored_models)
     assert tab.numel() == n_workers * n_workers * n_expert
-    out = buf.new_empty((batch_size, buf.shape[1]))
+    out = _recv_empty(buf, batch_size)
     with torch.cuda.device(buf.device):
         ok = _run(name, fn, _comm(buf.device), _ptr(buf), _ptr(out), _ptr(tab), _ptr(st), buf.shape[0], batch_size,
                   buf.shape[1] * buf.element_size(), n_expert, n_workers, _stream(), soft=True)

@@ -343,8 +343,8 @@ int fmoe_global_gather(fmoe_comm_t comm, const void* global_in, void* local_out,
  * kernel and published with flags; no NCCL call is made.
  *
  * fmoe_peer_enable is collective over the communicator: every rank allocates a
- * landing area of 2 slots of slot_bytes (+4 KiB of flags), the ranks swap CUDA IPC
- * handles and map each other's areas.  If any rank cannot (no peer access, IPC
+ * landing area of 2 slots of slot_bytes (+4 KiB of flags, + an optional receive pool), the
+ * ranks swap CUDA IPC handles and map each other's areas.  If any rank cannot (no peer access, IPC
  * closed to the process), the form stays off on every rank and FMOE_OK is
  * returned; fmoe_peer_slot_bytes then reports 0.
  *
@@ -373,7 +373,15 @@ int fmoe_peer_plan(const int64_t* all_expert_count_host, const uint8_t* stored_m
                    int32_t rank, int32_t n_expert, int32_t n_workers, int32_t reverse,
                    fmoe_peer_seg_t* push, int32_t* n_push, fmoe_peer_seg_t* pull, int32_t* n_pull,
                    int32_t max_segs, int64_t* slot_rows);
-int fmoe_peer_enable(fmoe_comm_t comm, int64_t slot_bytes, fmoe_stream_t stream);
+int fmoe_peer_enable(fmoe_comm_t comm, int64_t slot_bytes, int64_t pool_bytes, fmoe_stream_t stream);
+/* Receive pool (pool_bytes > 0 above): a region of the same peer-mapped allocation out of which a
+ * host can allocate the OUTPUT buffers of fmoe_peer_global_scatter / _gather; rows then land in the
+ * output directly instead of in a slot from which they are copied once more.  fmoe_pool_alloc /
+ * fmoe_pool_free have the signature torch.cuda.memory.CUDAPluggableAllocator expects (first-fit
+ * sub-allocation of the region, NULL when it is exhausted); fmoe_peer_pool_bytes: its size. */
+int64_t fmoe_peer_pool_bytes(fmoe_comm_t comm);
+void* fmoe_pool_alloc(ptrdiff_t size, int device, void* stream);
+void fmoe_pool_free(void* ptr, ptrdiff_t size, int device, void* stream);
 /* Queues a wait of the exchange's consume step for rows that no peer will ever announce, bounded by
  * timeout_ms: when it expires the kernel raises bit 32 of fmoe_device_status and returns; the
  * exchange state is untouched.  Lets a host check that its handling of an expired wait works

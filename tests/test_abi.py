@@ -123,3 +123,13 @@ def test_product_never_imports_oracle():
         for f in files:
             if f.endswith((".py", ".cu", ".cuh", ".h")):
                 assert "oracle" not in open(os.path.join(base, f)).read().lower().replace("test oracle", ""), f
+
+
+def test_pool_allocator_without_a_pool():
+    """The torch-allocator entry points answer NULL (out of memory) when no receive pool exists,
+    and accept a free of memory they do not own."""
+    import ctypes
+    from fastermoe_b200 import _lib
+    assert _lib.lib.fmoe_pool_alloc(1 << 20, 0, None) is None
+    _lib.lib.fmoe_pool_free(ctypes.c_void_p(4096), 1 << 20, 0, None)
+    assert _lib.lib.fmoe_peer_pool_bytes(None) == 0
