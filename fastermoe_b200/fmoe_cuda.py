@@ -374,15 +374,23 @@ def _recv_pool(device):
     return _recv_pools[idx]
 
 
+_pool_backoff = {}
+
+
 def _recv_empty(like, rows):
-    """Output buffer of a peer exchange: from the receive pool when there is one and it has room."""
+    """Output buffer of a peer exchange: from the receive pool when there is one and it has room
+    (after a refusal the pool is left alone for the next 64 requests: a failed request is slow)."""
     pool = _recv_pool(like.device)
     if pool is not None:
-        try:
-            with torch.cuda.use_mem_pool(pool[0], device=like.device):
-                return like.new_empty((rows, like.shape[1]))
-        except torch.OutOfMemoryError:
-            pass
+        idx = like.device.index
+        if _pool_backoff.get(idx, 0) > 0:
+            _pool_backoff[idx] -= 1
+        else:
+            try:
+                with torch.cuda.use_mem_pool(pool[0], device=like.device):
+                    return like.new_empty((rows, like.shape[1]))
+            except torch.OutOfMemoryError:
+                _pool_backoff[idx] = 64
     return like.new_empty((rows, like.shape[1]))
 
 
