@@ -54,3 +54,12 @@ def test_full_size_configs():
     needs_gpus()
     run_ranks(dist_worker.gpu_full_size, 2, limit_s=400)
 
+
+def test_receive_pool_exhaustion(monkeypatch):
+    """With a 1 MB receive pool some exchange outputs fit in it and most do not: rows are then received
+    through the landing slots and copied; both ways in one run give the same layer results."""
+    needs_gpus()
+    monkeypatch.setenv("FMOE_B200_PEER_POOL_MB", "1")
+    run_ranks(dist_worker.gpu_layer_bf16, 2)
+    monkeypatch.setenv("FMOE_B200_PEER_POOL_MB", "0")
+    run_ranks(dist_worker.gpu_layer_bf16, 2)
