@@ -104,6 +104,20 @@ def gpu_exchange(rank, world, port):
                                       torch.from_numpy(gecs[rank]).to(dev).view(world, E),
                                       torch.from_numpy(stored).to(dev).view(world, E), E, world)
         assert np.array_equal(cc.cpu().numpy(), O.generate_cached_count(lecs[rank], gecs[rank], stored, rank, E, world))
+    # more row segments than one launch of the peer kernels takes (128): several launches per phase
+    if fc.peer_slot_bytes(dev) > 0:
+        E2 = 80
+        lecs2 = all_lecs(world, E2, 6, lo=0, hi=5)
+        table2, _, _ = O.expert_exchange(lecs2, E2, world)
+        none2 = np.zeros(world * E2, bool)
+        bufs2 = [np.random.default_rng(10 + r).standard_normal((int(lecs2[r].sum()), 8)).astype(np.float32) for r in range(world)]
+        want2 = O.global_scatter(bufs2, lecs2, none2, E2, world)
+        for rnd in range(3):
+            mine = torch.from_numpy(bufs2[rank]).to(dev) + rnd
+            out = fc.peer_global_scatter(mine, torch.from_numpy(table2.copy()), torch.from_numpy(none2), want2[rank].shape[0], E2, world)
+            assert out is not None and torch.equal(out, torch.from_numpy(want2[rank]).to(dev) + rnd), "many-segment scatter"
+            back = fc.peer_global_gather(out, torch.from_numpy(table2.copy()), torch.from_numpy(none2), mine.shape[0], E2, world)
+            assert torch.equal(back, mine), "many-segment gather"
     # mismatched buffer size is caught before anything is queued
     try:
         fc.global_scatter(torch.zeros(int(lecs[rank].sum()), d, device=dev), torch.from_numpy(lecs[rank]),
