@@ -144,6 +144,23 @@ def workload_config(n_gpus):
             "parallelism": f"ep{n_gpus}", "l2": "inputs larger than L2 (no flush)"}
 
 
+def bind_to_gpu_cpus(local_rank):
+    """Sets this process's CPU affinity to the cores NVML reports as local to its GPU (no-op on failure)."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+        index = int(visible.split(",")[local_rank]) if visible and visible.split(",")[local_rank].isdigit() else local_rank
+        handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+        words = pynvml.nvmlDeviceGetCpuAffinity(handle, (os.cpu_count() + 63) // 64)
+        cpus = {64 * i + b for i, w in enumerate(words) for b in range(64) if (w >> b) & 1}
+        allowed = cpus & os.sched_getaffinity(0)
+        if allowed:
+            os.sched_setaffinity(0, allowed)
+    except Exception:
+        pass
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -156,6 +173,9 @@ def run_ours(args):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
+        # One process per GPU: run it (and allocate its pinned batch) on the CPUs next to its GPU, as a
+        # launcher with NUMA binding would; otherwise the ranks' host-to-device copies cross sockets.
+        bind_to_gpu_cpus(local_rank)
         dist.init_process_group("nccl", device_id=dev)
 
     T, d, h, E, k = (CFG[n] for n in ("tokens_per_gpu", "d_model", "d_hidden", "experts_per_gpu", "top_k"))
