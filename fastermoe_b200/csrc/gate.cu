@@ -71,6 +71,40 @@ topk_forward_kernel(const T* __restrict__ logits, int64_t n_tokens, int n_expert
     }
 }
 
+// Few experts (<= 32): one THREAD per token; a warp then reads 32 consecutive rows, i.e. one
+// contiguous stretch of the logits, and no lane idles.  Same order as the warp kernel.
+template <typename T>
+__global__ void __launch_bounds__(256)
+topk_forward_small_kernel(const T* __restrict__ logits, int64_t n_tokens, int n_expert, int k, T* __restrict__ values,
+                          int64_t* __restrict__ indices) {
+    const int64_t tok = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (tok >= n_tokens) return;
+    const T* row = logits + tok * n_expert;
+    float best[kTopKMax];
+    int best_i[kTopKMax];
+#pragma unroll
+    for (int j = 0; j < kTopKMax; ++j) { best[j] = -INFINITY; best_i[j] = INT_MAX; }
+    for (int e = 0; e < n_expert; ++e) {
+        float v = to_float(row[e]);
+        int vi = e;
+#pragma unroll
+        for (int j = 0; j < kTopKMax; ++j) {
+            if (j < k && ranks_before(v, vi, best[j], best_i[j])) {
+                const float tv = best[j]; const int ti = best_i[j];
+                best[j] = v; best_i[j] = vi;
+                v = tv; vi = ti;
+            }
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < kTopKMax; ++j) {
+        if (j < k) {
+            values[tok * k + j] = row[best_i[j]];
+            indices[tok * k + j] = best_i[j];
+        }
+    }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256)
 topk_backward_kernel(const T* __restrict__ grad_values, const int64_t* __restrict__ indices, int64_t n_tokens,
@@ -100,6 +134,16 @@ extern "C" int fmoe_gate_topk(const void* logits, int64_t n_tokens, int32_t n_ex
     if (n_tokens == 0) return 0;
     FMOE_REQUIRE(logits && values && indices, "gate_topk: null pointer");
     cudaStream_t st = (cudaStream_t)stream;
+    if (n_expert_total <= 32) {
+        const unsigned nb = (unsigned)ceil_div(n_tokens, 256);
+        switch (dtype) {
+            case FMOE_F32: topk_forward_small_kernel<float><<<nb, 256, 0, st>>>((const float*)logits, n_tokens, n_expert_total, k, (float*)values, indices); break;
+            case FMOE_F16: topk_forward_small_kernel<__half><<<nb, 256, 0, st>>>((const __half*)logits, n_tokens, n_expert_total, k, (__half*)values, indices); break;
+            default: topk_forward_small_kernel<__nv_bfloat16><<<nb, 256, 0, st>>>((const __nv_bfloat16*)logits, n_tokens, n_expert_total, k, (__nv_bfloat16*)values, indices); break;
+        }
+        FMOE_CHECK_LAUNCH();
+        return 0;
+    }
     const unsigned blocks = (unsigned)ceil_div(n_tokens, 8);
     switch (dtype) {
         case FMOE_F32: topk_forward_kernel<float><<<blocks, 256, 0, st>>>((const float*)logits, n_tokens, n_expert_total, k, (float*)values, indices); break;

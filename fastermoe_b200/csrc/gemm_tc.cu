@@ -1102,14 +1102,16 @@ bias_grad_tc_kernel(const uint16_t* __restrict__ dy, const int64_t* __restrict__
 }
 
 // Adds up the per-block partial column sums that the input-gradient kernel left in the
-// scratch buffer: out[e, col] = sum over the 32-row blocks of expert e, in block order.
+// scratch buffer: out[e, col] = sum over the 32-row blocks of expert e.  Four thread rows
+// take a quarter of the blocks each (in block order) and the quarters are added in order,
+// so the result does not depend on timing.
 template <bool BF16>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(512)
 colsum_finish_kernel(const float* __restrict__ partial, const int64_t* __restrict__ seg, const __grid_constant__ HostSegs hs,
                      uint16_t* __restrict__ out, int n_cols, int accumulate) {
-    const int e = blockIdx.y;
+    __shared__ float2 part[4][128];
+    const int e = blockIdx.y, q = threadIdx.y;
     const int col = (blockIdx.x * 128 + threadIdx.x) * 2;
-    if (col >= n_cols) return;
     int base = 0;
     for (int j = 0; j < e; ++j) {
         const int64_t lo = hs.n ? (int64_t)hs.lo[j] : seg[j], hi = hs.n ? (int64_t)hs.hi[j] : seg[j + 1];
@@ -1117,20 +1119,29 @@ colsum_finish_kernel(const float* __restrict__ partial, const int64_t* __restric
     }
     const int64_t lo = hs.n ? (int64_t)hs.lo[e] : seg[e], hi = hs.n ? (int64_t)hs.hi[e] : seg[e + 1];
     const int nb = (int)((hi - lo + 31) >> 5);
+    const int per = (nb + 3) >> 2;
+    const int b0 = min(nb, q * per), b1 = min(nb, b0 + per);
     float t0 = 0.f, t1 = 0.f;
-    const float* src = partial + (size_t)base * n_cols + col;
-    int b = 0;
-    for (; b + 3 < nb; b += 4) {
-        const float2 v0 = *reinterpret_cast<const float2*>(src + (size_t)b * n_cols);
-        const float2 v1 = *reinterpret_cast<const float2*>(src + (size_t)(b + 1) * n_cols);
-        const float2 v2 = *reinterpret_cast<const float2*>(src + (size_t)(b + 2) * n_cols);
-        const float2 v3 = *reinterpret_cast<const float2*>(src + (size_t)(b + 3) * n_cols);
-        t0 += v0.x; t1 += v0.y; t0 += v1.x; t1 += v1.y; t0 += v2.x; t1 += v2.y; t0 += v3.x; t1 += v3.y;
+    if (col < n_cols) {
+        const float* src = partial + (size_t)base * n_cols + col;
+        int b = b0;
+        for (; b + 3 < b1; b += 4) {
+            const float2 v0 = *reinterpret_cast<const float2*>(src + (size_t)b * n_cols);
+            const float2 v1 = *reinterpret_cast<const float2*>(src + (size_t)(b + 1) * n_cols);
+            const float2 v2 = *reinterpret_cast<const float2*>(src + (size_t)(b + 2) * n_cols);
+            const float2 v3 = *reinterpret_cast<const float2*>(src + (size_t)(b + 3) * n_cols);
+            t0 += v0.x; t1 += v0.y; t0 += v1.x; t1 += v1.y; t0 += v2.x; t1 += v2.y; t0 += v3.x; t1 += v3.y;
+        }
+        for (; b < b1; ++b) {
+            const float2 v = *reinterpret_cast<const float2*>(src + (size_t)b * n_cols);
+            t0 += v.x; t1 += v.y;
+        }
     }
-    for (; b < nb; ++b) {
-        const float2 v = *reinterpret_cast<const float2*>(src + (size_t)b * n_cols);
-        t0 += v.x; t1 += v.y;
-    }
+    part[q][threadIdx.x] = make_float2(t0, t1);
+    __syncthreads();
+    if (q != 0 || col >= n_cols) return;
+    t0 = part[0][threadIdx.x].x + part[1][threadIdx.x].x + part[2][threadIdx.x].x + part[3][threadIdx.x].x;
+    t1 = part[0][threadIdx.x].y + part[1][threadIdx.x].y + part[2][threadIdx.x].y + part[3][threadIdx.x].y;
     uint32_t* o = reinterpret_cast<uint32_t*>(out + (size_t)e * n_cols + col);
     if (accumulate) {
         float x0, x1;
@@ -1251,10 +1262,10 @@ int tc_linear_backward(const LinearBwdArgs& a, cudaStream_t st) {
         if (a.grad_x_colsum) {
             const HostSegs& hs = a.host_segs ? *a.host_segs : kNoSegs;
             dim3 grid((unsigned)ceil_div(a.in_feat, 256), (unsigned)a.n_expert);
-            if (bf16) colsum_finish_kernel<true><<<grid, 128, 0, st>>>((const float*)a.scratch, a.seg_offsets, hs,
-                                                                       (uint16_t*)a.grad_x_colsum, (int)a.in_feat, 0);
-            else colsum_finish_kernel<false><<<grid, 128, 0, st>>>((const float*)a.scratch, a.seg_offsets, hs,
-                                                                   (uint16_t*)a.grad_x_colsum, (int)a.in_feat, 0);
+            if (bf16) colsum_finish_kernel<true><<<grid, dim3(128, 4), 0, st>>>((const float*)a.scratch, a.seg_offsets, hs,
+                                                                                (uint16_t*)a.grad_x_colsum, (int)a.in_feat, 0);
+            else colsum_finish_kernel<false><<<grid, dim3(128, 4), 0, st>>>((const float*)a.scratch, a.seg_offsets, hs,
+                                                                            (uint16_t*)a.grad_x_colsum, (int)a.in_feat, 0);
             FMOE_CHECK_LAUNCH();
         }
     }
