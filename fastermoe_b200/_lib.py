@@ -13,6 +13,7 @@ LIB_PATH = os.path.join(_HERE, "libfmoe_b200.so")
 
 F32, F16, BF16 = 0, 1, 2
 ACT_NONE, ACT_RELU, ACT_GELU = 0, 1, 2
+GEMM_FORMS = {"auto": 0, "pair": 1, "tc1": 2, "simt": 3}
 MAX_EXPERTS = 4096
 
 
@@ -58,6 +59,8 @@ _SIGS = {
     "fmoe_version": (c_int32, []),
     "fmoe_built_for_sm": (c_int32, []),
     "fmoe_device_status": (I32, [POINTER(c_int32)]),
+    "fmoe_gemm_set_form": (I32, [I32]),
+    "fmoe_gemm_set_sm_limit": (I32, [I32]),
     "fmoe_routing_scratch_bytes": (c_size_t, [I64, I32]),
     "fmoe_expert_count": (I32, [P, P, I64, I32, P]),
     "fmoe_assign_pos": (I32, [P, P, P, I64, I32, P, P]),
@@ -70,6 +73,8 @@ _SIGS = {
     "fmoe_local_gather": (I32, [P, P, P, I64, I64, I64, P, P]),
     "fmoe_local_gather_inv": (I32, [P, P, P, I64, I64, P]),
     "fmoe_local_gather_sum": (I32, [P, P, P, I64, I32, I64, I32, P]),
+    "fmoe_local_gather_add_scratch_bytes": (c_size_t, [I64]),
+    "fmoe_local_gather_add": (I32, [P, P, P, I64, I64, I64, I32, P, P]),
     "fmoe_combine_forward": (I32, [P, P, P, P, I64, I32, I64, I32, P]),
     "fmoe_combine_backward": (I32, [P, P, P, P, P, P, I64, I32, I64, I32, P]),
     "fmoe_linear_scratch_bytes": (c_size_t, [I64, I64, I64, I32, I32]),

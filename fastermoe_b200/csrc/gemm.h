@@ -14,6 +14,28 @@ struct HostSegs {
     int hi[kMaxHostSegs];
 };
 
+#ifdef __CUDACC__
+// Row range [lo, hi) of expert e, made safe for buffers of n_rows rows: the offsets come from
+// device memory that no host code has looked at, so a range is clamped to start no earlier than
+// the previous expert's end and to end no later than n_rows.  Valid offsets (non-decreasing,
+// last one <= n_rows) pass through unchanged.  Returns true when something had to be clamped.
+__device__ __forceinline__ bool safe_seg_range(const int64_t* __restrict__ off, const HostSegs& hs, int e, int64_t n_rows,
+                                               int64_t& lo, int64_t& hi) {
+    int64_t prev_hi = 0;
+    bool clamped = false;
+    for (int j = 0; j <= e; ++j) {
+        const int64_t raw_lo = hs.n ? (int64_t)hs.lo[j] : off[j], raw_hi = hs.n ? (int64_t)hs.hi[j] : off[j + 1];
+        lo = raw_lo < prev_hi ? prev_hi : raw_lo;
+        if (lo > n_rows) lo = n_rows;
+        hi = raw_hi < lo ? lo : raw_hi;
+        if (hi > n_rows) hi = n_rows;
+        clamped |= lo != raw_lo || hi != raw_hi;
+        prev_hi = hi;
+    }
+    return clamped;
+}
+#endif
+
 struct LinearArgs {
     const void* x;       // [n_rows, in_feat]
     const void* weight;  // [n_expert, out_feat, in_feat]
@@ -46,6 +68,9 @@ struct LinearBwdArgs {
 
 int simt_linear_forward(const LinearArgs& a, cudaStream_t st);
 int simt_linear_backward(const LinearBwdArgs& a, cudaStream_t st);
+
+// Current FMOE_GEMM_* form (see fmoe_gemm_set_form).
+int gemm_form();
 
 // Picks the tensor-core kernels when the shapes allow it, else the FFMA kernels.
 int dispatch_linear_forward(const LinearArgs& a, cudaStream_t st);

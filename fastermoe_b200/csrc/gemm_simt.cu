@@ -47,19 +47,17 @@ struct TileMap {
     int rows;      // valid rows in the tile
 };
 
-__device__ __forceinline__ int64_t seg_lo(const int64_t* __restrict__ off, const HostSegs& hs, int e) {
-    return hs.n ? (int64_t)hs.lo[e] : off[e];
-}
-__device__ __forceinline__ int64_t seg_hi(const int64_t* __restrict__ off, const HostSegs& hs, int e) {
-    return hs.n ? (int64_t)hs.hi[e] : off[e + 1];
-}
-
-// Maps a linear m-tile index to (expert, rows) by walking the segment table.
+// Maps a linear m-tile index to (expert, rows) by walking the segment table (ranges are clamped
+// to the buffer's n_rows rows and to run forwards, see safe_seg_range).
 __device__ __forceinline__ bool find_tile(const int64_t* __restrict__ off, const HostSegs& hs, int n_expert,
-                                          int64_t tile, TileMap& tm) {
-    int64_t acc = 0;
+                                          int64_t n_rows, int64_t tile, TileMap& tm) {
+    int64_t acc = 0, prev_hi = 0;
     for (int e = 0; e < n_expert; ++e) {
-        const int64_t lo = seg_lo(off, hs, e), cnt = seg_hi(off, hs, e) - lo;
+        int64_t lo = hs.n ? (int64_t)hs.lo[e] : off[e], hi = hs.n ? (int64_t)hs.hi[e] : off[e + 1];
+        lo = min(max(lo, prev_hi), n_rows);
+        hi = min(max(hi, lo), n_rows);
+        prev_hi = hi;
+        const int64_t cnt = hi - lo;
         const int64_t nt = (cnt + BM - 1) / BM;
         if (tile < acc + nt) {
             const int64_t r0 = lo + (tile - acc) * BM;
@@ -79,12 +77,12 @@ template <typename T, int MODE>
 __global__ void __launch_bounds__(TH)
 rows_gemm_kernel(const T* __restrict__ a, const T* __restrict__ w, const T* __restrict__ bias,
                  const int64_t* __restrict__ off, const __grid_constant__ HostSegs hs, T* __restrict__ c,
-                 T* __restrict__ pre_out, const T* __restrict__ act_pre, int n_expert, int64_t in_feat,
+                 T* __restrict__ pre_out, const T* __restrict__ act_pre, int n_expert, int64_t n_rows, int64_t in_feat,
                  int64_t out_feat, int act) {
     __shared__ float As[BK][BM + 1];
     __shared__ float Bs[BK][BN + 1];
     TileMap tm;
-    if (!find_tile(off, hs, n_expert, blockIdx.x, tm)) return;
+    if (!find_tile(off, hs, n_expert, n_rows, blockIdx.x, tm)) return;
     const int64_t kdim = MODE == 0 ? in_feat : out_feat;  // contraction length
     const int64_t ndim = MODE == 0 ? out_feat : in_feat;  // output columns
     const int64_t n0 = (int64_t)blockIdx.y * BN;
@@ -143,12 +141,13 @@ rows_gemm_kernel(const T* __restrict__ a, const T* __restrict__ w, const T* __re
 template <typename T>
 __global__ void __launch_bounds__(TH)
 wgrad_kernel(const T* __restrict__ dy, const T* __restrict__ x, const int64_t* __restrict__ off,
-             const __grid_constant__ HostSegs hs, T* __restrict__ dw, int64_t in_feat, int64_t out_feat,
+             const __grid_constant__ HostSegs hs, T* __restrict__ dw, int64_t n_rows, int64_t in_feat, int64_t out_feat,
              int accumulate) {
     __shared__ float As[BK][BM + 1];
     __shared__ float Bs[BK][BN + 1];
     const int e = blockIdx.z;
-    const int64_t lo = seg_lo(off, hs, e), hi = seg_hi(off, hs, e);
+    int64_t lo, hi;
+    safe_seg_range(off, hs, e, n_rows, lo, hi);
     const int64_t n0 = (int64_t)blockIdx.x * BM, k0 = (int64_t)blockIdx.y * BN;
     const int nv = (int)min((int64_t)BM, out_feat - n0), kv = (int)min((int64_t)BN, in_feat - k0);
     const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
@@ -194,12 +193,13 @@ wgrad_kernel(const T* __restrict__ dy, const T* __restrict__ x, const int64_t* _
 template <typename T>
 __global__ void __launch_bounds__(256)
 bias_grad_kernel(const T* __restrict__ dy, const int64_t* __restrict__ off,
-                 const __grid_constant__ HostSegs hs, T* __restrict__ db, int64_t out_feat, int accumulate) {
+                 const __grid_constant__ HostSegs hs, T* __restrict__ db, int64_t n_rows, int64_t out_feat, int accumulate) {
     __shared__ float red[8][33];
     const int e = blockIdx.y;
     const int cx = threadIdx.x % 32, ry = threadIdx.x / 32;
     const int64_t col = (int64_t)blockIdx.x * 32 + cx;
-    const int64_t lo = seg_lo(off, hs, e), hi = seg_hi(off, hs, e);
+    int64_t lo, hi;
+    safe_seg_range(off, hs, e, n_rows, lo, hi);
     float s = 0.f;
     if (col < out_feat)
         for (int64_t m = lo + ry; m < hi; m += 8) s += to_float<T>(dy[m * out_feat + col]);
@@ -224,7 +224,7 @@ int forward_t(const LinearArgs& a, cudaStream_t st) {
     dim3 grid((unsigned)m_tiles, (unsigned)ceil_div(a.out_feat, BN));
     rows_gemm_kernel<T, 0><<<grid, TH, 0, st>>>((const T*)a.x, (const T*)a.weight, (const T*)a.bias,
                                                  a.seg_offsets, hs, (T*)a.y, (T*)a.pre_act, nullptr,
-                                                 a.n_expert, a.in_feat, a.out_feat, a.activation);
+                                                 a.n_expert, a.n_rows, a.in_feat, a.out_feat, a.activation);
     FMOE_CHECK_LAUNCH();
     return 0;
 }
@@ -237,20 +237,20 @@ int backward_t(const LinearBwdArgs& a, cudaStream_t st) {
         dim3 grid((unsigned)m_tiles, (unsigned)ceil_div(a.in_feat, BN));
         rows_gemm_kernel<T, 1><<<grid, TH, 0, st>>>((const T*)a.grad_y, (const T*)a.weight, nullptr,
                                                      a.seg_offsets, hs, (T*)a.grad_x, nullptr,
-                                                     (const T*)a.act_pre, a.n_expert, a.in_feat,
+                                                     (const T*)a.act_pre, a.n_expert, a.n_rows, a.in_feat,
                                                      a.out_feat, a.activation);
         FMOE_CHECK_LAUNCH();
     }
     if (a.grad_w) {
         dim3 grid((unsigned)ceil_div(a.out_feat, BM), (unsigned)ceil_div(a.in_feat, BN), (unsigned)a.n_expert);
         wgrad_kernel<T><<<grid, TH, 0, st>>>((const T*)a.grad_y, (const T*)a.x, a.seg_offsets, hs,
-                                              (T*)a.grad_w, a.in_feat, a.out_feat, a.accumulate);
+                                              (T*)a.grad_w, a.n_rows, a.in_feat, a.out_feat, a.accumulate);
         FMOE_CHECK_LAUNCH();
     }
     if (a.grad_b) {
         dim3 grid((unsigned)ceil_div(a.out_feat, 32), (unsigned)a.n_expert);
         bias_grad_kernel<T><<<grid, 256, 0, st>>>((const T*)a.grad_y, a.seg_offsets, hs, (T*)a.grad_b,
-                                                   a.out_feat, a.accumulate);
+                                                   a.n_rows, a.out_feat, a.accumulate);
         FMOE_CHECK_LAUNCH();
     }
     return 0;

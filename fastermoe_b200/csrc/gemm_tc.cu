@@ -26,6 +26,8 @@
 #include "common.cuh"
 #include "gemm.h"
 #include <cuda.h>
+#include <algorithm>
+#include <atomic>
 #include <cstdlib>
 #include <mutex>
 
@@ -82,8 +84,7 @@ struct Params {
     float* colsum;  // DGRAD: fp32 partial column sums of the output, one row per 32-row block, or null
     int tma_store;  // outputs have tensor maps: full 32-row blocks leave through TMA stores
     int* status;  // device status word
-    int debug;    // FMOE_B200_DEBUG bits (profiling experiments): 1 = no global stores, 2 = no TMEM loads,
-                  // 8 = per-row stores instead of TMA stores
+    int64_t n_rows;  // rows of the ragged-side buffers (FWD/DGRAD: A and the output; WGRAD: both operands)
 };
 
 struct Shared {
@@ -480,25 +481,35 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    for (int e = threadIdx.x; e < p.n_expert; e += THREADS) {
-        sh->seg_lo[e] = hs.n ? hs.lo[e] : (int)p.seg[e];
-        sh->seg_hi[e] = hs.n ? hs.hi[e] : (int)p.seg[e + 1];
-    }
-    __syncthreads();
     if (threadIdx.x == 0) {
+        // Segment offsets come from device memory that no host code has looked at: ranges are made
+        // to run forwards and to end inside the buffers (code 8 in the status word when that
+        // changed anything), so tile counts, scratch indices and stores stay in bounds.
         const int nt = (p.n_out + BN - 1) / BN;
         int acc = 0, blk = 0;
+        int64_t prev_hi = 0;
+        bool clamped = false;
         sh->cum_tiles[0] = 0;
         sh->blk_base[0] = 0;
         for (int e = 0; e < p.n_expert; ++e) {
+            const int64_t raw_lo = hs.n ? (int64_t)hs.lo[e] : p.seg[e], raw_hi = hs.n ? (int64_t)hs.hi[e] : p.seg[e + 1];
+            int64_t lo = raw_lo < prev_hi ? prev_hi : raw_lo;
+            if (lo > p.n_rows) lo = p.n_rows;
+            int64_t hi = raw_hi < lo ? lo : raw_hi;
+            if (hi > p.n_rows) hi = p.n_rows;
+            clamped |= lo != raw_lo || hi != raw_hi;
+            prev_hi = hi;
+            sh->seg_lo[e] = (int)lo;
+            sh->seg_hi[e] = (int)hi;
             int mt;
             if (MODE == MODE_WGRAD) mt = (p.out_rows_per_expert + TILE_M - 1) / TILE_M;
-            else mt = (sh->seg_hi[e] - sh->seg_lo[e] + TILE_M - 1) / TILE_M;
+            else mt = ((int)(hi - lo) + TILE_M - 1) / TILE_M;
             acc += mt * nt;
             sh->cum_tiles[e + 1] = acc;
-            blk += (sh->seg_hi[e] - sh->seg_lo[e] + 31) >> 5;
+            blk += ((int)(hi - lo) + 31) >> 5;
             sh->blk_base[e + 1] = blk;
         }
+        if (clamped && blockIdx.x == 0) atomicCAS(p.status, 0, 8);
     }
     if (warp == 0) {
         if (CTA2) {
@@ -714,13 +725,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 for (int c = 0; c < COLS_PER_WARP / CW; ++c) {
                     if (col_lo + c * CW >= p.n_out) break;
                     uint32_t raw[CW];
-                    if (!(p.debug & 2)) {
-                        tc_ld32(taddr + c * CW, raw);
-                        if (CW == 64) tc_ld32(taddr + c * CW + 32, raw + 32);
-                    } else {
-#pragma unroll
-                        for (int i = 0; i < CW; ++i) raw[i] = 0;
-                    }
+                    tc_ld32(taddr + c * CW, raw);
+                    if (CW == 64) tc_ld32(taddr + c * CW + 32, raw + 32);
                     if (c > 0 && aux_src) row_load(aux, aux_src + c * CW, aux_row);
                     tc_wait_ld();
                     float* v = reinterpret_cast<float*>(raw);
@@ -814,7 +820,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                             }
                         }
                     }
-                    if (!(p.debug & 1)) {
+                    {
                         if (p.tma_store) {   // an earlier bulk store may still be reading the buffer
                             if (lane == 0) tma_store_wait_read();
                             __syncwarp();
@@ -955,30 +961,40 @@ const HostSegs kNoSegs = {};
 // from pairs: measured 1.16 vs 1.36 PFLOP/s on dense input.  Default: pairs for the
 // forward and input-gradient products when segments are long and there is work for every
 // pair; FMOE_B200_GEMM=pair / tc1 forces one form for all products.
-enum { FORM_AUTO = 0, FORM_PAIR = 1, FORM_SINGLE = 2 };
+// The environment gives the initial values (read once); fmoe_gemm_set_form / fmoe_gemm_set_sm_limit
+// change them at run time.
+std::atomic<int> g_form{-1}, g_sm_limit{-1};
 int forced_form() {
-    const char* p = getenv("FMOE_B200_GEMM");
-    if (p && p[0] == 'p') return FORM_PAIR;
-    if (p && p[0] == 't') return FORM_SINGLE;
-    return FORM_AUTO;
+    int f = g_form.load(std::memory_order_relaxed);
+    if (f < 0) {
+        const char* p = getenv("FMOE_B200_GEMM");
+        f = FMOE_GEMM_AUTO;
+        if (p && p[0] == 'p') f = FMOE_GEMM_PAIR;
+        else if (p && p[0] == 't') f = FMOE_GEMM_SINGLE;
+        else if (p && p[0] == 's') f = FMOE_GEMM_SIMT;
+        g_form.store(f, std::memory_order_relaxed);
+    }
+    return f;
 }
 bool use_pairs(int mode, int64_t n_rows, int n_expert, int64_t n_out) {
     const int form = forced_form();
-    if (form == FORM_PAIR) return n_rows >= 2048;
-    if (form == FORM_SINGLE || mode == MODE_WGRAD) return false;
+    if (form == FMOE_GEMM_PAIR) return n_rows >= 2048;
+    if (form == FMOE_GEMM_SINGLE || mode == MODE_WGRAD) return false;
     const int64_t pair_tiles = ceil_div(n_rows, 256) * ceil_div(n_out, BN);
     return n_rows >= (int64_t)512 * n_expert && pair_tiles >= 2 * (sm_count() / 2);
 }
 
-// CTAs the persistent GEMM grids may use: all SMs, or fewer with FMOE_B200_GEMM_SMS=n (to leave
-// SMs to kernels on other streams; measured with the smart schedule on 2 GPUs: 148 -> 132 CTAs
-// changes its step time by under 2 %, so no reserve is made by default).
+// CTAs the persistent GEMM grids may use: all SMs, or fewer (FMOE_B200_GEMM_SMS=n, or
+// fmoe_gemm_set_sm_limit) to leave SMs to kernels that run beside them on other streams.
 int cta_cap() {
-    int cap = sm_count();
-    if (const char* e = getenv("FMOE_B200_GEMM_SMS")) {
-        const int v = atoi(e);
-        if (v > 0) cap = std::min(cap, v);
+    int lim = g_sm_limit.load(std::memory_order_relaxed);
+    if (lim < 0) {
+        const char* e = getenv("FMOE_B200_GEMM_SMS");
+        lim = e ? std::max(atoi(e), 0) : 0;
+        g_sm_limit.store(lim, std::memory_order_relaxed);
     }
+    int cap = sm_count();
+    if (lim > 0) cap = std::min(cap, lim);
     return std::max(cap, 2);
 }
 
@@ -987,12 +1003,11 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const HostSegs* hsp, co
            int64_t out_rows, cudaStream_t st) {
     const HostSegs& hs = hsp ? *hsp : kNoSegs;
     Params p = p_in;
-    if (const char* dbg = getenv("FMOE_B200_DEBUG")) p.debug = atoi(dbg);
     static_assert(CW == 32, "the output tensor maps assume 32-column staging buffers");
     OutMaps om;
     memset(&om, 0, sizeof(om));
     p.tma_store = 0;
-    if (!(p.debug & 8) && out_rows > 0 && p.out) {
+    if (out_rows > 0 && p.out) {
         if (int rc = make_out_map(&om.out, p.out, out_rows, p.n_out, p.is_bf16 != 0)) return rc;
         if (p.pre_out) {
             if (int rc = make_out_map(&om.out2, p.pre_out, out_rows, p.n_out, p.is_bf16 != 0)) return rc;
@@ -1023,7 +1038,6 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const HostSegs* hsp, co
             int n = 0;
             FMOE_CUDA_TRY(cudaOccupancyMaxActiveClusters(&n, kern, &cfg));
             max_pairs[dev] = n > 0 ? n : 1;
-            if (p.debug & 4) fprintf(stderr, "[fmoe] resident CTA pairs: %d (SMs: %d)\n", n, sm_count());
         }
         const int64_t pairs = std::max<int64_t>(1, std::min<int64_t>(max_tiles, std::min(max_pairs[dev], cta_cap() / 2)));
         cfg.gridDim = dim3((unsigned)(2 * pairs));
@@ -1049,13 +1063,14 @@ bool shape_ok(int64_t n_rows, int64_t in_feat, int64_t out_feat, int n_expert, i
 template <bool BF16, int CL>
 __global__ void __launch_bounds__(256)
 bias_grad_tc_kernel(const uint16_t* __restrict__ dy, const int64_t* __restrict__ seg,
-                    const __grid_constant__ HostSegs hs, uint16_t* __restrict__ db, int out_feat, int accumulate) {
+                    const __grid_constant__ HostSegs hs, uint16_t* __restrict__ db, int64_t n_rows, int out_feat, int accumulate) {
     constexpr int RL = 256 / CL, COLS = CL * 8;
     __shared__ float red[RL][COLS + 1];
     const int e = blockIdx.y;
     const int cl = threadIdx.x % CL, ry = threadIdx.x / CL;
     const int col = blockIdx.x * COLS + cl * 8;
-    const int64_t lo = hs.n ? (int64_t)hs.lo[e] : seg[e], hi = hs.n ? (int64_t)hs.hi[e] : seg[e + 1];
+    int64_t lo, hi;
+    safe_seg_range(seg, hs, e, n_rows, lo, hi);
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     if (col < out_feat) {
         const uint16_t* base = dy + col;
@@ -1108,16 +1123,21 @@ bias_grad_tc_kernel(const uint16_t* __restrict__ dy, const int64_t* __restrict__
 template <bool BF16>
 __global__ void __launch_bounds__(512)
 colsum_finish_kernel(const float* __restrict__ partial, const int64_t* __restrict__ seg, const __grid_constant__ HostSegs hs,
-                     uint16_t* __restrict__ out, int n_cols, int accumulate) {
+                     uint16_t* __restrict__ out, int64_t n_rows, int n_cols, int accumulate) {
     __shared__ float2 part[4][128];
     const int e = blockIdx.y, q = threadIdx.y;
     const int col = (blockIdx.x * 128 + threadIdx.x) * 2;
+    // the same (clamped) ranges and 32-row block numbering as the kernel that wrote the partial sums
     int base = 0;
-    for (int j = 0; j < e; ++j) {
-        const int64_t lo = hs.n ? (int64_t)hs.lo[j] : seg[j], hi = hs.n ? (int64_t)hs.hi[j] : seg[j + 1];
-        base += (int)((hi - lo + 31) >> 5);
+    int64_t lo = 0, hi = 0, prev_hi = 0;
+    for (int j = 0; j <= e; ++j) {
+        if (j) base += (int)((hi - lo + 31) >> 5);
+        lo = hs.n ? (int64_t)hs.lo[j] : seg[j];
+        hi = hs.n ? (int64_t)hs.hi[j] : seg[j + 1];
+        lo = min(max(lo, prev_hi), n_rows);
+        hi = min(max(hi, lo), n_rows);
+        prev_hi = hi;
     }
-    const int64_t lo = hs.n ? (int64_t)hs.lo[e] : seg[e], hi = hs.n ? (int64_t)hs.hi[e] : seg[e + 1];
     const int nb = (int)((hi - lo + 31) >> 5);
     const int per = (nb + 3) >> 2;
     const int b0 = min(nb, q * per), b1 = min(nb, b0 + per);
@@ -1157,11 +1177,11 @@ int launch_bias_grad(const LinearBwdArgs& a, const HostSegs& hs, cudaStream_t st
     if (narrow) {
         dim3 grid((unsigned)ceil_div(a.out_feat, 64), (unsigned)a.n_expert);
         bias_grad_tc_kernel<BF16, 8><<<grid, 256, 0, st>>>((const uint16_t*)a.grad_y, a.seg_offsets, hs, (uint16_t*)a.grad_b,
-                                                            (int)a.out_feat, a.accumulate);
+                                                            a.n_rows, (int)a.out_feat, a.accumulate);
     } else {
         dim3 grid((unsigned)ceil_div(a.out_feat, 128), (unsigned)a.n_expert);
         bias_grad_tc_kernel<BF16, 16><<<grid, 256, 0, st>>>((const uint16_t*)a.grad_y, a.seg_offsets, hs, (uint16_t*)a.grad_b,
-                                                             (int)a.out_feat, a.accumulate);
+                                                             a.n_rows, (int)a.out_feat, a.accumulate);
     }
     FMOE_CHECK_LAUNCH();
     return 0;
@@ -1197,7 +1217,7 @@ int tc_linear_forward(const LinearArgs& a, cudaStream_t st) {
     Params p{};
     p.seg = a.seg_offsets; p.n_expert = a.n_expert; p.n_out = (int)a.out_feat; p.n_contr = (int)a.in_feat;
     p.w_rows = (int)a.out_feat; p.out = a.y; p.pre_out = a.pre_act; p.bias = a.bias; p.act = a.activation;
-    p.is_bf16 = bf16; p.status = status_ptr();
+    p.is_bf16 = bf16; p.status = status_ptr(); p.n_rows = a.n_rows;
     const int tile_m = pair ? 256 : BM;
     const int64_t max_tiles = (ceil_div(a.n_rows, tile_m) + a.n_expert) * ceil_div(a.out_feat, BN);
     return pair ? launch<MODE_FWD, true>(ma, mb, a.host_segs, p, max_tiles, a.n_rows, st)
@@ -1248,7 +1268,7 @@ int tc_linear_backward(const LinearBwdArgs& a, cudaStream_t st) {
         Params p{};
         p.seg = a.seg_offsets; p.n_expert = a.n_expert; p.n_out = (int)a.in_feat; p.n_contr = (int)a.out_feat;
         p.w_rows = (int)a.out_feat; p.out = a.grad_x; p.act_pre = a.act_pre; p.act = a.activation;
-        p.is_bf16 = bf16; p.status = status_ptr();
+        p.is_bf16 = bf16; p.status = status_ptr(); p.n_rows = a.n_rows;
         if (a.grad_x_colsum) {
             FMOE_REQUIRE(a.scratch && aligned16(a.scratch) && ((uintptr_t)a.grad_x_colsum & 3) == 0,
                          "linear_backward: column sums of grad_x need the scratch buffer of fmoe_linear_scratch_bytes");
@@ -1263,9 +1283,9 @@ int tc_linear_backward(const LinearBwdArgs& a, cudaStream_t st) {
             const HostSegs& hs = a.host_segs ? *a.host_segs : kNoSegs;
             dim3 grid((unsigned)ceil_div(a.in_feat, 256), (unsigned)a.n_expert);
             if (bf16) colsum_finish_kernel<true><<<grid, dim3(128, 4), 0, st>>>((const float*)a.scratch, a.seg_offsets, hs,
-                                                                                (uint16_t*)a.grad_x_colsum, (int)a.in_feat, 0);
+                                                                                (uint16_t*)a.grad_x_colsum, a.n_rows, (int)a.in_feat, 0);
             else colsum_finish_kernel<false><<<grid, dim3(128, 4), 0, st>>>((const float*)a.scratch, a.seg_offsets, hs,
-                                                                            (uint16_t*)a.grad_x_colsum, (int)a.in_feat, 0);
+                                                                            (uint16_t*)a.grad_x_colsum, a.n_rows, (int)a.in_feat, 0);
             FMOE_CHECK_LAUNCH();
         }
     }
@@ -1279,7 +1299,7 @@ int tc_linear_backward(const LinearBwdArgs& a, cudaStream_t st) {
         Params p{};
         p.seg = a.seg_offsets; p.n_expert = a.n_expert; p.n_out = (int)a.in_feat; p.n_contr = 0;
         p.out_rows_per_expert = (int)a.out_feat; p.out = a.grad_w; p.accumulate = a.accumulate;
-        p.is_bf16 = bf16; p.status = status_ptr();
+        p.is_bf16 = bf16; p.status = status_ptr(); p.n_rows = a.n_rows;
         const bool pair = use_pairs(MODE_WGRAD, a.n_rows, a.n_expert, a.in_feat);
         const int64_t max_tiles = (int64_t)a.n_expert * ceil_div(a.out_feat, pair ? 256 : BM) * ceil_div(a.in_feat, BN);
         if (int rc = pair ? launch<MODE_WGRAD, true>(ma, mb, a.host_segs, p, max_tiles, (int64_t)a.n_expert * a.out_feat, st)
@@ -1296,6 +1316,7 @@ int tc_linear_backward(const LinearBwdArgs& a, cudaStream_t st) {
 }
 
 int* device_status_ptr() { return status_ptr(); }
+int gemm_form() { return forced_form(); }
 
 int read_device_status(int* out) {
     int v = 0;
@@ -1305,6 +1326,18 @@ int read_device_status(int* out) {
 }
 
 }  // namespace fmoe
+
+extern "C" int fmoe_gemm_set_form(int32_t form) {
+    FMOE_REQUIRE(form >= FMOE_GEMM_AUTO && form <= FMOE_GEMM_SIMT, "gemm_set_form: unknown form %d", form);
+    fmoe::g_form.store(form, std::memory_order_relaxed);
+    return 0;
+}
+
+extern "C" int fmoe_gemm_set_sm_limit(int32_t n_sms) {
+    FMOE_REQUIRE(n_sms >= 0, "gemm_set_sm_limit: n_sms=%d", n_sms);
+    fmoe::g_sm_limit.store(n_sms, std::memory_order_relaxed);
+    return 0;
+}
 
 extern "C" int fmoe_device_status_clear(void) {
     const int zero = 0;

@@ -7,12 +7,9 @@ using namespace fmoe;
 
 namespace {
 
-// FMOE_B200_GEMM=simt forces the FFMA kernels (used by tests to cross-check the
-// tensor-core kernels); anything else lets the shape decide.
-bool force_simt() {
-    const char* p = getenv("FMOE_B200_GEMM");
-    return p && p[0] == 's';
-}
+// FMOE_GEMM_SIMT forces the FFMA kernels (used by tests to cross-check the tensor-core
+// kernels); anything else lets the shape decide.
+bool force_simt() { return gemm_form() == FMOE_GEMM_SIMT; }
 
 int check_common(int64_t n_rows, int64_t in_feat, int64_t out_feat, int n_expert, int dtype, int act,
                  const int64_t* seg) {
@@ -28,11 +25,12 @@ int check_common(int64_t n_rows, int64_t in_feat, int64_t out_feat, int n_expert
 // out[e, c] = sum of grad_x[r, c] over the rows of expert e (plain kernel for the FFMA path).
 template <typename T>
 __global__ void colsum_rows_kernel(const T* __restrict__ gx, const int64_t* __restrict__ seg, const HostSegs hs,
-                                   T* __restrict__ out, int64_t n_cols) {
+                                   T* __restrict__ out, int64_t n_rows, int64_t n_cols) {
     const int e = blockIdx.y;
     const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (c >= n_cols) return;
-    const int64_t lo = hs.n ? (int64_t)hs.lo[e] : seg[e], hi = hs.n ? (int64_t)hs.hi[e] : seg[e + 1];
+    int64_t lo, hi;
+    safe_seg_range(seg, hs, e, n_rows, lo, hi);
     float s = 0.f;
     for (int64_t r = lo; r < hi; ++r) s += to_float<T>(gx[r * n_cols + c]);
     out[(int64_t)e * n_cols + c] = from_float<T>(s);
@@ -43,9 +41,9 @@ int colsum_rows(const LinearBwdArgs& a, cudaStream_t st) {
     const HostSegs& hs = a.host_segs ? *a.host_segs : none;
     dim3 grid((unsigned)ceil_div(a.in_feat, 128), (unsigned)a.n_expert);
     switch (a.dtype) {
-        case FMOE_F32: colsum_rows_kernel<float><<<grid, 128, 0, st>>>((const float*)a.grad_x, a.seg_offsets, hs, (float*)a.grad_x_colsum, a.in_feat); break;
-        case FMOE_F16: colsum_rows_kernel<__half><<<grid, 128, 0, st>>>((const __half*)a.grad_x, a.seg_offsets, hs, (__half*)a.grad_x_colsum, a.in_feat); break;
-        default: colsum_rows_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>((const __nv_bfloat16*)a.grad_x, a.seg_offsets, hs, (__nv_bfloat16*)a.grad_x_colsum, a.in_feat); break;
+        case FMOE_F32: colsum_rows_kernel<float><<<grid, 128, 0, st>>>((const float*)a.grad_x, a.seg_offsets, hs, (float*)a.grad_x_colsum, a.n_rows, a.in_feat); break;
+        case FMOE_F16: colsum_rows_kernel<__half><<<grid, 128, 0, st>>>((const __half*)a.grad_x, a.seg_offsets, hs, (__half*)a.grad_x_colsum, a.n_rows, a.in_feat); break;
+        default: colsum_rows_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>((const __nv_bfloat16*)a.grad_x, a.seg_offsets, hs, (__nv_bfloat16*)a.grad_x_colsum, a.n_rows, a.in_feat); break;
     }
     FMOE_CHECK_LAUNCH();
     return 0;

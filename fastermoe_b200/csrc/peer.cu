@@ -108,9 +108,12 @@ peer_rows_kernel(const __grid_constant__ PeerSegs t, const __grid_constant__ Pee
                  const __grid_constant__ PeerLaunch a, const uint4* __restrict__ src, uint4* __restrict__ out) {
     __shared__ int s_last;
     __shared__ unsigned long long s_dest[kMaxPeers];
+    __shared__ unsigned long long s_dead;   // peers whose announcement never came: nothing is stored there
     unsigned long long* hdr = (unsigned long long*)b.base[a.rank];
     {
         const int p = threadIdx.x;
+        if (p == 0) s_dead = 0ull;
+        __syncthreads();
         if (p < a.world && p != a.rank) {
             if (kPush) {
                 if (a.announce && blockIdx.x == 0) {
@@ -118,9 +121,15 @@ peer_rows_kernel(const __grid_constant__ PeerSegs t, const __grid_constant__ Pee
                     peer_hdr[kDestWord + a.parity * kMaxPeers + a.rank] = a.my_dest;
                     st_release_sys(peer_hdr + kAnnWord + a.parity * kMaxPeers + a.rank, a.epoch);
                 }
-                // where peer p wants its rows
-                if (!wait_flag(hdr + kAnnWord + a.parity * kMaxPeers + p, a.epoch, 0, a.timeout_ns)) atomicOr(a.status, 16);
-                s_dest[p] = hdr[kDestWord + a.parity * kMaxPeers + p];
+                // Where peer p wants its rows.  Without an announcement of this epoch the word holds
+                // an older epoch's address (or nothing), so rows for that peer are dropped, not stored.
+                const bool announced = wait_flag(hdr + kAnnWord + a.parity * kMaxPeers + p, a.epoch, 0, a.timeout_ns);
+                const unsigned long long dest = hdr[kDestWord + a.parity * kMaxPeers + p];
+                s_dest[p] = dest;
+                if (!announced || dest < (unsigned long long)kHeaderBytes) {
+                    atomicOr(a.status, 16);
+                    atomicOr(&s_dead, 1ull << p);
+                }
             } else {           // everyone's rows of this epoch must have landed
                 if (!wait_flag(hdr + a.parity * kMaxPeers + p, a.epoch, 0, a.timeout_ns)) atomicOr(a.status, 32);
             }
@@ -129,13 +138,19 @@ peer_rows_kernel(const __grid_constant__ PeerSegs t, const __grid_constant__ Pee
     }
     const int lane = threadIdx.x & 31;
     const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
-    if (row < t.prefix[t.n]) {
+    bool live = row < t.prefix[t.n];
+    int k = 0;
+    if (live) {
         int lo = 0, hi = t.n - 1;  // last segment whose prefix <= row
         while (lo < hi) {
             const int mid = (lo + hi + 1) >> 1;
             if (t.prefix[mid] <= row) lo = mid; else hi = mid - 1;
         }
-        const int k = lo, off = row - t.prefix[k];
+        k = lo;
+        if (kPush && t.dst_sel[k] != kLocal && ((s_dead >> t.dst_sel[k]) & 1ull)) live = false;
+    }
+    if (live) {
+        const int off = row - t.prefix[k];
         const uint4* s;
         uint4* d;
         if (kPush) {
@@ -440,20 +455,38 @@ extern "C" int fmoe_peer_enable(fmoe_comm_t comm, int64_t slot_bytes, int64_t po
     slot_bytes = (slot_bytes + 255) & ~(int64_t)255;
 
     // Every step below is taken by all ranks, whatever happened before, so that the
-    // collectives match; `ok` carries this rank's verdict to the final agreement.
+    // collectives match: every allocation is made before the first agreement and a failure
+    // only lowers `ok`, this rank's verdict; the final verdict is the AND over all ranks.
     int ok = 1;
     char* own = nullptr;
+    char* dev_buf = nullptr;
+    unsigned int* counter = nullptr;
     cudaIpcMemHandle_t handle;
     memset(&handle, 0, sizeof(handle));
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle is 64 bytes");
+    const size_t rec = sizeof(cudaIpcMemHandle_t) + 8;     // handle + verdict
     if (cudaMalloc((void**)&own, (size_t)kHeaderBytes + 2 * (size_t)slot_bytes + (size_t)pool_bytes) != cudaSuccess) { ok = 0; own = nullptr; }
     if (ok && (cudaMemset(own, 0, kHeaderBytes) != cudaSuccess || cudaDeviceSynchronize() != cudaSuccess)) ok = 0;
     if (ok && cudaIpcGetMemHandle(&handle, own) != cudaSuccess) ok = 0;
+    if (cudaMalloc((void**)&counter, 2 * sizeof(unsigned int)) != cudaSuccess) { ok = 0; counter = nullptr; }
+    if (counter && cudaMemset(counter, 0, 2 * sizeof(unsigned int)) != cudaSuccess) ok = 0;
     (void)cudaGetLastError();
-
-    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle is 64 bytes");
-    const size_t rec = sizeof(cudaIpcMemHandle_t) + 8;     // handle + verdict
-    char* dev_buf = nullptr;
-    FMOE_CUDA_TRY(cudaMalloc((void**)&dev_buf, rec * (W + 1)));
+    char* base[kMaxPeers] = {};
+    auto release_all = [&]() {
+        for (int p = 0; p < W; ++p)
+            if (base[p] && p != c->rank) cudaIpcCloseMemHandle(base[p]);
+        if (own) cudaFree(own);
+        if (counter) cudaFree(counter);
+        if (dev_buf) cudaFree(dev_buf);
+        (void)cudaGetLastError();
+    };
+    // The gather buffer is the one allocation without which no agreement can be reached at all:
+    // its failure is an error of this call (the peers then fail in the collective, not silently).
+    if (cudaMalloc((void**)&dev_buf, rec * (W + 1)) != cudaSuccess) {
+        dev_buf = nullptr;
+        release_all();
+        return fail(FMOE_ERR_CUDA, "peer_enable: cannot allocate %zu bytes for the handle exchange", rec * (W + 1));
+    }
     std::vector<char> host(rec * (W + 1), 0);
     auto gather = [&](int verdict) -> int {
         memcpy(host.data(), &handle, sizeof(handle));
@@ -465,10 +498,9 @@ extern "C" int fmoe_peer_enable(fmoe_comm_t comm, int64_t slot_bytes, int64_t po
         return 0;
     };
     auto verdict_of = [&](int p) { int v; memcpy(&v, host.data() + rec * (p + 1) + sizeof(handle), sizeof(int)); return v; };
-    if (int rc = gather(ok)) { cudaFree(dev_buf); if (own) cudaFree(own); return rc; }
+    if (int rc = gather(ok)) { release_all(); return rc; }
     for (int p = 0; p < W; ++p) ok &= verdict_of(p);
 
-    char* base[kMaxPeers] = {};
     if (ok) {
         base[c->rank] = own;
         for (int p = 0; p < W; ++p) {
@@ -482,20 +514,15 @@ extern "C" int fmoe_peer_enable(fmoe_comm_t comm, int64_t slot_bytes, int64_t po
         (void)cudaGetLastError();
     }
     // second agreement: everybody mapped everybody
-    if (int rc = gather(ok)) { cudaFree(dev_buf); return rc; }
+    if (int rc = gather(ok)) { release_all(); return rc; }
     int all = 1;
     for (int p = 0; p < W; ++p) all &= verdict_of(p);
-    cudaFree(dev_buf);
     if (!all) {
-        for (int p = 0; p < W; ++p)
-            if (base[p] && p != c->rank) cudaIpcCloseMemHandle(base[p]);
-        if (own) cudaFree(own);
-        (void)cudaGetLastError();
+        release_all();
         return 0;                                // stays off, on every rank
     }
-    unsigned int* counter = nullptr;
-    FMOE_CUDA_TRY(cudaMalloc((void**)&counter, 2 * sizeof(unsigned int)));
-    FMOE_CUDA_TRY(cudaMemset(counter, 0, 2 * sizeof(unsigned int)));
+    cudaFree(dev_buf);
+    dev_buf = nullptr;
     for (int p = 0; p < W; ++p) c->peer.base[p] = base[p];
     c->peer.counter = counter;
     c->peer.epoch = 0;

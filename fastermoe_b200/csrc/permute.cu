@@ -346,6 +346,95 @@ int combine_bwd_t(const void* grad_out, const void* buf, const int64_t* inv, con
     return 0;
 }
 
+// ---- index_add_ with a fixed summation order ---------------------------------
+// out[pos[i],:] += buf[i,:] over all i, rows of out that nothing maps to are zero (the
+// zeros + index_add_ of fmoe/functions.py:77-81).  torch's index_add_ uses floating-point
+// atomics, so its rounding depends on arrival order; here the rows that collide on one output
+// row are listed first (integer atomics: the SET per output row does not depend on timing) and
+// then added in ascending i.
+constexpr int kListLen = 8;   // source rows listed per output row; longer collision chains are found by scanning pos
+
+__global__ void bucket_rows_kernel(const int64_t* __restrict__ pos, int64_t n, int64_t n_out, int* __restrict__ cnt,
+                                   int* __restrict__ lists) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int64_t p = pos[i];
+    if (p < 0 || p >= n_out) return;
+    const int slot = atomicAdd(cnt + p, 1);
+    if (slot < kListLen) lists[p * kListLen + slot] = (int)i;
+}
+
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(kRowThreads)
+rows_add_kernel(const T* __restrict__ buf, const int64_t* __restrict__ pos, const int* __restrict__ cnt,
+                const int* __restrict__ lists, T* __restrict__ out, int64_t n, int64_t n_out, int64_t d) {
+    constexpr int N = VEC ? Pack<T>::N : 1;
+    const int lane = threadIdx.x & 31;
+    const int64_t t = (int64_t)blockIdx.x * kRowWarps + (threadIdx.x >> 5);
+    if (t >= n_out) return;
+    const int c = cnt[t];
+    // the listed source rows, sorted ascending: lane j holds the j-th smallest
+    int mine = 0x7fffffff;
+    if (c <= kListLen) {
+        const int v = lane < c ? lists[t * kListLen + lane] : 0x7fffffff;
+        int rank = 0;
+        for (int j = 0; j < kListLen; ++j) {
+            const int o = __shfl_sync(0xffffffffu, v, j);
+            rank += (o < v) ? 1 : 0;
+        }
+        for (int j = 0; j < kListLen; ++j) {
+            const int o = __shfl_sync(0xffffffffu, v, j), r = __shfl_sync(0xffffffffu, rank, j);
+            if (r == lane && j < c) mine = o;
+        }
+    }
+    for (int64_t cb = 0; cb < d; cb += 32 * N) {      // the same trip count on every lane: the body shuffles
+        const int64_t c0 = cb + (int64_t)lane * N;
+        const bool live = c0 < d;
+        float acc[N];
+#pragma unroll
+        for (int i = 0; i < N; ++i) acc[i] = 0.f;
+        auto add_row = [&](int64_t s) {
+            if (!live) return;
+            if (VEC) {
+                float f[N];
+                unpack<T>(__ldg(reinterpret_cast<const uint4*>(buf + s * d + c0)), f);
+#pragma unroll
+                for (int i = 0; i < N; ++i) acc[i] += f[i];
+            } else {
+                acc[0] += to_float<T>(buf[s * d + c0]);
+            }
+        };
+        if (c <= kListLen) {
+            for (int j = 0; j < c; ++j) add_row(__shfl_sync(0xffffffffu, mine, j));
+        } else {
+            for (int64_t base = 0; base < n; base += 32) {
+                const bool hit = base + lane < n && pos[base + lane] == t;
+                unsigned m = __ballot_sync(0xffffffffu, hit);
+                while (m) {
+                    const int b = __ffs(m) - 1;
+                    m &= m - 1;
+                    add_row(base + b);
+                }
+            }
+        }
+        if (!live) continue;
+        if (VEC) *reinterpret_cast<uint4*>(out + t * d + c0) = pack<T>(acc);
+        else out[t * d + c0] = from_float<T>(acc[0]);
+    }
+}
+
+template <typename T>
+int rows_add_t(const void* buf, const int64_t* pos, void* out, int64_t n, int64_t n_out, int64_t d, int* cnt,
+               int* lists, cudaStream_t st) {
+    const unsigned blocks = (unsigned)ceil_div(n_out, kRowWarps);
+    if (vec_ok<T>(d, {buf, out}))
+        rows_add_kernel<T, true><<<blocks, kRowThreads, 0, st>>>((const T*)buf, pos, cnt, lists, (T*)out, n, n_out, d);
+    else
+        rows_add_kernel<T, false><<<blocks, kRowThreads, 0, st>>>((const T*)buf, pos, cnt, lists, (T*)out, n, n_out, d);
+    FMOE_CHECK_LAUNCH();
+    return 0;
+}
+
 int check_typed(int64_t n_tokens, int top_k, int64_t d, int dtype) {
     FMOE_REQUIRE(n_tokens >= 0 && top_k > 0 && d > 0, "bad sizes: tokens=%lld top_k=%d d=%lld",
                  (long long)n_tokens, top_k, (long long)d);
@@ -392,6 +481,32 @@ extern "C" int fmoe_local_gather(const void* buf, const int64_t* pos, void* out,
         FMOE_CHECK_LAUNCH();
     }
     return rows_copy(buf, inv_scratch, out, n_out_rows, n_rows, row_bytes, 1, st);
+}
+
+extern "C" size_t fmoe_local_gather_add_scratch_bytes(int64_t n_out_rows) {
+    return (size_t)(n_out_rows > 0 ? n_out_rows : 0) * (1 + kListLen) * sizeof(int) + 16;
+}
+
+extern "C" int fmoe_local_gather_add(const void* buf, const int64_t* pos, void* out, int64_t n_rows,
+                                     int64_t n_out_rows, int64_t d, int32_t dtype, void* scratch,
+                                     fmoe_stream_t stream) {
+    if (int rc = check_typed(n_out_rows, 1, d, dtype)) return rc;
+    FMOE_REQUIRE(n_rows >= 0 && n_rows < ((int64_t)1 << 31), "local_gather_add: n_rows=%lld", (long long)n_rows);
+    if (n_out_rows == 0) return 0;
+    FMOE_REQUIRE(out && scratch && (n_rows == 0 || (pos && buf)), "local_gather_add: null pointer");
+    cudaStream_t st = (cudaStream_t)stream;
+    int* cnt = (int*)scratch;
+    int* lists = cnt + n_out_rows;
+    FMOE_CUDA_TRY(cudaMemsetAsync(cnt, 0, (size_t)n_out_rows * sizeof(int), st));
+    if (n_rows > 0) {
+        bucket_rows_kernel<<<(unsigned)ceil_div(n_rows, 256), 256, 0, st>>>(pos, n_rows, n_out_rows, cnt, lists);
+        FMOE_CHECK_LAUNCH();
+    }
+    switch (dtype) {
+        case FMOE_F32: return rows_add_t<float>(buf, pos, out, n_rows, n_out_rows, d, cnt, lists, st);
+        case FMOE_F16: return rows_add_t<__half>(buf, pos, out, n_rows, n_out_rows, d, cnt, lists, st);
+        default: return rows_add_t<__nv_bfloat16>(buf, pos, out, n_rows, n_out_rows, d, cnt, lists, st);
+    }
 }
 
 extern "C" int fmoe_local_gather_sum(const void* buf, const int64_t* inv, void* out, int64_t n_tokens,

@@ -31,7 +31,7 @@ _DT = {torch.float32: _lib.F32, torch.float16: _lib.F16, torch.bfloat16: _lib.BF
 # Kernel launches issued by one call of each C entry point (for launch accounting).
 _KERNELS = {"expert_count": 1, "assign_pos": 4, "count_and_pos": 4, "limit_by_capacity": 1,
             "prune_gate_by_capacity": 4, "local_scatter": 1, "local_gather": 3, "local_gather_inv": 1,
-            "local_gather_sum": 1, "combine_forward": 1, "combine_backward": 1, "linear_forward": 1,
+            "local_gather_sum": 1, "local_gather_add": 3, "combine_forward": 1, "combine_backward": 1, "linear_forward": 1,
             "linear_backward": 3, "expert_exchange": 2, "generate_cached_count": 1,
             "peer_scatter": 2, "peer_gather": 2}
 
@@ -87,6 +87,45 @@ def _run(name, fn, *args, soft=False):
         p.events.append((name, a, b))
         return ok
     return chk(fn(*args), name)
+
+
+def set_gemm_form(name):
+    """Forces the kernels of the grouped expert GEMM: "auto", "pair", "tc1" or "simt"."""
+    check(lib.fmoe_gemm_set_form(_lib.GEMM_FORMS[name]), "gemm_set_form")
+
+
+def set_gemm_sm_limit(n_sms):
+    """Upper bound on the SMs the tensor-core GEMM grids occupy (0: all of them)."""
+    check(lib.fmoe_gemm_set_sm_limit(int(n_sms)), "gemm_set_sm_limit")
+
+
+def device_status(device=None):
+    """The status word of ``device`` (0: no bounded wait expired, no offsets were clamped).
+    Waits for the work queued on the device."""
+    st = ctypes.c_int32(0)
+    with torch.cuda.device(device):
+        check(lib.fmoe_device_status(ctypes.byref(st)), "device_status")
+    return st.value
+
+
+def check_status(device=None):
+    """Raises RuntimeError when a kernel of this library reported trouble since the last clear:
+    an expired bounded wait (results of that step are incomplete) or clamped segment offsets."""
+    v = device_status(device)
+    if v:
+        with torch.cuda.device(device):
+            lib.fmoe_device_status_clear()
+        what = []
+        if v & 15:
+            what.append({8: "segment offsets overshot the buffer and were clamped",
+                         7: "misaligned shared memory"}.get(v & 15, f"tensor-core kernel wait {v & 15} expired"))
+        if v & 16:
+            what.append("a peer never announced where it receives rows")
+        if v & 32:
+            what.append("rows from a peer did not arrive in time")
+        if v & 64:
+            what.append("more rows were routed to a GPU than its expert-side buffers hold")
+        raise RuntimeError(f"fastermoe_b200: device status {v}: " + "; ".join(what))
 
 
 def _dtype_code(t):
@@ -208,14 +247,26 @@ def offsets_from_counts(expert_count, device):
     return dev
 
 
+def _check_host_counts(expert_count, n_rows, what):
+    """Counts that live on the host are checked against the buffer before anything is queued
+    (counts on the device cannot be: the kernels clamp them instead and raise status code 8)."""
+    if not expert_count.is_cuda:
+        total = int(expert_count.sum())
+        if total != n_rows or bool((expert_count < 0).any()):
+            raise RuntimeError(f"{what}: expert_count sums to {total} but the buffer has {n_rows} rows "
+                               "(or a count is negative)")
+
+
 def linear_forward(input_buf, expert_count, weight, bias=None):
     """Y[seg_e] = X[seg_e] @ W_e^T + b_e for every expert (cuda/parallel_linear.cu:5-49)."""
+    _check_host_counts(expert_count, input_buf.shape[0], "linear_forward")
     off = offsets_from_counts(expert_count, input_buf.device)
     return linear_forward_act(input_buf, off, weight, bias, _lib.ACT_NONE)[0]
 
 
 def linear_backward(grad_output_buf, input_buf, expert_count, weight, bias=None):
     """Returns [dX, dW, db] (cuda/parallel_linear.cu:52-94); db is returned even without bias."""
+    _check_host_counts(expert_count, input_buf.shape[0], "linear_backward")
     off = offsets_from_counts(expert_count, input_buf.device)
     gx, gw, gb = linear_backward_act(grad_output_buf, input_buf, off, weight, None, _lib.ACT_NONE,
                                      need_bias=True)
@@ -573,6 +624,18 @@ def local_gather_sum(buf, inv, n_tokens, top_k):
     with torch.cuda.device(buf.device):
         _run("local_gather_sum", lib.fmoe_local_gather_sum, _ptr(buf), _ptr(inv), _ptr(out), n_tokens, top_k, buf.shape[1],
                                         _dtype_code(buf), _stream())
+    return out
+
+
+def local_gather_add(buf, pos, out_rows):
+    """zeros(out_rows, d) with out[pos[i]] += buf[i] (index_add_ semantics), rows that collide added
+    in ascending i (fmoe/functions.py:77-81)."""
+    _check_cuda(buf, pos)
+    out = buf.new_empty((out_rows, buf.shape[1]))
+    with torch.cuda.device(buf.device):
+        scratch = _scratch(lib.fmoe_local_gather_add_scratch_bytes(out_rows), buf.device)
+        _run("local_gather_add", lib.fmoe_local_gather_add, _ptr(buf), _ptr(pos), _ptr(out), pos.numel(), out_rows,
+             buf.shape[1], _dtype_code(buf), _ptr(scratch), _stream())
     return out
 
 

@@ -159,9 +159,7 @@ def _local_scatter(inp, pos):
 def _local_gather(inp, pos, out_batch_size, maybe_overlap=True):
     """zeros(out_batch_size, d) then index_add_/index_copy_ at pos (fmoe/functions.py:77-84)."""
     if maybe_overlap:
-        out = torch.zeros(out_batch_size, inp.shape[-1], dtype=inp.dtype, device=inp.device)
-        out.index_add_(0, pos, inp)
-        return out
+        return fmoe_cuda.local_gather_add(inp.contiguous(), pos.contiguous(), out_batch_size)
     return fmoe_cuda.local_gather(inp.contiguous(), pos.contiguous(), out_batch_size)
 
 
@@ -497,13 +495,16 @@ class GateTopK(Function):
 
 
 def gate_topk(logits, k):
-    """Top-k over the last dimension: the library's kernel for CUDA float tensors with k <= 8,
-    torch.topk otherwise (CPU tensors, other dtypes).  Returns (values, indices)."""
-    if logits.is_cuda and k <= 8 and logits.dtype in (torch.float32, torch.float16, torch.bfloat16):
+    """Top-k over the last dimension with the library's kernel (CUDA tensors; k <= 8).  A CPU
+    tensor, which no GPU code path produces, is answered by torch.topk.  Returns (values, indices)."""
+    if logits.is_cuda:
+        if k > 8 or logits.dtype not in (torch.float32, torch.float16, torch.bfloat16):
+            raise RuntimeError(f"gate_topk: k={k}, dtype={logits.dtype} is outside what the kernel takes "
+                               "(k <= 8; float32, float16, bfloat16)")
         lead = logits.shape[:-1]
         val, idx = GateTopK.apply(logits.reshape(-1, logits.shape[-1]), k)
         return val.reshape(*lead, k), idx.reshape(*lead, k)
-    return torch.topk(logits, k=k, dim=-1, largest=True, sorted=False)
+    return torch.topk(logits, k=k, dim=-1, largest=True, sorted=False)      # CPU tensors: module set-up and tests only
 
 
 class Slice(Function):

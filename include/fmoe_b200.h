@@ -48,12 +48,24 @@ const char* fmoe_last_error_string(void);
 int fmoe_version(void);
 int fmoe_built_for_sm(void);
 /* Reads the status word that the tensor-core kernels raise when one of their
- * bounded waits expires (0 = none; 1..4 = which wait; bits 16 and 32: waits of
- * the peer-memory exchange).  Copies from the device,
+ * bounded waits expires (0 = none; 1..4 = which wait; 7 = misaligned shared memory;
+ * 8 = segment offsets that overshot the buffer or ran backwards were clamped; bits 16
+ * and 32: waits of the peer-memory exchange).  Copies from the device,
  * so it waits for the work queued before it.  No counterpart in the reference. */
 int fmoe_device_status(int32_t* status_out);
 /* Sets the status word back to 0 (after the caller has dealt with an expired wait). */
 int fmoe_device_status_clear(void);
+/* Which kernels fmoe_linear_forward / fmoe_linear_backward use for 16-bit tensors whose shapes
+ * the tensor-core kernels take: AUTO picks CTA pairs (256-row tiles) or single CTAs by size,
+ * PAIR / SINGLE force one of them, SIMT forces the FFMA kernels.  Process-wide; the initial
+ * value comes from the environment (FMOE_B200_GEMM=pair|tc1|simt), read once.  Tests use it to
+ * cross-check the forms.  The reference has one form (cuBLAS, cuda/parallel_linear.cuh:73-145). */
+enum { FMOE_GEMM_AUTO = 0, FMOE_GEMM_PAIR = 1, FMOE_GEMM_SINGLE = 2, FMOE_GEMM_SIMT = 3 };
+int fmoe_gemm_set_form(int32_t form);
+/* Upper bound on the SMs the persistent tensor-core GEMM grids occupy (0: all), so that kernels
+ * on other streams (the token exchange) find free SMs beside them.  Process-wide; initial value
+ * from FMOE_B200_GEMM_SMS, read once.  No counterpart in the reference. */
+int fmoe_gemm_set_sm_limit(int32_t n_sms);
 
 /* ------------------------------------------------------------------------
  * Gate top-k                                         (selection: bit-exact)
@@ -186,6 +198,17 @@ int fmoe_local_gather_inv(const void* buf, const int64_t* inv, void* out,
  * ascending j in fp32 (the reference adds with atomics in arbitrary order). */
 int fmoe_local_gather_sum(const void* buf, const int64_t* inv, void* out,
                           int64_t n_tokens, int32_t top_k, int64_t d, int32_t dtype,
+                          fmoe_stream_t stream);
+
+/* _local_gather with maybe_overlap=True for an arbitrary index vector: fmoe/functions.py:77-81
+ * (zeros + index_add_).  out has n_out_rows rows of d elements; out[pos[i],:] += buf[i,:] over
+ * i in [0,n_rows), rows that nothing maps to are zero, entries of pos outside [0,n_out_rows)
+ * are skipped.  Rows that collide on one output row are added in ascending i in fp32 (torch
+ * adds with floating-point atomics in arrival order).  scratch:
+ * fmoe_local_gather_add_scratch_bytes(n_out_rows) bytes, 16-byte aligned. */
+size_t fmoe_local_gather_add_scratch_bytes(int64_t n_out_rows);
+int fmoe_local_gather_add(const void* buf, const int64_t* pos, void* out, int64_t n_rows,
+                          int64_t n_out_rows, int64_t d, int32_t dtype, void* scratch,
                           fmoe_stream_t stream);
 
 /* Weighted combine: fmoe/layers.py:319-322 (bmm of score[T,1,k] with x[T,k,d]),

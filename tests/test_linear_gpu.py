@@ -1,7 +1,8 @@
 """Grouped expert GEMM (fmoe_linear) forward/backward against per-expert fp32 matmuls.
 
-Tolerances are BASELINE's: fp32 rtol 1e-5; bf16/fp16 rtol 2e-2 against an fp32
-reference (absolute floors scale with the magnitude of the accumulated sums)."""
+Tolerances: fp32 rtol 1e-5 (absolute floor for long sums that cancel); bf16/fp16 rtol 2e-2
+against an fp32 reference, with an absolute floor of a few output roundings (2^-9 relative for
+bf16) of a typical element, which only matters for entries that cancel to almost nothing."""
 import numpy as np
 import pytest
 import torch
@@ -33,10 +34,13 @@ def reference(x, counts, w, b, gy):
     return y, gx, gw, gb
 
 
-def tolerances(dtype, k):
+def tolerances(dtype, k, want, roundings=1):
+    """``roundings``: 16-bit roundings between the inputs and this result (1 for a single product;
+    more when intermediate tensors of a chain were stored in 16 bits and the reference kept fp32)."""
     if dtype == torch.float32:
         return dict(rtol=1e-5, atol=1e-5 * float(np.sqrt(k)))
-    return dict(rtol=2e-2, atol=2e-2 * float(np.sqrt(k)))
+    rms = float(want.float().pow(2).mean().sqrt()) if want.numel() else 0.0
+    return dict(rtol=2e-2, atol=4 * roundings * 2.0 ** -9 * rms)
 
 
 SHAPES = [
@@ -64,10 +68,10 @@ def test_linear_forward_backward(fc, dtype, counts, fin, fout, bias):
     y = fc.linear_forward(x, cnt, w, b)
     gx, gw, gb = fc.linear_backward(gy, x, cnt, w, b)
     wy, wgx, wgw, wgb = reference(x, counts, w, b, gy)
-    torch.testing.assert_close(y.float(), wy, **tolerances(dtype, fin))
-    torch.testing.assert_close(gx.float(), wgx, **tolerances(dtype, fout))
-    torch.testing.assert_close(gw.float(), wgw, **tolerances(dtype, max(counts)))
-    torch.testing.assert_close(gb.float(), wgb, **tolerances(dtype, max(counts)))
+    torch.testing.assert_close(y.float(), wy, **tolerances(dtype, fin, wy))
+    torch.testing.assert_close(gx.float(), wgx, **tolerances(dtype, fout, wgx))
+    torch.testing.assert_close(gw.float(), wgw, **tolerances(dtype, max(counts), wgw))
+    torch.testing.assert_close(gb.float(), wgb, **tolerances(dtype, max(counts), wgb))
     # the count vector may also live on the GPU
     y2 = fc.linear_forward(x, cnt.cuda(), w, b)
     assert torch.equal(y, y2)
@@ -103,5 +107,7 @@ def test_fused_mlp_matches_autograd(fc, dtype, act):
     yr = torch.cat(outs)
     yr.backward(gy.float())
     want = [yr.detach()] + [t.grad for t in leaves]
-    for name, g, w_, k in zip(["y", "gx", "gw1", "gb1", "gw2", "gb2"], got, want, [h, h, 157, 157, 157, 157]):
-        torch.testing.assert_close(g.float(), w_, **tolerances(dtype, k), msg=lambda m, n=name: f"{n}: {m}")
+    # the hidden activations and their gradient are stored in 16 bits on the way, the reference keeps fp32
+    for name, g, w_, k, nr in zip(["y", "gx", "gw1", "gb1", "gw2", "gb2"], got, want, [h, h, 157, 157, 157, 157],
+                                  [2, 3, 3, 3, 2, 1]):
+        torch.testing.assert_close(g.float(), w_, **tolerances(dtype, k, w_, nr), msg=lambda m, n=name: f"{n}: {m}")
