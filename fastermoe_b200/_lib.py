@@ -96,7 +96,16 @@ _SIGS = {
     "fmoe_peer_pool_bytes": (I64, [P]),
     "fmoe_pool_alloc": (P, [c_size_t, I32, P]),
     "fmoe_pool_free": (None, [P, c_size_t, I32, P]),
-    "fmoe_peer_wait_probe": (I32, [P, I32, P]),
+    "fmoe_peer_wait_probe": (I32, [P, I32, I32, P]),
+    "fmoe_peer_set_timeout_ms": (I32, [P, I32]),
+    "fmoe_peer_plan_bytes": (c_size_t, [I32, I32]),
+    "fmoe_peer_plan_offsets_at": (I64, [I32, I32]),
+    "fmoe_peer_plan_table_at": (I64, [I32, I32]),
+    "fmoe_peer_plan_exchange": (I32, [P, P, P, I64, P, I32, P]),
+    "fmoe_peer_plan_from_table": (I32, [P, P, P, I32, I32, I32, P, P]),
+    "fmoe_peer_plan_read": (I32, [P, I32, I32, I32, P, I32, POINTER(c_int32), POINTER(c_int64), POINTER(c_int64), POINTER(c_int32)]),
+    "fmoe_peer_scatter_planned": (I32, [P, P, P, P, I64, I64, I64, I32, P]),
+    "fmoe_peer_gather_planned": (I32, [P, P, P, P, I64, I64, I64, I32, P]),
     "fmoe_device_status_clear": (I32, []),
     "fmoe_peer_slot_bytes": (I64, [P]),
     "fmoe_peer_global_scatter": (I32, [P, P, P, P, P, I64, I64, I64, I32, I32, P]),

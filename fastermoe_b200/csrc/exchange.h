@@ -34,8 +34,7 @@ struct PeerState {
     int64_t slot_bytes = 0;
     int64_t pool_bytes = 0;            // receive pool behind the two slots (0: none)
     char* base[kMaxPeers] = {};
-    unsigned int* counter = nullptr;   // device word for last-block detection
-    unsigned long long epoch = 0;      // exchanges done over peer memory (same on every rank)
+    unsigned int* counter = nullptr;   // device words for last-block detection
     unsigned long long timeout_ns = 0;
 };
 

@@ -3,12 +3,27 @@
 // kernel, with no NCCL send/receive pairs and no staging pass on the sender.
 //
 // Same data movement as cuda/global_exchange.cuh:75-124 of the reference (which
-// issues one ncclSend/ncclRecv per expert and peer); the row layout on both sides
-// is the one plan_scatter describes.
+// issues one ncclSend/ncclRecv per expert and peer and needs the counts on the host);
+// the row layout on both sides is the reference's (expert-major, then source worker,
+// bracketed by the rows kept local for shadowed workers).
 //
 // Every rank owns an allocation that its peers map through CUDA IPC:
 //
-//     [ header 4 KiB | slot 0 | slot 1 | receive pool ]
+//     [ header 4 MiB | slot 0 | slot 1 | receive pool ]
+//
+// The header holds flags, the count tables the ranks write into each other, and the
+// exchange epochs.  Nothing of the protocol lives on the host: epochs are device words
+// that the kernels advance themselves, and the row plan of an exchange is built ON THE
+// DEVICE from the count table (peer_plan_kernel), so a layer's forward never has to read
+// the counts back.
+//
+// Count exchange + plan (one block): every rank writes its local expert counts (and the
+// row capacity of its expert-side buffers) into every peer's header, waits for the
+// peers' tables, and derives from the full [W][W][E] table every rank's token-side
+// offsets and expert-side layout, the row segments it has to push in either direction,
+// and the offsets of its own experts' rows (what the grouped GEMM reads).  If any rank
+// would receive more rows than it announced room for, every rank sees it (same table,
+// same capacities): all plans become empty and bit 64 of the status word is raised.
 //
 // One exchange, numbered by an epoch that advances in step on all ranks (parity = epoch & 1):
 //   1. push kernel: its first block ANNOUNCES where this rank wants its incoming rows (a byte
@@ -19,7 +34,7 @@
 //      arrived[parity][rank] = epoch in every peer's header;
 //   2. consume kernel: waits for arrived == epoch from every peer; nothing else when the
 //      announced place was the output buffer itself, else it copies the rows that came from
-//      peers out of the slot into the output.
+//      peers out of the slot into the output.  Its last block advances the epoch word.
 // The output buffer can be announced directly when it lies in the receive pool: the Python
 // layer allocates exchange outputs there through a torch memory pool whose allocator is
 // fmoe_pool_alloc/fmoe_pool_free below, so tensor lifetimes stay with torch's caching
@@ -27,14 +42,16 @@
 // is made by a kernel that is stream-ordered after every earlier use of the announced memory
 // on its GPU, and entry `parity` is rewritten two epochs later, after the peers have arrived
 // for the epoch in between, so neither the memory nor the entry is overwritten while in use.
+// A receiver whose landing place is too small announces a refusal instead: senders drop the
+// rows for it and raise bit 64.
 //
 // All waits are bounded (wall-clock limit, FMOE_B200_PEER_TIMEOUT_MS, default
-// 20000): when one expires the kernel raises bit 16 (no announcement) or 32 (rows
-// not arrived) in the device status word and carries on, so that the stream drains.
+// 20000): when one expires the kernel raises bit 16 (no announcement / no count table) or
+// 32 (rows not arrived) in the device status word and carries on, so that the stream
+// drains; rows for a peer that never announced are dropped, not stored anywhere.
 //
-// Whether an exchange goes over peer memory must be decided identically on all
-// ranks; the entry points therefore take the all-gathered count table, from which
-// every rank derives every other rank's layout and the largest slot any rank needs.
+// The kernels of one communicator must be issued in one total order (one stream, or
+// streams ordered by events): the epoch words are per communicator.
 #include "common.cuh"
 #include "exchange.h"
 #include <cstdlib>
@@ -50,20 +67,86 @@ void* pool_take(int device, size_t bytes);
 void pool_give(int device, void* ptr, size_t bytes);
 namespace {
 
-constexpr int kHeaderBytes = 4096;
-// header words (u64): arrived[2][kMaxPeers] at byte 0, ann[2][kMaxPeers] at 1024, dest[2][kMaxPeers] at 2048
-constexpr int kAnnWord = 1024 / 8, kDestWord = 2048 / 8;
-constexpr int kPeerSegMax = 128;
-constexpr int kLocal = 255;                 // dst_sel of rows that stay on this GPU
-static_assert(3 * 2 * kMaxPeers * 8 <= kHeaderBytes, "flags fit the header");
+// ---- header layout (byte offsets) ----------------------------------------------------------
+constexpr int64_t kHeaderBytes = 4 << 20;
+constexpr int kArrivedOff = 0;        // u64 [2][kMaxPeers]   rows of epoch e from rank p have landed
+constexpr int kAnnOff = 1024;         // u64 [2][kMaxPeers]   rank p announced its landing place for epoch e
+constexpr int kDestOff = 2048;        // u64 [2][kMaxPeers]   that place (byte offset in p's allocation)
+constexpr int kCntFlagOff = 3072;     // u64 [2][kMaxPeers]   rank p's counts of count-exchange c are here
+constexpr int kSeqOff = 4096;         // u64 [2]              own words: exchange epoch, count-exchange epoch
+constexpr int kCapsOff = 5120;        // i64 [2][kMaxPeers]   expert-side row capacity of rank p
+constexpr int kTableOff = 8192;       // i64 [2][kTableMax]   count tables [W][W*E]
+constexpr int64_t kTableMax = ((1 << 20) - kTableOff) / 16;   // entries (W*W*E) per parity
+constexpr int64_t kCompatOff = 2 << 20;   // 2 MiB: uploaded table + flags + plan of the host-table entry points
+constexpr int64_t kProbeBytes = 128 << 10;    // tail of that area: the empty plan of fmoe_peer_wait_probe
+constexpr int64_t kCompatBytes = (2 << 20) - kProbeBytes;
+static_assert(kArrivedOff + 2 * kMaxPeers * 8 <= kAnnOff && kCapsOff + 2 * kMaxPeers * 8 <= kTableOff, "flag arrays overlap");
+constexpr unsigned long long kRefused = ~0ull;   // announcement of a receiver that has no room
 
-struct PeerSegs {
-    int n;
-    int prefix[kPeerSegMax + 1];            // rows before segment k
-    int src_row[kPeerSegMax], dst_row[kPeerSegMax];
-    unsigned char dst_sel[kPeerSegMax];     // destination rank, or kLocal
+constexpr int kLocal = 255;                 // destination of rows that stay on this GPU
+enum { LIST_PUSH_FWD = 0, LIST_PULL_FWD = 1, LIST_PUSH_BWD = 2, LIST_PULL_BWD = 3 };
+
+// ---- the plan as it lies in device memory -------------------------------------------------------
+// Built by peer_plan_kernel, read by the exchange kernels (and, through own_offsets, by the
+// grouped GEMM).  S = (2W-1)*E segment slots per list: (W-1)*E for rows kept local because their
+// expert is shadowed here, E for rows of this rank's own experts, (W-1)*E for rows to/from peers
+// (expert-major, peers in the order rank+1, rank+2, ... so that ranks working in step store into
+// different GPUs).  Slots without rows stay in the lists with rows = 0.
+struct PlanHead {
+    int32_t n_expert, n_workers, rank, n_slots;
+    int32_t overflow, pad0;
+    int64_t expert_rows, token_rows;      // rows of this rank's expert-side / token-side buffers
+    int64_t max_expert_rows, max_token_rows;  // the largest of those over all ranks
 };
-struct PeerBases { char* base[kMaxPeers]; };
+struct PlanDims {
+    int E, W, S;
+    int64_t WE, T;        // W*E, W*W*E
+    size_t own_off, table_off, stored_off, caps_off, eptr_off, lay_off, total_off, lists_off, bytes;
+};
+__host__ __device__ inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+__host__ __device__ inline PlanDims plan_dims(int E, int W) {
+    PlanDims d;
+    d.E = E; d.W = W; d.S = (2 * W - 1) * E;
+    d.WE = (int64_t)W * E; d.T = d.WE * W;
+    size_t o = align_up(sizeof(PlanHead), 64);
+    d.own_off = o;    o = align_up(o + (size_t)(E + 1) * 8, 64);          // i64 own_offsets[E+1]
+    d.table_off = o;  o = align_up(o + (size_t)d.T * 8, 64);              // i64 table[W][W*E]
+    d.stored_off = o; o = align_up(o + (size_t)d.WE, 64);                 // u8 stored[W*E]
+    d.caps_off = o;   o = align_up(o + (size_t)W * 8, 64);                // i64 caps[W]
+    d.eptr_off = o;   o = align_up(o + (size_t)W * (d.WE + 1) * 4, 64);   // i32 eptr[W][W*E+1]
+    d.lay_off = o;    o = align_up(o + (size_t)W * (d.S + 1) * 4, 64);    // i32 lay[W][S+1]: expert-side scan of every rank
+    d.total_off = o;  o = align_up(o + (size_t)W * 8, 64);
+    d.lists_off = o;  o = align_up(o + (size_t)4 * (4 * (size_t)d.S + 1) * 4, 64);  // 4 x {prefix[S+1], sel[S], src[S], dst[S]}
+    d.bytes = o;
+    return d;
+}
+struct ListView { int* prefix; int* sel; int* src; int* dst; };
+__host__ __device__ inline ListView list_view(char* plan, const PlanDims& d, int which) {
+    int* base = (int*)(plan + d.lists_off) + (size_t)which * (4 * (size_t)d.S + 1);
+    return ListView{base, base + d.S + 1, base + 2 * d.S + 1, base + 3 * d.S + 1};
+}
+
+// Position m of rank p's expert-side buffer order (the reference's layout, cuda/global_exchange.cuh:82-140):
+//   m in [0, p*E):              rows p keeps for shadowed expert (j, i), j = m / E < p
+//   m in [p*E, p*E + E*W):      rows from source j for p's expert i, (i, j) = divmod(m - p*E, W)
+//   m in [p*E + E*W, (2W-1)*E): rows p keeps for shadowed expert (j, i), j > p
+// Returns the row count of that position.
+__device__ __forceinline__ int64_t lay_count(const int64_t* table, const unsigned char* stored, int p, int E, int W, int m) {
+    const int64_t WE = (int64_t)W * E;
+    if (m < p * E) return stored[m] ? table[p * WE + m] : 0;
+    const int q = m - p * E;
+    if (q < E * W) {
+        const int i = q / W, j = q % W;
+        if (stored[p * E + i] && j != p) return 0;
+        return table[j * WE + p * E + i];
+    }
+    const int idx = (p + 1) * E + (q - E * W);
+    return stored[idx] ? table[p * WE + idx] : 0;
+}
+__device__ __forceinline__ int lay_pos_recv(int p, int E, int W, int i, int j) { return p * E + i * W + j; }
+__device__ __forceinline__ int lay_pos_shadow(int p, int E, int W, int idx) {      // idx = j*E + i, j != p
+    return idx < p * E ? idx : idx - E + E * W;
+}
 
 __device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long long* p) {
     unsigned long long v;
@@ -79,290 +162,400 @@ __device__ __forceinline__ unsigned long long now_ns() {
     return t;
 }
 
-// Waits until *flag + slack >= want; gives up after timeout_ns (or 2^28 polls).
-__device__ bool wait_flag(const unsigned long long* flag, unsigned long long want, unsigned long long slack,
-                          unsigned long long timeout_ns) {
-    if (ld_acquire_sys(flag) + slack >= want) return true;
+// Waits until *flag >= want; gives up after timeout_ns (or 2^28 polls).
+__device__ bool wait_flag(const unsigned long long* flag, unsigned long long want, unsigned long long timeout_ns) {
+    if (ld_acquire_sys(flag) >= want) return true;
     const unsigned long long t0 = now_ns();
     for (unsigned it = 0; it < (1u << 28); ++it) {
-        if (ld_acquire_sys(flag) + slack >= want) return true;
+        if (ld_acquire_sys(flag) >= want) return true;
         if (now_ns() - t0 > timeout_ns) return false;
         __nanosleep(256);
     }
     return false;
 }
 
-struct PeerLaunch {
-    int rank, world, parity;
-    int announce, signal_last;              // this launch opens / closes the push phase
-    unsigned long long epoch, timeout_ns;
-    unsigned long long my_dest;             // push: byte offset in this rank's allocation where its rows shall land
-    int64_t row_vecs, slot_off;             // 16-byte units per row; consume: byte offset of the slot
-    unsigned int* counter;
+struct PeerBases { char* base[kMaxPeers]; };
+
+// Exclusive scan by one warp over n values given by a functor; out[m] = sum of value(0..m-1),
+// out[n] = total.  Returns the total (same on every lane).
+template <typename F>
+__device__ __forceinline__ int64_t warp_scan_store(int n, F value, int* out, int lane) {
+    int64_t run = 0;
+    for (int base = 0; base < n; base += 32) {
+        const int m = base + lane;
+        const int64_t v = m < n ? value(m) : 0;
+        int64_t inc = v;
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+            const int64_t o = __shfl_up_sync(0xffffffffu, inc, off);
+            if (lane >= off) inc += o;
+        }
+        if (m < n) out[m] = (int)(run + inc - v);
+        run += __shfl_sync(0xffffffffu, inc, 31);
+    }
+    if (lane == 0) out[n] = (int)run;
+    return run;
+}
+
+struct PlanArgs {
+    int rank, world, n_expert;
+    int exchange;                          // 1: swap counts through the peers' headers; 0: the table is given
+    const int64_t* lec;                    // exchange: this rank's counts [W*E]
+    const int64_t* table_in;               // else: the full table [W][W*E]
+    const unsigned char* stored_in;        // [W*E] or null (nothing shadowed)
+    const int64_t* caps_in;                // given table: capacities [W] or null (unlimited)
+    int64_t cap_rows;                      // exchange: this rank's capacity (< 0: unlimited)
+    unsigned long long timeout_ns;
     int* status;
+    char* plan;
 };
 
-template <bool kPush>
 __global__ void __launch_bounds__(256)
-peer_rows_kernel(const __grid_constant__ PeerSegs t, const __grid_constant__ PeerBases b,
-                 const __grid_constant__ PeerLaunch a, const uint4* __restrict__ src, uint4* __restrict__ out) {
+peer_plan_kernel(const __grid_constant__ PeerBases b, const __grid_constant__ PlanArgs a) {
+    const int E = a.n_expert, W = a.world, r = a.rank;
+    const PlanDims d = plan_dims(E, W);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, n_warps = blockDim.x >> 5;
+    PlanHead* head = (PlanHead*)a.plan;
+    int64_t* own = (int64_t*)(a.plan + d.own_off);
+    int64_t* table = (int64_t*)(a.plan + d.table_off);
+    unsigned char* stored = (unsigned char*)(a.plan + d.stored_off);
+    int64_t* caps = (int64_t*)(a.plan + d.caps_off);
+    int* eptr = (int*)(a.plan + d.eptr_off);
+    int* lay = (int*)(a.plan + d.lay_off);
+    int64_t* total = (int64_t*)(a.plan + d.total_off);
+    __shared__ int s_bad;
+    if (tid == 0) s_bad = 0;
+
+    // ---- 1. the full count table -----------------------------------------------------------
+    if (a.exchange) {
+        unsigned long long* hdr = (unsigned long long*)b.base[r];
+        const unsigned long long c = __ldcg(hdr + kSeqOff / 8 + 1) + 1;
+        const int par = (int)(c & 1);
+        for (int64_t t = tid; t < (int64_t)W * d.WE; t += blockDim.x) {     // (peer, idx): my counts into everyone's table
+            const int p = (int)(t / d.WE);
+            const int64_t idx = t % d.WE;
+            int64_t* dst = (int64_t*)(b.base[p] + kTableOff) + (int64_t)par * kTableMax + (int64_t)r * d.WE + idx;
+            *dst = a.lec[idx];
+        }
+        if (tid < W) ((int64_t*)(b.base[tid] + kCapsOff))[par * kMaxPeers + r] = a.cap_rows;
+        __threadfence_system();
+        __syncthreads();
+        if (tid < W && tid != r)
+            st_release_sys((unsigned long long*)(b.base[tid] + kCntFlagOff) + par * kMaxPeers + r, c);
+        if (tid < W && tid != r) {
+            if (!wait_flag(hdr + kCntFlagOff / 8 + par * kMaxPeers + tid, c, a.timeout_ns)) {
+                atomicOr(a.status, 16);
+                s_bad = 1;
+            }
+        }
+        __syncthreads();
+        const int64_t* src = (const int64_t*)(b.base[r] + kTableOff) + (int64_t)par * kTableMax;
+        for (int64_t t = tid; t < d.T; t += blockDim.x) table[t] = __ldcg(src + t);
+        if (tid < W) caps[tid] = __ldcg((const int64_t*)(b.base[r] + kCapsOff) + par * kMaxPeers + tid);
+        if (tid == 0) hdr[kSeqOff / 8 + 1] = c;
+    } else {
+        for (int64_t t = tid; t < d.T; t += blockDim.x) table[t] = a.table_in[t];
+        if (tid < W) caps[tid] = a.caps_in ? a.caps_in[tid] : -1;
+    }
+    for (int64_t t = tid; t < d.WE; t += blockDim.x) stored[t] = a.stored_in ? a.stored_in[t] : 0;
+    __syncthreads();
+    // counts must be sane before they become row offsets
+    for (int64_t t = tid; t < d.T; t += blockDim.x)
+        if (table[t] < 0 || table[t] >= ((int64_t)1 << 31)) s_bad = 1;
+    __syncthreads();
+
+    // ---- 2. token-side offsets and expert-side layout of every rank (one warp per rank) -------
+    for (int p = warp; p < W; p += n_warps) {
+        const int64_t* row = table + (int64_t)p * d.WE;
+        const int64_t tok = warp_scan_store((int)d.WE, [&](int m) { return row[m]; }, eptr + (size_t)p * (d.WE + 1), lane);
+        const int64_t ex = warp_scan_store(d.S, [&](int m) { return lay_count(table, stored, p, E, W, m); },
+                                           lay + (size_t)p * (d.S + 1), lane);
+        if (lane == 0) {
+            total[p] = ex;
+            if (tok >= ((int64_t)1 << 31) || ex >= ((int64_t)1 << 31)) s_bad = 1;
+            if (caps[p] >= 0 && ex > caps[p]) { s_bad = 1; atomicOr(a.status, 64); }
+        }
+    }
+    __syncthreads();
+    const bool bad = s_bad != 0;
+
+    // ---- 3. this rank's segments --------------------------------------------------------------
+    const int64_t* mine = table + (int64_t)r * d.WE;
+    const int* my_eptr = eptr + (size_t)r * (d.WE + 1);
+    const int* my_lay = lay + (size_t)r * (d.S + 1);
+    ListView L[4];
+    for (int w = 0; w < 4; ++w) L[w] = list_view(a.plan, d, w);
+    // the row counts are staged in the prefix arrays first and scanned in place afterwards
+    for (int s = tid; s < d.S; s += blockDim.x) {
+        int sel = kLocal, tok = 0, ex = 0;
+        int64_t rows_pf = 0, rows_lf = 0, rows_pb = 0, rows_lb = 0;   // push fwd, pull fwd, push bwd, pull bwd
+        int src_pb = 0, dst_pb = 0, src_lf = 0, src_lb = 0;
+        if (s < (W - 1) * E) {                      // rows kept here for a shadowed expert of another rank
+            const int idx = s < r * E ? s : s + E;
+            tok = my_eptr[idx];
+            ex = my_lay[lay_pos_shadow(r, E, W, idx)];
+            rows_pf = rows_pb = stored[idx] ? mine[idx] : 0;
+            src_pb = ex; dst_pb = tok;
+        } else if (s < W * E) {                     // rows for this rank's own experts
+            const int i = s - (W - 1) * E, idx = r * E + i;
+            tok = my_eptr[idx];
+            ex = my_lay[lay_pos_recv(r, E, W, i, r)];
+            rows_pf = rows_pb = mine[idx];
+            src_pb = ex; dst_pb = tok;
+        } else {                                    // rows exchanged with peer p for expert i (of p outbound, of r inbound)
+            const int q = s - W * E, i = q / (W - 1), dlt = q % (W - 1) + 1, p = (r + dlt) % W;
+            sel = p;
+            const int out_idx = p * E + i;          // my rows for expert i of rank p
+            const int64_t out_rows = stored[out_idx] ? 0 : mine[out_idx];
+            const int64_t in_rows = stored[r * E + i] ? 0 : table[(int64_t)p * d.WE + r * E + i];
+            tok = my_eptr[out_idx];
+            ex = (lay + (size_t)p * (d.S + 1))[lay_pos_recv(p, E, W, i, r)];      // where they sit in p's expert-side buffer
+            rows_pf = out_rows;                                                   // forward push: tok (mine) -> ex (p's)
+            rows_lb = out_rows;                                                   // backward pull: they come back to tok
+            const int my_ex = my_lay[lay_pos_recv(r, E, W, i, p)];                // p's rows in my expert-side buffer
+            const int p_tok = (eptr + (size_t)p * (d.WE + 1))[r * E + i];         // and in p's token-side buffer
+            rows_lf = in_rows;                                                    // forward pull: slot[my_ex] -> out[my_ex]
+            rows_pb = in_rows;                                                    // backward push: my_ex (mine) -> p_tok (p's)
+            src_pb = my_ex; dst_pb = p_tok;
+            src_lf = my_ex; src_lb = tok;
+        }
+        L[LIST_PUSH_FWD].sel[s] = sel; L[LIST_PUSH_FWD].src[s] = tok;    L[LIST_PUSH_FWD].dst[s] = ex;
+        L[LIST_PUSH_BWD].sel[s] = sel; L[LIST_PUSH_BWD].src[s] = src_pb; L[LIST_PUSH_BWD].dst[s] = dst_pb;
+        L[LIST_PULL_FWD].sel[s] = kLocal; L[LIST_PULL_FWD].src[s] = src_lf; L[LIST_PULL_FWD].dst[s] = src_lf;
+        L[LIST_PULL_BWD].sel[s] = kLocal; L[LIST_PULL_BWD].src[s] = src_lb; L[LIST_PULL_BWD].dst[s] = src_lb;
+        if (bad) rows_pf = rows_lf = rows_pb = rows_lb = 0;
+        L[LIST_PUSH_FWD].prefix[s] = (int)rows_pf; L[LIST_PULL_FWD].prefix[s] = (int)rows_lf;
+        L[LIST_PUSH_BWD].prefix[s] = (int)rows_pb; L[LIST_PULL_BWD].prefix[s] = (int)rows_lb;
+    }
+    __syncthreads();
+    // in-place exclusive scans: one warp per list (each lane reads its count before it writes its prefix)
+    for (int w = warp; w < 4; w += n_warps) {
+        int* pre = L[w].prefix;
+        int64_t run = 0;
+        for (int base = 0; base < d.S; base += 32) {
+            const int m = base + lane;
+            const int64_t v = m < d.S ? pre[m] : 0;
+            int64_t inc = v;
+#pragma unroll
+            for (int off = 1; off < 32; off <<= 1) {
+                const int64_t o = __shfl_up_sync(0xffffffffu, inc, off);
+                if (lane >= off) inc += o;
+            }
+            __syncwarp();
+            if (m < d.S) pre[m] = (int)(run + inc - v);
+            run += __shfl_sync(0xffffffffu, inc, 31);
+        }
+        if (lane == 0) pre[d.S] = (int)run;
+    }
+    // ---- 4. what the GEMM and the host read ----------------------------------------------------
+    for (int i = tid; i <= E; i += blockDim.x)
+        own[i] = bad ? 0 : (int64_t)my_lay[i < E ? lay_pos_recv(r, E, W, i, 0) : r * E + E * W];
+    if (tid == 0) {
+        head->n_expert = E; head->n_workers = W; head->rank = r; head->n_slots = d.S;
+        head->overflow = bad ? 1 : 0; head->pad0 = 0;
+        head->expert_rows = bad ? 0 : total[r];
+        head->token_rows = bad ? 0 : (int64_t)my_eptr[d.WE];
+        int64_t me = 0, mt = 0;
+        for (int p = 0; p < W; ++p) {
+            me = max(me, total[p]);
+            mt = max(mt, (int64_t)(eptr + (size_t)p * (d.WE + 1))[d.WE]);
+        }
+        head->max_expert_rows = me; head->max_token_rows = mt;
+    }
+}
+
+struct MoveArgs {
+    int rank, world, dir;                  // dir 0: global_scatter (token -> expert side), 1: global_gather
+    int direct;                            // rows land in the output buffer itself (it lies in the receive pool)
+    int probe;                             // waits for an epoch nobody will publish; touches no state
+    unsigned long long my_dest;            // push: byte offset of the landing place in this rank's allocation (direct)
+    int64_t slot_bytes, row_bytes;
+    int64_t in_rows, out_rows;             // rows of the buffers given to this call
+    unsigned long long timeout_ns;
+    unsigned int* counter;
+    int* status;
+    const char* plan;
+};
+
+// Row `row` of a list -> its segment, by bisection of the prefix array in shared memory.
+__device__ __forceinline__ int find_seg(const int* prefix, int n, int row) {
+    int lo = 0, hi = n - 1;        // last segment whose prefix <= row
+    while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (prefix[mid] <= row) lo = mid; else hi = mid - 1;
+    }
+    return lo;
+}
+
+__device__ __forceinline__ void copy_row(const uint4* __restrict__ s, uint4* __restrict__ d, int64_t row_vecs, int lane) {
+    // Rows in a slot were written by other GPUs while this kernel may already have been running:
+    // read through L2 (ld.cg), never through the non-coherent path.
+    int64_t c = lane;
+    for (; c + 96 < row_vecs; c += 128) {
+        const uint4 v0 = __ldcg(s + c), v1 = __ldcg(s + c + 32), v2 = __ldcg(s + c + 64), v3 = __ldcg(s + c + 96);
+        d[c] = v0; d[c + 32] = v1; d[c + 64] = v2; d[c + 96] = v3;
+    }
+    for (; c < row_vecs; c += 32) d[c] = __ldcg(s + c);
+}
+
+constexpr int kMoveThreads = 256, kMoveWarps = kMoveThreads / 32;
+
+template <bool kPush>
+__global__ void __launch_bounds__(kMoveThreads)
+peer_move_kernel(const __grid_constant__ PeerBases b, const __grid_constant__ MoveArgs a, const uint4* __restrict__ src,
+                 uint4* __restrict__ out) {
+    extern __shared__ int s_prefix[];                // [S + 1]
     __shared__ int s_last;
     __shared__ unsigned long long s_dest[kMaxPeers];
-    __shared__ unsigned long long s_dead;   // peers whose announcement never came: nothing is stored there
+    __shared__ unsigned long long s_dead;            // peers that get no rows: never announced, or refused
+    const PlanHead* head = (const PlanHead*)a.plan;
+    const PlanDims d = plan_dims(head->n_expert, head->n_workers);
+    const ListView L = list_view(const_cast<char*>(a.plan), d, (kPush ? LIST_PUSH_FWD : LIST_PULL_FWD) + 2 * a.dir);
     unsigned long long* hdr = (unsigned long long*)b.base[a.rank];
+    const unsigned long long epoch = __ldcg(hdr + kSeqOff / 8) + 1 + (a.probe ? (1ull << 40) : 0ull);
+    const int parity = (int)(epoch & 1);
+    const int64_t row_vecs = a.row_bytes / 16;
+    // what this rank receives in this exchange and whether the place it was given can hold it
+    const int64_t recv_rows = a.dir == 0 ? head->expert_rows : head->token_rows;
+    const int64_t send_rows = a.dir == 0 ? head->token_rows : head->expert_rows;
+    const bool room = recv_rows <= a.out_rows && send_rows <= a.in_rows &&
+                      (a.direct || recv_rows * a.row_bytes <= a.slot_bytes);
+    for (int i = threadIdx.x; i <= d.S; i += kMoveThreads) s_prefix[i] = L.prefix[i];
+    if (threadIdx.x == 0) s_dead = 0ull;
+    __syncthreads();
     {
         const int p = threadIdx.x;
-        if (p == 0) s_dead = 0ull;
-        __syncthreads();
         if (p < a.world && p != a.rank) {
             if (kPush) {
-                if (a.announce && blockIdx.x == 0) {
+                if (blockIdx.x == 0 && !a.probe) {
                     unsigned long long* peer_hdr = (unsigned long long*)b.base[p];
-                    peer_hdr[kDestWord + a.parity * kMaxPeers + a.rank] = a.my_dest;
-                    st_release_sys(peer_hdr + kAnnWord + a.parity * kMaxPeers + a.rank, a.epoch);
+                    const unsigned long long place = !room ? kRefused
+                        : a.direct ? a.my_dest : (unsigned long long)(kHeaderBytes + (int64_t)parity * a.slot_bytes);
+                    peer_hdr[kDestOff / 8 + parity * kMaxPeers + a.rank] = place;
+                    st_release_sys(peer_hdr + kAnnOff / 8 + parity * kMaxPeers + a.rank, epoch);
                 }
                 // Where peer p wants its rows.  Without an announcement of this epoch the word holds
                 // an older epoch's address (or nothing), so rows for that peer are dropped, not stored.
-                const bool announced = wait_flag(hdr + kAnnWord + a.parity * kMaxPeers + p, a.epoch, 0, a.timeout_ns);
-                const unsigned long long dest = hdr[kDestWord + a.parity * kMaxPeers + p];
+                const bool announced = wait_flag(hdr + kAnnOff / 8 + parity * kMaxPeers + p, epoch, a.timeout_ns);
+                const unsigned long long dest = __ldcg(hdr + kDestOff / 8 + parity * kMaxPeers + p);
                 s_dest[p] = dest;
-                if (!announced || dest < (unsigned long long)kHeaderBytes) {
-                    atomicOr(a.status, 16);
-                    atomicOr(&s_dead, 1ull << p);
-                }
+                if (!announced) { atomicOr(a.status, 16); atomicOr(&s_dead, 1ull << p); }
+                else if (dest == kRefused || dest < (unsigned long long)kHeaderBytes) { atomicOr(a.status, 64); atomicOr(&s_dead, 1ull << p); }
             } else {           // everyone's rows of this epoch must have landed
-                if (!wait_flag(hdr + a.parity * kMaxPeers + p, a.epoch, 0, a.timeout_ns)) atomicOr(a.status, 32);
+                if (!wait_flag(hdr + kArrivedOff / 8 + parity * kMaxPeers + p, epoch, a.timeout_ns)) atomicOr(a.status, 32);
             }
         }
+        if (kPush && threadIdx.x == 0 && blockIdx.x == 0 && !room) atomicOr(a.status, 64);
         __syncthreads();
     }
     const int lane = threadIdx.x & 31;
-    const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
-    bool live = row < t.prefix[t.n];
-    int k = 0;
-    if (live) {
-        int lo = 0, hi = t.n - 1;  // last segment whose prefix <= row
-        while (lo < hi) {
-            const int mid = (lo + hi + 1) >> 1;
-            if (t.prefix[mid] <= row) lo = mid; else hi = mid - 1;
-        }
-        k = lo;
-        if (kPush && t.dst_sel[k] != kLocal && ((s_dead >> t.dst_sel[k]) & 1ull)) live = false;
-    }
-    if (live) {
-        const int off = row - t.prefix[k];
+    // without room nothing moves, not even the local rows; rows that landed in the output itself need no copy
+    const int total = (!room || (!kPush && a.direct)) ? 0 : s_prefix[d.S];
+    const uint4* slot = (const uint4*)(b.base[a.rank] + kHeaderBytes + (int64_t)parity * a.slot_bytes);
+    for (int row = blockIdx.x * kMoveWarps + (threadIdx.x >> 5); row < total; row += gridDim.x * kMoveWarps) {
+        const int k = find_seg(s_prefix, d.S, row), off = row - s_prefix[k];
         const uint4* s;
-        uint4* d;
+        uint4* dptr;
         if (kPush) {
-            s = src + (int64_t)(t.src_row[k] + off) * a.row_vecs;
-            const int sel = t.dst_sel[k];
-            d = (sel == kLocal ? out : (uint4*)(b.base[sel] + s_dest[sel])) + (int64_t)(t.dst_row[k] + off) * a.row_vecs;
+            const int sel = L.sel[k];
+            if (sel != kLocal && ((s_dead >> sel) & 1ull)) continue;
+            s = src + (int64_t)(L.src[k] + off) * row_vecs;
+            dptr = (sel == kLocal ? out : (uint4*)(b.base[sel] + s_dest[sel])) + (int64_t)(L.dst[k] + off) * row_vecs;
         } else {
-            s = (const uint4*)(b.base[a.rank] + a.slot_off) + (int64_t)(t.src_row[k] + off) * a.row_vecs;
-            d = out + (int64_t)(t.dst_row[k] + off) * a.row_vecs;
+            s = slot + (int64_t)(L.src[k] + off) * row_vecs;
+            dptr = out + (int64_t)(L.dst[k] + off) * row_vecs;
         }
-        // Rows in the slot were written by other GPUs while this kernel may already have
-        // been running: read them through L2 (ld.cg), never through the non-coherent path.
-        int64_t c = lane;
-        for (; c + 96 < a.row_vecs; c += 128) {
-            const uint4 v0 = __ldcg(s + c), v1 = __ldcg(s + c + 32), v2 = __ldcg(s + c + 64), v3 = __ldcg(s + c + 96);
-            d[c] = v0; d[c + 32] = v1; d[c + 64] = v2; d[c + 96] = v3;
-        }
-        for (; c < a.row_vecs; c += 32) d[c] = __ldcg(s + c);
+        copy_row(s, dptr, row_vecs, lane);
     }
-    if (kPush && a.signal_last) {
-        // All of this block's stores are ordered before thread 0's fence by the barrier,
-        // and the fence is cumulative: one fence per block publishes them.
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            __threadfence_system();
-            s_last = atomicAdd(a.counter, 1u) == gridDim.x - 1;
-        }
-        __syncthreads();
-        if (s_last) {
-            __threadfence_system();
+    if (!kPush && a.dir == 1 && !a.probe) {
+        // global_gather's contract: token-side rows past the ones the counts describe are zero
+        const int64_t first = room ? head->token_rows : 0;
+        for (int64_t row = first + blockIdx.x * kMoveWarps + (threadIdx.x >> 5); row < a.out_rows; row += (int64_t)gridDim.x * kMoveWarps)
+            for (int64_t c = lane; c < row_vecs; c += 32) out[row * row_vecs + c] = make_uint4(0, 0, 0, 0);
+    }
+    if (a.probe) return;
+    // The last block to finish publishes (push: the rows have landed; consume: the epoch is over).
+    // All of a block's stores are ordered before thread 0's fence by the barrier, and the fence is
+    // cumulative: one fence per block publishes them.
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence_system();
+        s_last = atomicAdd(a.counter + (kPush ? 0 : 1), 1u) == gridDim.x - 1;
+    }
+    __syncthreads();
+    if (s_last) {
+        __threadfence_system();
+        if (kPush) {
             const int p = threadIdx.x;
-            if (p < a.world && p != a.rank) {
-                unsigned long long* peer_hdr = (unsigned long long*)b.base[p];
-                st_release_sys(peer_hdr + a.parity * kMaxPeers + a.rank, a.epoch);
-            }
-            if (threadIdx.x == 0) *a.counter = 0;
+            if (p < a.world && p != a.rank)
+                st_release_sys((unsigned long long*)b.base[p] + kArrivedOff / 8 + parity * kMaxPeers + a.rank, epoch);
+        } else if (threadIdx.x == 0) {
+            hdr[kSeqOff / 8] = epoch;
         }
+        if (threadIdx.x == 0) a.counter[kPush ? 0 : 1] = 0;
     }
 }
 
-struct Seg { int sel; int64_t src_row, dst_row, rows; };
+int launch_plan(Comm* c, int rank, int W, int E, bool exchange, const int64_t* lec, const int64_t* table,
+                const uint8_t* stored, const int64_t* caps, int64_t cap_rows, void* plan, cudaStream_t st) {
+    FMOE_REQUIRE(E > 0 && W > 0 && W <= kMaxPeers && rank >= 0 && rank < W, "peer plan: bad E=%d W=%d rank=%d", E, W, rank);
+    FMOE_REQUIRE((int64_t)W * W * E <= kTableMax, "peer plan: W*W*E = %lld exceeds %lld", (long long)W * W * E, (long long)kTableMax);
+    FMOE_REQUIRE(plan && ((uintptr_t)plan & 63) == 0, "peer plan: plan buffer must be 64-byte aligned");
+    PeerBases b;
+    memset(&b, 0, sizeof(b));
+    PlanArgs a;
+    memset(&a, 0, sizeof(a));
+    a.rank = rank; a.world = W; a.n_expert = E; a.exchange = exchange ? 1 : 0;
+    a.lec = lec; a.table_in = table; a.stored_in = stored; a.caps_in = caps; a.cap_rows = cap_rows;
+    a.plan = (char*)plan;
+    a.status = device_status_ptr();
+    FMOE_REQUIRE(a.status, "peer plan: no device status word");
+    if (exchange) {
+        FMOE_REQUIRE(c && c->peer.slot_bytes > 0, "peer plan: the peer-memory exchange is off");
+        for (int p = 0; p < kMaxPeers; ++p) b.base[p] = c->peer.base[p];
+        a.timeout_ns = c->peer.timeout_ns;
+    }
+    peer_plan_kernel<<<1, 256, 0, st>>>(b, a);
+    FMOE_CHECK_LAUNCH();
+    return 0;
+}
 
-template <bool kPush>
-int launch_phase(Comm* c, const std::vector<Seg>& segs, const void* src, void* out, int64_t row_bytes, int parity,
-                 unsigned long long my_dest, cudaStream_t st) {
+int launch_move(Comm* c, const void* in, void* out, const void* plan, int E, int64_t in_rows, int64_t out_rows,
+                int64_t row_bytes, bool reverse, cudaStream_t st) {
+    FMOE_REQUIRE(row_bytes > 0 && row_bytes % 16 == 0, "peer exchange: row_bytes=%lld (a positive multiple of 16)", (long long)row_bytes);
+    FMOE_REQUIRE(in_rows >= 0 && out_rows >= 0 && in_rows < ((int64_t)1 << 31) && out_rows < ((int64_t)1 << 31),
+                 "peer exchange: rows in=%lld out=%lld", (long long)in_rows, (long long)out_rows);
+    FMOE_REQUIRE((in || in_rows == 0) && (out || out_rows == 0) && plan, "peer exchange: null buffer");
+    FMOE_REQUIRE((((uintptr_t)in | (uintptr_t)out) & 15) == 0, "peer exchange: buffers must be 16-byte aligned");
     PeerBases b;
     for (int p = 0; p < kMaxPeers; ++p) b.base[p] = c->peer.base[p];
-    PeerLaunch a;
-    a.rank = c->rank; a.world = c->world; a.parity = parity;
-    a.epoch = c->peer.epoch; a.timeout_ns = c->peer.timeout_ns;
-    a.my_dest = my_dest;
-    a.row_vecs = row_bytes / 16;
-    a.slot_off = kHeaderBytes + (int64_t)parity * c->peer.slot_bytes;
-    a.counter = c->peer.counter;
-    a.status = device_status_ptr();
-    FMOE_REQUIRE(a.status, "peer exchange: no device status word");
-    PeerSegs t;
-    size_t i = 0;
-    bool first = true;
-    do {
-        t.n = 0;
-        t.prefix[0] = 0;
-        for (; i < segs.size() && t.n < kPeerSegMax; ++i) {
-            const Seg& s = segs[i];
-            if (s.rows == 0) continue;
-            t.dst_sel[t.n] = (unsigned char)s.sel;
-            t.src_row[t.n] = (int)s.src_row; t.dst_row[t.n] = (int)s.dst_row;
-            t.prefix[t.n + 1] = t.prefix[t.n] + (int)s.rows;
-            ++t.n;
-        }
-        if (t.n == 0) t.prefix[1] = 0;
-        a.announce = first;
-        a.signal_last = i >= segs.size();
-        const unsigned blocks = (unsigned)std::max<int64_t>(1, ceil_div(t.n ? t.prefix[t.n] : 0, 8));
-        peer_rows_kernel<kPush><<<blocks, 256, 0, st>>>(t, b, a, (const uint4*)src, (uint4*)out);
-        FMOE_CHECK_LAUNCH();
-        first = false;
-    } while (i < segs.size());
-    return 0;
-}
-
-// Expert-side row of segment (expert i of rank p, source rank j), as plan_scatter lays
-// rank p's buffer out; -1 for segments that are not exchanged.  table is [W][W][E]:
-// rows that rank `src` routes to expert e of rank `dst`.
-struct Layout {
-    std::vector<int64_t> off;     // [i + j * E]
-    std::vector<int64_t> shadow;  // [j * E + i]: row of the block of rank p's own rows for shadowed expert (j, i)
-    int64_t total = 0;
-};
-
-void expert_layout(const int64_t* table, const uint8_t* stored, int p, int E, int W, Layout& L) {
-    const int64_t* lec = table + (int64_t)p * W * E;
-    L.off.assign((size_t)E * W, -1);
-    L.shadow.assign((size_t)E * W, -1);
-    int64_t rp = 0;
-    auto local_block = [&](int j) {
-        for (int i = 0; i < E; ++i) {
-            const int idx = i + j * E;
-            if (stored[idx]) { L.shadow[idx] = rp; rp += lec[idx]; }
-        }
-    };
-    for (int j = 0; j < p; ++j) local_block(j);
-    for (int i = 0; i < E; ++i)
-        for (int j = 0; j < W; ++j) {
-            const int64_t g = table[((int64_t)j * W + p) * E + i];
-            if (g > 0 && (!stored[p * E + i] || j == p)) { L.off[i + j * E] = rp; rp += g; }
-        }
-    for (int j = p + 1; j < W; ++j) local_block(j);
-    L.total = rp;
-}
-
-// Row segments of one exchange for rank r: `push` = what its push kernel stores (sel = kLocal:
-// the rows stay on this GPU and go straight to the output), `pull` = what its consume kernel
-// copies out of its own landing slot.  slot_rows = rows of the largest slot any rank needs (the
-// same on every rank, because it depends on the shared table only).
-struct Plan {
-    std::vector<Seg> push, pull;
-    int64_t slot_rows = 0, expert_rows = 0, token_rows = 0, max_rows = 0;
-};
-
-int plan_peer(const int64_t* table, const uint8_t* stored, int r, int E, int W, bool reverse, Plan& plan) {
-    FMOE_REQUIRE(table && stored && E > 0 && W > 0 && r >= 0 && r < W, "peer exchange: bad argument");
-    const size_t n = (size_t)W * E;
-    for (size_t i = 0; i < n * W; ++i) FMOE_REQUIRE(table[i] >= 0, "peer exchange: negative count at %zu", i);
-    // token-side offsets of every rank, expert-side layout of every rank
-    std::vector<std::vector<int64_t>> eptr(W, std::vector<int64_t>(n + 1, 0));
-    std::vector<Layout> lay(W);
-    int64_t max_token = 0, max_expert = 0;
-    for (int p = 0; p < W; ++p) {
-        for (size_t i = 0; i < n; ++i) eptr[p][i + 1] = eptr[p][i] + table[(size_t)p * n + i];
-        expert_layout(table, stored, p, E, W, lay[p]);
-        max_token = std::max(max_token, eptr[p][n]);
-        max_expert = std::max(max_expert, lay[p].total);
-    }
-    plan.slot_rows = reverse ? max_token : max_expert;
-    plan.max_rows = std::max(max_token, max_expert);
-    plan.expert_rows = lay[r].total;
-    plan.token_rows = eptr[r][n];
-    std::vector<Seg>& push = plan.push;
-    std::vector<Seg>& pull = plan.pull;
-    const int64_t* mine = table + (size_t)r * n;
-    // rows that stay here: own rows of shadowed experts, and rows for this rank's own experts
-    for (size_t idx = 0; idx < n; ++idx)
-        if ((int)(idx / E) != r && stored[idx] && mine[idx] > 0) {
-            const int64_t tok = eptr[r][idx], ex = lay[r].shadow[idx];
-            push.push_back(reverse ? Seg{kLocal, ex, tok, mine[idx]} : Seg{kLocal, tok, ex, mine[idx]});
-        }
-    for (int i = 0; i < E; ++i) {
-        const int64_t ex = lay[r].off[i + r * E];
-        if (ex < 0) continue;
-        const int64_t tok = eptr[r][r * E + i], rows = mine[r * E + i];
-        push.push_back(reverse ? Seg{kLocal, ex, tok, rows} : Seg{kLocal, tok, ex, rows});
-    }
-    // Peers are visited in the order r+1, r+2, ...: at any moment every rank stores into a
-    // different peer, so no GPU's NVLink ingress is shared by several senders.
-    for (int dlt = 1; dlt < W; ++dlt) {
-        const int p = (r + dlt) % W;
-        for (int i = 0; i < E; ++i) {
-            // rows this rank routes to expert i of rank p
-            const int64_t out_rows_pi = mine[p * E + i];
-            if (out_rows_pi > 0 && !stored[p * E + i]) {
-                const int64_t tok = eptr[r][p * E + i], ex = lay[p].off[i + r * E];
-                if (!reverse) push.push_back({p, tok, ex, out_rows_pi});   // to p's expert-side layout
-                else pull.push_back({kLocal, tok, tok, out_rows_pi});      // back, into this rank's token-side layout
-            }
-            // rows rank p routes to expert i of this rank
-            const int64_t in_rows_pi = table[((size_t)p * W + r) * E + i];
-            if (in_rows_pi > 0 && !stored[r * E + i]) {
-                const int64_t ex = lay[r].off[i + p * E], tok = eptr[p][r * E + i];
-                if (!reverse) pull.push_back({kLocal, ex, ex, in_rows_pi});
-                else push.push_back({p, ex, tok, in_rows_pi});             // to p's token-side layout
-            }
-        }
-    }
-    return 0;
-}
-
-int peer_move(fmoe_comm_t comm, const void* in, void* out, const int64_t* table, const uint8_t* stored,
-              int64_t in_rows, int64_t out_rows, int64_t row_bytes, int E, int W, bool reverse, cudaStream_t st) {
-    FMOE_REQUIRE(comm, "peer exchange: null communicator");
-    Comm* c = (Comm*)comm;
-    FMOE_REQUIRE(W == c->world, "peer exchange: n_workers=%d but communicator has %d ranks", W, c->world);
-    FMOE_REQUIRE(row_bytes > 0, "peer exchange: row_bytes=%lld", (long long)row_bytes);
-    if (c->peer.slot_bytes == 0 || row_bytes % 16 != 0) return FMOE_PEER_UNAVAILABLE;
-    Plan plan;
-    if (int rc = plan_peer(table, stored, c->rank, E, W, reverse, plan)) return rc;
-    if (plan.slot_rows * row_bytes > c->peer.slot_bytes || plan.max_rows >= ((int64_t)1 << 31))
-        return FMOE_PEER_UNAVAILABLE;     // same verdict on every rank: it depends on the shared table only
-
-    const int64_t token_rows = reverse ? out_rows : in_rows, expert_rows = reverse ? in_rows : out_rows;
-    if (expert_rows != plan.expert_rows)
-        return fail(FMOE_ERR_MISMATCH, "peer exchange: expert-side buffer has %lld rows, counts say %lld",
-                    (long long)expert_rows, (long long)plan.expert_rows);
-    if (token_rows < plan.token_rows)
-        return fail(FMOE_ERR_MISMATCH, "peer exchange: token-side buffer has %lld rows, counts say %lld",
-                    (long long)token_rows, (long long)plan.token_rows);
-    FMOE_REQUIRE((in || in_rows == 0) && (out || out_rows == 0), "peer exchange: null buffer");
-    FMOE_REQUIRE((((uintptr_t)in | (uintptr_t)out) & 15) == 0, "peer exchange: buffers must be 16-byte aligned");
-    if (reverse && out_rows > plan.token_rows)
-        FMOE_CUDA_TRY(cudaMemsetAsync((char*)out + plan.token_rows * row_bytes, 0,
-                                      (size_t)(out_rows - plan.token_rows) * row_bytes, st));
-    c->peer.epoch += 1;
-    const int parity = (int)(c->peer.epoch & 1);
     // Rows can land in the output itself when it lies in this rank's receive pool.
     char* pool = c->peer.base[c->rank] + kHeaderBytes + 2 * c->peer.slot_bytes;
-    const int64_t recv_bytes = (reverse ? out_rows : plan.expert_rows) * row_bytes;
+    const int64_t recv_bytes = out_rows * row_bytes;
     const bool direct = c->peer.pool_bytes > 0 && (char*)out >= pool && (char*)out + recv_bytes <= pool + c->peer.pool_bytes;
-    const unsigned long long my_dest = direct ? (unsigned long long)((char*)out - c->peer.base[c->rank])
-                                              : (unsigned long long)(kHeaderBytes + (int64_t)parity * c->peer.slot_bytes);
-    if (int rc = launch_phase<true>(c, plan.push, in, out, row_bytes, parity, my_dest, st)) return rc;
-    static const std::vector<Seg> nothing;
-    return launch_phase<false>(c, direct ? nothing : plan.pull, nullptr, out, row_bytes, parity, 0, st);
+    MoveArgs a;
+    memset(&a, 0, sizeof(a));
+    a.rank = c->rank; a.world = c->world; a.dir = reverse ? 1 : 0; a.direct = direct ? 1 : 0;
+    a.my_dest = direct ? (unsigned long long)((char*)out - c->peer.base[c->rank]) : 0;
+    a.slot_bytes = c->peer.slot_bytes; a.row_bytes = row_bytes; a.in_rows = in_rows; a.out_rows = out_rows;
+    a.timeout_ns = c->peer.timeout_ns; a.counter = c->peer.counter; a.plan = (const char*)plan;
+    a.status = device_status_ptr();
+    FMOE_REQUIRE(a.status, "peer exchange: no device status word");
+    const PlanDims d = plan_dims(E, c->world);
+    const size_t smem = (size_t)(d.S + 1) * sizeof(int);
+    FMOE_REQUIRE(smem <= 40 * 1024, "peer exchange: %d segment slots do not fit the kernels' shared memory", d.S);
+    const int cap_blocks = sm_count() * 8;
+    const unsigned push_blocks = (unsigned)std::max<int64_t>(1, std::min<int64_t>(ceil_div(in_rows, kMoveWarps), cap_blocks));
+    peer_move_kernel<true><<<push_blocks, kMoveThreads, smem, st>>>(b, a, (const uint4*)in, (uint4*)out);
+    FMOE_CHECK_LAUNCH();
+    // consume: one block when nothing has to be copied or cleared
+    const bool work = !direct || reverse;
+    // (direct + gather: only the usually empty tail of the token-side buffer may need clearing)
+    const unsigned pull_blocks = !work ? 1u : direct ? 16u
+        : (unsigned)std::max<int64_t>(1, std::min<int64_t>(ceil_div(out_rows, kMoveWarps), cap_blocks));
+    peer_move_kernel<false><<<pull_blocks, kMoveThreads, smem, st>>>(b, a, nullptr, (uint4*)out);
+    FMOE_CHECK_LAUNCH();
+    return 0;
 }
 
 }  // namespace
@@ -420,8 +613,11 @@ void pool_give(int device, void* ptr, size_t bytes) {
     p.free_[off] = len;
 }
 
+void peer_forget(Comm* c);
+
 void peer_release(Comm* c) {
     PeerState& ps = c->peer;
+    peer_forget(c);
     if (ps.slot_bytes == 0) return;
     cudaDeviceSynchronize();
     if (ps.pool_bytes) pool_register(c->device, nullptr, 0);
@@ -436,6 +632,165 @@ void peer_release(Comm* c) {
     ps.counter = nullptr;
     ps.slot_bytes = 0;
     (void)cudaGetLastError();
+}
+
+// ---- host mirror of the plan (no GPU): what the device builds, for inspection and tests -------
+namespace {
+struct Seg { int sel; int64_t src_row, dst_row, rows; };
+struct Layout {
+    std::vector<int64_t> off;     // [i + j * E]
+    std::vector<int64_t> shadow;  // [j * E + i]: row of the block of rank p's own rows for shadowed expert (j, i)
+    int64_t total = 0;
+};
+
+void expert_layout(const int64_t* table, const uint8_t* stored, int p, int E, int W, Layout& L) {
+    const int64_t* lec = table + (int64_t)p * W * E;
+    L.off.assign((size_t)E * W, -1);
+    L.shadow.assign((size_t)E * W, -1);
+    int64_t rp = 0;
+    auto local_block = [&](int j) {
+        for (int i = 0; i < E; ++i) {
+            const int idx = i + j * E;
+            if (stored[idx]) { L.shadow[idx] = rp; rp += lec[idx]; }
+        }
+    };
+    for (int j = 0; j < p; ++j) local_block(j);
+    for (int i = 0; i < E; ++i)
+        for (int j = 0; j < W; ++j) {
+            const int64_t g = table[((int64_t)j * W + p) * E + i];
+            if (g > 0 && (!stored[p * E + i] || j == p)) { L.off[i + j * E] = rp; rp += g; }
+        }
+    for (int j = p + 1; j < W; ++j) local_block(j);
+    L.total = rp;
+}
+
+struct Plan {
+    std::vector<Seg> push, pull;
+    int64_t slot_rows = 0, expert_rows = 0, token_rows = 0, max_rows = 0;
+};
+
+int plan_peer(const int64_t* table, const uint8_t* stored, int r, int E, int W, bool reverse, Plan& plan) {
+    FMOE_REQUIRE(table && stored && E > 0 && W > 0 && r >= 0 && r < W, "peer exchange: bad argument");
+    const size_t n = (size_t)W * E;
+    for (size_t i = 0; i < n * W; ++i) FMOE_REQUIRE(table[i] >= 0, "peer exchange: negative count at %zu", i);
+    std::vector<std::vector<int64_t>> eptr(W, std::vector<int64_t>(n + 1, 0));
+    std::vector<Layout> lay(W);
+    int64_t max_token = 0, max_expert = 0;
+    for (int p = 0; p < W; ++p) {
+        for (size_t i = 0; i < n; ++i) eptr[p][i + 1] = eptr[p][i] + table[(size_t)p * n + i];
+        expert_layout(table, stored, p, E, W, lay[p]);
+        max_token = std::max(max_token, eptr[p][n]);
+        max_expert = std::max(max_expert, lay[p].total);
+    }
+    plan.slot_rows = reverse ? max_token : max_expert;
+    plan.max_rows = std::max(max_token, max_expert);
+    plan.expert_rows = lay[r].total;
+    plan.token_rows = eptr[r][n];
+    std::vector<Seg>& push = plan.push;
+    std::vector<Seg>& pull = plan.pull;
+    const int64_t* mine = table + (size_t)r * n;
+    // rows that stay here: own rows of shadowed experts, and rows for this rank's own experts
+    for (size_t idx = 0; idx < n; ++idx)
+        if ((int)(idx / E) != r && stored[idx] && mine[idx] > 0) {
+            const int64_t tok = eptr[r][idx], ex = lay[r].shadow[idx];
+            push.push_back(reverse ? Seg{kLocal, ex, tok, mine[idx]} : Seg{kLocal, tok, ex, mine[idx]});
+        }
+    for (int i = 0; i < E; ++i) {
+        const int64_t ex = lay[r].off[i + r * E];
+        if (ex < 0) continue;
+        const int64_t tok = eptr[r][r * E + i], rows = mine[r * E + i];
+        push.push_back(reverse ? Seg{kLocal, ex, tok, rows} : Seg{kLocal, tok, ex, rows});
+    }
+    // Expert-major, peers in the order r+1, r+2, ...: ranks that work in step store into
+    // different GPUs at any moment, and a receiver's experts fill up in ascending order.
+    for (int i = 0; i < E; ++i)
+        for (int dlt = 1; dlt < W; ++dlt) {
+            const int p = (r + dlt) % W;
+            // rows this rank routes to expert i of rank p
+            const int64_t out_rows_pi = mine[p * E + i];
+            if (out_rows_pi > 0 && !stored[p * E + i]) {
+                const int64_t tok = eptr[r][p * E + i], ex = lay[p].off[i + r * E];
+                if (!reverse) push.push_back({p, tok, ex, out_rows_pi});   // to p's expert-side layout
+                else pull.push_back({kLocal, tok, tok, out_rows_pi});      // back, into this rank's token-side layout
+            }
+            // rows rank p routes to expert i of this rank
+            const int64_t in_rows_pi = table[((size_t)p * W + r) * E + i];
+            if (in_rows_pi > 0 && !stored[r * E + i]) {
+                const int64_t ex = lay[r].off[i + p * E], tok = eptr[p][r * E + i];
+                if (!reverse) pull.push_back({kLocal, ex, ex, in_rows_pi});
+                else push.push_back({p, ex, tok, in_rows_pi});             // to p's token-side layout
+            }
+        }
+    return 0;
+}
+
+// The host-table entry points keep their uploaded table, flags and plan in the compat area of the
+// header; a call whose table and flags equal the previous call's reuses the plan that is there.
+struct CompatCache {
+    std::vector<int64_t> table;
+    std::vector<uint8_t> stored;
+    int E = 0;
+    bool valid = false;
+};
+std::map<Comm*, CompatCache> g_compat;
+std::mutex g_compat_mtx;
+
+int peer_move_host_table(fmoe_comm_t comm, const void* in, void* out, const int64_t* table, const uint8_t* stored,
+                         int64_t in_rows, int64_t out_rows, int64_t row_bytes, int E, int W, bool reverse, cudaStream_t st) {
+    FMOE_REQUIRE(comm, "peer exchange: null communicator");
+    Comm* c = (Comm*)comm;
+    FMOE_REQUIRE(W == c->world, "peer exchange: n_workers=%d but communicator has %d ranks", W, c->world);
+    FMOE_REQUIRE(row_bytes > 0, "peer exchange: row_bytes=%lld", (long long)row_bytes);
+    if (c->peer.slot_bytes == 0 || row_bytes % 16 != 0) return FMOE_PEER_UNAVAILABLE;
+    const PlanDims d = plan_dims(E, W);
+    const size_t up_bytes = align_up((size_t)d.T * 8 + (size_t)d.WE, 64);
+    if ((int64_t)W * W * E > kTableMax || up_bytes + d.bytes > (size_t)kCompatBytes || (size_t)(d.S + 1) * 4 > 40 * 1024)
+        return FMOE_PEER_UNAVAILABLE;      // the same on every rank: it depends on E and W only
+    Plan plan;
+    if (int rc = plan_peer(table, stored, c->rank, E, W, reverse, plan)) return rc;
+    // Whether the rows fit must be decided identically on every rank, so only what the shared table
+    // says may enter: the largest buffer any rank receives fits a landing slot, or (when outputs are
+    // taken from the receive pools) a quarter of a pool, so that a pool can hold the four exchange
+    // outputs of a layer step.  A rank whose output then turns out to lie outside its pool AND to
+    // exceed its slot refuses the rows on the device (status bit 64) instead of hanging its peers.
+    const int64_t need = plan.slot_rows * row_bytes;
+    if (plan.max_rows >= ((int64_t)1 << 31) || (need > c->peer.slot_bytes && need * 4 > c->peer.pool_bytes))
+        return FMOE_PEER_UNAVAILABLE;
+    const int64_t token_rows = reverse ? out_rows : in_rows, expert_rows = reverse ? in_rows : out_rows;
+    if (expert_rows != plan.expert_rows)
+        return fail(FMOE_ERR_MISMATCH, "peer exchange: expert-side buffer has %lld rows, counts say %lld",
+                    (long long)expert_rows, (long long)plan.expert_rows);
+    if (token_rows < plan.token_rows)
+        return fail(FMOE_ERR_MISMATCH, "peer exchange: token-side buffer has %lld rows, counts say %lld",
+                    (long long)token_rows, (long long)plan.token_rows);
+    char* area = c->peer.base[c->rank] + kCompatOff;
+    char* dev_plan = area + up_bytes;
+    {
+        std::lock_guard<std::mutex> lk(g_compat_mtx);
+        CompatCache& cc = g_compat[c];
+        const bool same = cc.valid && cc.E == E && cc.table.size() == (size_t)d.T &&
+                          memcmp(cc.table.data(), table, (size_t)d.T * 8) == 0 && memcmp(cc.stored.data(), stored, (size_t)d.WE) == 0;
+        if (!same) {
+            cc.valid = false;
+            FMOE_CUDA_TRY(cudaMemcpyAsync(area, table, (size_t)d.T * 8, cudaMemcpyHostToDevice, st));
+            FMOE_CUDA_TRY(cudaMemcpyAsync(area + (size_t)d.T * 8, stored, (size_t)d.WE, cudaMemcpyHostToDevice, st));
+            if (int rc = launch_plan(c, c->rank, W, E, false, nullptr, (const int64_t*)area, (const uint8_t*)(area + (size_t)d.T * 8),
+                                     nullptr, -1, dev_plan, st))
+                return rc;
+            cc.table.assign(table, table + d.T);
+            cc.stored.assign(stored, stored + d.WE);
+            cc.E = E;
+            cc.valid = true;
+        }
+    }
+    return launch_move(c, in, out, dev_plan, E, in_rows, out_rows, row_bytes, reverse, st);
+}
+
+}  // namespace
+
+void peer_forget(Comm* c) {
+    std::lock_guard<std::mutex> lk(g_compat_mtx);
+    g_compat.erase(c);
 }
 
 }  // namespace fmoe
@@ -468,8 +823,8 @@ extern "C" int fmoe_peer_enable(fmoe_comm_t comm, int64_t slot_bytes, int64_t po
     if (cudaMalloc((void**)&own, (size_t)kHeaderBytes + 2 * (size_t)slot_bytes + (size_t)pool_bytes) != cudaSuccess) { ok = 0; own = nullptr; }
     if (ok && (cudaMemset(own, 0, kHeaderBytes) != cudaSuccess || cudaDeviceSynchronize() != cudaSuccess)) ok = 0;
     if (ok && cudaIpcGetMemHandle(&handle, own) != cudaSuccess) ok = 0;
-    if (cudaMalloc((void**)&counter, 2 * sizeof(unsigned int)) != cudaSuccess) { ok = 0; counter = nullptr; }
-    if (counter && cudaMemset(counter, 0, 2 * sizeof(unsigned int)) != cudaSuccess) ok = 0;
+    if (cudaMalloc((void**)&counter, 4 * sizeof(unsigned int)) != cudaSuccess) { ok = 0; counter = nullptr; }
+    if (counter && cudaMemset(counter, 0, 4 * sizeof(unsigned int)) != cudaSuccess) ok = 0;
     (void)cudaGetLastError();
     char* base[kMaxPeers] = {};
     auto release_all = [&]() {
@@ -525,7 +880,6 @@ extern "C" int fmoe_peer_enable(fmoe_comm_t comm, int64_t slot_bytes, int64_t po
     dev_buf = nullptr;
     for (int p = 0; p < W; ++p) c->peer.base[p] = base[p];
     c->peer.counter = counter;
-    c->peer.epoch = 0;
     const char* env = getenv("FMOE_B200_PEER_TIMEOUT_MS");
     long ms = env ? atol(env) : 20000;
     if (ms < 1) ms = 1;
@@ -543,31 +897,117 @@ extern "C" int64_t fmoe_peer_pool_bytes(fmoe_comm_t comm) { return comm ? ((Comm
 extern "C" void* fmoe_pool_alloc(ptrdiff_t size, int device, void*) { return pool_take(device, size > 0 ? (size_t)size : 1); }
 extern "C" void fmoe_pool_free(void* ptr, ptrdiff_t size, int device, void*) { pool_give(device, ptr, size > 0 ? (size_t)size : 1); }
 
-extern "C" int fmoe_peer_wait_probe(fmoe_comm_t comm, int32_t timeout_ms, fmoe_stream_t stream) {
+extern "C" size_t fmoe_peer_plan_bytes(int32_t n_expert, int32_t n_workers) {
+    if (n_expert <= 0 || n_workers <= 0) return 0;
+    return plan_dims(n_expert, n_workers).bytes;
+}
+
+extern "C" int64_t fmoe_peer_plan_offsets_at(int32_t n_expert, int32_t n_workers) {
+    if (n_expert <= 0 || n_workers <= 0) return -1;
+    return (int64_t)plan_dims(n_expert, n_workers).own_off;
+}
+
+extern "C" int64_t fmoe_peer_plan_table_at(int32_t n_expert, int32_t n_workers) {
+    if (n_expert <= 0 || n_workers <= 0) return -1;
+    return (int64_t)plan_dims(n_expert, n_workers).table_off;
+}
+
+extern "C" int fmoe_peer_plan_exchange(fmoe_comm_t comm, const int64_t* lec, const uint8_t* stored_models, int64_t cap_rows,
+                                       void* plan, int32_t n_expert, fmoe_stream_t stream) {
+    FMOE_REQUIRE(comm && lec, "peer_plan_exchange: null pointer");
+    Comm* c = (Comm*)comm;
+    if (c->peer.slot_bytes == 0) return FMOE_PEER_UNAVAILABLE;
+    return launch_plan(c, c->rank, c->world, n_expert, true, lec, nullptr, stored_models, nullptr, cap_rows, plan,
+                       (cudaStream_t)stream);
+}
+
+extern "C" int fmoe_peer_plan_from_table(const int64_t* all_expert_count, const uint8_t* stored_models, const int64_t* caps,
+                                         int32_t rank, int32_t n_expert, int32_t n_workers, void* plan, fmoe_stream_t stream) {
+    FMOE_REQUIRE(all_expert_count, "peer_plan_from_table: null table");
+    return launch_plan(nullptr, rank, n_workers, n_expert, false, nullptr, all_expert_count, stored_models, caps, -1, plan,
+                       (cudaStream_t)stream);
+}
+
+extern "C" int fmoe_peer_plan_read(const void* plan_host, int32_t n_expert, int32_t n_workers, int32_t list, fmoe_peer_seg_t* segs,
+                                   int32_t max_segs, int32_t* n_segs, int64_t* expert_rows, int64_t* token_rows, int32_t* overflow) {
+    FMOE_REQUIRE(plan_host && n_segs && list >= 0 && list < 4, "peer_plan_read: bad argument");
+    const PlanDims d = plan_dims(n_expert, n_workers);
+    const PlanHead* head = (const PlanHead*)plan_host;
+    FMOE_REQUIRE(head->n_expert == n_expert && head->n_workers == n_workers && head->n_slots == d.S,
+                 "peer_plan_read: the buffer does not hold a plan for E=%d W=%d", n_expert, n_workers);
+    const ListView L = list_view((char*)const_cast<void*>(plan_host), d, list);
+    int k = 0;
+    for (int s = 0; s < d.S; ++s) {
+        const int rows = L.prefix[s + 1] - L.prefix[s];
+        if (rows == 0) continue;
+        if (segs) {
+            FMOE_REQUIRE(k < max_segs, "peer_plan_read: more than max_segs=%d segments", max_segs);
+            segs[k] = {L.sel[s] == kLocal ? n_workers : L.sel[s], 0, L.src[s], L.dst[s], rows};
+        }
+        ++k;
+    }
+    *n_segs = k;
+    if (expert_rows) *expert_rows = head->expert_rows;
+    if (token_rows) *token_rows = head->token_rows;
+    if (overflow) *overflow = head->overflow;
+    return 0;
+}
+
+extern "C" int fmoe_peer_scatter_planned(fmoe_comm_t comm, const void* local_in, void* global_out, const void* plan,
+                                         int64_t in_rows, int64_t out_rows, int64_t row_bytes, int32_t n_expert,
+                                         fmoe_stream_t stream) {
+    FMOE_REQUIRE(comm, "peer exchange: null communicator");
+    Comm* c = (Comm*)comm;
+    if (c->peer.slot_bytes == 0) return FMOE_PEER_UNAVAILABLE;
+    return launch_move(c, local_in, global_out, plan, n_expert, in_rows, out_rows, row_bytes, false, (cudaStream_t)stream);
+}
+
+extern "C" int fmoe_peer_gather_planned(fmoe_comm_t comm, const void* global_in, void* local_out, const void* plan,
+                                        int64_t in_rows, int64_t out_rows, int64_t row_bytes, int32_t n_expert,
+                                        fmoe_stream_t stream) {
+    FMOE_REQUIRE(comm, "peer exchange: null communicator");
+    Comm* c = (Comm*)comm;
+    if (c->peer.slot_bytes == 0) return FMOE_PEER_UNAVAILABLE;
+    return launch_move(c, global_in, local_out, plan, n_expert, in_rows, out_rows, row_bytes, true, (cudaStream_t)stream);
+}
+
+extern "C" int fmoe_peer_wait_probe(fmoe_comm_t comm, int32_t timeout_ms, int32_t push, fmoe_stream_t stream) {
     FMOE_REQUIRE(comm, "peer_wait_probe: null communicator");
     Comm* c = (Comm*)comm;
     FMOE_REQUIRE(c->peer.slot_bytes > 0, "peer_wait_probe: the peer-memory exchange is off");
     FMOE_REQUIRE(timeout_ms >= 1 && timeout_ms <= 10000, "peer_wait_probe: timeout_ms=%d (1..10000)", timeout_ms);
-    // A consume phase without rows that waits for an epoch no peer will ever publish.
-    const unsigned long long epoch = c->peer.epoch, limit = c->peer.timeout_ns;
-    c->peer.epoch = epoch + (1ull << 40);
-    c->peer.timeout_ns = (unsigned long long)timeout_ms * 1000000ull;
+    // One block of the push (or consume) kernel that waits for an epoch no peer will ever publish:
+    // it announces nothing, moves nothing, and leaves the epoch words alone.  The plan it reads is a
+    // zeroed one (no rows) in the compat area's tail.
     PeerBases b;
     for (int p = 0; p < kMaxPeers; ++p) b.base[p] = c->peer.base[p];
-    PeerSegs t;
-    t.n = 0; t.prefix[0] = 0; t.prefix[1] = 0;
-    PeerLaunch a;
-    a.rank = c->rank; a.world = c->world; a.parity = 0;
-    a.announce = 0; a.signal_last = 0; a.my_dest = 0;
-    a.epoch = c->peer.epoch; a.timeout_ns = c->peer.timeout_ns;
-    a.row_vecs = 1; a.slot_off = kHeaderBytes;
-    a.counter = c->peer.counter;
+    char* plan = c->peer.base[c->rank] + kCompatOff + kCompatBytes;
+    const PlanDims pd = plan_dims(1, c->world);
+    FMOE_REQUIRE(pd.bytes <= (size_t)kProbeBytes, "peer_wait_probe: plan of %zu bytes", pd.bytes);
+    FMOE_CUDA_TRY(cudaMemsetAsync(plan, 0, pd.bytes, (cudaStream_t)stream));
+    PlanHead head;
+    memset(&head, 0, sizeof(head));
+    head.n_expert = 1; head.n_workers = c->world; head.rank = c->rank; head.n_slots = pd.S;
+    FMOE_CUDA_TRY(cudaMemcpyAsync(plan, &head, sizeof(head), cudaMemcpyHostToDevice, (cudaStream_t)stream));
+    MoveArgs a;
+    memset(&a, 0, sizeof(a));
+    a.rank = c->rank; a.world = c->world; a.probe = 1; a.direct = 1;
+    a.slot_bytes = c->peer.slot_bytes; a.row_bytes = 16;
+    a.timeout_ns = (unsigned long long)timeout_ms * 1000000ull;
+    a.counter = c->peer.counter + 2;
+    a.plan = plan;
     a.status = device_status_ptr();
-    c->peer.epoch = epoch;
-    c->peer.timeout_ns = limit;
     FMOE_REQUIRE(a.status, "peer_wait_probe: no device status word");
-    peer_rows_kernel<false><<<1, 256, 0, (cudaStream_t)stream>>>(t, b, a, nullptr, nullptr);
+    const size_t smem = (size_t)(pd.S + 1) * sizeof(int);
+    if (push) peer_move_kernel<true><<<1, kMoveThreads, smem, (cudaStream_t)stream>>>(b, a, nullptr, nullptr);
+    else peer_move_kernel<false><<<1, kMoveThreads, smem, (cudaStream_t)stream>>>(b, a, nullptr, nullptr);
     FMOE_CHECK_LAUNCH();
+    return 0;
+}
+
+extern "C" int fmoe_peer_set_timeout_ms(fmoe_comm_t comm, int32_t timeout_ms) {
+    FMOE_REQUIRE(comm && timeout_ms >= 1, "peer_set_timeout_ms: bad argument");
+    ((Comm*)comm)->peer.timeout_ns = (unsigned long long)timeout_ms * 1000000ull;
     return 0;
 }
 
@@ -579,16 +1019,16 @@ extern "C" int fmoe_peer_global_scatter(fmoe_comm_t comm, const void* local_in, 
                                         const int64_t* all_expert_count_host, const uint8_t* stored_models_host,
                                         int64_t in_rows, int64_t out_rows, int64_t row_bytes, int32_t n_expert,
                                         int32_t n_workers, fmoe_stream_t stream) {
-    return peer_move(comm, local_in, global_out, all_expert_count_host, stored_models_host, in_rows, out_rows,
-                     row_bytes, n_expert, n_workers, false, (cudaStream_t)stream);
+    return peer_move_host_table(comm, local_in, global_out, all_expert_count_host, stored_models_host, in_rows, out_rows,
+                                row_bytes, n_expert, n_workers, false, (cudaStream_t)stream);
 }
 
 extern "C" int fmoe_peer_global_gather(fmoe_comm_t comm, const void* global_in, void* local_out,
                                        const int64_t* all_expert_count_host, const uint8_t* stored_models_host,
                                        int64_t in_rows, int64_t out_rows, int64_t row_bytes, int32_t n_expert,
                                        int32_t n_workers, fmoe_stream_t stream) {
-    return peer_move(comm, global_in, local_out, all_expert_count_host, stored_models_host, in_rows, out_rows,
-                     row_bytes, n_expert, n_workers, true, (cudaStream_t)stream);
+    return peer_move_host_table(comm, global_in, local_out, all_expert_count_host, stored_models_host, in_rows, out_rows,
+                                row_bytes, n_expert, n_workers, true, (cudaStream_t)stream);
 }
 
 extern "C" int fmoe_peer_plan(const int64_t* all_expert_count_host, const uint8_t* stored_models_host, int32_t rank,

@@ -33,7 +33,7 @@ _KERNELS = {"expert_count": 1, "assign_pos": 4, "count_and_pos": 4, "limit_by_ca
             "prune_gate_by_capacity": 4, "local_scatter": 1, "local_gather": 3, "local_gather_inv": 1,
             "local_gather_sum": 1, "local_gather_add": 3, "combine_forward": 1, "combine_backward": 1, "linear_forward": 1,
             "linear_backward": 3, "expert_exchange": 2, "generate_cached_count": 1,
-            "peer_scatter": 2, "peer_gather": 2}
+            "peer_scatter": 2, "peer_gather": 2, "peer_plan": 1}
 
 
 class Profile:
@@ -468,6 +468,106 @@ def peer_global_gather(output_buf, all_expert_count, stored_models, batch_size, 
     """Inverse of peer_global_scatter; same contract."""
     return _peer_move(lib.fmoe_peer_global_gather, "peer_gather", output_buf, all_expert_count, stored_models,
                       batch_size, n_expert, n_workers)
+
+
+class PeerPlan:
+    """Plan of a layer call's exchanges as the device built it (fmoe_peer_plan_exchange /
+    fmoe_peer_plan_from_table).  ``own_offsets`` (int64 [E+1]) and ``table`` (int64 [W, W, E]) are
+    views into the plan buffer on the device; nothing is copied to the host."""
+    __slots__ = ("buf", "n_expert", "n_workers", "own_offsets", "table")
+
+    def __init__(self, buf, n_expert, n_workers):
+        self.buf, self.n_expert, self.n_workers = buf, n_expert, n_workers
+        at = int(lib.fmoe_peer_plan_offsets_at(n_expert, n_workers))
+        self.own_offsets = buf[at: at + 8 * (n_expert + 1)].view(torch.int64)
+        at = int(lib.fmoe_peer_plan_table_at(n_expert, n_workers))
+        n = n_workers * n_workers * n_expert
+        self.table = buf[at: at + 8 * n].view(torch.int64).view(n_workers, n_workers, n_expert)
+
+    def read(self, which):
+        """Decodes list ``which`` (0 push/1 pull of global_scatter, 2/3 of global_gather) on the host:
+        (segments [(dst_rank, src_row, dst_row, rows)], expert_rows, token_rows, overflow).  Synchronises."""
+        host = self.buf.cpu().numpy()
+        d = lib.fmoe_peer_plan_bytes(self.n_expert, self.n_workers)
+        cap = (2 * self.n_workers - 1) * self.n_expert
+        segs = (_lib.PeerSeg * cap)()
+        n, er, tr, ov = ctypes.c_int32(), ctypes.c_int64(), ctypes.c_int64(), ctypes.c_int32()
+        check(lib.fmoe_peer_plan_read(host.ctypes.data, self.n_expert, self.n_workers, which,
+                                      ctypes.cast(segs, ctypes.c_void_p), cap, ctypes.byref(n), ctypes.byref(er),
+                                      ctypes.byref(tr), ctypes.byref(ov)), "peer_plan_read")
+        assert d == host.size
+        return ([(segs[i].dst_rank, segs[i].src_row, segs[i].dst_row, segs[i].rows) for i in range(n.value)],
+                er.value, tr.value, ov.value)
+
+
+def _plan_buffer(n_expert, n_workers, device):
+    return torch.empty(int(lib.fmoe_peer_plan_bytes(n_expert, n_workers)), dtype=torch.uint8, device=device)
+
+
+def peer_plan_exchange(local_expert_count, stored_models, cap_rows, n_expert):
+    """Swaps the local expert counts (int64 [W*E], CUDA) with all peers through peer memory and builds
+    the exchange plan on the device; nothing comes back to the host.  ``stored_models``: bool/uint8
+    [W*E] CUDA tensor or None; ``cap_rows``: rows of this rank's expert-side buffers.  Returns a
+    PeerPlan, or None when the peer-memory form is off."""
+    _check_cuda(local_expert_count, stored_models)
+    dev = local_expert_count.device
+    assert local_expert_count.dtype == torch.int64
+    rank, world = comm_rank(dev)
+    assert local_expert_count.numel() == n_expert * world
+    plan = _plan_buffer(n_expert, world, dev)
+    st = stored_models.view(torch.uint8) if stored_models is not None and stored_models.dtype == torch.bool else stored_models
+    with torch.cuda.device(dev):
+        ok = _run("peer_plan", lib.fmoe_peer_plan_exchange, _comm(dev), _ptr(local_expert_count), _ptr(st), int(cap_rows),
+                  _ptr(plan), n_expert, _stream(), soft=True)
+    return PeerPlan(plan, n_expert, world) if ok else None
+
+
+def peer_plan_from_table(all_expert_count, stored_models, rank, n_expert, n_workers, caps=None):
+    """The same plan for ``rank`` from a full count table [W, W, E] that is already on the device."""
+    _check_cuda(all_expert_count, stored_models, caps)
+    dev = all_expert_count.device
+    assert all_expert_count.dtype == torch.int64 and all_expert_count.numel() == n_workers * n_workers * n_expert
+    plan = _plan_buffer(n_expert, n_workers, dev)
+    st = stored_models.view(torch.uint8) if stored_models is not None and stored_models.dtype == torch.bool else stored_models
+    with torch.cuda.device(dev):
+        _run("peer_plan", lib.fmoe_peer_plan_from_table, _ptr(all_expert_count), _ptr(st), _ptr(caps), rank, n_expert,
+             n_workers, _ptr(plan), _stream())
+    return PeerPlan(plan, n_expert, n_workers)
+
+
+def _planned_move(fn, name, buf, plan, out_rows):
+    _check_cuda(buf)
+    out = _recv_empty(buf, out_rows)
+    with torch.cuda.device(buf.device):
+        _run(name, fn, _comm(buf.device), _ptr(buf), _ptr(out), _ptr(plan.buf), buf.shape[0], out_rows,
+             buf.shape[1] * buf.element_size(), plan.n_expert, _stream())
+    return out
+
+
+def peer_scatter_planned(input_buf, plan, out_rows):
+    """global_scatter driven by a PeerPlan: [A, d] token-side rows -> [out_rows, d] expert-side buffer
+    (out_rows may exceed the rows that arrive; the rest is left untouched)."""
+    return _planned_move(lib.fmoe_peer_scatter_planned, "peer_scatter", input_buf, plan, out_rows)
+
+
+def peer_gather_planned(output_buf, plan, out_rows):
+    """global_gather driven by a PeerPlan: expert-side rows -> [out_rows, d] token-side buffer."""
+    return _planned_move(lib.fmoe_peer_gather_planned, "peer_gather", output_buf, plan, out_rows)
+
+
+def nosync_capacity(token_rows, row_bytes, n_workers, device):
+    """Rows to give the expert-side buffers of a forward that does not read the counts back: the worst
+    case (every rank routes everything here) when the receive pool can hold two such buffers beside
+    the two token-side ones, else what the pool does hold; 0 when that leaves less than 1.5 x the
+    balanced load (the caller then reads the counts as before)."""
+    c = _comms.get(device.index if device.index is not None else torch.cuda.current_device())
+    if c is None or int(lib.fmoe_peer_slot_bytes(c)) == 0:
+        return 0
+    pool = int(lib.fmoe_peer_pool_bytes(c))
+    worst = n_workers * token_rows
+    fits = int((0.9 * pool - 2 * token_rows * row_bytes) // (2 * row_bytes)) if row_bytes else 0
+    cap = min(worst, fits)
+    return cap if cap >= int(1.5 * token_rows) else 0
 
 
 def exchange_cache_info(sent_models, num_expert, world_size):

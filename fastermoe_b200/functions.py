@@ -82,7 +82,7 @@ def count_by_gate(gate, num_expert, world_size, require_pos=True):
 class Routing:
     """Everything the layer derives from the gate indices for one forward."""
     __slots__ = ("pos", "inv", "lec_dev", "offsets_dev", "own_offsets_dev", "n_rows", "n_recv", "lec", "gec",
-                 "own_counts", "_aec", "_agec", "rank", "early")
+                 "own_counts", "_aec", "_agec", "rank", "early", "plan")
 
     @property
     def aec(self):
@@ -97,8 +97,12 @@ class Routing:
         return self._agec
 
 
-def route(gate, num_expert, world_size, before_wait=None):
-    """Bucketing + count exchange with at most one device-to-host copy.
+def route(gate, num_expert, world_size, before_wait=None, cap_rows=0):
+    """Bucketing + count exchange with at most one device-to-host copy, and none at all with
+    ``cap_rows`` > 0: the counts are then swapped through peer memory and the exchange plan is built
+    on the device (``routing.plan``); the expert-side buffers get ``cap_rows`` rows, the offsets of
+    this worker's experts stay on the device (``own_offsets_dev``), and ``lec``/``gec``/``aec`` are
+    not available on the host.
 
     ``before_wait(routing)``, if given, is called right before the host waits for
     the count table (world_size > 1 only) with ``pos``/``inv`` already queued; what
@@ -110,7 +114,7 @@ def route(gate, num_expert, world_size, before_wait=None):
     the count table, and the host-side slicing after the wait is a few numpy
     views, so the GPU idles as briefly as possible around the one sync."""
     r = Routing()
-    r._aec = r._agec = r.early = None
+    r._aec = r._agec = r.early = r.plan = None
     with torch.no_grad():
         flat = gate.reshape(-1)
         n_tot = num_expert * world_size
@@ -119,6 +123,14 @@ def route(gate, num_expert, world_size, before_wait=None):
             r.n_rows = flat.numel()
             r.lec = r.gec = r.own_offsets_dev = r.own_counts = None
             r.rank = 0
+            return r
+        if cap_rows > 0:
+            r.plan = fmoe_cuda.peer_plan_exchange(r.lec_dev, None, cap_rows, num_expert)
+        if r.plan is not None:
+            r.rank, _ = fmoe_cuda.comm_rank(gate.device)
+            r.own_offsets_dev = r.plan.own_offsets
+            r.n_rows, r.n_recv = flat.numel(), int(cap_rows)
+            r.lec = r.gec = r.own_counts = None
             return r
         aec, _, _ = fmoe_cuda.expert_exchange(r.lec_dev, num_expert, world_size)
         r.rank, _ = fmoe_cuda.comm_rank(gate.device)
@@ -401,6 +413,23 @@ class Exchange:
             if out is not None:
                 return out
         return fmoe_cuda.global_gather(buf, self.lec, self.gec, self.stored, out_rows, self.world_size)
+
+
+class PlannedExchange:
+    """One layer call's all-to-all-v driven by a plan that lives on the device (fmoe_cuda.PeerPlan):
+    the host knows neither the counts nor how many rows arrive; ``fwd_batch_size`` is the capacity
+    of the expert-side buffers."""
+    __slots__ = ("plan", "fwd_batch_size", "world_size", "num_expert")
+
+    def __init__(self, plan, cap_rows, world_size):
+        self.plan, self.fwd_batch_size, self.world_size = plan, int(cap_rows), world_size
+        self.num_expert = plan.n_expert
+
+    def scatter(self, buf, out_rows):
+        return fmoe_cuda.peer_scatter_planned(buf, self.plan, out_rows)
+
+    def gather(self, buf, out_rows):
+        return fmoe_cuda.peer_gather_planned(buf, self.plan, out_rows)
 
 
 _ACT_CODES = {"none": _lib.ACT_NONE, "relu": _lib.ACT_RELU, "gelu": _lib.ACT_GELU}

@@ -9,7 +9,7 @@ import torch.nn.functional as F
 
 from .naive_gate import NaiveGate
 from .gshard_gate import balance_loss_top1
-from ..functions import count_by_gate
+from ..functions import count_by_gate, gate_topk
 
 nw_per_node = 4
 
@@ -30,7 +30,7 @@ class HirGate(NaiveGate):
         gate_score = self.gate(inp)
         off_node = ~self.mask.to(inp.device)
 
-        top2_val, top2_idx = torch.topk(gate_score, k=2, dim=-1)
+        top2_val, top2_idx = gate_topk(gate_score, 2)
         n_tok = gate_score.shape[0]
         with torch.no_grad():
             top1_idx = top2_idx.view(-1, 2)[:, 0]
@@ -49,8 +49,7 @@ class HirGate(NaiveGate):
             ogn_thres = int(n_tok * self.ogn_ratio)
 
         if int(leaving.sum().item()) < ogn_thres:
-            topk_val, topk_idx = torch.topk(gate_score, k=self.top_k)
-            return topk_idx, F.softmax(topk_val, dim=-1)
+            return top2_idx, F.softmax(top2_val, dim=-1)
 
         with torch.no_grad():
             # The ogn_thres tokens with the strongest off-node first choice keep it
@@ -59,7 +58,7 @@ class HirGate(NaiveGate):
             _, keep = torch.topk(top1_val.view(-1), k=ogn_thres)
             cand = gate_score.detach().clone()
             cand[:, limited] = float("-inf")
-            _, topk_idx = torch.topk(cand, k=self.top_k)
+            _, topk_idx = gate_topk(cand, self.top_k)
             topk_idx[keep, 1] = top1_idx.view(-1)[keep]
 
         rows = torch.arange(n_tok, device=inp.device).repeat_interleave(2)

@@ -7,7 +7,7 @@ import torch.nn as nn
 
 from . import fmoe_cuda
 from .functions import (AllGather, Exchange, ExpertCounts, MOECache, MOEGatherCombine, MOELinear,
-                        MOEScatterFused, Slice, cached_count_host, ensure_comm, route)
+                        MOEScatterFused, PlannedExchange, Slice, cached_count_host, ensure_comm, route)
 from .gates import NaiveGate
 
 
@@ -94,12 +94,21 @@ def _fmoe_general_global_forward(inp, gate, expert_fn, policy_fn, experts, num_e
     top_k = gate.shape[1] if gate.dim() == 2 else 1
     n_tokens = inp.shape[0]
     early = None
+    cap_rows = 0
+    no_policy = policy_fn is None or getattr(policy_fn, "never_shadows", False)
     if world_size > 1 and not enable_fuse:
-        # the local scatter needs the positions only: queue it before the host waits for the counts
-        def early(r, inp=inp):
-            with torch.no_grad():
-                return fmoe_cuda.local_scatter(inp.detach().contiguous(), r.pos, pos_div=top_k, n_rows=r.pos.numel())
-    routing = route(gate, num_expert, world_size, before_wait=early)
+        # Nothing has to come back to the host when no shadowing policy wants to see the counts, the
+        # experts are one fused module (it reads its segment offsets on the device) and the rows
+        # travel through peer memory: buffers are then sized for the worst case the pool can hold.
+        if no_policy and fused and os.environ.get("FMOE_B200_NOSYNC", "1") != "0":
+            cap_rows = fmoe_cuda.nosync_capacity(n_tokens * top_k, inp.shape[1] * inp.element_size(), world_size,
+                                                 inp.device)
+        if cap_rows == 0:
+            # the local scatter needs the positions only: queue it before the host waits for the counts
+            def early(r, inp=inp):
+                with torch.no_grad():
+                    return fmoe_cuda.local_scatter(inp.detach().contiguous(), r.pos, pos_div=top_k, n_rows=r.pos.numel())
+    routing = route(gate, num_expert, world_size, before_wait=early, cap_rows=cap_rows)
 
     if world_size == 1:
         # No exchange, no host copies: buffers have one row per gate entry; rows past
@@ -110,9 +119,16 @@ def _fmoe_general_global_forward(inp, gate, expert_fn, policy_fn, experts, num_e
         x = expert_fn(x, [[experts] if fused else experts], counts, num_expert)
         exch = None
         n_rows = routing.n_rows
+    elif routing.plan is not None:
+        # No host copy of the counts: plan, offsets and row counts stay on the device.
+        stored = _no_shadow_flags(world_size, num_expert)
+        exch = PlannedExchange(routing.plan, routing.n_recv, world_size)
+        n_rows = routing.n_rows
+        x = MOEScatterFused.apply(inp, routing.pos, routing.inv, top_k, n_rows, exch)
+        x = expert_fn(x, [[experts]], ExpertCounts(routing.own_offsets_dev), num_expert)
     else:
         shadows = {} if shadows is None else shadows
-        if policy_fn is None or getattr(policy_fn, "never_shadows", False):
+        if no_policy:
             # No shadowing: every row goes to its expert's owner; nothing else to plan on the host.
             stored, any_shadow = _no_shadow_flags(world_size, num_expert), False
             if fused:
@@ -250,8 +266,18 @@ class FMoE(nn.Module):
                 mark_module_parallel_comm(self.experts, expert_dp_comm)
         mark_module_parallel_comm(self.gate, "moe")
 
+    def check_status(self, device=None):
+        """Raises RuntimeError when a kernel of the library reported trouble on ``device`` since the last
+        check: a bounded wait that expired (a peer did not deliver: that step's results are incomplete),
+        more rows routed to a GPU than its buffers hold, or clamped segment offsets.  Waits for the
+        queued work; call it where the training loop synchronises anyway (e.g. after reading the loss).
+        With FMOE_B200_CHECK_STATUS=1 every forward starts with this check (of the previous step)."""
+        fmoe_cuda.check_status(device)
+
     def forward(self, inp):
         r"""gate -> route -> experts -> weighted sum of the top-k expert outputs."""
+        if os.environ.get("FMOE_B200_CHECK_STATUS", "0") == "1" and inp.is_cuda:
+            self.check_status(inp.device)
         if self.world_size > 1:
             ensure_comm(inp, self.moe_group)
         if self.mp_size > 1:

@@ -361,56 +361,89 @@ int fmoe_global_gather(fmoe_comm_t comm, const void* global_in, void* local_out,
                        int32_t n_workers, void* staging, fmoe_stream_t stream);
 
 /* Peer-memory form of the two exchanges above (no counterpart in the reference,
- * which always goes through ncclSend/ncclRecv, cuda/global_exchange.cuh:75-124):
- * rows are stored straight into the destination GPU's memory over NVLink by a copy
- * kernel and published with flags; no NCCL call is made.
+ * which always goes through ncclSend/ncclRecv, cuda/global_exchange.cuh:75-124, and needs the
+ * counts on the host): rows are stored straight into the destination GPU's memory over NVLink
+ * by a copy kernel and published with flags; no NCCL call is made, and the row plan is built on
+ * the device, so the host never has to read the counts.
  *
- * fmoe_peer_enable is collective over the communicator: every rank allocates a
- * landing area of 2 slots of slot_bytes (+4 KiB of flags, + an optional receive pool), the
- * ranks swap CUDA IPC handles and map each other's areas.  If any rank cannot (no peer access, IPC
- * closed to the process), the form stays off on every rank and FMOE_OK is
- * returned; fmoe_peer_slot_bytes then reports 0.
+ * fmoe_peer_enable is collective over the communicator: every rank allocates a landing area
+ * (4 MiB of flags, count tables and scratch; 2 slots of slot_bytes; an optional receive pool of
+ * pool_bytes), the ranks swap CUDA IPC handles and map each other's areas.  If any rank cannot
+ * (no peer access, IPC closed to the process), the form stays off on every rank and FMOE_OK is
+ * returned; fmoe_peer_slot_bytes then reports 0.  This call allocates device memory and
+ * synchronises; nothing else in this section does.
  *
- * fmoe_peer_global_scatter / _gather take all_expert_count_host[W][W][E] (rows that
- * rank s routes to expert e of rank d at [s][d][e]; the table fmoe_expert_exchange
- * gathers), because each rank needs the layout of every other rank's buffer, and
- * because the decision to use this form must be the same everywhere: they return
- * FMOE_PEER_UNAVAILABLE, having queued nothing, when the form is off, row_bytes is
- * not a multiple of 16 or some rank would need more than one slot; the caller then
- * uses fmoe_global_scatter / _gather.  Buffers, row counts and stored_models_host
- * mean what they mean there.  Waits on other ranks are bounded
- * (FMOE_B200_PEER_TIMEOUT_MS, default 20000): an expired wait raises bit 16 or 32
- * of fmoe_device_status. */
+ * The kernels of one communicator keep their epochs in device memory and must be queued in one
+ * total order (one stream, or streams ordered by events), the same order on every rank.  Waits
+ * on other ranks are bounded (FMOE_B200_PEER_TIMEOUT_MS, default 20000): an expired wait
+ * raises bit 16 or 32 of fmoe_device_status, rows for a peer that never announced are dropped;
+ * bit 64: a rank had no room for the rows routed to it (nothing was stored out of bounds). */
 #define FMOE_PEER_UNAVAILABLE 1
-/* The row segments of one such exchange for `rank` (host only, no GPU needed; for inspection and
- * tests).  push: rows its push kernel stores, dst_rank == n_workers meaning "stays on this GPU,
- * written to the output buffer", else rows src_row.. of its input go to rows dst_row.. of dst_rank's
- * landing slot.  pull: rows its consume kernel copies from its own slot (src_row) to its output
- * (dst_row).  reverse = 0: global_scatter, 1: global_gather.  slot_rows: rows of the largest slot
- * any rank needs.  Pass push = pull = NULL to get the counts only. */
 typedef struct {
     int32_t dst_rank, reserved;
     int64_t src_row, dst_row, rows;
 } fmoe_peer_seg_t;
-int fmoe_peer_plan(const int64_t* all_expert_count_host, const uint8_t* stored_models_host,
-                   int32_t rank, int32_t n_expert, int32_t n_workers, int32_t reverse,
-                   fmoe_peer_seg_t* push, int32_t* n_push, fmoe_peer_seg_t* pull, int32_t* n_pull,
-                   int32_t max_segs, int64_t* slot_rows);
 int fmoe_peer_enable(fmoe_comm_t comm, int64_t slot_bytes, int64_t pool_bytes, fmoe_stream_t stream);
+int64_t fmoe_peer_slot_bytes(fmoe_comm_t comm);
 /* Receive pool (pool_bytes > 0 above): a region of the same peer-mapped allocation out of which a
- * host can allocate the OUTPUT buffers of fmoe_peer_global_scatter / _gather; rows then land in the
- * output directly instead of in a slot from which they are copied once more.  fmoe_pool_alloc /
- * fmoe_pool_free have the signature torch.cuda.memory.CUDAPluggableAllocator expects (first-fit
- * sub-allocation of the region, NULL when it is exhausted); fmoe_peer_pool_bytes: its size. */
+ * host can allocate the OUTPUT buffers of the exchanges; rows then land in the output directly
+ * instead of in a slot from which they are copied once more.  fmoe_pool_alloc / fmoe_pool_free have
+ * the signature torch.cuda.memory.CUDAPluggableAllocator expects (first-fit sub-allocation of the
+ * region, NULL when it is exhausted); fmoe_peer_pool_bytes: its size. */
 int64_t fmoe_peer_pool_bytes(fmoe_comm_t comm);
 void* fmoe_pool_alloc(ptrdiff_t size, int device, void* stream);
 void fmoe_pool_free(void* ptr, ptrdiff_t size, int device, void* stream);
-/* Queues a wait of the exchange's consume step for rows that no peer will ever announce, bounded by
- * timeout_ms: when it expires the kernel raises bit 32 of fmoe_device_status and returns; the
- * exchange state is untouched.  Lets a host check that its handling of an expired wait works
- * without a peer having to fail. */
-int fmoe_peer_wait_probe(fmoe_comm_t comm, int32_t timeout_ms, fmoe_stream_t stream);
-int64_t fmoe_peer_slot_bytes(fmoe_comm_t comm);
+
+/* The plan of a layer call's exchanges, built on the device.  It stands for the five host copies
+ * and the host-side pointer arithmetic of prepare_forward + global_scatter / global_gather
+ * (fmoe/functions.py:45-69, cuda/global_exchange.cuh:60-230).
+ *   plan: device buffer of fmoe_peer_plan_bytes(n_expert, n_workers) bytes, 64-byte aligned; it
+ *     must stay alive until the last exchange that uses it (forward and backward) has run.
+ *   fmoe_peer_plan_exchange: collective.  lec = this rank's local expert counts [W*E] (device);
+ *     the ranks write them into each other's landing areas (no NCCL), so afterwards every rank
+ *     holds the full table [W][W][E].  stored_models (device, may be NULL = none) = shadowed
+ *     experts [W*E], identical on all ranks.  cap_rows = rows of this rank's expert-side buffers
+ *     (< 0: unchecked); if any rank would receive more, every rank's plan comes out empty and bit
+ *     64 is raised on all of them.  Returns FMOE_PEER_UNAVAILABLE when the form is off.
+ *   fmoe_peer_plan_from_table: the same plan for `rank` from a full table already on the device
+ *     (e.g. the one fmoe_expert_exchange gathered); caps (device, [W], may be NULL).  Not
+ *     collective, needs no communicator.
+ * At byte fmoe_peer_plan_offsets_at() of the plan: int64 [n_expert+1], the row offsets of this
+ * rank's experts in its expert-side buffer (the seg_offsets of fmoe_linear_*; valid when none of
+ * this rank's own experts is shadowed).  At fmoe_peer_plan_table_at(): the table, int64 [W][W][E].
+ * fmoe_peer_plan_read decodes one list of a plan that was copied to the host (list 0: rows the
+ * push kernel of global_scatter moves, 1: rows its consume kernel copies out of a slot, 2 and 3:
+ * the same for global_gather); dst_rank == n_workers means "stays on this GPU". */
+size_t fmoe_peer_plan_bytes(int32_t n_expert, int32_t n_workers);
+int64_t fmoe_peer_plan_offsets_at(int32_t n_expert, int32_t n_workers);
+int64_t fmoe_peer_plan_table_at(int32_t n_expert, int32_t n_workers);
+int fmoe_peer_plan_exchange(fmoe_comm_t comm, const int64_t* lec, const uint8_t* stored_models,
+                            int64_t cap_rows, void* plan, int32_t n_expert, fmoe_stream_t stream);
+int fmoe_peer_plan_from_table(const int64_t* all_expert_count, const uint8_t* stored_models,
+                              const int64_t* caps, int32_t rank, int32_t n_expert, int32_t n_workers,
+                              void* plan, fmoe_stream_t stream);
+int fmoe_peer_plan_read(const void* plan_host, int32_t n_expert, int32_t n_workers, int32_t list,
+                        fmoe_peer_seg_t* segs, int32_t max_segs, int32_t* n_segs, int64_t* expert_rows,
+                        int64_t* token_rows, int32_t* overflow);
+/* global_scatter / global_gather (cuda/global_exchange.cu:26-80) driven by such a plan.  in_rows /
+ * out_rows are the rows of the buffers as allocated: they may exceed what the counts describe
+ * (buffers sized for the worst case); a buffer that is too small makes this rank refuse the rows
+ * (bit 64).  The gather clears token-side rows past the ones the counts describe.  Returns
+ * FMOE_PEER_UNAVAILABLE when the form is off. */
+int fmoe_peer_scatter_planned(fmoe_comm_t comm, const void* local_in, void* global_out, const void* plan,
+                              int64_t in_rows, int64_t out_rows, int64_t row_bytes, int32_t n_expert,
+                              fmoe_stream_t stream);
+int fmoe_peer_gather_planned(fmoe_comm_t comm, const void* global_in, void* local_out, const void* plan,
+                             int64_t in_rows, int64_t out_rows, int64_t row_bytes, int32_t n_expert,
+                             fmoe_stream_t stream);
+/* The same exchanges with the reference's argument style: all_expert_count_host[W][W][E] (rows that
+ * rank s routes to expert e of rank d at [s][d][e]; the table fmoe_expert_exchange gathers) and the
+ * flags on the HOST.  The table is uploaded and planned on the device (a call with the same table
+ * and flags as the previous one reuses its plan).  They return FMOE_PEER_UNAVAILABLE, having
+ * queued nothing, when the form is off, row_bytes is not a multiple of 16, or the largest buffer
+ * any rank receives fits neither a landing slot nor a quarter of a receive pool -- a verdict that
+ * depends on the shared table only, so it is the same on every rank; the caller then uses
+ * fmoe_global_scatter / _gather.  Buffers and row counts mean what they mean there. */
 int fmoe_peer_global_scatter(fmoe_comm_t comm, const void* local_in, void* global_out,
                              const int64_t* all_expert_count_host,
                              const uint8_t* stored_models_host, int64_t in_rows,
@@ -421,6 +454,25 @@ int fmoe_peer_global_gather(fmoe_comm_t comm, const void* global_in, void* local
                             const uint8_t* stored_models_host, int64_t in_rows,
                             int64_t out_rows, int64_t row_bytes, int32_t n_expert,
                             int32_t n_workers, fmoe_stream_t stream);
+/* Host mirror of the plan (no GPU; for inspection and tests): the row segments of one exchange
+ * for `rank`.  push: rows its push kernel stores, dst_rank == n_workers meaning "stays on this
+ * GPU, written to the output buffer", else rows src_row.. of its input go to rows dst_row.. of
+ * dst_rank's landing place.  pull: rows its consume kernel copies from its own slot (src_row) to
+ * its output (dst_row).  reverse = 0: global_scatter, 1: global_gather.  slot_rows: rows of the
+ * largest buffer any rank receives.  Pass push = pull = NULL to get the counts only. */
+int fmoe_peer_plan(const int64_t* all_expert_count_host, const uint8_t* stored_models_host,
+                   int32_t rank, int32_t n_expert, int32_t n_workers, int32_t reverse,
+                   fmoe_peer_seg_t* push, int32_t* n_push, fmoe_peer_seg_t* pull, int32_t* n_pull,
+                   int32_t max_segs, int64_t* slot_rows);
+/* Queues one block of the exchange's push (push != 0) or consume step that waits, for at most
+ * timeout_ms, for an epoch that no peer will ever publish: when the wait expires the kernel raises
+ * bit 16 (push) or 32 (consume) of fmoe_device_status and returns; it announces nothing, stores
+ * nothing and leaves the exchange state untouched.  Lets a host check that its handling of an
+ * expired wait works without a peer having to fail. */
+int fmoe_peer_wait_probe(fmoe_comm_t comm, int32_t timeout_ms, int32_t push, fmoe_stream_t stream);
+/* Limit of the waits on other ranks in the kernels queued from now on (initially
+ * FMOE_B200_PEER_TIMEOUT_MS or 20000). */
+int fmoe_peer_set_timeout_ms(fmoe_comm_t comm, int32_t timeout_ms);
 
 /* exchange_cache_info(sent_models, num_expert, world_size):
  * cuda/fmoe_cuda.cpp:24-27, cuda/global_exchange.cuh:232-249.  All-gather of

@@ -84,14 +84,14 @@ def gpu_exchange(rank, world, port):
             assert fc.peer_global_scatter(odd, table, torch.from_numpy(stored), want[rank].shape[0], E, world) is None
             st = ctypes.c_int32(-1)
             assert fc.lib.fmoe_device_status(ctypes.byref(st)) == 0 and st.value == 0, f"device status {st.value}"
-            if True:
-                # a wait for rows that nobody sends ends by itself, raises the status bit and leaves the
-                # exchange usable
-                import time
+            # a wait for an announcement (push) or for rows (consume) that nobody sends ends by itself,
+            # raises the status bit and leaves the exchange usable
+            import time
+            for push, bit in ((0, 32), (1, 16)):
                 t0 = time.time()
                 with torch.cuda.device(dev):
-                    assert fc.lib.fmoe_peer_wait_probe(fc._comm(dev), 150, fc._stream()) == 0, fc._lib.last_error()
-                assert fc.lib.fmoe_device_status(ctypes.byref(st)) == 0 and st.value & 32, f"status {st.value}"
+                    assert fc.lib.fmoe_peer_wait_probe(fc._comm(dev), 150, push, fc._stream()) == 0, fc._lib.last_error()
+                assert fc.lib.fmoe_device_status(ctypes.byref(st)) == 0 and st.value == bit, f"status {st.value}"
                 assert 0.1 < time.time() - t0 < 5.0
                 assert fc.lib.fmoe_device_status_clear() == 0
                 assert fc.lib.fmoe_device_status(ctypes.byref(st)) == 0 and st.value == 0
@@ -118,6 +118,14 @@ def gpu_exchange(rank, world, port):
             assert out is not None and torch.equal(out, torch.from_numpy(want2[rank]).to(dev) + rnd), "many-segment scatter"
             back = fc.peer_global_gather(out, torch.from_numpy(table2.copy()), torch.from_numpy(none2), mine.shape[0], E2, world)
             assert torch.equal(back, mine), "many-segment gather"
+    if fc.peer_slot_bytes(dev) > 0:
+        _late_rank_exchange(fc, rank, world, dev)
+        _planned_exchange_with_capacity(fc, rank, world, dev)
+    # shadow flags of every rank (cuda/global_exchange.cuh:232-249)
+    mine = torch.from_numpy(np.random.default_rng(40 + rank).random(E) < 0.5).to(dev)
+    sent, stored_all = fc.exchange_cache_info(mine, E, world)
+    want_flags = np.stack([np.random.default_rng(40 + r).random(E) < 0.5 for r in range(world)])
+    assert sent is mine and np.array_equal(stored_all.cpu().numpy(), want_flags)
     # mismatched buffer size is caught before anything is queued
     try:
         fc.global_scatter(torch.zeros(int(lecs[rank].sum()), d, device=dev), torch.from_numpy(lecs[rank]),
@@ -135,6 +143,107 @@ def gpu_exchange(rank, world, port):
     assert np.array_equal(pruned.cpu().numpy(), want[rank][2])
     assert np.array_equal(new_lec.cpu().numpy(), want[rank][0]) and np.array_equal(new_gec.cpu().numpy(), want[rank][1])
     finish("nccl")
+
+
+def _late_rank_exchange(fc, rank, world, dev):
+    """One rank joins an exchange only after the others have given up waiting for it (a failure made
+    on the host; every wait involved is bounded).  The others must not have stored a single row into
+    the late rank's memory -- neither where it receives this exchange nor where it received the
+    exchanges before (the addresses its stale announcements still name) -- they report the expired
+    waits in the status word, and the next exchange works again."""
+    E, d = 2, 16
+    late = world - 1
+    lecs = all_lecs(world, E, 77, lo=1, hi=6)
+    table, _, _ = O.expert_exchange(lecs, E, world)
+    none = np.zeros(world * E, bool)
+    bufs = [np.random.default_rng(50 + r).standard_normal((int(lecs[r].sum()), d)).astype(np.float32) for r in range(world)]
+    want = O.global_scatter(bufs, lecs, none, E, world)
+    plan = fc.peer_plan_from_table(torch.from_numpy(table.copy()).to(dev), None, rank, E, world)
+    mine = torch.from_numpy(bufs[rank]).to(dev)
+    rows = want[rank].shape[0]
+    # two ordinary exchanges first: their outputs stay alive and are what stale announcements name
+    old = [fc.peer_scatter_planned(mine, plan, rows) for _ in range(2)]
+    for o in old:
+        assert torch.equal(o, torch.from_numpy(want[rank]).to(dev))
+    snap = [o.clone() for o in old]
+
+    def exchange_into_sevens():
+        out = fc._recv_empty(mine, rows)
+        out.fill_(7.0)
+        with torch.cuda.device(dev):
+            rc = fc.lib.fmoe_peer_scatter_planned(fc._comm(dev), fc._ptr(mine), fc._ptr(out), fc._ptr(plan.buf), mine.shape[0],
+                                                  rows, d * 4, E, fc._stream())
+        assert rc == 0, fc._lib.last_error()
+        torch.cuda.synchronize()
+        return out
+
+    moves, _ = O.scatter_moves(lecs, none, rank, E, world)
+    if rank != late:
+        assert fc.lib.fmoe_peer_set_timeout_ms(fc._comm(dev), 300) == 0
+        out = exchange_into_sevens()
+        assert fc.lib.fmoe_peer_set_timeout_ms(fc._comm(dev), 4000) == 0
+        st = fc.device_status(dev)
+        assert st & 16 and st & 32, f"expired waits not reported: {st}"
+        assert fc.lib.fmoe_device_status_clear() == 0
+        for (src, src_row, dst_row, n) in moves:       # rows of the ranks that took part arrived, the late rank's did not
+            got = out[dst_row:dst_row + n]
+            if src == late:
+                assert bool((got == 7).all()), "rows appeared from a rank that never pushed"
+            else:
+                assert torch.equal(got, torch.from_numpy(bufs[src][src_row:src_row + n]).to(dev))
+    dist.barrier()
+    if rank == late:
+        out = exchange_into_sevens()               # the others' announcements and arrival flags are long there
+        assert fc.device_status(dev) == 0
+        for (src, src_row, dst_row, n) in moves:
+            got = out[dst_row:dst_row + n]
+            if src == late:
+                assert torch.equal(got, torch.from_numpy(bufs[src][src_row:src_row + n]).to(dev))
+            else:
+                assert bool((got == 7).all()), "a rank that gave up waiting stored rows all the same"
+        for o, s_ in zip(old, snap):
+            assert torch.equal(o, s_), "rows were stored at an address from an older announcement"
+    dist.barrier()
+    out = fc.peer_scatter_planned(mine, plan, rows)
+    assert torch.equal(out, torch.from_numpy(want[rank]).to(dev)), "exchange after a late rank"
+    assert fc.device_status(dev) == 0
+
+
+def _planned_exchange_with_capacity(fc, rank, world, dev):
+    """Counts swapped through peer memory, plan built on the device, buffers larger than what arrives;
+    then a capacity that one rank exceeds: every rank's plan comes out empty, nothing is stored."""
+    E, d = 3, 24
+    lecs = all_lecs(world, E, 91, lo=0, hi=7)
+    table, _, gecs = O.expert_exchange(lecs, E, world)
+    none = np.zeros(world * E, bool)
+    bufs = [np.random.default_rng(60 + r).standard_normal((int(lecs[r].sum()), d)).astype(np.float32) for r in range(world)]
+    want = O.global_scatter(bufs, lecs, none, E, world)
+    recv = want[rank].shape[0]
+    mine = torch.from_numpy(bufs[rank]).to(dev)
+    for rnd in range(3):
+        cap = recv + 5 + rnd
+        plan = fc.peer_plan_exchange(torch.from_numpy(lecs[rank]).to(dev), None, cap, E)
+        assert plan is not None and torch.equal(plan.table.cpu(), torch.from_numpy(table))
+        own = np.concatenate([[0], np.cumsum(gecs[rank].reshape(world, E).sum(0))])
+        assert np.array_equal(plan.own_offsets.cpu().numpy(), own)
+        out = fc.peer_scatter_planned(mine + rnd, plan, cap)
+        assert torch.equal(out[:recv], torch.from_numpy(want[rank]).to(dev) + rnd), "planned scatter layout"
+        back = fc.peer_gather_planned(out, plan, mine.shape[0] + 3)
+        assert torch.equal(back[:-3], mine + rnd) and not back[-3:].any(), "planned gather is not the inverse"
+    assert fc.device_status(dev) == 0
+    # rank 0 announces one row less than it would receive
+    cap = want[0].shape[0] - 1 if rank == 0 else recv + 1
+    plan = fc.peer_plan_exchange(torch.from_numpy(lecs[rank]).to(dev), None, max(cap, 0), E)
+    assert plan.read(0)[3] == 1 and not plan.own_offsets.any()
+    out = fc._recv_empty(mine, recv + 1)
+    out.fill_(3.0)
+    with torch.cuda.device(dev):
+        assert fc.lib.fmoe_peer_scatter_planned(fc._comm(dev), fc._ptr(mine), fc._ptr(out), fc._ptr(plan.buf), mine.shape[0],
+                                                recv + 1, d * 4, E, fc._stream()) == 0
+    assert bool((out == 3).all()), "rows moved although a rank had no room"
+    assert fc.device_status(dev) & 64
+    assert fc.lib.fmoe_device_status_clear() == 0
+    dist.barrier()
 
 
 def _make_layer(world, rank, E, d, h, k, act, bias, tens, dtype=torch.float32, gate=None):
@@ -185,6 +294,12 @@ def gpu_layer(rank, world, port):
         for name in ("w1", "w2") + (("b1", "b2") if bias else ()):
             want = sum(w["grad_" + name][sl] for w in wants)
             torch.testing.assert_close(got[name].cpu(), want, rtol=1e-5, atol=2e-4, msg=lambda s, n=name: f"{n}: {s}")
+        # the same layer when the host reads the counts (no device-built plan): bit-identical
+        os.environ["FMOE_B200_NOSYNC"] = "0"
+        synced = _run_layer(m, xs[rank].cuda())
+        os.environ["FMOE_B200_NOSYNC"] = "1"
+        for name, v in got.items():
+            assert torch.equal(synced[name], v), f"host-planned and device-planned exchange differ in {name}"
         # smart schedule against the plain one, all pipeline granularities
         for gran in ("1", "2", "4"):
             os.environ["FMOE_FUSE_GRAN"] = gran

@@ -18,7 +18,7 @@ def free_port():
 
 def world_sizes():
     n = torch.cuda.device_count() if torch.cuda.is_available() else 0
-    return [w for w in (2, 4) if w <= n]
+    return [w for w in (2, 4, 8) if w <= n]
 
 
 def needs_gpus():
