@@ -252,8 +252,8 @@ def _check_host_counts(expert_count, n_rows, what):
     (counts on the device cannot be: the kernels clamp them instead and raise status code 8)."""
     if not expert_count.is_cuda:
         total = int(expert_count.sum())
-        if total != n_rows or bool((expert_count < 0).any()):
-            raise RuntimeError(f"{what}: expert_count sums to {total} but the buffer has {n_rows} rows "
+        if total > n_rows or bool((expert_count < 0).any()):
+            raise RuntimeError(f"{what}: expert_count sums to {total} but the buffer has only {n_rows} rows "
                                "(or a count is negative)")
 
 

@@ -3,5 +3,5 @@ from .base_gate import BaseGate
 from .naive_gate import NaiveGate
 from .gshard_gate import GShardGate
 from .switch_gate import SwitchGate
-from .hir_gate import HirGate, gen_hir_gate
+from .hir_gate import HirGate, HirCapacityGate, gen_hir_gate, gen_hir_capacity_gate
 from .utils import limit_by_capacity

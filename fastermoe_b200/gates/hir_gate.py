@@ -25,6 +25,7 @@ class HirGate(NaiveGate):
         self.register_buffer("mask", on_node, persistent=False)
         self.stored_models = None
         self.policy_fn = None
+        self.last_stored = None     # the policy's answer of the latest forward (bool [W, E], CPU)
 
     def forward(self, inp):
         gate_score = self.gate(inp)
@@ -43,6 +44,7 @@ class HirGate(NaiveGate):
             stored = self.policy_fn(aec.view(-1).cpu().view(w, w, e) if w > 1 else aec.cpu().view(1, 1, e),
                                     agec.view(-1).cpu().view(w, w, e) if w > 1 else agec.cpu().view(1, 1, e),
                                     e, w, inp.shape[-1], True)
+            self.last_stored = stored.reshape(w, e).cpu()
             # Experts shadowed on every worker are as good as local ones.
             limited = off_node & ~stored.reshape(-1).to(off_node.device)
             leaving = limited[top1_idx]
@@ -64,6 +66,46 @@ class HirGate(NaiveGate):
         rows = torch.arange(n_tok, device=inp.device).repeat_interleave(2)
         topk_val = gate_score[rows, topk_idx.view(-1)].view(-1, self.top_k)
         return topk_idx, F.softmax(topk_val, dim=-1)
+
+
+class HirCapacityGate(HirGate):
+    """HirGate followed by the capacity limit of the GShard-style gates (fmoe/gates/gshard_gate.py:36-39
+    applied to fmoe/gates/hir_gate.py's selection): each expert accepts at most ceil(cap_rate * tokens)
+    rows, entries beyond that become -1; scores are those of the selection before pruning.
+
+    ``spare_shadowed``: experts that the shadowing policy (consulted by HirGate on the unpruned counts)
+    replicates on every worker are exempt from the limit -- their rows are computed where they
+    originate, so no single GPU is overloaded by them.  ``last_selection`` keeps the unpruned indices."""
+
+    def __init__(self, d_model, n_expert, world_size, node_rank, workers_per_node=None, cap_rate=1.2,
+                 spare_shadowed=False, rank=0):
+        super().__init__(d_model, n_expert, world_size, node_rank, workers_per_node)
+        self.cap_rate, self.spare_shadowed, self.rank = cap_rate, spare_shadowed, rank
+        self.last_selection = None
+
+    def forward(self, inp):
+        import math
+        from .utils import limit_by_capacity
+        idx, score = super().forward(inp)
+        self.last_selection = idx
+        cap = math.ceil(self.cap_rate * inp.shape[0])
+        if self.spare_shadowed and self.last_stored is not None:
+            per_expert = torch.full((self.num_expert,), cap, dtype=torch.int32)
+            per_expert[self.last_stored[self.rank]] = torch.iinfo(torch.int32).max
+            cap = per_expert
+        _, _, idx = limit_by_capacity(idx.contiguous(), self.num_expert, self.world_size, cap)
+        return idx, score
+
+
+def gen_hir_capacity_gate(rank, workers_per_node=None, cap_rate=1.2, spare_shadowed=False):
+    """Gate factory like gen_hir_gate for HirCapacityGate."""
+    wpn = nw_per_node if workers_per_node is None else workers_per_node
+
+    def _gen(d_model, n_expert, world_size, top_k=2):
+        assert top_k == 2
+        return HirCapacityGate(d_model, n_expert, world_size, rank // wpn, workers_per_node=wpn, cap_rate=cap_rate,
+                               spare_shadowed=spare_shadowed, rank=rank)
+    return _gen
 
 
 def gen_hir_gate(rank, workers_per_node=None):

@@ -13,11 +13,15 @@ def limit_by_capacity(topk_idx, num_expert, world_size, capacity):
     rank order up to ``capacity``, send the grants back, and set the local gate
     entries beyond each grant to -1 (lowest flat index kept first).
 
+    ``capacity``: rows each local expert accepts, an int or an int tensor [num_expert].
     Returns ``(new_lec, new_gec, topk_idx)``.
     """
     with torch.no_grad():
         n_tot = num_expert * world_size
-        cap = torch.full((num_expert,), int(capacity), dtype=torch.int32, device=topk_idx.device)
+        if torch.is_tensor(capacity):     # one allowance per local expert
+            cap = capacity.to(device=topk_idx.device, dtype=torch.int32).reshape(num_expert).clone()
+        else:
+            cap = torch.full((num_expert,), int(capacity), dtype=torch.int32, device=topk_idx.device)
         lec32 = torch.zeros(n_tot, dtype=torch.int32, device=topk_idx.device)
         fmoe_native.expert_count(topk_idx.reshape(-1).contiguous(), lec32)
         lec = lec32.long()

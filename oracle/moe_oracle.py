@@ -304,10 +304,12 @@ def moe_layer(x, gate_idx, gate_score, w1, b1, w2, b2, act="gelu"):
 
 
 def moe_layer_fwd_bwd(x, gate_w, gate_b, w1, b1, w2, b2, top_k, act="gelu", softmax_scores=False,
-                      gate_idx=None, grad_out=None):
+                      gate_idx=None, grad_out=None, score_idx=None):
     """Forward + backward of gate -> experts -> combine on the CPU.  Returns a dict
     with the output and the gradients of every input that requires grad.  The loss is
-    ``sum(out * grad_out)`` (``grad_out`` None = ones = out.sum())."""
+    ``sum(out * grad_out)`` (``grad_out`` None = ones = out.sum()).  ``gate_idx`` prescribes the
+    experts (-1 = pruned entry); ``score_idx`` (default: gate_idx) the experts whose logits give
+    the scores, for gates that compute scores before a capacity limit prunes entries."""
     leaves = {}
     for name, t in (("x", x), ("gate_w", gate_w), ("gate_b", gate_b), ("w1", w1), ("b1", b1), ("w2", w2), ("b2", b2)):
         leaves[name] = None if t is None else t.detach().clone().requires_grad_(True)
@@ -316,7 +318,7 @@ def moe_layer_fwd_bwd(x, gate_w, gate_b, w1, b1, w2, b2, top_k, act="gelu", soft
         # Use prescribed indices (e.g. after capacity pruning); scores follow the indices.
         logits = torch.nn.functional.linear(leaves["x"], leaves["gate_w"], leaves["gate_b"])
         idx = gate_idx
-        score = torch.gather(logits, 1, gate_idx.clamp(min=0))
+        score = torch.gather(logits, 1, (gate_idx if score_idx is None else score_idx).clamp(min=0))
         if softmax_scores:
             score = torch.softmax(score, dim=-1)
     out = moe_layer(leaves["x"], idx, score, leaves["w1"], leaves["b1"], leaves["w2"], leaves["b2"], act)
