@@ -610,16 +610,20 @@ def run_ours(args):
     launches = prof.launches
 
     e2e_ms = e2e_eager_ms = None
+    used_graph = False
     if not args.skip_e2e:
         for _ in range(2):
             step_e2e()
         e2e_eager_ms = e2e_ms = env.timed(step_e2e, args.steps)
-        if world == 1:
-            # The single-GPU step never waits on the host, so the whole forward+backward is replayed as
-            # one CUDA graph (fastermoe_b200.GraphedStep): per step one device-to-device copy of the
-            # prefetched batch into the captured input, one graph launch, one read of the loss.
+        graphable = world == 1 or "planned on the device" in (exchange_form(layer, dev) or "")
+        if graphable:
+            # The step never waits on the host (at N > 1: counts swapped through peer memory, plan built on
+            # the device), so the whole forward+backward is replayed as one CUDA graph
+            # (fastermoe_b200.GraphedStep): per step one device-to-device copy of the prefetched batch
+            # into the captured input, one graph launch, one read of the loss.
             from fastermoe_b200 import GraphedStep
             graphed = GraphedStep(layer, x_dev.detach(), input_grad=True)
+            used_graph = True
 
             def step_e2e_graph():
                 return graphed(take()).item()
@@ -683,7 +687,7 @@ def run_ours(args):
                  "h2d_bytes_per_step": x_host.numel() * x_host.element_size(), "d2h_bytes_per_step": 4,
                  "note": "a training step: the batch is copied in, only the scalar loss is read back (the [T,d] "
                          "output and the gradients stay on the device)",
-                 "ms_per_step": e2e_ms / args.steps, "cuda_graph": world == 1,
+                 "ms_per_step": e2e_ms / args.steps, "cuda_graph": used_graph,
                  "eager_ms_per_step": e2e_eager_ms / args.steps} if e2e_ms else None),
         "gpu_launches": launches, "clocks": clocks, "roofline": roofline,
         "layer_tensor_roofline_frac": layer_frac, "per_op_ms": per_op,

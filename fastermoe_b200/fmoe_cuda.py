@@ -428,9 +428,50 @@ def _recv_pool(device):
 _pool_backoff = {}
 
 
-def _recv_empty(like, rows):
+class ReceiveArena:
+    """Exchange outputs that are handed out again, in the same order, step after step: what a step
+    that is captured in a CUDA graph needs (no allocation inside the capture, the same addresses at
+    every replay).  The i-th request of a step gets the i-th buffer; buffers are created (from the
+    receive pool when it has room) the first time a request is seen, which must happen outside a
+    capture.  Only one step may be in flight: a buffer is reused as soon as the next step asks for it."""
+
+    def __init__(self):
+        self.bufs, self.next = [], 0
+
+    def begin_step(self):
+        self.next = 0
+
+    def get(self, like, rows):
+        i = self.next
+        self.next += 1
+        if i < len(self.bufs):
+            b = self.bufs[i]
+            if b.shape == (rows, like.shape[1]) and b.dtype == like.dtype and b.device == like.device:
+                return b
+            raise RuntimeError("ReceiveArena: the sequence of exchange buffers changed between steps "
+                               f"(request {i}: {tuple(b.shape)} {b.dtype} before, {(rows, like.shape[1])} {like.dtype} now)")
+        if torch.cuda.is_current_stream_capturing():
+            raise RuntimeError("ReceiveArena: a new exchange buffer was requested during graph capture; run the step "
+                               "once before capturing")
+        b = _recv_empty(like, rows, arena=False)
+        self.bufs.append(b)
+        return b
+
+
+_arena = None
+
+
+def set_receive_arena(arena):
+    """Installs (None: removes) the ReceiveArena that serves the exchange outputs from now on."""
+    global _arena
+    _arena = arena
+
+
+def _recv_empty(like, rows, arena=True):
     """Output buffer of a peer exchange: from the receive pool when there is one and it has room
     (after a refusal the pool is left alone for the next 64 requests: a failed request is slow)."""
+    if arena and _arena is not None:
+        return _arena.get(like, rows)
     pool = _recv_pool(like.device)
     if pool is not None:
         idx = like.device.index

@@ -1,14 +1,17 @@
 r"""CUDA-graph capture of a training step of an MoE layer.
 
-At ``world_size == 1`` the layer's forward and backward never read anything back
-to the host (bucket sizes stay on the device; the grouped GEMMs take their tile
-list from the device-resident offsets), so a whole step is a fixed sequence of
-kernel launches and can be replayed as one CUDA graph.  What remains on the host
-per step is one graph launch, which removes the launch gaps at the start of a
-step that follows a synchronising read of the loss.
+The layer's forward and backward never read anything back to the host when the bucket sizes can
+stay on the device: always at ``world_size == 1`` (the grouped GEMMs take their tile list from the
+device-resident offsets), and at ``world_size > 1`` when the counts are swapped through peer memory
+and the exchange plan is built on the device (no shadowing policy, fused experts; see
+layers._fmoe_general_global_forward).  A whole step is then a fixed sequence of kernel launches and
+can be replayed as one CUDA graph.  What remains on the host per step is one graph launch, which
+removes the launch gaps at the start of a step that follows a synchronising read of the loss.
 
-With ``world_size > 1`` the forward waits for the count table on the host (buffer
-sizes depend on it), so it cannot be captured; ``GraphedStep`` refuses such modules.
+With ``world_size > 1`` the captured kernels wait for the peers' rows: every rank must replay its
+graph once per step, in step with the others.  Exchange outputs come from a ReceiveArena (the same
+buffers at every replay).  A forward that has to read the counts (shadowing policy, NCCL exchange)
+cannot be captured: the capture then fails with the error of the host read.
 """
 import torch
 
@@ -30,12 +33,12 @@ class GraphedStep:
     """
 
     def __init__(self, module, example_input, loss_fn=None, warmup=3, input_grad=False):
-        if getattr(module, "world_size", 1) != 1:
-            raise ValueError("GraphedStep: the expert-parallel forward (world_size > 1) waits on the host for the "
-                             "count table and cannot be captured in a CUDA graph")
         if not example_input.is_cuda:
             raise ValueError("GraphedStep: example_input must be a CUDA tensor")
         self.module = module
+        from . import fmoe_cuda
+        self._fc = fmoe_cuda
+        self.arena = fmoe_cuda.ReceiveArena() if getattr(module, "world_size", 1) > 1 else None
         self.loss_fn = loss_fn if loss_fn is not None else (lambda out: out.sum(dtype=torch.float32))
         self.static_input = example_input.detach().clone().requires_grad_(input_grad)
         # Parameters that already took part in a backward pass on another stream make autograd
@@ -64,9 +67,16 @@ class GraphedStep:
         self.input_grad = self.static_input.grad
 
     def _step(self):
-        out = self.module(self.static_input)
-        loss = self.loss_fn(out)
-        loss.backward()
+        if self.arena is not None:
+            self.arena.begin_step()
+            self._fc.set_receive_arena(self.arena)
+        try:
+            out = self.module(self.static_input)
+            loss = self.loss_fn(out)
+            loss.backward()
+        finally:
+            if self.arena is not None:
+                self._fc.set_receive_arena(None)
         return out, loss
 
     def __call__(self, x):

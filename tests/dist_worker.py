@@ -395,6 +395,44 @@ def check_layer_bf16(rank, world):
         same_up_to_rounding(shadow[name], base[name], "shadow " + name, 1 if name in ("out", "x") else world)
 
 
+def gpu_graph_step(rank, world, port):
+    init(rank, world, port, "nccl")
+    check_graph_step(rank, world)
+    finish("nccl")
+
+
+def check_graph_step(rank, world):
+    """A whole expert-parallel forward+backward step replayed as one CUDA graph on every rank equals the
+    eager step, also when the routing of the replayed batch differs from the captured one."""
+    from fastermoe_b200 import GraphedStep
+    T, d, h, E, k = 1000, 256, 512, 2, 2
+    tens = O.make_layer_inputs(T * world, d, h, E * world, seed=8, gate_std=0.5)
+    m = _make_layer(world, rank, E, d, h, k, "gelu", True, tens, dtype=torch.bfloat16)
+    g = torch.Generator().manual_seed(100 + rank)
+    xs = [torch.randn(T, d, generator=g).bfloat16().cuda() for _ in range(3)]
+
+    def eager(x):
+        m.zero_grad(set_to_none=True)
+        xi = x.clone().requires_grad_(True)
+        out = m(xi)
+        loss = out.sum(dtype=torch.float32)
+        loss.backward()
+        return out.detach().clone(), loss.detach().clone(), xi.grad.clone(), {n: p.grad.clone() for n, p in m.named_parameters()}
+
+    want = [eager(x) for x in xs[1:]]
+    step = GraphedStep(m, xs[0], input_grad=True)
+    for x, (out, loss, gx, grads) in zip(xs[1:], want):
+        got_loss = step(x)
+        torch.cuda.synchronize()
+        assert torch.equal(step.output, out) and torch.equal(got_loss, loss)
+        assert torch.equal(step.input_grad, gx)
+        for n, p in m.named_parameters():
+            assert torch.equal(p.grad, grads[n]), n
+    from fastermoe_b200 import fmoe_cuda as fc
+    assert fc.device_status() == 0
+    dist.barrier()
+
+
 def gpu_config5(rank, world, port):
     init(rank, world, port, "nccl")
     check_config5(rank, world)

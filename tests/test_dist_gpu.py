@@ -42,7 +42,7 @@ def run_ranks(fn, world, limit_s=240):
                 p.terminate()
 
 
-@pytest.mark.parametrize("fn", ["gpu_exchange", "gpu_layer", "gpu_layer_bf16", "gpu_config5"])
+@pytest.mark.parametrize("fn", ["gpu_exchange", "gpu_layer", "gpu_layer_bf16", "gpu_config5", "gpu_graph_step"])
 def test_expert_parallel(fn):
     needs_gpus()
     for world in world_sizes():

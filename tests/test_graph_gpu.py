@@ -45,13 +45,3 @@ def test_graphed_step_equals_eager(dtype):
     # a pinned host tensor is accepted as input
     host = xs[2].cpu().pin_memory()
     assert torch.equal(step(host), want[1][1])
-
-
-def test_graphed_step_refuses_expert_parallel_layers():
-    from fastermoe_b200 import GraphedStep
-
-    class Fake(torch.nn.Module):
-        world_size = 2
-
-    with pytest.raises(ValueError, match="world_size"):
-        GraphedStep(Fake(), torch.zeros(1, device="cuda"))
