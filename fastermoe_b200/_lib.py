@@ -28,6 +28,13 @@ class Move(ctypes.Structure):
                 ("rows", c_int64), ("local", c_int32), ("step", c_int32)]
 
 
+class Arrival(ctypes.Structure):
+    """Mirror of fmoe_arrival_t."""
+    _fields_ = [("comm", c_void_p), ("plan", c_void_p), ("out", c_void_p), ("in_rows", c_int64), ("out_rows", c_int64),
+                ("row_bytes", c_int64), ("n_expert", c_int32), ("overlap_sms", c_int32), ("gather", c_int32),
+                ("use", c_int32)]
+
+
 class FusedGeometry(ctypes.Structure):
     """Mirror of fmoe_fused_geometry_t."""
     _fields_ = [("n_steps", c_int32), ("gran", c_int32), ("global_rows", c_int64), ("shadow_rows", c_int64)]
@@ -106,6 +113,11 @@ _SIGS = {
     "fmoe_peer_plan_read": (I32, [P, I32, I32, I32, P, I32, POINTER(c_int32), POINTER(c_int64), POINTER(c_int64), POINTER(c_int32)]),
     "fmoe_peer_scatter_planned": (I32, [P, P, P, P, I64, I64, I64, I32, P]),
     "fmoe_peer_gather_planned": (I32, [P, P, P, P, I64, I64, I64, I32, P]),
+    "fmoe_peer_scatter_planned_async": (I32, [P, P, P, P, I64, I64, I64, I32, I32, P, P]),
+    "fmoe_peer_arrival_finish": (I32, [P, P]),
+    "fmoe_peer_gather_planned_async": (I32, [P, P, P, P, I64, I64, I64, I32, I32, I32, P, P]),
+    "fmoe_linear_forward_overlapped": (I32, [P, P, P, P, P, P, I64, I64, I64, I32, I32, I32, P, P, P]),
+    "fmoe_linear_backward_overlapped": (I32, [P, P, P, P, P, P, P, P, P, I64, I64, I64, I32, I32, I32, I32, P, P, P, P]),
     "fmoe_device_status_clear": (I32, []),
     "fmoe_peer_slot_bytes": (I64, [P]),
     "fmoe_peer_global_scatter": (I32, [P, P, P, P, P, I64, I64, I64, I32, I32, P]),

@@ -35,6 +35,8 @@ struct PeerState {
     int64_t pool_bytes = 0;            // receive pool behind the two slots (0: none)
     char* base[kMaxPeers] = {};
     unsigned int* counter = nullptr;   // device words for last-block detection
+    cudaStream_t side = nullptr;       // the overlapped push runs here, beside the GEMM on the caller's stream
+    cudaEvent_t fork = nullptr, join = nullptr;
     unsigned long long timeout_ns = 0;
 };
 
@@ -44,6 +46,20 @@ struct Comm {
     std::vector<cudaEvent_t> events;  // pool reused by the smart schedule
     PeerState peer;
 };
+
+// What a grouped GEMM needs to start on rows while they are still arriving (see fmoe_arrival_t).
+struct ArrivalWait {
+    const unsigned long long* flags = nullptr;   // [2][kMaxPeers][kArrivalExperts] in this GPU's landing area
+    const unsigned long long* seq = nullptr;     // this GPU's exchange epoch word
+    const int* src_off = nullptr;                // [E*W + 1]: first row of (expert i, source j) at [i*W + j]
+    int world = 0, n_expert = 0;
+    int reserve_sms = 0;                         // SMs to leave to the push kernel
+};
+constexpr int kArrivalExperts = 256;
+
+int arrival_wait_of(const fmoe_arrival_t* arrival, ArrivalWait* w);
+// The completion counters (GemmDone in gemm.h) of an overlapped gather's handle; nulls when it is not pending.
+int done_words_of(const fmoe_arrival_t* departure, int** done, int** expected, int** ready, int* reserve_sms);
 
 // Device address of the status word that bounded waits raise (per device).
 int* device_status_ptr();

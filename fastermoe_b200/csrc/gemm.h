@@ -36,6 +36,26 @@ __device__ __forceinline__ bool safe_seg_range(const int64_t* __restrict__ off, 
 }
 #endif
 
+// Rows of the ragged-side input that are still arriving from other GPUs (see ArrivalWait in exchange.h;
+// the struct is repeated here in plain form so that the GEMM code does not depend on the exchange code).
+struct GemmArrival {
+    const unsigned long long* flags;   // [2][64][256]: flags[(parity * 64 + source) * 256 + expert] >= epoch: rows are there
+    const unsigned long long* seq;     // epoch word: the rows belong to epoch *seq + 1
+    const int* src_off;                // [n_expert * world + 1]: first row of (expert, source)
+    int world;
+    int reserve_sms;                   // SMs left to the kernel that delivers the rows
+};
+
+// Per-expert completion of a product's output rows, for a kernel that forwards them while the
+// product is still running: every epilogue warp adds 1 to done[e] when its part of a tile of expert e
+// is stored; block 0 writes expected[e] (the count at which expert e is complete) and then *ready = 1.
+struct GemmDone {
+    int* done;       // [n_expert], zero before the launch
+    int* expected;   // [n_expert]
+    int* ready;      // [1], zero before the launch
+    int reserve_sms;
+};
+
 struct LinearArgs {
     const void* x;       // [n_rows, in_feat]
     const void* weight;  // [n_expert, out_feat, in_feat]
@@ -46,6 +66,8 @@ struct LinearArgs {
     int64_t n_rows, in_feat, out_feat;
     int n_expert, dtype, activation;
     const HostSegs* host_segs = nullptr;  // when set, replaces seg_offsets
+    const GemmArrival* arrival = nullptr;  // x is still being filled by an exchange
+    const GemmDone* done = nullptr;        // y is forwarded expert by expert while the product runs
 };
 
 struct LinearBwdArgs {
@@ -64,6 +86,12 @@ struct LinearBwdArgs {
     // [n_expert, in_feat] or null: per-expert column sums of grad_x (what the bias gradient of
     // the layer that produced x is, when grad_x is the gradient of its output)
     void* grad_x_colsum = nullptr;
+    // grad_y is still being filled by an exchange: the input-gradient product waits tile by tile;
+    // after_input_grad (called once, before anything that needs all of grad_y) closes the exchange
+    const GemmArrival* arrival = nullptr;
+    int (*after_input_grad)(void*) = nullptr;
+    void* after_ctx = nullptr;
+    const GemmDone* done = nullptr;        // grad_x is forwarded expert by expert while its product runs
 };
 
 int simt_linear_forward(const LinearArgs& a, cudaStream_t st);

@@ -85,6 +85,15 @@ struct Params {
     int tma_store;  // outputs have tensor maps: full 32-row blocks leave through TMA stores
     int* status;  // device status word
     int64_t n_rows;  // rows of the ragged-side buffers (FWD/DGRAD: A and the output; WGRAD: both operands)
+    // FWD/DGRAD whose A rows are still arriving from other GPUs (null: they are all there)
+    const unsigned long long* arr_flags;
+    const unsigned long long* arr_seq;
+    const int* arr_src_off;
+    int arr_world;
+    // FWD/DGRAD whose output rows are forwarded while the product runs (null: nobody is waiting)
+    int* done;
+    int* done_expected;
+    int* done_ready;
 };
 
 struct Shared {
@@ -140,6 +149,24 @@ __device__ __forceinline__ bool mbar_wait(unsigned long long* bar, uint32_t pari
             atomicCAS(status, 0, code);
             return false;
         }
+    }
+}
+// Bounded wait for rows that another GPU delivers: flag >= epoch.  Raises status code 5 on expiry.
+__device__ __forceinline__ bool arrival_wait(const unsigned long long* flag, unsigned long long epoch, Shared* sh, int* status) {
+    unsigned long long v;
+    asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(flag) : "memory");
+    if (v >= epoch) return true;
+    const unsigned long long t0 = clock64();
+    while (true) {
+        asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(flag) : "memory");
+        if (v >= epoch) return true;
+        if (*(volatile int*)&sh->abort) return false;
+        if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+            *(volatile int*)&sh->abort = 1;
+            atomicCAS(status, 0, 5);
+            return false;
+        }
+        __nanosleep(100);
     }
 }
 // --- cluster (CTA pair) helpers ---
@@ -510,6 +537,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             sh->blk_base[e + 1] = blk;
         }
         if (clamped && blockIdx.x == 0) atomicCAS(p.status, 0, 8);
+        if (MODE != MODE_WGRAD && p.done && blockIdx.x == 0) {
+            // completions per expert: every epilogue warp of every CTA of the group, once per tile
+            for (int e = 0; e < p.n_expert; ++e)
+                p.done_expected[e] = (sh->cum_tiles[e + 1] - sh->cum_tiles[e]) * EPI_WARPS * (CTA2 ? 2 : 1);
+            __threadfence();
+            *(volatile int*)p.done_ready = 1;
+        }
     }
     if (warp == 0) {
         if (CTA2) {
@@ -529,15 +563,38 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
     if (warp == 0) {
         // ---- TMA producer -----------------------------------------------------
-        if (lane == 0) {
+        // Lane 0 issues the copies.  When the rows of A are still arriving from other GPUs, the lanes
+        // first wait, one source rank each, for the sources whose rows this CTA's part of the tile reads.
+        {
             int s = 0, e_cur = 0;
             uint32_t ph = 0;
             bool ok = true;
             const int my_row = cta * BM;      // this CTA's rows inside the tile
             const int my_col = cta * B_COLS;  // this CTA's share of the tile's B columns (pairs)
+            const bool arriving = MODE != MODE_WGRAD && p.arr_flags != nullptr;
+            unsigned long long epoch = 0;
+            int seen_e = -1;
+            bool seen = false;                // this lane's source has delivered its rows of expert seen_e
+            if (arriving) epoch = __ldcg(p.arr_seq) + 1;
             for (int tile = first_tile; tile < total_tiles && ok; tile += tile_step) {
                 Tile t;
                 locate<MODE, TILE_M>(sh, p, tile, e_cur, t);
+                if (arriving && t.chunks > 0) {
+                    if (t.e != seen_e) { seen_e = t.e; seen = false; }
+                    const int r_lo = t.row0 + my_row, r_hi = min(t.row0 + t.rows, r_lo + BM);
+                    bool good = true;
+                    if (lane < p.arr_world && !seen && r_hi > r_lo) {
+                        const int b0 = p.arr_src_off[t.e * p.arr_world + lane], b1 = p.arr_src_off[t.e * p.arr_world + lane + 1];
+                        if (b1 > b0 && b0 < r_hi && b1 > r_lo) {
+                            good = arrival_wait(p.arr_flags + ((size_t)(epoch & 1) * 64 + lane) * 256 + t.e, epoch, sh, p.status);
+                            seen = good;
+                        }
+                    }
+                    good = __all_sync(0xffffffffu, good);
+                    if (!good) { ok = false; break; }
+                    asm volatile("fence.proxy.async.global;" ::: "memory");   // rows written through the generic proxy, read by TMA
+                }
+                if (lane == 0)
                 for (int ch = 0; ch < t.chunks; ++ch) {
                     if (!(ok = mbar_wait(&sh->empty[s], ph ^ 1, sh, p.status, 1))) break;
                     uint8_t* a_dst = tiles + s * STAGE_BYTES;
@@ -589,6 +646,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     }
                     if (++s == STAGES) { s = 0; ph ^= 1; }
                 }
+                ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
             }
         }
     } else if (warp == 1) {
@@ -863,6 +921,16 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 else mbar_arrive(&sh->tmem_empty[acc]);
             }
             if (++acc == 2) { acc = 0; acc_ph ^= 1; }
+            if (MODE != MODE_WGRAD && p.done) {
+                // this warp's part of the tile is in memory: bulk stores complete, plain stores of the
+                // other lanes ordered before the fence by the barrier above
+                if (lane == 0) {
+                    if (p.tma_store) tma_store_wait_all();
+                    asm volatile("fence.proxy.async.global;" ::: "memory");
+                    __threadfence();
+                    atomicAdd(p.done + t.e, 1);
+                }
+            }
         }
         if (p.tma_store && lane == 0) tma_store_wait_all();
     }
@@ -1000,7 +1068,8 @@ int cta_cap() {
 
 template <int MODE, bool CTA2>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, const HostSegs* hsp, const Params& p_in, int64_t max_tiles,
-           int64_t out_rows, cudaStream_t st) {
+           int64_t out_rows, cudaStream_t st, int reserve_sms = 0) {
+    reserve_sms = (reserve_sms + 1) / 2 * 2;      // the kernel beside this one occupies whole SM pairs
     const HostSegs& hs = hsp ? *hsp : kNoSegs;
     Params p = p_in;
     static_assert(CW == 32, "the output tensor maps assume 32-column staging buffers");
@@ -1039,10 +1108,12 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const HostSegs* hsp, co
             FMOE_CUDA_TRY(cudaOccupancyMaxActiveClusters(&n, kern, &cfg));
             max_pairs[dev] = n > 0 ? n : 1;
         }
-        const int64_t pairs = std::max<int64_t>(1, std::min<int64_t>(max_tiles, std::min(max_pairs[dev], cta_cap() / 2)));
+        const int cap = std::max(2, std::min(cta_cap(), sm_count() - reserve_sms));
+        const int64_t pairs = std::max<int64_t>(1, std::min<int64_t>(max_tiles, std::min(max_pairs[dev], cap / 2)));
         cfg.gridDim = dim3((unsigned)(2 * pairs));
     } else {
-        cfg.gridDim = dim3((unsigned)std::max<int64_t>(1, std::min<int64_t>(max_tiles, cta_cap())));
+        const int cap = std::max(1, std::min(cta_cap(), sm_count() - reserve_sms));
+        cfg.gridDim = dim3((unsigned)std::max<int64_t>(1, std::min<int64_t>(max_tiles, cap)));
     }
     FMOE_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, ma, mb, hs, om, p));
     return 0;
@@ -1220,8 +1291,18 @@ int tc_linear_forward(const LinearArgs& a, cudaStream_t st) {
     p.is_bf16 = bf16; p.status = status_ptr(); p.n_rows = a.n_rows;
     const int tile_m = pair ? 256 : BM;
     const int64_t max_tiles = (ceil_div(a.n_rows, tile_m) + a.n_expert) * ceil_div(a.out_feat, BN);
-    return pair ? launch<MODE_FWD, true>(ma, mb, a.host_segs, p, max_tiles, a.n_rows, st)
-                : launch<MODE_FWD, false>(ma, mb, a.host_segs, p, max_tiles, a.n_rows, st);
+    int reserve = 0;
+    if (a.arrival) {
+        p.arr_flags = a.arrival->flags; p.arr_seq = a.arrival->seq; p.arr_src_off = a.arrival->src_off;
+        p.arr_world = a.arrival->world;
+        reserve = a.arrival->reserve_sms;
+    }
+    if (a.done) {
+        p.done = a.done->done; p.done_expected = a.done->expected; p.done_ready = a.done->ready;
+        reserve = std::max(reserve, a.done->reserve_sms);
+    }
+    return pair ? launch<MODE_FWD, true>(ma, mb, a.host_segs, p, max_tiles, a.n_rows, st, reserve)
+                : launch<MODE_FWD, false>(ma, mb, a.host_segs, p, max_tiles, a.n_rows, st, reserve);
 }
 
 // A side stream and a pair of events per device, created on first use: the bias
@@ -1252,7 +1333,15 @@ int tc_linear_backward(const LinearBwdArgs& a, cudaStream_t st) {
     const bool bf16 = a.dtype == FMOE_BF16;
     SideStream* side = nullptr;
     const bool overlap_bias = a.grad_b && (a.grad_x || a.grad_w) && a.n_rows > 0;
-    if (overlap_bias) {
+    // grad_y still arriving: only the input-gradient product may start; everything else (the bias
+    // gradient on the side stream included) is queued after the exchange has been closed
+    const bool arriving = a.arrival != nullptr;
+    bool closed = !arriving;
+    if (arriving && !(a.grad_x && a.n_rows > 0)) {
+        if (a.after_input_grad) { if (int rc = a.after_input_grad(a.after_ctx)) return rc; }
+        closed = true;
+    }
+    auto queue_bias = [&]() -> int {
         if (int rc = side_stream(&side)) return rc;
         const HostSegs& hs = a.host_segs ? *a.host_segs : kNoSegs;
         FMOE_CUDA_TRY(cudaEventRecord(side->fork, st));
@@ -1260,6 +1349,12 @@ int tc_linear_backward(const LinearBwdArgs& a, cudaStream_t st) {
         if (int rc = bf16 ? launch_bias_grad<true>(a, hs, side->stream) : launch_bias_grad<false>(a, hs, side->stream))
             return rc;
         FMOE_CUDA_TRY(cudaEventRecord(side->join, side->stream));
+        return 0;
+    };
+    if (overlap_bias && !closed) {
+        // queued below, after the input-gradient product
+    } else if (overlap_bias) {
+        if (int rc = queue_bias()) return rc;
     }
     if (a.grad_x && a.n_rows > 0) {
         CUtensorMap ma, mb;
@@ -1276,9 +1371,24 @@ int tc_linear_backward(const LinearBwdArgs& a, cudaStream_t st) {
         }
         const bool pair = use_pairs(MODE_DGRAD, a.n_rows, a.n_expert, a.in_feat);
         const int64_t max_tiles = (ceil_div(a.n_rows, pair ? 256 : BM) + a.n_expert) * ceil_div(a.in_feat, BN);
-        if (int rc = pair ? launch<MODE_DGRAD, true>(ma, mb, a.host_segs, p, max_tiles, a.n_rows, st)
-                          : launch<MODE_DGRAD, false>(ma, mb, a.host_segs, p, max_tiles, a.n_rows, st))
+        int reserve = 0;
+        if (arriving && !closed) {
+            p.arr_flags = a.arrival->flags; p.arr_seq = a.arrival->seq; p.arr_src_off = a.arrival->src_off;
+            p.arr_world = a.arrival->world;
+            reserve = a.arrival->reserve_sms;
+        }
+        if (a.done) {
+            p.done = a.done->done; p.done_expected = a.done->expected; p.done_ready = a.done->ready;
+            reserve = std::max(reserve, a.done->reserve_sms);
+        }
+        if (int rc = pair ? launch<MODE_DGRAD, true>(ma, mb, a.host_segs, p, max_tiles, a.n_rows, st, reserve)
+                          : launch<MODE_DGRAD, false>(ma, mb, a.host_segs, p, max_tiles, a.n_rows, st, reserve))
             return rc;
+        if (!closed) {
+            if (a.after_input_grad) { if (int rc = a.after_input_grad(a.after_ctx)) return rc; }
+            closed = true;
+            if (overlap_bias) { if (int rc = queue_bias()) return rc; }
+        }
         if (a.grad_x_colsum) {
             const HostSegs& hs = a.host_segs ? *a.host_segs : kNoSegs;
             dim3 grid((unsigned)ceil_div(a.in_feat, 256), (unsigned)a.n_expert);
@@ -1302,8 +1412,10 @@ int tc_linear_backward(const LinearBwdArgs& a, cudaStream_t st) {
         p.is_bf16 = bf16; p.status = status_ptr(); p.n_rows = a.n_rows;
         const bool pair = use_pairs(MODE_WGRAD, a.n_rows, a.n_expert, a.in_feat);
         const int64_t max_tiles = (int64_t)a.n_expert * ceil_div(a.out_feat, pair ? 256 : BM) * ceil_div(a.in_feat, BN);
-        if (int rc = pair ? launch<MODE_WGRAD, true>(ma, mb, a.host_segs, p, max_tiles, (int64_t)a.n_expert * a.out_feat, st)
-                          : launch<MODE_WGRAD, false>(ma, mb, a.host_segs, p, max_tiles, (int64_t)a.n_expert * a.out_feat, st))
+        // (a push that forwards grad_x may still be running on its SMs)
+        const int reserve = a.done ? a.done->reserve_sms : 0;
+        if (int rc = pair ? launch<MODE_WGRAD, true>(ma, mb, a.host_segs, p, max_tiles, (int64_t)a.n_expert * a.out_feat, st, reserve)
+                          : launch<MODE_WGRAD, false>(ma, mb, a.host_segs, p, max_tiles, (int64_t)a.n_expert * a.out_feat, st, reserve))
             return rc;
     }
     if (overlap_bias) {

@@ -1,5 +1,6 @@
 // fmoe_linear entry points: argument checks and back-end selection.
 #include "common.cuh"
+#include "exchange.h"
 #include "gemm.h"
 #include <cstdlib>
 
@@ -111,3 +112,87 @@ extern "C" int fmoe_linear_backward_colsum(const void* grad_y, const void* x, co
     return dispatch_linear_backward(a, (cudaStream_t)stream);
 }
 
+
+// ---- the same products on rows that an exchange is still delivering, or that one forwards at once --
+namespace {
+struct FinishCtx { const fmoe_arrival_t* arrival; fmoe_stream_t stream; };
+int finish_arrival(void* ctx) {
+    FinishCtx* f = (FinishCtx*)ctx;
+    return fmoe_peer_arrival_finish(f->arrival, f->stream);
+}
+int gemm_arrival_of(const fmoe_arrival_t* arrival, GemmArrival* g, bool* pending) {
+    ArrivalWait w;
+    *pending = false;
+    if (!arrival || arrival->gather) return 0;
+    if (int rc = arrival_wait_of(arrival, &w)) return rc;
+    *pending = w.flags != nullptr;
+    g->flags = w.flags; g->seq = w.seq; g->src_off = w.src_off; g->world = w.world; g->reserve_sms = w.reserve_sms;
+    return 0;
+}
+int gemm_done_of(const fmoe_arrival_t* departure, GemmDone* g, bool* pending) {
+    *pending = false;
+    if (int rc = done_words_of(departure, &g->done, &g->expected, &g->ready, &g->reserve_sms)) return rc;
+    *pending = g->done != nullptr;
+    return 0;
+}
+}  // namespace
+
+extern "C" int fmoe_linear_forward_overlapped(const void* x, const void* weight, const void* bias,
+                                              const int64_t* seg_offsets, void* y, void* pre_act, int64_t n_rows,
+                                              int64_t in_feat, int64_t out_feat, int32_t n_expert, int32_t dtype,
+                                              int32_t activation, const fmoe_arrival_t* arrival,
+                                              const fmoe_arrival_t* departure, fmoe_stream_t stream) {
+    if (int rc = check_common(n_rows, in_feat, out_feat, n_expert, dtype, activation, seg_offsets)) return rc;
+    GemmArrival ga;
+    GemmDone gd;
+    bool arriving = false, leaving = false;
+    if (int rc = gemm_arrival_of(arrival, &ga, &arriving)) return rc;
+    if (int rc = gemm_done_of(departure, &gd, &leaving)) return rc;
+    if (n_rows > 0) FMOE_REQUIRE(x && weight && y, "linear_forward: null pointer");
+    LinearArgs a{x, weight, bias, seg_offsets, y, pre_act, n_rows, in_feat, out_feat, n_expert, dtype, activation};
+    // only the tensor-core kernel can start on rows that are still arriving / report finished experts
+    const bool tc = n_rows > 0 && !force_simt() && tc_forward_supported(a);
+    FMOE_REQUIRE(!leaving || (tc && n_expert == departure->n_expert),
+                 "linear_forward: an overlapped gather was started for a product the tensor-core kernels do not take");
+    const bool overlap = arriving && tc && n_expert == arrival->n_expert;
+    if (arriving && !overlap) {
+        if (int rc = fmoe_peer_arrival_finish(arrival, stream)) return rc;
+    }
+    if (overlap) a.arrival = &ga;
+    if (leaving) a.done = &gd;
+    if (n_rows > 0) {
+        if (int rc = dispatch_linear_forward(a, (cudaStream_t)stream)) return rc;
+    }
+    return overlap ? fmoe_peer_arrival_finish(arrival, stream) : 0;
+}
+
+extern "C" int fmoe_linear_backward_overlapped(const void* grad_y, const void* x, const void* weight,
+                                               const int64_t* seg_offsets, const void* act_pre, void* grad_x,
+                                               void* grad_w, void* grad_b, void* grad_x_colsum, int64_t n_rows,
+                                               int64_t in_feat, int64_t out_feat, int32_t n_expert, int32_t dtype,
+                                               int32_t activation, int32_t accumulate, void* scratch,
+                                               const fmoe_arrival_t* arrival, const fmoe_arrival_t* departure,
+                                               fmoe_stream_t stream) {
+    if (int rc = check_common(n_rows, in_feat, out_feat, n_expert, dtype, activation, seg_offsets)) return rc;
+    FMOE_REQUIRE(n_rows == 0 || (grad_y && weight), "linear_backward: null pointer");
+    FMOE_REQUIRE(!grad_w || x || n_rows == 0, "linear_backward: weight gradient needs the forward input");
+    GemmArrival ga;
+    GemmDone gd;
+    bool arriving = false, leaving = false;
+    if (int rc = gemm_arrival_of(arrival, &ga, &arriving)) return rc;
+    if (int rc = gemm_done_of(departure, &gd, &leaving)) return rc;
+    LinearBwdArgs a{grad_y, x, weight, seg_offsets, act_pre, grad_x, grad_w, grad_b, n_rows, in_feat,
+                    out_feat, n_expert, dtype, activation, accumulate, scratch};
+    a.grad_x_colsum = grad_x_colsum;
+    const bool tc = n_rows > 0 && !force_simt() && tc_backward_supported(a);
+    FMOE_REQUIRE(!leaving || (tc && grad_x && n_expert == departure->n_expert),
+                 "linear_backward: an overlapped gather was started for a product the tensor-core kernels do not take");
+    const bool overlap = arriving && tc && n_expert == arrival->n_expert;
+    if (arriving && !overlap) {
+        if (int rc = fmoe_peer_arrival_finish(arrival, stream)) return rc;
+    }
+    FinishCtx ctx{arrival, stream};
+    if (overlap) { a.arrival = &ga; a.after_input_grad = finish_arrival; a.after_ctx = &ctx; }
+    if (leaving) a.done = &gd;
+    return dispatch_linear_backward(a, (cudaStream_t)stream);
+}

@@ -77,6 +77,8 @@ constexpr int kSeqOff = 4096;         // u64 [2]              own words: exchang
 constexpr int kCapsOff = 5120;        // i64 [2][kMaxPeers]   expert-side row capacity of rank p
 constexpr int kTableOff = 8192;       // i64 [2][kTableMax]   count tables [W][W*E]
 constexpr int64_t kTableMax = ((1 << 20) - kTableOff) / 16;   // entries (W*W*E) per parity
+constexpr int64_t kExpArrOff = 1 << 20;   // u64 [2][kMaxPeers][kArrivalExperts]: rows of (source p, this GPU's expert i) landed
+static_assert(2 * kMaxPeers * kArrivalExperts * 8 <= (1 << 20), "arrival flags fit their MiB");
 constexpr int64_t kCompatOff = 2 << 20;   // 2 MiB: uploaded table + flags + plan of the host-table entry points
 constexpr int64_t kProbeBytes = 128 << 10;    // tail of that area: the empty plan of fmoe_peer_wait_probe
 constexpr int64_t kCompatBytes = (2 << 20) - kProbeBytes;
@@ -101,7 +103,7 @@ struct PlanHead {
 struct PlanDims {
     int E, W, S;
     int64_t WE, T;        // W*E, W*W*E
-    size_t own_off, table_off, stored_off, caps_off, eptr_off, lay_off, total_off, lists_off, bytes;
+    size_t own_off, table_off, stored_off, caps_off, eptr_off, lay_off, total_off, lists_off, segdone_off, done_off, bytes;
 };
 __host__ __device__ inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 __host__ __device__ inline PlanDims plan_dims(int E, int W) {
@@ -117,6 +119,8 @@ __host__ __device__ inline PlanDims plan_dims(int E, int W) {
     d.lay_off = o;    o = align_up(o + (size_t)W * (d.S + 1) * 4, 64);    // i32 lay[W][S+1]: expert-side scan of every rank
     d.total_off = o;  o = align_up(o + (size_t)W * 8, 64);
     d.lists_off = o;  o = align_up(o + (size_t)4 * (4 * (size_t)d.S + 1) * 4, 64);  // 4 x {prefix[S+1], sel[S], src[S], dst[S]}
+    d.segdone_off = o; o = align_up(o + (size_t)d.S * 4, 64);             // i32 rows of each push segment stored so far (overlapped push)
+    d.done_off = o;   o = align_up(o + (size_t)(4 * E + 16) * 4, 64);     // i32 done[2][E], expected[2][E], ready[2]: see GemmDone
     d.bytes = o;
     return d;
 }
@@ -347,6 +351,8 @@ peer_plan_kernel(const __grid_constant__ PeerBases b, const __grid_constant__ Pl
         }
         if (lane == 0) pre[d.S] = (int)run;
     }
+    for (int s = tid; s < d.S; s += blockDim.x) ((int*)(a.plan + d.segdone_off))[s] = 0;
+    for (int s = tid; s < 4 * E + 16; s += blockDim.x) ((int*)(a.plan + d.done_off))[s] = 0;
     // ---- 4. what the GEMM and the host read ----------------------------------------------------
     for (int i = tid; i <= E; i += blockDim.x)
         own[i] = bad ? 0 : (int64_t)my_lay[i < E ? lay_pos_recv(r, E, W, i, 0) : r * E + E * W];
@@ -375,6 +381,9 @@ struct MoveArgs {
     unsigned int* counter;
     int* status;
     const char* plan;
+    int* done;                             // overlapped gather: per-expert completion counters of the producing GEMM,
+    int* expected;                         //   the counts at which an expert is complete,
+    int* ready;                            //   and the word that says those counts are valid
 };
 
 // Row `row` of a list -> its segment, by bisection of the prefix array in shared memory.
@@ -496,6 +505,173 @@ peer_move_kernel(const __grid_constant__ PeerBases b, const __grid_constant__ Mo
     }
 }
 
+// ---- push that runs beside the consumer of its rows ---------------------------------------------
+// The same protocol as peer_move_kernel<true> for global_scatter, shaped to run on a few SMs while a
+// grouped GEMM occupies the others and starts on an expert's rows as soon as they are complete:
+//   * a warp moves units of kUnitRows consecutive rows of the push list (expert-major order);
+//   * every segment = rows of one (destination, expert); when its last row has been stored, the warp
+//     that stored it publishes flag[parity][this rank][expert] = epoch in the destination's landing
+//     area (this GPU's own for rows that stay); segments without rows are published at once;
+//   * the last block publishes the whole-exchange `arrived` flags as the plain push does, so the
+//     consume step that closes the epoch is unchanged.
+constexpr int kUnitRows = 32, kPushThreads = 1024, kPushWarps = kPushThreads / 32;
+
+// n consecutive rows of a contiguous block.  The block is moved in pieces of 512 bytes per warp
+// (one 16-byte load per lane) and eight pieces are in flight per lane before the first store is
+// issued -- a warp is latency-bound otherwise, all the more while a GEMM on the other SMs keeps
+// the memory system busy.  (Rows of a segment are contiguous on both sides, so the block is too.)
+__device__ __forceinline__ void copy_rows(const uint4* __restrict__ s, uint4* __restrict__ d, int n, int64_t row_vecs, int lane) {
+    const int64_t vecs = (int64_t)n * row_vecs;
+    int64_t c = lane;
+    for (; c + 7 * 32 < vecs; c += 8 * 32) {
+        uint4 v[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = __ldcg(s + c + 32 * i);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) d[c + 32 * i] = v[i];
+    }
+    for (; c < vecs; c += 32) d[c] = __ldcg(s + c);
+}
+
+__device__ __forceinline__ void publish_segment(const PeerBases& b, const MoveArgs& a, int W, int E, int s, int parity,
+                                                unsigned long long epoch) {
+    int p, i;
+    if (s < (W - 1) * E) return;                                  // rows kept for shadowed experts: not used in this mode
+    if (s < W * E) { p = a.rank; i = s - (W - 1) * E; }
+    else { const int q = s - W * E; i = q / (W - 1); p = (a.rank + q % (W - 1) + 1) % W; }
+    if (i >= kArrivalExperts) return;
+    unsigned long long* flag = (unsigned long long*)(b.base[p] + kExpArrOff) + ((size_t)parity * kMaxPeers + a.rank) * kArrivalExperts + i;
+    st_release_sys(flag, epoch);
+}
+
+__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+// Bounded wait until the GEMM that produces this GPU's expert-side rows has stored all rows of expert i.
+__device__ bool wait_expert_done(const MoveArgs& a, int i) {
+    const unsigned long long t0 = now_ns();
+    for (unsigned it = 0; it < (1u << 28); ++it) {
+        if (ld_acquire_gpu(a.ready) != 0 && ld_acquire_gpu(a.done + i) >= ld_acquire_gpu(a.expected + i)) return true;
+        if (now_ns() - t0 > a.timeout_ns) return false;
+        __nanosleep(200);
+    }
+    return false;
+}
+
+// kGather = false: global_scatter whose rows a GEMM on this GPU's peers consumes as they land (see above).
+// kGather = true:  global_gather whose rows a GEMM on THIS GPU is still producing: a unit of rows is
+//   moved once the expert it belongs to is complete (per-expert counters that the GEMM's epilogue
+//   advances, GemmDone); the receivers wait for the whole exchange as usual.
+template <bool kGather>
+__global__ void __launch_bounds__(kPushThreads, 1)
+peer_push_overlap_kernel(const __grid_constant__ PeerBases b, const __grid_constant__ MoveArgs a, const uint4* __restrict__ src,
+                         uint4* __restrict__ out) {
+    extern __shared__ int s_prefix[];                // [S + 1]
+    __shared__ int s_last;
+    __shared__ unsigned long long s_dest[kMaxPeers];
+    __shared__ unsigned long long s_dead;
+    const PlanHead* head = (const PlanHead*)a.plan;
+    const int E = head->n_expert, W = head->n_workers;
+    const PlanDims d = plan_dims(E, W);
+    const ListView L = list_view(const_cast<char*>(a.plan), d, kGather ? LIST_PUSH_BWD : LIST_PUSH_FWD);
+    int* seg_done = (int*)(const_cast<char*>(a.plan) + d.segdone_off);
+    unsigned long long* hdr = (unsigned long long*)b.base[a.rank];
+    const unsigned long long epoch = __ldcg(hdr + kSeqOff / 8) + 1;
+    const int parity = (int)(epoch & 1);
+    const int64_t row_vecs = a.row_bytes / 16;
+    // (the output lies in the receive pool: no slot is involved)
+    const bool room = kGather ? (head->token_rows <= a.out_rows && head->expert_rows <= a.in_rows)
+                              : (head->expert_rows <= a.out_rows && head->token_rows <= a.in_rows);
+    for (int i = threadIdx.x; i <= d.S; i += kPushThreads) s_prefix[i] = L.prefix[i];
+    if (threadIdx.x == 0) s_dead = 0ull;
+    __syncthreads();
+    {
+        const int p = threadIdx.x;
+        if (p < W && p != a.rank) {
+            if (blockIdx.x == 0) {
+                unsigned long long* peer_hdr = (unsigned long long*)b.base[p];
+                peer_hdr[kDestOff / 8 + parity * kMaxPeers + a.rank] = room ? a.my_dest : kRefused;
+                st_release_sys(peer_hdr + kAnnOff / 8 + parity * kMaxPeers + a.rank, epoch);
+            }
+            const bool announced = wait_flag(hdr + kAnnOff / 8 + parity * kMaxPeers + p, epoch, a.timeout_ns);
+            const unsigned long long dest = __ldcg(hdr + kDestOff / 8 + parity * kMaxPeers + p);
+            s_dest[p] = dest;
+            if (!announced) { atomicOr(a.status, 16); atomicOr(&s_dead, 1ull << p); }
+            else if (dest == kRefused || dest < (unsigned long long)kHeaderBytes) { atomicOr(a.status, 64); atomicOr(&s_dead, 1ull << p); }
+        }
+        if (threadIdx.x == 0 && blockIdx.x == 0 && !room) atomicOr(a.status, 64);
+        __syncthreads();
+    }
+    const int total = room ? s_prefix[d.S] : 0;
+    if (!kGather && room && blockIdx.x == 0)          // nothing will ever be stored for these: their consumers need not wait
+        for (int s = (W - 1) * E + threadIdx.x; s < d.S; s += kPushThreads)
+            if (s_prefix[s + 1] == s_prefix[s]) publish_segment(b, a, W, E, s, parity, epoch);
+    const int lane = threadIdx.x & 31;
+    const int n_units = (total + kUnitRows - 1) / kUnitRows;
+    int done_expert = -1;                             // kGather: the expert this warp saw complete last
+    bool gave_up = false;
+    for (int u = blockIdx.x * kPushWarps + (threadIdx.x >> 5); u < n_units; u += gridDim.x * kPushWarps) {
+        int row = u * kUnitRows;
+        const int row_end = min(row + kUnitRows, total);
+        int k = find_seg(s_prefix, d.S, row);
+        while (row < row_end) {
+            const int n = min(row_end, s_prefix[k + 1]) - row;
+            const int sel = L.sel[k];
+            bool dead = sel != kLocal && ((s_dead >> sel) & 1ull);
+            if (kGather && k >= (W - 1) * E) {
+                const int i = k < W * E ? k - (W - 1) * E : (k - W * E) / (W - 1);
+                if (i != done_expert && !gave_up) {
+                    int ok = 1;
+                    if (lane == 0) ok = wait_expert_done(a, i) ? 1 : 0;
+                    ok = __shfl_sync(0xffffffffu, ok, 0);
+                    if (ok) done_expert = i;
+                    else { gave_up = true; if (lane == 0) atomicOr(a.status, 32); }
+                }
+                dead = dead || gave_up;               // rows that were never produced are not forwarded
+            }
+            if (!dead) {
+                const uint4* s = src + (int64_t)(L.src[k] + (row - s_prefix[k])) * row_vecs;
+                uint4* dptr = (sel == kLocal ? out : (uint4*)(b.base[sel] + s_dest[sel])) + (int64_t)(L.dst[k] + (row - s_prefix[k])) * row_vecs;
+                copy_rows(s, dptr, n, row_vecs, lane);
+            }
+            __syncwarp();
+            if (!kGather && lane == 0) {
+                // the warp's stores are ordered before this fence by the barrier above; the fence is cumulative
+                __threadfence_system();
+                const int before = atomicAdd(seg_done + k, n);
+                if (before + n == s_prefix[k + 1] - s_prefix[k] && !dead) {
+                    __threadfence_system();
+                    publish_segment(b, a, W, E, k, parity, epoch);
+                }
+            }
+            row += n;
+            ++k;
+            while (k < d.S && s_prefix[k + 1] == s_prefix[k]) ++k;
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence_system();
+        s_last = atomicAdd(a.counter, 1u) == gridDim.x - 1;
+    }
+    __syncthreads();
+    if (s_last) {
+        __threadfence_system();
+        const int p = threadIdx.x;
+        if (p < W && p != a.rank)
+            st_release_sys((unsigned long long*)b.base[p] + kArrivedOff / 8 + parity * kMaxPeers + a.rank, epoch);
+        // the plan may serve another exchange
+        if (!kGather) for (int s = threadIdx.x; s < d.S; s += kPushThreads) seg_done[s] = 0;
+        if (kGather) {
+            for (int i = threadIdx.x; i < E; i += kPushThreads) a.done[i] = 0;
+            if (threadIdx.x == 0) *a.ready = 0;
+        }
+        if (threadIdx.x == 0) a.counter[0] = 0;
+    }
+}
+
 int launch_plan(Comm* c, int rank, int W, int E, bool exchange, const int64_t* lec, const int64_t* table,
                 const uint8_t* stored, const int64_t* caps, int64_t cap_rows, void* plan, cudaStream_t st) {
     FMOE_REQUIRE(E > 0 && W > 0 && W <= kMaxPeers && rank >= 0 && rank < W, "peer plan: bad E=%d W=%d rank=%d", E, W, rank);
@@ -521,11 +697,21 @@ int launch_plan(Comm* c, int rank, int W, int E, bool exchange, const int64_t* l
 }
 
 int launch_move(Comm* c, const void* in, void* out, const void* plan, int E, int64_t in_rows, int64_t out_rows,
-                int64_t row_bytes, bool reverse, cudaStream_t st) {
+                int64_t row_bytes, bool reverse, cudaStream_t st, int phases = 3, int overlap_sms = 0, int done_use = 0);
+
+bool lies_in_pool(Comm* c, const void* out, int64_t bytes) {
+    char* pool = c->peer.base[c->rank] + kHeaderBytes + 2 * c->peer.slot_bytes;
+    return c->peer.pool_bytes > 0 && (char*)out >= pool && (char*)out + bytes <= pool + c->peer.pool_bytes;
+}
+
+// phases: bit 0 = push, bit 1 = consume.  overlap_sms > 0 (push of a scatter into a pool buffer only):
+// the few-SM push that publishes per-expert arrival flags.
+int launch_move(Comm* c, const void* in, void* out, const void* plan, int E, int64_t in_rows, int64_t out_rows,
+                int64_t row_bytes, bool reverse, cudaStream_t st, int phases, int overlap_sms, int done_use) {
     FMOE_REQUIRE(row_bytes > 0 && row_bytes % 16 == 0, "peer exchange: row_bytes=%lld (a positive multiple of 16)", (long long)row_bytes);
     FMOE_REQUIRE(in_rows >= 0 && out_rows >= 0 && in_rows < ((int64_t)1 << 31) && out_rows < ((int64_t)1 << 31),
                  "peer exchange: rows in=%lld out=%lld", (long long)in_rows, (long long)out_rows);
-    FMOE_REQUIRE((in || in_rows == 0) && (out || out_rows == 0) && plan, "peer exchange: null buffer");
+    FMOE_REQUIRE((in || in_rows == 0 || !(phases & 1)) && (out || out_rows == 0) && plan, "peer exchange: null buffer");
     FMOE_REQUIRE((((uintptr_t)in | (uintptr_t)out) & 15) == 0, "peer exchange: buffers must be 16-byte aligned");
     PeerBases b;
     for (int p = 0; p < kMaxPeers; ++p) b.base[p] = c->peer.base[p];
@@ -545,9 +731,34 @@ int launch_move(Comm* c, const void* in, void* out, const void* plan, int E, int
     const size_t smem = (size_t)(d.S + 1) * sizeof(int);
     FMOE_REQUIRE(smem <= 40 * 1024, "peer exchange: %d segment slots do not fit the kernels' shared memory", d.S);
     const int cap_blocks = sm_count() * 8;
-    const unsigned push_blocks = (unsigned)std::max<int64_t>(1, std::min<int64_t>(ceil_div(in_rows, kMoveWarps), cap_blocks));
-    peer_move_kernel<true><<<push_blocks, kMoveThreads, smem, st>>>(b, a, (const uint4*)in, (uint4*)out);
-    FMOE_CHECK_LAUNCH();
+    if ((phases & 1) && overlap_sms > 0) {
+        FMOE_REQUIRE(direct, "peer exchange: the overlapped push needs an output in the receive pool");
+        // clusters of two blocks: the push then occupies whole SM pairs and leaves the others to the
+        // CTA pairs of the GEMM that runs beside it
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)((overlap_sms + 1) / 2 * 2));
+        cfg.blockDim = dim3(kPushThreads);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = st;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        if (reverse) {
+            const PlanDims pd = plan_dims(E, c->world);
+            int* words = (int*)((char*)const_cast<void*>(plan) + pd.done_off);
+            a.done = words + (size_t)done_use * E; a.expected = words + (size_t)(2 + done_use) * E; a.ready = words + 4 * (size_t)E + done_use;
+            FMOE_CUDA_TRY(cudaLaunchKernelEx(&cfg, peer_push_overlap_kernel<true>, b, a, (const uint4*)in, (uint4*)out));
+        } else {
+            FMOE_CUDA_TRY(cudaLaunchKernelEx(&cfg, peer_push_overlap_kernel<false>, b, a, (const uint4*)in, (uint4*)out));
+        }
+    } else if (phases & 1) {
+        const unsigned push_blocks = (unsigned)std::max<int64_t>(1, std::min<int64_t>(ceil_div(in_rows, kMoveWarps), cap_blocks));
+        peer_move_kernel<true><<<push_blocks, kMoveThreads, smem, st>>>(b, a, (const uint4*)in, (uint4*)out);
+        FMOE_CHECK_LAUNCH();
+    }
+    if (!(phases & 2)) return 0;
     // consume: one block when nothing has to be copied or cleared
     const bool work = !direct || reverse;
     // (direct + gather: only the usually empty tail of the token-side buffer may need clearing)
@@ -630,6 +841,10 @@ void peer_release(Comm* c) {
     }
     if (ps.counter) cudaFree(ps.counter);
     ps.counter = nullptr;
+    if (ps.side) cudaStreamDestroy(ps.side);
+    if (ps.fork) cudaEventDestroy(ps.fork);
+    if (ps.join) cudaEventDestroy(ps.join);
+    ps.side = nullptr; ps.fork = ps.join = nullptr;
     ps.slot_bytes = 0;
     (void)cudaGetLastError();
 }
@@ -878,6 +1093,14 @@ extern "C" int fmoe_peer_enable(fmoe_comm_t comm, int64_t slot_bytes, int64_t po
     }
     cudaFree(dev_buf);
     dev_buf = nullptr;
+    {
+        int lo = 0, hi = 0;
+        cudaDeviceGetStreamPriorityRange(&lo, &hi);
+        if (cudaStreamCreateWithPriority(&c->peer.side, cudaStreamNonBlocking, hi) != cudaSuccess) c->peer.side = nullptr;
+        if (cudaEventCreateWithFlags(&c->peer.fork, cudaEventDisableTiming) != cudaSuccess) c->peer.fork = nullptr;
+        if (cudaEventCreateWithFlags(&c->peer.join, cudaEventDisableTiming) != cudaSuccess) c->peer.join = nullptr;
+        (void)cudaGetLastError();
+    }
     for (int p = 0; p < W; ++p) c->peer.base[p] = base[p];
     c->peer.counter = counter;
     const char* env = getenv("FMOE_B200_PEER_TIMEOUT_MS");
@@ -969,6 +1192,97 @@ extern "C" int fmoe_peer_gather_planned(fmoe_comm_t comm, const void* global_in,
     Comm* c = (Comm*)comm;
     if (c->peer.slot_bytes == 0) return FMOE_PEER_UNAVAILABLE;
     return launch_move(c, global_in, local_out, plan, n_expert, in_rows, out_rows, row_bytes, true, (cudaStream_t)stream);
+}
+
+namespace fmoe {
+// Fills what a grouped GEMM needs to wait for the rows of the exchange that was queued last.
+int arrival_wait_of(const fmoe_arrival_t* arrival, ArrivalWait* w) {
+    *w = ArrivalWait{};
+    if (!arrival || !arrival->comm) return 0;
+    Comm* c = (Comm*)arrival->comm;
+    FMOE_REQUIRE(c->peer.slot_bytes > 0 && arrival->plan, "arrival: stale handle");
+    const int E = arrival->n_expert, W = c->world;
+    const PlanDims d = plan_dims(E, W);
+    w->flags = (const unsigned long long*)(c->peer.base[c->rank] + kExpArrOff);
+    w->seq = (const unsigned long long*)(c->peer.base[c->rank] + kSeqOff);
+    w->src_off = (const int*)((const char*)arrival->plan + d.lay_off) + (size_t)c->rank * (d.S + 1) + (size_t)c->rank * E;
+    w->world = W;
+    w->n_expert = E;
+    w->reserve_sms = arrival->overlap_sms;
+    return 0;
+}
+}  // namespace fmoe
+
+extern "C" int fmoe_peer_scatter_planned_async(fmoe_comm_t comm, const void* local_in, void* global_out, const void* plan,
+                                               int64_t in_rows, int64_t out_rows, int64_t row_bytes, int32_t n_expert,
+                                               int32_t overlap_sms, fmoe_stream_t stream, fmoe_arrival_t* arrival) {
+    FMOE_REQUIRE(comm && arrival, "peer exchange: null pointer");
+    Comm* c = (Comm*)comm;
+    memset(arrival, 0, sizeof(*arrival));
+    if (c->peer.slot_bytes == 0) return FMOE_PEER_UNAVAILABLE;
+    cudaStream_t st = (cudaStream_t)stream;
+    const bool can = overlap_sms > 0 && c->peer.side && c->peer.fork && c->peer.join && c->world <= 32 &&
+                     n_expert <= kArrivalExperts && lies_in_pool(c, global_out, out_rows * row_bytes) && overlap_sms < sm_count();
+    if (!can)      // the plain exchange on the caller's stream; nothing left to finish
+        return launch_move(c, local_in, global_out, plan, n_expert, in_rows, out_rows, row_bytes, false, st);
+    FMOE_CUDA_TRY(cudaEventRecord(c->peer.fork, st));
+    FMOE_CUDA_TRY(cudaStreamWaitEvent(c->peer.side, c->peer.fork, 0));
+    if (int rc = launch_move(c, local_in, global_out, plan, n_expert, in_rows, out_rows, row_bytes, false, c->peer.side, 1, overlap_sms))
+        return rc;
+    FMOE_CUDA_TRY(cudaEventRecord(c->peer.join, c->peer.side));
+    arrival->comm = comm; arrival->plan = plan; arrival->out = global_out;
+    arrival->in_rows = in_rows; arrival->out_rows = out_rows; arrival->row_bytes = row_bytes;
+    arrival->n_expert = n_expert; arrival->overlap_sms = overlap_sms;
+    return 0;
+}
+
+extern "C" int fmoe_peer_arrival_finish(const fmoe_arrival_t* arrival, fmoe_stream_t stream) {
+    FMOE_REQUIRE(arrival, "arrival_finish: null pointer");
+    if (!arrival->comm) return 0;                 // the exchange was queued whole
+    Comm* c = (Comm*)arrival->comm;
+    cudaStream_t st = (cudaStream_t)stream;
+    FMOE_CUDA_TRY(cudaStreamWaitEvent(st, c->peer.join, 0));
+    return launch_move(c, nullptr, arrival->out, arrival->plan, arrival->n_expert, arrival->in_rows, arrival->out_rows,
+                       arrival->row_bytes, arrival->gather != 0, st, 2, 0);
+}
+
+namespace fmoe {
+int done_words_of(const fmoe_arrival_t* departure, int** done, int** expected, int** ready, int* reserve_sms) {
+    *done = *expected = *ready = nullptr;
+    *reserve_sms = 0;
+    if (!departure || !departure->comm) return 0;
+    Comm* c = (Comm*)departure->comm;
+    FMOE_REQUIRE(departure->gather && departure->plan, "departure: not the handle of an overlapped gather");
+    const int E = departure->n_expert;
+    const PlanDims d = plan_dims(E, c->world);
+    int* words = (int*)((char*)const_cast<void*>(departure->plan) + d.done_off);
+    const int use = departure->use;
+    *done = words + (size_t)use * E; *expected = words + (size_t)(2 + use) * E; *ready = words + 4 * (size_t)E + use;
+    *reserve_sms = departure->overlap_sms;
+    return 0;
+}
+}  // namespace fmoe
+
+extern "C" int fmoe_peer_gather_planned_async(fmoe_comm_t comm, const void* global_in, void* local_out, const void* plan,
+                                              int64_t in_rows, int64_t out_rows, int64_t row_bytes, int32_t n_expert,
+                                              int32_t overlap_sms, int32_t use, fmoe_stream_t stream, fmoe_arrival_t* departure) {
+    FMOE_REQUIRE(comm && departure && (use == 0 || use == 1), "peer exchange: bad argument");
+    Comm* c = (Comm*)comm;
+    memset(departure, 0, sizeof(*departure));
+    if (c->peer.slot_bytes == 0) return FMOE_PEER_UNAVAILABLE;
+    cudaStream_t st = (cudaStream_t)stream;
+    const bool can = overlap_sms > 0 && c->peer.side && c->peer.fork && c->peer.join && c->world <= 32 &&
+                     lies_in_pool(c, local_out, out_rows * row_bytes) && overlap_sms < sm_count();
+    if (!can) return 0;     // nothing queued: the caller runs the plain gather after the product (departure->comm == NULL)
+    FMOE_CUDA_TRY(cudaEventRecord(c->peer.fork, st));
+    FMOE_CUDA_TRY(cudaStreamWaitEvent(c->peer.side, c->peer.fork, 0));
+    if (int rc = launch_move(c, global_in, local_out, plan, n_expert, in_rows, out_rows, row_bytes, true, c->peer.side, 1, overlap_sms, use))
+        return rc;
+    FMOE_CUDA_TRY(cudaEventRecord(c->peer.join, c->peer.side));
+    departure->comm = comm; departure->plan = plan; departure->out = local_out;
+    departure->in_rows = in_rows; departure->out_rows = out_rows; departure->row_bytes = row_bytes;
+    departure->n_expert = n_expert; departure->overlap_sms = overlap_sms; departure->gather = 1; departure->use = use;
+    return 0;
 }
 
 extern "C" int fmoe_peer_wait_probe(fmoe_comm_t comm, int32_t timeout_ms, int32_t push, fmoe_stream_t stream) {

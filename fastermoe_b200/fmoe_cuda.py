@@ -591,6 +591,52 @@ def peer_scatter_planned(input_buf, plan, out_rows):
     return _planned_move(lib.fmoe_peer_scatter_planned, "peer_scatter", input_buf, plan, out_rows)
 
 
+class PendingArrival:
+    """Rows of a global_scatter that are still on their way (fmoe_arrival_t): give it to the grouped
+    GEMM that reads them (``linear_forward_act`` / ``linear_backward_act``), which closes the exchange,
+    or call ``finish()``.  Holds the buffers the exchange uses."""
+
+    def __init__(self, handle, keep):
+        self.handle, self.keep, self.open = handle, keep, bool(handle.comm)
+
+    def finish(self):
+        if self.open:
+            self.open = False
+            dev = self.keep[0].device
+            with torch.cuda.device(dev):
+                _run("peer_arrival_finish", lib.fmoe_peer_arrival_finish, ctypes.byref(self.handle), _stream())
+
+
+def peer_scatter_planned_async(input_buf, plan, out_rows, overlap_sms):
+    """peer_scatter_planned whose push runs beside the caller's stream on ``overlap_sms`` SMs.  Returns
+    (out, PendingArrival); ``out`` may only be read by the GEMM the pending object is given to, or after
+    ``finish()``.  Falls back to the plain exchange (pending object already closed) when it cannot overlap."""
+    _check_cuda(input_buf)
+    out = _recv_empty(input_buf, out_rows)
+    h = _lib.Arrival()
+    with torch.cuda.device(input_buf.device):
+        _run("peer_scatter", lib.fmoe_peer_scatter_planned_async, _comm(input_buf.device), _ptr(input_buf), _ptr(out),
+             _ptr(plan.buf), input_buf.shape[0], out_rows, input_buf.shape[1] * input_buf.element_size(), plan.n_expert,
+             int(overlap_sms), _stream(), ctypes.byref(h))
+    return out, PendingArrival(h, (input_buf, out, plan.buf))
+
+
+def peer_gather_planned_async(output_buf, plan, out_rows, overlap_sms, use):
+    """Starts a peer_gather_planned whose rows a grouped GEMM, queued next with the returned handle as
+    ``departure``, is about to write into ``output_buf``.  Returns (out, PendingArrival) -- close it
+    with ``finish()`` after that GEMM -- or (None, None) when it cannot overlap (nothing was queued)."""
+    _check_cuda(output_buf)
+    out = _recv_empty(output_buf, out_rows)
+    h = _lib.Arrival()
+    with torch.cuda.device(output_buf.device):
+        _run("peer_gather", lib.fmoe_peer_gather_planned_async, _comm(output_buf.device), _ptr(output_buf), _ptr(out),
+             _ptr(plan.buf), output_buf.shape[0], out_rows, output_buf.shape[1] * output_buf.element_size(),
+             plan.n_expert, int(overlap_sms), int(use), _stream(), ctypes.byref(h))
+    if not h.comm:
+        return None, None
+    return out, PendingArrival(h, (output_buf, out, plan.buf))
+
+
 def peer_gather_planned(output_buf, plan, out_rows):
     """global_gather driven by a PeerPlan: expert-side rows -> [out_rows, d] token-side buffer."""
     return _planned_move(lib.fmoe_peer_gather_planned, "peer_gather", output_buf, plan, out_rows)
@@ -806,17 +852,30 @@ def combine_backward(grad_out, buf, inv, score, need_score_grad=True):
     return grad_buf, grad_score
 
 
-def linear_forward_act(x, seg_offsets, weight, bias, activation, want_pre=False):
+def linear_forward_act(x, seg_offsets, weight, bias, activation, want_pre=False, arrival=None, departure=None, out=None):
     """Grouped GEMM with fused bias and activation.  Returns (y, act_deriv or None);
     ``act_deriv`` (with ``want_pre`` and GELU) holds gelu'(pre-activation), the factor
-    that linear_backward_act multiplies into the input gradient."""
+    that linear_backward_act multiplies into the input gradient.  ``arrival``: a PendingArrival
+    whose exchange is still filling ``x``; the call closes it.  ``departure``: a PendingArrival of
+    peer_gather_planned_async that forwards ``out`` (the preallocated y) while the product runs; the
+    caller closes it."""
     _check_cuda(x, seg_offsets, weight, bias)
     n_expert, out_feat, in_feat = weight.shape
     assert x.shape[1] == in_feat and x.dtype == weight.dtype
     assert seg_offsets.dtype == torch.int64 and seg_offsets.numel() == n_expert + 1
-    y = x.new_empty((x.shape[0], out_feat))
+    y = out if out is not None else x.new_empty((x.shape[0], out_feat))
+    assert y.shape == (x.shape[0], out_feat) and y.dtype == x.dtype and y.is_contiguous()
     pre = x.new_empty((x.shape[0], out_feat)) if want_pre else None
     with torch.cuda.device(x.device):
+        arriving = arrival is not None and arrival.open
+        if arriving or departure is not None:
+            if arriving:
+                arrival.open = False
+            _run("linear_forward", lib.fmoe_linear_forward_overlapped, _ptr(x), _ptr(weight), _ptr(bias), _ptr(seg_offsets),
+                 _ptr(y), _ptr(pre), x.shape[0], in_feat, out_feat, n_expert, _dtype_code(x), activation,
+                 ctypes.byref(arrival.handle) if arriving else None,
+                 ctypes.byref(departure.handle) if departure is not None else None, _stream())
+            return y, pre
         _run("linear_forward", lib.fmoe_linear_forward, _ptr(x), _ptr(weight), _ptr(bias), _ptr(seg_offsets), _ptr(y),
                                       _ptr(pre), x.shape[0], in_feat, out_feat, n_expert, _dtype_code(x),
                                       activation, _stream())
@@ -824,7 +883,8 @@ def linear_forward_act(x, seg_offsets, weight, bias, activation, want_pre=False)
 
 
 def linear_backward_act(grad_y, x, seg_offsets, weight, act_pre, activation, need_bias=True,
-                        need_input_grad=True, grad_w=None, grad_b=None, accumulate=False, want_gx_colsum=False):
+                        need_input_grad=True, grad_w=None, grad_b=None, accumulate=False, want_gx_colsum=False,
+                        arrival=None, departure=None, grad_x=None):
     """Grouped GEMM backward.  ``act_pre`` (shape of x) fuses the backward of the
     activation that produced ``x`` into the input gradient: for ReLU pass the activation
     output, for GELU the derivative buffer of linear_forward_act.  Returns (dX, dW, db), and with
@@ -833,12 +893,24 @@ def linear_backward_act(grad_y, x, seg_offsets, weight, act_pre, activation, nee
     _check_cuda(grad_y, x, seg_offsets, weight, act_pre)
     n_expert, out_feat, in_feat = weight.shape
     n_rows = grad_y.shape[0]
-    gx = x.new_empty((n_rows, in_feat)) if need_input_grad else None
+    gx = (grad_x if grad_x is not None else x.new_empty((n_rows, in_feat))) if need_input_grad else None
     gw = grad_w if grad_w is not None else torch.empty_like(weight)
     gb = grad_b if grad_b is not None else (weight.new_empty((n_expert, out_feat)) if need_bias else None)
     with torch.cuda.device(x.device):
         nbytes = lib.fmoe_linear_scratch_bytes(n_rows, in_feat, out_feat, n_expert, _dtype_code(x))
         scratch = _scratch(nbytes, x.device)
+        arriving = arrival is not None and arrival.open
+        if arriving or departure is not None:
+            # grad_y is still arriving (the call closes that exchange) and / or grad_x is forwarded as it is produced
+            if arriving:
+                arrival.open = False
+            cs = weight.new_empty((n_expert, in_feat)) if want_gx_colsum else None
+            _run("linear_backward", lib.fmoe_linear_backward_overlapped, _ptr(grad_y), _ptr(x), _ptr(weight),
+                 _ptr(seg_offsets), _ptr(act_pre), _ptr(gx), _ptr(gw), _ptr(gb), _ptr(cs), n_rows, in_feat,
+                 out_feat, n_expert, _dtype_code(x), activation, 1 if accumulate else 0, _ptr(scratch),
+                 ctypes.byref(arrival.handle) if arriving else None,
+                 ctypes.byref(departure.handle) if departure is not None else None, _stream())
+            return (gx, gw, gb, cs) if want_gx_colsum else (gx, gw, gb)
         if want_gx_colsum:
             assert need_input_grad
             cs = weight.new_empty((n_expert, in_feat))

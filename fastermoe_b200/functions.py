@@ -25,9 +25,10 @@ class ExpertCounts:
     else ``None``.  Accepted wherever the reference passes ``fwd_expert_count``.
     """
 
-    def __init__(self, offsets, counts_cpu=None):
+    def __init__(self, offsets, counts_cpu=None, exchange=None):
         self.offsets = offsets
         self.counts_cpu = counts_cpu
+        self.exchange = exchange     # PlannedExchange whose scatter fills the rows (may still be arriving)
 
     @staticmethod
     def wrap(counts, device):
@@ -419,16 +420,56 @@ class PlannedExchange:
     """One layer call's all-to-all-v driven by a plan that lives on the device (fmoe_cuda.PeerPlan):
     the host knows neither the counts nor how many rows arrive; ``fwd_batch_size`` is the capacity
     of the expert-side buffers."""
-    __slots__ = ("plan", "fwd_batch_size", "world_size", "num_expert")
+    __slots__ = ("plan", "fwd_batch_size", "world_size", "num_expert", "overlap_sms", "pending", "token_rows", "early")
 
-    def __init__(self, plan, cap_rows, world_size):
+    def __init__(self, plan, cap_rows, world_size, overlap_sms=0, token_rows=0):
         self.plan, self.fwd_batch_size, self.world_size = plan, int(cap_rows), world_size
         self.num_expert = plan.n_expert
+        # > 0: the pushes run on that many SMs beside the grouped GEMMs that read (scatter) or write
+        # (gather) their rows; FusedExpertMLP takes part; the caller sets it only when that module follows
+        self.overlap_sms, self.pending = int(overlap_sms), None
+        self.token_rows = int(token_rows)       # rows of this rank's token-side buffers
+        self.early = None                       # (expert-side tensor, token-side result, pending) of a gather started early
+
+    def flush(self):
+        """Closes a scatter whose rows nobody waited for tile by tile, and a gather that was started early."""
+        if self.pending is not None:
+            self.pending.finish()
+            self.pending = None
+        if self.early is not None:
+            self.early[2].finish()
+
+    def begin_gather(self, buf, use):
+        """Called right before the GEMM that writes ``buf`` (expert side): starts the gather that
+        forwards its rows as experts complete.  Returns the handle for that GEMM, or None."""
+        self.flush()
+        self.early = None
+        if self.overlap_sms <= 0 or self.token_rows <= 0:
+            return None
+        out, pend = fmoe_cuda.peer_gather_planned_async(buf, self.plan, self.token_rows, self.overlap_sms, use)
+        if pend is None:
+            return None
+        self.early = (buf, out, pend)
+        return pend
+
+    def take_pending(self):
+        p, self.pending = self.pending, None
+        return p
 
     def scatter(self, buf, out_rows):
+        self.flush()
+        if self.overlap_sms > 0:
+            out, self.pending = fmoe_cuda.peer_scatter_planned_async(buf, self.plan, out_rows, self.overlap_sms)
+            return out
         return fmoe_cuda.peer_scatter_planned(buf, self.plan, out_rows)
 
     def gather(self, buf, out_rows):
+        early, self.early = self.early, None
+        if early is not None:
+            early[2].finish()
+            if early[0].data_ptr() == buf.data_ptr() and early[1].shape[0] == out_rows:
+                return early[1]                 # the rows are already here
+        self.flush()
         return fmoe_cuda.peer_gather_planned(buf, self.plan, out_rows)
 
 
@@ -456,12 +497,18 @@ class FusedExpertMLP(Function):
     applied in the epilogue of the second layer's input-gradient GEMM."""
 
     @staticmethod
-    def forward(ctx, x, offsets, w1, b1, w2, b2, act):
+    def forward(ctx, x, offsets, w1, b1, w2, b2, act, exch=None):
+        """``exch``: the PlannedExchange whose scatter produced ``x`` (and whose scatter of the output
+        gradient will produce ``grad_y``); a pending arrival of it is waited for tile by tile."""
         x = x.contiguous()
         want_pre = act == _lib.ACT_GELU and (x.requires_grad or w1.requires_grad)
-        h, pre = fmoe_cuda.linear_forward_act(x, offsets, w1, b1, act, want_pre=want_pre)
-        y, _ = fmoe_cuda.linear_forward_act(h, offsets, w2, b2, _lib.ACT_NONE)
-        ctx.act = act
+        arrival = exch.take_pending() if exch is not None else None
+        h, pre = fmoe_cuda.linear_forward_act(x, offsets, w1, b1, act, want_pre=want_pre, arrival=arrival)
+        y = x.new_empty((x.shape[0], w2.shape[1]))
+        # the gather that follows the experts starts now and forwards y expert by expert
+        departure = exch.begin_gather(y, 0) if exch is not None and hasattr(exch, "begin_gather") else None
+        fmoe_cuda.linear_forward_act(h, offsets, w2, b2, _lib.ACT_NONE, departure=departure, out=y)
+        ctx.act, ctx.exch = act, exch
         ctx.has_bias = (b1 is not None, b2 is not None)
         ctx.save_for_backward(x, offsets, w1, w2, h, pre)
         return y
@@ -470,6 +517,7 @@ class FusedExpertMLP(Function):
     def backward(ctx, grad_y):
         x, offsets, w1, w2, h, pre = ctx.saved_tensors
         act = ctx.act
+        arrival = ctx.exch.take_pending() if ctx.exch is not None else None
         act_pre = None
         if act == _lib.ACT_RELU:
             act_pre = h
@@ -479,14 +527,20 @@ class FusedExpertMLP(Function):
         # second layer returns it, so the first layer's backward does not read gh once more for it.
         if ctx.has_bias[0]:
             gh, gw2, gb2, gb1 = fmoe_cuda.linear_backward_act(grad_y.contiguous(), h, offsets, w2, act_pre, act,
-                                                              need_bias=ctx.has_bias[1], want_gx_colsum=True)
+                                                              need_bias=ctx.has_bias[1], want_gx_colsum=True,
+                                                              arrival=arrival)
         else:
             gh, gw2, gb2 = fmoe_cuda.linear_backward_act(grad_y.contiguous(), h, offsets, w2, act_pre, act,
-                                                         need_bias=ctx.has_bias[1])
+                                                         need_bias=ctx.has_bias[1], arrival=arrival)
             gb1 = None
+        gx, departure = None, None
+        if ctx.needs_input_grad[0] and ctx.exch is not None and hasattr(ctx.exch, "begin_gather"):
+            gx = x.new_empty(x.shape)
+            departure = ctx.exch.begin_gather(gx, 1)        # the input gradient travels back as it is produced
         gx, gw1, _ = fmoe_cuda.linear_backward_act(gh, x, offsets, w1, None, _lib.ACT_NONE, need_bias=False,
-                                                   need_input_grad=ctx.needs_input_grad[0])
-        return gx, None, gw1, gb1, gw2, gb2, None
+                                                   need_input_grad=ctx.needs_input_grad[0], departure=departure,
+                                                   grad_x=gx)
+        return gx, None, gw1, gb1, gw2, gb2, None, None
 
 
 class AllGather(Function):

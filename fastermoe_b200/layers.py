@@ -122,10 +122,15 @@ def _fmoe_general_global_forward(inp, gate, expert_fn, policy_fn, experts, num_e
     elif routing.plan is not None:
         # No host copy of the counts: plan, offsets and row counts stay on the device.
         stored = _no_shadow_flags(world_size, num_expert)
-        exch = PlannedExchange(routing.plan, routing.n_recv, world_size)
+        # the push of the scatter runs beside the experts' first GEMM (and, in the backward pass, beside
+        # the input-gradient GEMM of the second layer) when the experts module can wait for rows tile by tile
+        overlap = 0
+        if getattr(experts, "consumes_arrival", None) is not None and experts.consumes_arrival(inp):
+            overlap = int(os.environ.get("FMOE_B200_OVERLAP_SMS", "0"))
+        exch = PlannedExchange(routing.plan, routing.n_recv, world_size, overlap_sms=overlap, token_rows=routing.n_rows)
         n_rows = routing.n_rows
         x = MOEScatterFused.apply(inp, routing.pos, routing.inv, top_k, n_rows, exch)
-        x = expert_fn(x, [[experts]], ExpertCounts(routing.own_offsets_dev), num_expert)
+        x = expert_fn(x, [[experts]], ExpertCounts(routing.own_offsets_dev, exchange=exch), num_expert)
     else:
         shadows = {} if shadows is None else shadows
         if no_policy:

@@ -28,15 +28,23 @@ class _Expert(nn.Module):
         self.h4toh = FMoELinear(num_expert, d_hidden, d_model, bias=bias, rank=rank)
         self.activation = activation
 
+    def consumes_arrival(self, inp):
+        """True when forward() reads its input with the fused kernels, which can start on rows of an
+        exchange that are still arriving (and later on the arriving output gradient)."""
+        return inp.is_cuda and activation_code(self.activation) is not None
+
     def forward(self, inp, fwd_expert_count):
         code = activation_code(self.activation)
+        exch = getattr(fwd_expert_count, "exchange", None)
         if code is None or not inp.is_cuda:
+            if exch is not None:
+                exch.flush()
             x = self.htoh4(inp, fwd_expert_count)
             x = self.activation(x)
             return self.h4toh(x, fwd_expert_count)
         counts = ExpertCounts.wrap(fwd_expert_count, inp.device)
         return FusedExpertMLP.apply(inp, counts.offsets, self.htoh4.weight, self.htoh4.bias,
-                                    self.h4toh.weight, self.h4toh.bias, code)
+                                    self.h4toh.weight, self.h4toh.bias, code, exch)
 
 
 def _gen_policy(alpha, constants=None):

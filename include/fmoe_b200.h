@@ -436,6 +436,62 @@ int fmoe_peer_scatter_planned(fmoe_comm_t comm, const void* local_in, void* glob
 int fmoe_peer_gather_planned(fmoe_comm_t comm, const void* global_in, void* local_out, const void* plan,
                              int64_t in_rows, int64_t out_rows, int64_t row_bytes, int32_t n_expert,
                              fmoe_stream_t stream);
+/* global_scatter overlapped with the grouped GEMM that consumes its rows (the smart schedule's aim,
+ * cuda/fused_compute.cuh:289-349, without splitting the GEMM into per-step launches).  The push runs
+ * on a stream of the communicator's own, on overlap_sms SMs, and publishes per (source rank, expert)
+ * when that expert's rows from that source are complete; fmoe_linear_forward_overlapped /
+ * fmoe_linear_backward_overlapped, queued on `stream` right after this call and given the handle,
+ * leave overlap_sms SMs free and let each tile wait (bounded; status code 5 on expiry) only for the
+ * sources whose rows it reads.  fmoe_peer_arrival_finish, queued on `stream` after that GEMM, joins
+ * the push and closes the exchange; no other exchange of the communicator may be queued in between.
+ * Falls back, on every rank alike only if every rank passes the same overlap_sms, to the plain
+ * exchange queued whole on `stream` (arrival->comm == NULL: nothing to wait for or to finish) when
+ * global_out does not lie in the receive pool or overlap_sms is 0. */
+typedef struct {
+    fmoe_comm_t comm;      /* NULL: the exchange was queued whole, nothing is pending */
+    const void* plan;
+    void* out;
+    int64_t in_rows, out_rows, row_bytes;
+    int32_t n_expert, overlap_sms;
+    int32_t gather, use;   /* gather != 0: handle of fmoe_peer_gather_planned_async (use: which of the plan's two counter sets) */
+} fmoe_arrival_t;
+int fmoe_peer_scatter_planned_async(fmoe_comm_t comm, const void* local_in, void* global_out, const void* plan,
+                                    int64_t in_rows, int64_t out_rows, int64_t row_bytes, int32_t n_expert,
+                                    int32_t overlap_sms, fmoe_stream_t stream, fmoe_arrival_t* arrival);
+int fmoe_peer_arrival_finish(const fmoe_arrival_t* arrival, fmoe_stream_t stream);
+/* global_gather overlapped with the grouped GEMM that PRODUCES its rows.  Queue it on `stream` right
+ * BEFORE that GEMM (fmoe_linear_forward_overlapped / fmoe_linear_backward_overlapped with the handle
+ * as `departure`): the push starts on the communicator's own stream, on overlap_sms SMs, and forwards
+ * an expert's rows as soon as the GEMM's epilogue reports that expert complete (counters inside the
+ * plan; `use` 0 or 1 picks one of its two sets, so that the forward and the backward pass of a layer
+ * call do not share one).  fmoe_peer_arrival_finish with the handle, queued after the GEMM, joins the
+ * push and closes the exchange.  When it cannot overlap (local_out outside the receive pool,
+ * overlap_sms 0) it queues NOTHING and leaves departure->comm NULL: the caller then runs
+ * fmoe_peer_gather_planned after the GEMM. */
+int fmoe_peer_gather_planned_async(fmoe_comm_t comm, const void* global_in, void* local_out, const void* plan,
+                                   int64_t in_rows, int64_t out_rows, int64_t row_bytes, int32_t n_expert,
+                                   int32_t overlap_sms, int32_t use, fmoe_stream_t stream, fmoe_arrival_t* departure);
+/* fmoe_linear_forward / fmoe_linear_backward_colsum (arguments as there) beside an exchange:
+ *   arrival (may be NULL): the scatter that is still delivering x (forward) or grad_y (backward).  The
+ *     call consumes the handle: the forward closes the exchange after its product, the backward
+ *     between the input-gradient product (which waits tile by tile) and the weight- and bias-gradient
+ *     products (which need every row).  Shapes the tensor-core kernels do not take close the exchange
+ *     first and run as usual.
+ *   departure (may be NULL): the gather that forwards y (forward) or grad_x (backward) while the
+ *     product runs; the caller closes it with fmoe_peer_arrival_finish afterwards.  All products of the
+ *     call leave departure->overlap_sms SMs to the push. */
+int fmoe_linear_forward_overlapped(const void* x, const void* weight, const void* bias,
+                                   const int64_t* seg_offsets, void* y, void* pre_act, int64_t n_rows,
+                                   int64_t in_feat, int64_t out_feat, int32_t n_expert, int32_t dtype,
+                                   int32_t activation, const fmoe_arrival_t* arrival,
+                                   const fmoe_arrival_t* departure, fmoe_stream_t stream);
+int fmoe_linear_backward_overlapped(const void* grad_y, const void* x, const void* weight,
+                                    const int64_t* seg_offsets, const void* act_pre, void* grad_x,
+                                    void* grad_w, void* grad_b, void* grad_x_colsum, int64_t n_rows,
+                                    int64_t in_feat, int64_t out_feat, int32_t n_expert, int32_t dtype,
+                                    int32_t activation, int32_t accumulate, void* scratch,
+                                    const fmoe_arrival_t* arrival, const fmoe_arrival_t* departure,
+                                    fmoe_stream_t stream);
 /* The same exchanges with the reference's argument style: all_expert_count_host[W][W][E] (rows that
  * rank s routes to expert e of rank d at [s][d][e]; the table fmoe_expert_exchange gathers) and the
  * flags on the HOST.  The table is uploaded and planned on the device (a call with the same table

@@ -376,6 +376,18 @@ def check_layer_bf16(rank, world):
         # two 16-bit runs that order their (fp32) sums differently, e.g. per pipeline step
         torch.testing.assert_close(a.float(), b_.float(), rtol=2e-2, atol=8 * roundings * 2.0 ** -9 * rms(b_),
                                    msg=lambda s_: f"{name}: {s_}")
+    # the scatter's push running beside the GEMM that reads its rows: same bits
+    for sms in ("4", "16"):
+        os.environ["FMOE_B200_OVERLAP_SMS"] = sms
+        try:
+            for _ in range(2):
+                over = _run_layer(m, x)
+        finally:
+            os.environ["FMOE_B200_OVERLAP_SMS"] = "0"
+        for name, v in base.items():
+            assert torch.equal(over[name], v), f"overlapped exchange ({sms} SMs) differs in {name}"
+    from fastermoe_b200 import fmoe_cuda as fc
+    assert fc.device_status() == 0
     os.environ["FMOE_FUSE_GRAN"] = "1"
     m.enable_fuse = True
     fused = _run_layer(m, x)
@@ -420,14 +432,20 @@ def check_graph_step(rank, world):
         return out.detach().clone(), loss.detach().clone(), xi.grad.clone(), {n: p.grad.clone() for n, p in m.named_parameters()}
 
     want = [eager(x) for x in xs[1:]]
-    step = GraphedStep(m, xs[0], input_grad=True)
-    for x, (out, loss, gx, grads) in zip(xs[1:], want):
-        got_loss = step(x)
-        torch.cuda.synchronize()
-        assert torch.equal(step.output, out) and torch.equal(got_loss, loss)
-        assert torch.equal(step.input_grad, gx)
-        for n, p in m.named_parameters():
-            assert torch.equal(p.grad, grads[n]), n
+    for sms in ("0", "8"):                # without and with the pushes running beside the GEMMs (a second stream in the graph)
+        os.environ["FMOE_B200_OVERLAP_SMS"] = sms
+        try:
+            step = GraphedStep(m, xs[0], input_grad=True)
+            for x, (out, loss, gx, grads) in zip(xs[1:], want):
+                got_loss = step(x)
+                torch.cuda.synchronize()
+                assert torch.equal(step.output, out) and torch.equal(got_loss, loss)
+                assert torch.equal(step.input_grad, gx)
+                for n, p in m.named_parameters():
+                    assert torch.equal(p.grad, grads[n]), n
+        finally:
+            os.environ["FMOE_B200_OVERLAP_SMS"] = "0"
+        del step
     from fastermoe_b200 import fmoe_cuda as fc
     assert fc.device_status() == 0
     dist.barrier()
