@@ -573,26 +573,33 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             const int my_col = cta * B_COLS;  // this CTA's share of the tile's B columns (pairs)
             const bool arriving = MODE != MODE_WGRAD && p.arr_flags != nullptr;
             unsigned long long epoch = 0;
-            int seen_e = -1;
+            int seen_e = -1, next_e = -1;
             bool seen = false;                // this lane's source has delivered its rows of expert seen_e
+            unsigned long long next_val = 0;  // its flag for expert next_e, read ahead of need
             if (arriving) epoch = __ldcg(p.arr_seq) + 1;
             for (int tile = first_tile; tile < total_tiles && ok; tile += tile_step) {
                 Tile t;
                 locate<MODE, TILE_M>(sh, p, tile, e_cur, t);
                 if (arriving && t.chunks > 0) {
-                    if (t.e != seen_e) { seen_e = t.e; seen = false; }
+                    const unsigned long long* my_flags = p.arr_flags + ((size_t)(epoch & 1) * 64 + lane) * 256;
+                    // the flag of the expert that comes next was read while the previous tile was being loaded
+                    if (t.e != seen_e) { seen = next_e == t.e && next_val >= epoch; seen_e = t.e; }
                     const int r_lo = t.row0 + my_row, r_hi = min(t.row0 + t.rows, r_lo + BM);
                     bool good = true;
                     if (lane < p.arr_world && !seen && r_hi > r_lo) {
                         const int b0 = p.arr_src_off[t.e * p.arr_world + lane], b1 = p.arr_src_off[t.e * p.arr_world + lane + 1];
                         if (b1 > b0 && b0 < r_hi && b1 > r_lo) {
-                            good = arrival_wait(p.arr_flags + ((size_t)(epoch & 1) * 64 + lane) * 256 + t.e, epoch, sh, p.status);
+                            good = arrival_wait(my_flags + t.e, epoch, sh, p.status);
                             seen = good;
                         }
                     }
                     good = __all_sync(0xffffffffu, good);
                     if (!good) { ok = false; break; }
                     asm volatile("fence.proxy.async.global;" ::: "memory");   // rows written through the generic proxy, read by TMA
+                    if (lane < p.arr_world && t.e + 1 < p.n_expert) {
+                        asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(next_val) : "l"(my_flags + t.e + 1) : "memory");
+                        next_e = t.e + 1;
+                    }
                 }
                 if (lane == 0)
                 for (int ch = 0; ch < t.chunks; ++ch) {

@@ -91,9 +91,11 @@ enum { LIST_PUSH_FWD = 0, LIST_PULL_FWD = 1, LIST_PUSH_BWD = 2, LIST_PULL_BWD = 
 // ---- the plan as it lies in device memory -------------------------------------------------------
 // Built by peer_plan_kernel, read by the exchange kernels (and, through own_offsets, by the
 // grouped GEMM).  S = (2W-1)*E segment slots per list: (W-1)*E for rows kept local because their
-// expert is shadowed here, E for rows of this rank's own experts, (W-1)*E for rows to/from peers
-// (expert-major, peers in the order rank+1, rank+2, ... so that ranks working in step store into
-// different GPUs).  Slots without rows stay in the lists with rows = 0.
+// expert is shadowed here, then E groups of W slots, group i = local expert index i: first the rows
+// of this rank's own expert i (they stay here), then the rows exchanged with the peers rank+1,
+// rank+2, ... for their / this rank's expert i.  Expert-major order lets a consumer start on expert 0
+// while later experts are still on their way; the ring order of the peers lets ranks that work in
+// step store into different GPUs.  Slots without rows stay in the lists with rows = 0.
 struct PlanHead {
     int32_t n_expert, n_workers, rank, n_slots;
     int32_t overflow, pad0;
@@ -300,14 +302,14 @@ peer_plan_kernel(const __grid_constant__ PeerBases b, const __grid_constant__ Pl
             ex = my_lay[lay_pos_shadow(r, E, W, idx)];
             rows_pf = rows_pb = stored[idx] ? mine[idx] : 0;
             src_pb = ex; dst_pb = tok;
-        } else if (s < W * E) {                     // rows for this rank's own experts
-            const int i = s - (W - 1) * E, idx = r * E + i;
+        } else if ((s - (W - 1) * E) % W == 0) {    // rows for this rank's own expert i
+            const int i = (s - (W - 1) * E) / W, idx = r * E + i;
             tok = my_eptr[idx];
             ex = my_lay[lay_pos_recv(r, E, W, i, r)];
             rows_pf = rows_pb = mine[idx];
             src_pb = ex; dst_pb = tok;
         } else {                                    // rows exchanged with peer p for expert i (of p outbound, of r inbound)
-            const int q = s - W * E, i = q / (W - 1), dlt = q % (W - 1) + 1, p = (r + dlt) % W;
+            const int q = s - (W - 1) * E, i = q / W, dlt = q % W, p = (r + dlt) % W;
             sel = p;
             const int out_idx = p * E + i;          // my rows for expert i of rank p
             const int64_t out_rows = stored[out_idx] ? 0 : mine[out_idx];
@@ -535,10 +537,8 @@ __device__ __forceinline__ void copy_rows(const uint4* __restrict__ s, uint4* __
 
 __device__ __forceinline__ void publish_segment(const PeerBases& b, const MoveArgs& a, int W, int E, int s, int parity,
                                                 unsigned long long epoch) {
-    int p, i;
     if (s < (W - 1) * E) return;                                  // rows kept for shadowed experts: not used in this mode
-    if (s < W * E) { p = a.rank; i = s - (W - 1) * E; }
-    else { const int q = s - W * E; i = q / (W - 1); p = (a.rank + q % (W - 1) + 1) % W; }
+    const int q = s - (W - 1) * E, i = q / W, p = (a.rank + q % W) % W;
     if (i >= kArrivalExperts) return;
     unsigned long long* flag = (unsigned long long*)(b.base[p] + kExpArrOff) + ((size_t)parity * kMaxPeers + a.rank) * kArrivalExperts + i;
     st_release_sys(flag, epoch);
@@ -608,47 +608,123 @@ peer_push_overlap_kernel(const __grid_constant__ PeerBases b, const __grid_const
     if (!kGather && room && blockIdx.x == 0)          // nothing will ever be stored for these: their consumers need not wait
         for (int s = (W - 1) * E + threadIdx.x; s < d.S; s += kPushThreads)
             if (s_prefix[s + 1] == s_prefix[s]) publish_segment(b, a, W, E, s, parity, epoch);
-    const int lane = threadIdx.x & 31;
-    const int n_units = (total + kUnitRows - 1) / kUnitRows;
-    int done_expert = -1;                             // kGather: the expert this warp saw complete last
-    bool gave_up = false;
-    for (int u = blockIdx.x * kPushWarps + (threadIdx.x >> 5); u < n_units; u += gridDim.x * kPushWarps) {
-        int row = u * kUnitRows;
-        const int row_end = min(row + kUnitRows, total);
-        int k = find_seg(s_prefix, d.S, row);
-        while (row < row_end) {
-            const int n = min(row_end, s_prefix[k + 1]) - row;
-            const int sel = L.sel[k];
-            bool dead = sel != kLocal && ((s_dead >> sel) & 1ull);
-            if (kGather && k >= (W - 1) * E) {
-                const int i = k < W * E ? k - (W - 1) * E : (k - W * E) / (W - 1);
-                if (i != done_expert && !gave_up) {
-                    int ok = 1;
-                    if (lane == 0) ok = wait_expert_done(a, i) ? 1 : 0;
-                    ok = __shfl_sync(0xffffffffu, ok, 0);
-                    if (ok) done_expert = i;
-                    else { gave_up = true; if (lane == 0) atomicOr(a.status, 32); }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    // Units of rows are dealt to the moving warps round-robin, so at any time all of them work on one
+    // stretch of the list; a stretch should be about one expert's rows, so that experts complete one
+    // after the other.
+    //   gather:  all 32 warps of a block move rows; nothing is published per segment.
+    //   scatter: warps 0..30 move rows and never wait for their stores; warp 31 publishes.  A mover that
+    //     has issued the stores of its unit of round r bumps the round's counter in shared memory.  The
+    //     publisher takes all rounds that every mover has finished, issues ONE system fence for them --
+    //     their stores are ordered before it through the counters, and the fence is cumulative --
+    //     books their rows per segment and raises the flags of the segments that are complete.  The
+    //     fence waits for the stores in flight (10+ microseconds on a busy link), but only the
+    //     publisher waits: the movers may run kRing rounds ahead of what it has taken.
+    constexpr int kMovers = kGather ? kPushWarps : kPushWarps - 1;
+    constexpr int kRing = 16;
+    __shared__ int s_issued[kRing];                   // movers that have finished round r (slot r % kRing)
+    __shared__ int s_taken;                           // rounds the publisher has taken
+    if (threadIdx.x < kRing) s_issued[threadIdx.x] = 0;
+    if (threadIdx.x == 0) s_taken = 0;
+    __syncthreads();
+    const int movers_total = (int)gridDim.x * kMovers;
+    const int unit_rows = max(4, min(kUnitRows, total / max(1, E * movers_total)));
+    const int n_units = (total + unit_rows - 1) / unit_rows;
+    const int n_rounds = (n_units + movers_total - 1) / movers_total;
+    if (kGather || warp < kMovers) {
+        int done_expert = -1;                             // kGather: the expert this warp saw complete last
+        bool gave_up = false;
+        for (int r = 0; r < n_rounds; ++r) {
+            if (!kGather && r >= kRing) {                 // the ring slot of round r must have been taken
+                if (lane == 0) {
+                    unsigned spins = 0;
+                    while (*(volatile int*)&s_taken + kRing <= r) {
+                        __nanosleep(100);
+                        if (++spins > (1u << 24)) { atomicOr(a.status, 32); break; }    // never seen: do not hang
+                    }
                 }
-                dead = dead || gave_up;               // rows that were never produced are not forwarded
+                __syncwarp();
             }
-            if (!dead) {
-                const uint4* s = src + (int64_t)(L.src[k] + (row - s_prefix[k])) * row_vecs;
-                uint4* dptr = (sel == kLocal ? out : (uint4*)(b.base[sel] + s_dest[sel])) + (int64_t)(L.dst[k] + (row - s_prefix[k])) * row_vecs;
-                copy_rows(s, dptr, n, row_vecs, lane);
+            const int u = r * movers_total + (int)blockIdx.x * kMovers + warp;
+            int row = u * unit_rows;
+            const int row_end = u < n_units ? min(row + unit_rows, total) : row;
+            int k = row < row_end ? find_seg(s_prefix, d.S, row) : 0;
+            while (row < row_end) {
+                const int n = min(row_end, s_prefix[k + 1]) - row;
+                const int sel = L.sel[k];
+                bool dead = sel != kLocal && ((s_dead >> sel) & 1ull);
+                if (kGather && k >= (W - 1) * E) {
+                    const int i = (k - (W - 1) * E) / W;
+                    if (i != done_expert && !gave_up) {
+                        int ok = 1;
+                        if (lane == 0) ok = wait_expert_done(a, i) ? 1 : 0;
+                        ok = __shfl_sync(0xffffffffu, ok, 0);
+                        if (ok) done_expert = i;
+                        else { gave_up = true; if (lane == 0) atomicOr(a.status, 32); }
+                    }
+                    dead = dead || gave_up;               // rows that were never produced are not forwarded
+                }
+                if (!dead) {
+                    const uint4* sp = src + (int64_t)(L.src[k] + (row - s_prefix[k])) * row_vecs;
+                    uint4* dptr = (sel == kLocal ? out : (uint4*)(b.base[sel] + s_dest[sel])) + (int64_t)(L.dst[k] + (row - s_prefix[k])) * row_vecs;
+                    copy_rows(sp, dptr, n, row_vecs, lane);
+                }
+                row += n;
+                ++k;
+                while (k < d.S && s_prefix[k + 1] == s_prefix[k]) ++k;
+            }
+            if (!kGather) {
+                __syncwarp();
+                if (lane == 0) { __threadfence_block(); atomicAdd(&s_issued[r % kRing], 1); }
+            }
+        }
+    } else {
+        int next = 0;
+        unsigned idle = 0;
+        while (next < n_rounds) {
+            if (idle > (1u << 24)) { if (lane == 0) atomicOr(a.status, 32); break; }            // never seen: do not hang
+            // rounds [next, hi) have been finished by every mover (rounds complete in order per mover, so a
+            // full counter of round r implies nothing about r+1: check them one by one)
+            int hi = next;
+            if (lane == 0) {
+                while (hi < n_rounds && hi < next + kRing && *(volatile int*)&s_issued[hi % kRing] == kMovers) ++hi;
+                if (hi == next) __nanosleep(200);
+            }
+            hi = __shfl_sync(0xffffffffu, hi, 0);
+            if (hi == next) { ++idle; continue; }
+            idle = 0;
+            __threadfence_block();
+            __threadfence_system();
+            // lanes book the units of the taken rounds
+            for (int idx = lane; idx < (hi - next) * kMovers; idx += 32) {
+                const int r = next + idx / kMovers, w = idx % kMovers;
+                const int u = r * movers_total + (int)blockIdx.x * kMovers + w;
+                if (u >= n_units) continue;
+                int row = u * unit_rows;
+                const int row_end = min(row + unit_rows, total);
+                int k = find_seg(s_prefix, d.S, row);
+                while (row < row_end) {
+                    const int n = min(row_end, s_prefix[k + 1]) - row;
+                    const int sel = L.sel[k];
+                    const bool dead = sel != kLocal && ((s_dead >> sel) & 1ull);
+                    const int before = atomicAdd(seg_done + k, n);
+                    if (before + n == s_prefix[k + 1] - s_prefix[k] && !dead) {
+                        __threadfence_system();       // the other blocks' shares of the segment were fenced before they were booked
+                        publish_segment(b, a, W, E, k, parity, epoch);
+                    }
+                    row += n;
+                    ++k;
+                    while (k < d.S && s_prefix[k + 1] == s_prefix[k]) ++k;
+                }
             }
             __syncwarp();
-            if (!kGather && lane == 0) {
-                // the warp's stores are ordered before this fence by the barrier above; the fence is cumulative
-                __threadfence_system();
-                const int before = atomicAdd(seg_done + k, n);
-                if (before + n == s_prefix[k + 1] - s_prefix[k] && !dead) {
-                    __threadfence_system();
-                    publish_segment(b, a, W, E, k, parity, epoch);
-                }
+            if (lane == 0) {
+                for (int r = next; r < hi; ++r) s_issued[r % kRing] = 0;
+                __threadfence_block();
+                *(volatile int*)&s_taken = hi;
             }
-            row += n;
-            ++k;
-            while (k < d.S && s_prefix[k + 1] == s_prefix[k]) ++k;
+            __syncwarp();
+            next = hi;
         }
     }
     __syncthreads();
@@ -910,15 +986,15 @@ int plan_peer(const int64_t* table, const uint8_t* stored, int r, int E, int W, 
             const int64_t tok = eptr[r][idx], ex = lay[r].shadow[idx];
             push.push_back(reverse ? Seg{kLocal, ex, tok, mine[idx]} : Seg{kLocal, tok, ex, mine[idx]});
         }
+    // Expert-major: the rows of this rank's own expert i, then the peers in the order r+1, r+2, ...:
+    // ranks that work in step store into different GPUs at any moment, and every receiver's
+    // experts fill up in ascending order.
     for (int i = 0; i < E; ++i) {
-        const int64_t ex = lay[r].off[i + r * E];
-        if (ex < 0) continue;
-        const int64_t tok = eptr[r][r * E + i], rows = mine[r * E + i];
-        push.push_back(reverse ? Seg{kLocal, ex, tok, rows} : Seg{kLocal, tok, ex, rows});
-    }
-    // Expert-major, peers in the order r+1, r+2, ...: ranks that work in step store into
-    // different GPUs at any moment, and a receiver's experts fill up in ascending order.
-    for (int i = 0; i < E; ++i)
+        const int64_t own_ex = lay[r].off[i + r * E];
+        if (own_ex >= 0) {
+            const int64_t tok = eptr[r][r * E + i], rows = mine[r * E + i];
+            push.push_back(reverse ? Seg{kLocal, own_ex, tok, rows} : Seg{kLocal, tok, own_ex, rows});
+        }
         for (int dlt = 1; dlt < W; ++dlt) {
             const int p = (r + dlt) % W;
             // rows this rank routes to expert i of rank p
@@ -936,6 +1012,7 @@ int plan_peer(const int64_t* table, const uint8_t* stored, int r, int E, int W, 
                 else push.push_back({p, ex, tok, in_rows_pi});             // to p's token-side layout
             }
         }
+    }
     return 0;
 }
 
