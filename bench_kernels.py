@@ -7,7 +7,7 @@ bench.py reports the layer; this script times each CUDA kernel family alone
 (CUDA events on the launching stream, L2 flushed between repetitions by writing a
 256 MiB buffer) and divides its algorithmic bytes / flops by the time:
 
-* routing kernels at the BASELINE config-2 size (32768 gate entries, launch-latency
+* routing kernels at the benchmark layer's size (32768 gate entries, launch-latency
   bound) and at a scaled synthetic size (2^24 entries, 16 experts) where HBM
   throughput is meaningful;
 * token permutation kernels at config-2 sizes (16384 tokens, top-2, d_model 1024, bf16);

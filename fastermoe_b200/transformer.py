@@ -60,33 +60,42 @@ def _gen_policy(alpha, constants=None):
     bw_net, bw_mm, data_size = c["bw_net"], c["bw_mm"], c["data_size"]
 
     def _global_policy(all_experts_count, all_global_expert_count, num_expert, world_size, d_model, fused):
-        aec, agec = all_experts_count, all_global_expert_count
+        # The reference evaluates this with a few dozen torch operators on tiny CPU tensors per call
+        # (several hundred microseconds at 8 workers, twice per layer call when the gate consults it
+        # too).  Same arithmetic here on numpy scalars, in float32 where torch computes in float32
+        # (int64 tensor x Python float); torch.sort gives the order so that ties break as there.
+        import numpy as np
+        f32 = np.float32
+        agec = all_global_expert_count.detach().cpu().numpy().astype(np.int64)
         if fused:
-            aec = aec.sum(dim=-1).view(world_size, world_size, 1)
-            agec = agec.sum(dim=-1).view(world_size, world_size, 1)
-        load = agec.sum(1).clone()  # [W, E or 1]: rows each worker's experts process
-        order = load.sort(0, descending=True)[1]
+            agec = agec.sum(-1).reshape(world_size, world_size, 1)
+        if agec.shape[2] != 1:
+            raise RuntimeError("the shadowing policy works at whole-worker granularity (fused experts) only")
+        recv = agec[:, :, 0]                                   # [worker, source]: rows worker's experts get from source
+        load = recv.sum(1)                                     # rows each worker's experts process
+        order = torch.from_numpy(load.reshape(world_size, 1).copy()).sort(0, descending=True)[1][:, 0].numpy()
 
         unit = alpha * d_model ** 2 * data_size
-        busiest = load.max(0)[0]
-        lat_plain = 3 * 4 * busiest * unit / bw_mm + 4 * busiest * d_model * data_size / bw_net
+        busiest = int(load.max())
+        lat_plain = f32(f32(f32(12 * busiest) * f32(unit)) / f32(bw_mm)) + f32(f32(4 * busiest * d_model * data_size) / f32(bw_net))
         model_cost = 2 * unit * num_expert / bw_net * 2
         comp_time = 12 * unit / bw_mm
 
-        best = float("+inf")
+        best = f32(np.inf)
+        load = load.copy()
         i = 0
         for i, index in enumerate(order):
             # Shadowing worker `index`: its rows are computed where they originate.
             load[index] = 0
-            load += agec[index].view(world_size, -1)
-            lat = load.max(0)[0] * comp_time + (i + 1) * model_cost
+            load += recv[index]
+            lat = f32(f32(f32(int(load.max())) * f32(comp_time)) + f32((i + 1) * model_cost))
             if lat < best:
                 best = lat
             elif lat > best:
                 break
-        res = aec.new_zeros(world_size, num_expert, dtype=torch.bool)
+        res = torch.zeros(world_size, num_expert, dtype=torch.bool)
         if lat_plain > best:
-            res[order[:i]] = True
+            res[torch.from_numpy(order[:i].astype(np.int64))] = True
         return res
 
     def _no_policy(all_experts_count, all_global_expert_count, num_expert, world_size, d_model, fused):

@@ -355,7 +355,7 @@ def hir_gate(x, weight, bias, n_expert, world_size, node_rank, stored, nw_per_no
 
 
 # ---------------------------------------------------------------------------
-# Synthetic workloads (BASELINE configurations)
+# Synthetic workloads
 # ---------------------------------------------------------------------------
 
 
@@ -365,7 +365,7 @@ def uniform_fan_in(shape, fan_in, gen):
 
 
 def make_layer_inputs(tokens, d_model, d_hidden, n_expert_total, seed, gate_std=None, gate_bias=None):
-    """Seeded synthetic tensors with the BASELINE value distributions: x ~ N(0,1);
+    """Seeded synthetic tensors with the benchmark workloads' value distributions: x ~ N(0,1);
     expert weights/biases U(+-1/sqrt(fan_in)); gate weight U(+-1/sqrt(d)) or
     N(0, gate_std) with zero (or given) bias."""
     g = torch.Generator().manual_seed(seed)

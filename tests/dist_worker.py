@@ -521,8 +521,8 @@ def check_config5(rank, world):
 # ------------------------------------------------------------------ CPU / gloo
 
 def gpu_full_size(rank, world, port):
-    """BASELINE configurations 3 and 4 at their per-GPU sizes (the 8-GPU runs shard the same work per
-    GPU), checked through properties that need no CPU oracle of that size: the exchange over peer
+    """The Zipf-routed (4 experts, d 2048, h 8192) and the one-expert (d 4096, h 16384) workloads at their
+    per-GPU sizes, checked through properties that need no CPU oracle of that size: the exchange over peer
     memory and over NCCL give bit-identical layers; the smart schedule equals the plain schedule
     within bf16 rounding; gradients are finite; no bounded wait expired."""
     init(rank, world, port, "nccl")
@@ -559,10 +559,12 @@ def gpu_full_size(rank, world, port):
         def without_table(self, lec, gec, stored, fwd_batch_size, world_size, table=None):
             plain_exchange(self, lec, gec, stored, fwd_batch_size, world_size, table=None)
         F.Exchange.__init__ = without_table
+        os.environ["FMOE_B200_NOSYNC"] = "0"          # counts read back, rows over NCCL send/receive
         try:
             nccl = _run_layer(m, x)
         finally:
             F.Exchange.__init__ = plain_exchange
+            os.environ["FMOE_B200_NOSYNC"] = "1"
         for name, v in peer.items():
             assert torch.equal(nccl[name], v), f"config 3: peer-memory and NCCL exchange differ in {name}"
     for name, v in peer.items():

@@ -50,7 +50,7 @@ def test_expert_parallel(fn):
 
 
 def test_full_size_configs():
-    """Per-GPU sizes of BASELINE configurations 3 and 4, on 2 GPUs (property checks)."""
+    """Per-GPU sizes of the Zipf-routed and the one-expert-per-GPU workloads, on 2 GPUs (property checks)."""
     needs_gpus()
     run_ranks(dist_worker.gpu_full_size, 2, limit_s=400)
 

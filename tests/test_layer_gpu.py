@@ -55,7 +55,7 @@ def test_state_dict_keys_match_reference_names():
 
 
 def test_cpu_baseline_config_fp32():
-    """BASELINE config 1 (2048 tokens, d 512, h 2048, 4 experts, top-2, fp32, GELU, seed 0)."""
+    """The CPU-runnable workload: 2048 tokens, d 512, h 2048, 4 experts, top-2, fp32, GELU, seed 0."""
     T, d, h, E, k = 2048, 512, 2048, 4, 2
     tens = O.make_layer_inputs(T, d, h, E, seed=0)
     want = O.moe_layer_fwd_bwd(tens["x"], tens["gate_w"], tens["gate_b"], tens["w1"], tens["b1"], tens["w2"],
@@ -80,7 +80,7 @@ def test_cpu_baseline_config_fp32():
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("softmax_scores", [False, True])
 def test_bf16_layer_against_fp32_oracle(dtype, softmax_scores):
-    """Scaled-down BASELINE config 2 (bf16, near-uniform routing): rtol 2e-2 against fp32."""
+    """The benchmark layer scaled down (bf16, near-uniform routing): rtol 2e-2 against fp32."""
     T, d, h, E, k = 1024, 256, 1024, 16, 2
     tens = O.make_layer_inputs(T, d, h, E, seed=1, gate_std=0.02)
     m = build_layer(E, d, h, k, "gelu", tens, dtype=dtype, softmax_scores=softmax_scores)

@@ -181,3 +181,40 @@ def test_oracle_matches_reference_linear(routing_golden):
         np.testing.assert_allclose((gy[sl].t() @ x[sl]).numpy(), z["linear/gw"][e], rtol=1e-5, atol=1e-5)
         np.testing.assert_allclose(gy[sl].sum(0).numpy(), z["linear/gb"][e], rtol=1e-5, atol=1e-5)
         p += c
+
+
+def test_policy_matches_the_reference_implementation_on_random_tables():
+    """The product's host-side policy against the reference's own _gen_policy (the staged copy of its
+    Python package), on random count tables: balanced, skewed, tiny and large worlds."""
+    import types
+    from oracle import stage_reference
+    if stage_reference.staged() is None and stage_reference.stage() is None:
+        pytest.skip("no staged copy of the reference's Python package")
+    import sys
+    saved = {n: m for n, m in sys.modules.items() if n == "fmoe_cuda" or n == "fmoe" or n.startswith("fmoe.")}
+    os.environ["FMOE_ENABLE_DYNREP"] = "1"
+    try:
+        stage_reference.import_reference(types.ModuleType("fmoe_cuda"))
+        from fmoe.transformer import _gen_policy as ref_gen
+        from fastermoe_b200.transformer import _gen_policy
+        rng = np.random.default_rng(11)
+        n_shadow = 0
+        for trial in range(300):
+            W = int(rng.choice([2, 3, 4, 8, 16]))
+            E = int(rng.choice([1, 2, 4]))
+            d_model = int(rng.choice([64, 256, 1024, 4096]))
+            alpha = float(rng.choice([2.0, 4.0]))
+            p = rng.dirichlet(np.full(W * E, float(rng.choice([0.05, 0.3, 5.0]))))
+            table = np.stack([rng.multinomial(int(rng.choice([64, 4096, 65536])), p).reshape(W, E) for _ in range(W)]).astype(np.int64)
+            aec = t(table).long()
+            agec = aec.transpose(0, 1).contiguous()
+            want = ref_gen(alpha)(aec.clone(), agec.clone(), E, W, d_model, True)
+            got = _gen_policy(alpha, constants="reference")(aec, agec, E, W, d_model, True)
+            assert torch.equal(got, want), (trial, W, E, d_model, alpha, table.tolist())
+            n_shadow += int(want.any())
+        assert 20 < n_shadow < 280, n_shadow           # both outcomes are exercised
+    finally:
+        os.environ["FMOE_ENABLE_DYNREP"] = "0"
+        for n in [n for n in sys.modules if n == "fmoe_cuda" or n == "fmoe" or n.startswith("fmoe.")]:
+            del sys.modules[n]
+        sys.modules.update(saved)

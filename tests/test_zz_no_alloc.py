@@ -57,6 +57,42 @@ def test_static_scratch_matches_caller_scratch_twice():
         assert int(ref[1][-1]) == int((g >= 0).sum())
 
 
+def test_static_calls_queued_back_to_back_and_edge_sizes():
+    """Calls that follow each other on one stream need no host synchronisation between them and
+    nothing cleared: three calls with different sizes and expert counts (more than 256 experts makes
+    the tile scan run several passes; n = 0 reads nothing) are queued without a sync, then every
+    output is compared with fmoe_count_and_pos and with the oracle."""
+    from fastermoe_b200 import _lib
+    from oracle import moe_oracle as O
+    lib = _lib.lib
+    rng = np.random.default_rng(1)
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    cases = [(200000, 8), (0, 5), (20000, 300), (777, 1)]
+    assert all(lib.fmoe_routing_scratch_bytes(n, e) <= lib.fmoe_static_scratch_capacity() for n, e in cases)
+    gates, outs = [], []
+    for n, n_expert in cases:                               # queued back to back, no sync in between
+        g = rng.integers(-1, n_expert, size=n)
+        gate = torch.from_numpy(g).cuda()
+        lec = torch.full((n_expert,), -5, dtype=torch.int64, device="cuda")
+        off = torch.full((n_expert + 1,), -5, dtype=torch.int64, device="cuda")
+        pos = torch.full((max(n, 1),), -5, dtype=torch.int64, device="cuda")
+        inv = torch.full((max(n, 1),), -5, dtype=torch.int64, device="cuda")
+        assert lib.fmoe_count_and_pos_static(_ptr(gate), n, n_expert, _ptr(lec), _ptr(off), _ptr(pos), _ptr(inv), stream) == 0
+        gates.append((g, gate))
+        outs.append((lec, off, pos, inv))
+    torch.cuda.synchronize()
+    for (n, n_expert), (g, gate), (lec, off, pos, inv) in zip(cases, gates, outs):
+        cnt = O.expert_count(g, n_expert)
+        want_pos = O.assign_pos(g, n_expert)
+        assert np.array_equal(lec.cpu().numpy(), cnt), (n, n_expert)
+        assert np.array_equal(off.cpu().numpy(), np.concatenate([[0], np.cumsum(cnt)])), (n, n_expert)
+        assert np.array_equal(pos.cpu().numpy()[:len(want_pos)], want_pos), (n, n_expert)
+        if n:
+            assert np.array_equal(inv.cpu().numpy(), O.inverse_pos(want_pos, n)), (n, n_expert)
+            ref, _ = _both(lib, gate, n_expert)
+            assert torch.equal(ref[2], pos) and torch.equal(ref[3], inv)
+
+
 def test_static_scratch_rejects_oversized_requests():
     from fastermoe_b200 import _lib
     lib = _lib.lib
