@@ -587,7 +587,7 @@ def gate_topk(logits, k):
         lead = logits.shape[:-1]
         val, idx = GateTopK.apply(logits.reshape(-1, logits.shape[-1]), k)
         return val.reshape(*lead, k), idx.reshape(*lead, k)
-    return torch.topk(logits, k=k, dim=-1, largest=True, sorted=False)      # CPU tensors: module set-up and tests only
+    return torch.topk(logits, k=k, dim=-1, largest=True, sorted=True)       # CPU tensors: module set-up and tests only
 
 
 class Slice(Function):

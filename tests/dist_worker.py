@@ -671,3 +671,22 @@ def cpu_grouped_ddp(rank, world, port):
     torch.testing.assert_close(net[0].weight.grad, sum(gs) / world)
     assert torch.equal(net[1].weight.grad, g_none)
     finish("gloo")
+
+
+def cpu_slice_allgather(rank, world, port):
+    """Slice / AllGather over a model-parallel group (fmoe/functions.py:333-375): the forward of one is
+    the backward of the other."""
+    init(rank, world, port, "gloo")
+    from fastermoe_b200.functions import AllGather, Slice
+    group = dist.group.WORLD
+    rows = 3
+    x = torch.arange(world * rows * 4, dtype=torch.float32).view(world * rows, 4).requires_grad_(True)   # the same on every rank
+    mine = Slice.apply(x, rank, world, group)
+    assert torch.equal(mine, x.detach()[rank * rows:(rank + 1) * rows])
+    full = AllGather.apply(mine * (rank + 1), rank, world, group)
+    want = torch.cat([x.detach()[r * rows:(r + 1) * rows] * (r + 1) for r in range(world)])
+    assert torch.equal(full.detach(), want)
+    full.sum().backward()
+    # AllGather.backward keeps this rank's slice of the gradient, Slice.backward gathers the slices
+    assert torch.equal(x.grad, torch.cat([torch.full((rows, 4), float(r + 1)) for r in range(world)]))
+    finish("gloo")

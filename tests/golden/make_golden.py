@@ -16,6 +16,7 @@ recorded is computed by the reference's unmodified Python:
 * _local_scatter / _local_gather         fmoe/functions.py:72-84
 * _gen_policy -> _global_policy          fmoe/transformer.py:33-86
 * HirGate.forward                        fmoe/gates/hir_gate.py:36-116
+* NoisyGate.forward (+ its loss)         fmoe/gates/noisy_gate.py:108-144
 """
 import os
 import sys
@@ -175,6 +176,35 @@ def hir_case(tag, bias_to, seed, policy_on):
 hir_case("few_leaving", 2, 11, False)      # bias towards an on-node expert -> plain top-2
 hir_case("many_leaving", 12, 12, False)    # bias towards an off-node expert -> limited
 hir_case("uniform", None, 13, True)
+
+# NoisyGate in training mode with a recorded noise sample (fmoe/gates/noisy_gate.py:108-144).
+def noisy_case(tag, T, d, E, k, seed):
+    from fmoe.gates.noisy_gate import NoisyGate
+    g = torch.Generator().manual_seed(seed)
+    gate = NoisyGate(d, E, 1, top_k=k)
+    with torch.no_grad():
+        gate.w_gate.copy_(torch.randn(d, E, generator=g) * 0.3)
+        gate.w_noise.copy_(torch.randn(d, E, generator=g) * 0.3)
+    gate.train()
+    x = torch.randn(T, d, generator=g).requires_grad_(True)
+    noise = torch.randn(T, E, generator=g)
+    real = torch.randn_like
+    torch.randn_like = lambda t, *a, **kw: noise.clone()
+    try:
+        idx, score = gate(x)
+    finally:
+        torch.randn_like = real
+    loss = gate.get_loss()
+    (score.sum() * 0.5 + loss).backward()
+    for name, t in dict(x=x, w_gate=gate.w_gate, w_noise=gate.w_noise, noise=noise, idx=idx, score=score, loss=loss,
+                        grad_x=x.grad, grad_w_gate=gate.w_gate.grad, grad_w_noise=gate.w_noise.grad).items():
+        out[f"noisy/{tag}/{name}"] = t.detach().numpy()
+    out[f"noisy/{tag}/meta"] = np.array([T, d, E, k])
+
+
+noisy_case("e8_k2", 64, 16, 8, 2, 21)
+noisy_case("e4_k3", 32, 8, 4, 3, 22)
+noisy_case("e2_k2", 16, 8, 2, 2, 23)        # top_k == number of experts: the load is the count of non-zero gates
 
 np.savez_compressed(os.path.join(HERE, "reference_cpu.npz"), **out)
 print("wrote", len(out), "arrays")

@@ -20,3 +20,8 @@ def test_exchange_plan_over_gloo(world):
 
 def test_grouped_data_parallel_over_gloo():
     mp.spawn(dist_worker.cpu_grouped_ddp, args=(2, free_port()), nprocs=2, join=True)
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_slice_and_allgather_over_gloo(world):
+    mp.spawn(dist_worker.cpu_slice_allgather, args=(world, free_port()), nprocs=world, join=True)
