@@ -60,6 +60,9 @@ constexpr int kArrivalExperts = 256;
 int arrival_wait_of(const fmoe_arrival_t* arrival, ArrivalWait* w);
 // The completion counters (GemmDone in gemm.h) of an overlapped gather's handle; nulls when it is not pending.
 int done_words_of(const fmoe_arrival_t* departure, int** done, int** expected, int** ready, int* reserve_sms);
+// Fills the remote-output description of a fused gather's handle (gather == 2); enabled = 0 otherwise.
+struct GemmRemoteOut;
+int remote_out_of(const fmoe_arrival_t* departure, GemmRemoteOut* ro);
 
 // Device address of the status word that bounded waits raise (per device).
 int* device_status_ptr();

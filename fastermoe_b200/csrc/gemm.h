@@ -56,6 +56,26 @@ struct GemmDone {
     int reserve_sms;
 };
 
+// Output rows that go straight to the GPUs that own the tokens (the global_gather that would follow
+// the product, done by the product's own epilogue with plain stores into peer memory): row r of
+// this GPU's expert-side order belongs to block (expert i, source j), src_off[i*W+j] <= r <
+// src_off[i*W+j+1], and lands at row dst_off[i*W+j] + (r - src_off[i*W+j]) of rank j's buffer, which
+// starts at base[j] + the offset rank j announced for this epoch in this GPU's header.
+constexpr int kRemoteMaxWorld = 32;
+struct GemmRemoteOut {
+    char* base[kRemoteMaxWorld];       // landing areas of all ranks as mapped here (own one at [rank])
+    const unsigned long long* header;  // this GPU's header: flag arrays at the byte offsets below, [2][stride] u64 each
+    const unsigned long long* seq;     // epoch word: this exchange is epoch *seq + 1
+    const int* src_off;                // [n_expert * world + 1]
+    const int* dst_off;                // [n_expert * world]
+    unsigned int* counter;             // zero before the launch: CTAs that have finished
+    unsigned long long my_dest;        // where this GPU receives (byte offset in its own area)
+    unsigned long long timeout_cycles;
+    int arrived_at, ann_at, dest_at, stride;   // header layout
+    int world, rank;
+    int enabled;
+};
+
 struct LinearArgs {
     const void* x;       // [n_rows, in_feat]
     const void* weight;  // [n_expert, out_feat, in_feat]
@@ -68,6 +88,7 @@ struct LinearArgs {
     const HostSegs* host_segs = nullptr;  // when set, replaces seg_offsets
     const GemmArrival* arrival = nullptr;  // x is still being filled by an exchange
     const GemmDone* done = nullptr;        // y is forwarded expert by expert while the product runs
+    const GemmRemoteOut* remote = nullptr; // y is not stored here at all: its rows go to their owners
 };
 
 struct LinearBwdArgs {
@@ -92,6 +113,7 @@ struct LinearBwdArgs {
     int (*after_input_grad)(void*) = nullptr;
     void* after_ctx = nullptr;
     const GemmDone* done = nullptr;        // grad_x is forwarded expert by expert while its product runs
+    const GemmRemoteOut* remote = nullptr; // grad_x is not stored here at all: its rows go to their owners
 };
 
 int simt_linear_forward(const LinearArgs& a, cudaStream_t st);

@@ -105,6 +105,7 @@ struct Shared {
     int cum_tiles[MAX_EXPERTS_TC + 1];
     int blk_base[MAX_EXPERTS_TC + 1];  // DGRAD with column sums: 32-row blocks before each expert
     int seg_lo[MAX_EXPERTS_TC], seg_hi[MAX_EXPERTS_TC];
+    unsigned long long rem_dest[kRemoteMaxWorld];   // remote output: where each rank receives (0: it never announced)
 };
 
 __device__ int g_status = 0;
@@ -470,7 +471,8 @@ __device__ __forceinline__ void locate(const Shared* sh, const Params& p, int ti
 template <int MODE, bool BF16, bool CTA2>
 __global__ void __launch_bounds__(THREADS, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                    const __grid_constant__ HostSegs hs, const __grid_constant__ OutMaps om, const Params p) {
+                    const __grid_constant__ HostSegs hs, const __grid_constant__ OutMaps om,
+                    const __grid_constant__ GemmRemoteOut ro, const Params p) {
     using C = Cfg<CTA2>;
     constexpr int STAGES = C::STAGES, STAGE_BYTES = C::STAGE_BYTES, TILE_M = C::TILE_M, B_COLS = C::B_COLS;
     // Pairs: TMA completions of both CTAs go straight to the leader's barriers, so the MMA
@@ -543,6 +545,33 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 p.done_expected[e] = (sh->cum_tiles[e + 1] - sh->cum_tiles[e]) * EPI_WARPS * (CTA2 ? 2 : 1);
             __threadfence();
             *(volatile int*)p.done_ready = 1;
+        }
+    }
+    const bool remote = MODE != MODE_WGRAD && ro.enabled != 0;
+    unsigned long long rem_epoch = 0;
+    if (remote) {
+        // where every rank wants the rows of this exchange (bounded wait for its announcement)
+        rem_epoch = __ldcg(ro.seq) + 1;
+        const int par = (int)(rem_epoch & 1);
+        const int q = threadIdx.x;
+        if (q < ro.world) {
+            unsigned long long dest = ro.my_dest;
+            if (q != ro.rank) {
+                const unsigned long long* flag = ro.header + ro.ann_at / 8 + par * ro.stride + q;
+                const unsigned long long t0 = clock64();
+                bool there = false;
+                while (!there) {
+                    unsigned long long v;
+                    asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(flag) : "memory");
+                    there = v >= rem_epoch;
+                    if (!there && clock64() - t0 > ro.timeout_cycles) break;
+                    if (!there) __nanosleep(100);
+                }
+                dest = there ? __ldcg(ro.header + ro.dest_at / 8 + par * ro.stride + q) : 0ull;
+                if (!there) atomicOr(p.status, 16);
+                else if (dest == ~0ull || dest == 0ull) { dest = 0ull; atomicOr(p.status, 64); }   // it has no room: its rows are dropped
+            }
+            sh->rem_dest[q] = dest;
         }
     }
     if (warp == 0) {
@@ -770,7 +799,22 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             const bool active = rows_here > 0 && col_lo < p.n_out;
             // Full 32-row blocks leave through TMA stores; ragged ones (the end of an expert's
             // segment: the rows below belong to the next expert) through per-row stores.
-            const bool bulk = p.tma_store && rows_here == 32;
+            const bool bulk = p.tma_store && rows_here == 32 && !remote;
+            // remote output: where this lane's row (tile row 32*quarter + lane) goes
+            unsigned long long my_rowptr = 0ull;
+            if (remote && active && lane < rows_here) {
+                const int r_abs = t.row0 + quarter * 32 + lane;
+                const int* so = ro.src_off + t.e * ro.world;
+                int j_lo = 0, j_hi = ro.world - 1;              // the block (expert, source j) that holds r_abs
+                while (j_lo < j_hi) {
+                    const int mid = (j_lo + j_hi) >> 1;
+                    if (so[mid + 1] > r_abs) j_hi = mid; else j_lo = mid + 1;
+                }
+                const unsigned long long dest = sh->rem_dest[j_lo];
+                if (dest)
+                    my_rowptr = (unsigned long long)(ro.base[j_lo] + dest) +
+                                ((unsigned long long)(ro.dst_off[t.e * ro.world + j_lo] + (r_abs - so[j_lo])) * ld) * 2ull;
+            }
             const bool row_ok = r < t.rows;
             const size_t row_off = (MODE == MODE_WGRAD ? (size_t)t.e * p.out_rows_per_expert : 0) + t.row0;
             uint16_t* out_blk = (uint16_t*)p.out + (row_off + quarter * 32) * ld + col_lo;  // block origin
@@ -911,7 +955,19 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                             if (lane < 16)
                                 *reinterpret_cast<float2*>(p.colsum + (size_t)blk * ld + col_lo + c * CW + cp * 2) = make_float2(lo, hi);
                         }
-                        if (bulk) {
+                        if (remote) {
+                            // rows leave for their owners: 16-byte pieces, 4 lanes per row, 8 rows per instruction
+                            constexpr int RPI = 32 / NCH;
+                            const int j = lane % NCH;
+#pragma unroll
+                            for (int it = 0; it < 32 / RPI; ++it) {
+                                const int row = it * RPI + lane / NCH;
+                                const unsigned long long rp = __shfl_sync(0xffffffffu, my_rowptr, row);
+                                if (row < rows_here && rp)
+                                    *reinterpret_cast<uint4*>(rp + (unsigned long long)(col_lo + c * CW + j * 8) * 2ull) = stage[stage_slot(row, j)];
+                            }
+                            __syncwarp();
+                        } else if (bulk) {
                             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                             __syncwarp();
                             if (lane == 0) tma_store_2d(&om.out, stage, col_lo + c * CW, (int)row_off + quarter * 32);
@@ -951,6 +1007,21 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
     tc_fence_before();
     __syncthreads();
+    if (remote && threadIdx.x == 0) {
+        // every store of this CTA is ordered before the fence by the barrier; the last CTA tells the
+        // peers that this GPU's rows of the epoch have landed (arrived[parity][this rank] = epoch)
+        __threadfence_system();
+        if (atomicAdd(ro.counter, 1u) == gridDim.x - 1) {
+            __threadfence_system();
+            const int par = (int)(rem_epoch & 1);
+            for (int q = 0; q < ro.world; ++q) {
+                if (q == ro.rank) continue;
+                unsigned long long* flag = (unsigned long long*)ro.base[q] + ro.arrived_at / 8 + par * ro.stride + ro.rank;
+                asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(flag), "l"(rem_epoch) : "memory");
+            }
+            *ro.counter = 0;
+        }
+    }
     if (CTA2) cluster_sync_all();  // the peer may still arrive on this CTA's barriers until here
     if (warp == 0) {
         if (CTA2) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
@@ -1073,9 +1144,12 @@ int cta_cap() {
     return std::max(cap, 2);
 }
 
+const GemmRemoteOut kNoRemote = {};
+
 template <int MODE, bool CTA2>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, const HostSegs* hsp, const Params& p_in, int64_t max_tiles,
-           int64_t out_rows, cudaStream_t st, int reserve_sms = 0) {
+           int64_t out_rows, cudaStream_t st, int reserve_sms = 0, const GemmRemoteOut* rop = nullptr) {
+    const GemmRemoteOut& ro = rop ? *rop : kNoRemote;
     reserve_sms = (reserve_sms + 1) / 2 * 2;      // the kernel beside this one occupies whole SM pairs
     const HostSegs& hs = hsp ? *hsp : kNoSegs;
     Params p = p_in;
@@ -1083,7 +1157,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const HostSegs* hsp, co
     OutMaps om;
     memset(&om, 0, sizeof(om));
     p.tma_store = 0;
-    if (out_rows > 0 && p.out) {
+    if (out_rows > 0 && p.out && !ro.enabled) {
         if (int rc = make_out_map(&om.out, p.out, out_rows, p.n_out, p.is_bf16 != 0)) return rc;
         if (p.pre_out) {
             if (int rc = make_out_map(&om.out2, p.pre_out, out_rows, p.n_out, p.is_bf16 != 0)) return rc;
@@ -1122,7 +1196,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const HostSegs* hsp, co
         const int cap = std::max(1, std::min(cta_cap(), sm_count() - reserve_sms));
         cfg.gridDim = dim3((unsigned)std::max<int64_t>(1, std::min<int64_t>(max_tiles, cap)));
     }
-    FMOE_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, ma, mb, hs, om, p));
+    FMOE_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, ma, mb, hs, om, ro, p));
     return 0;
 }
 
@@ -1308,8 +1382,8 @@ int tc_linear_forward(const LinearArgs& a, cudaStream_t st) {
         p.done = a.done->done; p.done_expected = a.done->expected; p.done_ready = a.done->ready;
         reserve = std::max(reserve, a.done->reserve_sms);
     }
-    return pair ? launch<MODE_FWD, true>(ma, mb, a.host_segs, p, max_tiles, a.n_rows, st, reserve)
-                : launch<MODE_FWD, false>(ma, mb, a.host_segs, p, max_tiles, a.n_rows, st, reserve);
+    return pair ? launch<MODE_FWD, true>(ma, mb, a.host_segs, p, max_tiles, a.n_rows, st, reserve, a.remote)
+                : launch<MODE_FWD, false>(ma, mb, a.host_segs, p, max_tiles, a.n_rows, st, reserve, a.remote);
 }
 
 // A side stream and a pair of events per device, created on first use: the bias
@@ -1388,8 +1462,8 @@ int tc_linear_backward(const LinearBwdArgs& a, cudaStream_t st) {
             p.done = a.done->done; p.done_expected = a.done->expected; p.done_ready = a.done->ready;
             reserve = std::max(reserve, a.done->reserve_sms);
         }
-        if (int rc = pair ? launch<MODE_DGRAD, true>(ma, mb, a.host_segs, p, max_tiles, a.n_rows, st, reserve)
-                          : launch<MODE_DGRAD, false>(ma, mb, a.host_segs, p, max_tiles, a.n_rows, st, reserve))
+        if (int rc = pair ? launch<MODE_DGRAD, true>(ma, mb, a.host_segs, p, max_tiles, a.n_rows, st, reserve, a.remote)
+                          : launch<MODE_DGRAD, false>(ma, mb, a.host_segs, p, max_tiles, a.n_rows, st, reserve, a.remote))
             return rc;
         if (!closed) {
             if (a.after_input_grad) { if (int rc = a.after_input_grad(a.after_ctx)) return rc; }

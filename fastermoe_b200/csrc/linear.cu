@@ -148,12 +148,15 @@ extern "C" int fmoe_linear_forward_overlapped(const void* x, const void* weight,
     bool arriving = false, leaving = false;
     if (int rc = gemm_arrival_of(arrival, &ga, &arriving)) return rc;
     if (int rc = gemm_done_of(departure, &gd, &leaving)) return rc;
-    if (n_rows > 0) FMOE_REQUIRE(x && weight && y, "linear_forward: null pointer");
+    GemmRemoteOut ro;
+    if (int rc = remote_out_of(departure, &ro)) return rc;
+    if (n_rows > 0) FMOE_REQUIRE(x && weight && (y || ro.enabled), "linear_forward: null pointer");
     LinearArgs a{x, weight, bias, seg_offsets, y, pre_act, n_rows, in_feat, out_feat, n_expert, dtype, activation};
     // only the tensor-core kernel can start on rows that are still arriving / report finished experts
     const bool tc = n_rows > 0 && !force_simt() && tc_forward_supported(a);
-    FMOE_REQUIRE(!leaving || (tc && n_expert == departure->n_expert),
+    FMOE_REQUIRE(!(leaving || ro.enabled) || (tc && n_expert == departure->n_expert),
                  "linear_forward: an overlapped gather was started for a product the tensor-core kernels do not take");
+    if (ro.enabled) a.remote = &ro;
     const bool overlap = arriving && tc && n_expert == arrival->n_expert;
     if (arriving && !overlap) {
         if (int rc = fmoe_peer_arrival_finish(arrival, stream)) return rc;
@@ -181,12 +184,15 @@ extern "C" int fmoe_linear_backward_overlapped(const void* grad_y, const void* x
     bool arriving = false, leaving = false;
     if (int rc = gemm_arrival_of(arrival, &ga, &arriving)) return rc;
     if (int rc = gemm_done_of(departure, &gd, &leaving)) return rc;
+    GemmRemoteOut ro;
+    if (int rc = remote_out_of(departure, &ro)) return rc;
     LinearBwdArgs a{grad_y, x, weight, seg_offsets, act_pre, grad_x, grad_w, grad_b, n_rows, in_feat,
                     out_feat, n_expert, dtype, activation, accumulate, scratch};
     a.grad_x_colsum = grad_x_colsum;
     const bool tc = n_rows > 0 && !force_simt() && tc_backward_supported(a);
-    FMOE_REQUIRE(!leaving || (tc && grad_x && n_expert == departure->n_expert),
+    FMOE_REQUIRE(!(leaving || ro.enabled) || (tc && (grad_x || ro.enabled) && n_expert == departure->n_expert),
                  "linear_backward: an overlapped gather was started for a product the tensor-core kernels do not take");
+    if (ro.enabled) a.remote = &ro;
     const bool overlap = arriving && tc && n_expert == arrival->n_expert;
     if (arriving && !overlap) {
         if (int rc = fmoe_peer_arrival_finish(arrival, stream)) return rc;

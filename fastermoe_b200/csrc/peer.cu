@@ -54,6 +54,7 @@
 // streams ordered by events): the epoch words are per communicator.
 #include "common.cuh"
 #include "exchange.h"
+#include "gemm.h"
 #include <cstdlib>
 #include <cstring>
 #include <iterator>
@@ -105,7 +106,7 @@ struct PlanHead {
 struct PlanDims {
     int E, W, S;
     int64_t WE, T;        // W*E, W*W*E
-    size_t own_off, table_off, stored_off, caps_off, eptr_off, lay_off, total_off, lists_off, segdone_off, done_off, bytes;
+    size_t own_off, table_off, stored_off, caps_off, eptr_off, lay_off, total_off, lists_off, segdone_off, done_off, back_off, bytes;
 };
 __host__ __device__ inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 __host__ __device__ inline PlanDims plan_dims(int E, int W) {
@@ -123,6 +124,7 @@ __host__ __device__ inline PlanDims plan_dims(int E, int W) {
     d.lists_off = o;  o = align_up(o + (size_t)4 * (4 * (size_t)d.S + 1) * 4, 64);  // 4 x {prefix[S+1], sel[S], src[S], dst[S]}
     d.segdone_off = o; o = align_up(o + (size_t)d.S * 4, 64);             // i32 rows of each push segment stored so far (overlapped push)
     d.done_off = o;   o = align_up(o + (size_t)(4 * E + 16) * 4, 64);     // i32 done[2][E], expected[2][E], ready[2]: see GemmDone
+    d.back_off = o;   o = align_up(o + (size_t)E * W * 4, 64);            // i32 [E][W]: token-side row, on rank j, of the rows it sent to this rank's expert i
     d.bytes = o;
     return d;
 }
@@ -355,6 +357,10 @@ peer_plan_kernel(const __grid_constant__ PeerBases b, const __grid_constant__ Pl
     }
     for (int s = tid; s < d.S; s += blockDim.x) ((int*)(a.plan + d.segdone_off))[s] = 0;
     for (int s = tid; s < 4 * E + 16; s += blockDim.x) ((int*)(a.plan + d.done_off))[s] = 0;
+    for (int s = tid; s < E * W; s += blockDim.x) {
+        const int i = s / W, j = s % W;
+        ((int*)(a.plan + d.back_off))[s] = (eptr + (size_t)j * (d.WE + 1))[r * E + i];
+    }
     // ---- 4. what the GEMM and the host read ----------------------------------------------------
     for (int i = tid; i <= E; i += blockDim.x)
         own[i] = bad ? 0 : (int64_t)my_lay[i < E ? lay_pos_recv(r, E, W, i, 0) : r * E + E * W];
@@ -1318,8 +1324,10 @@ extern "C" int fmoe_peer_arrival_finish(const fmoe_arrival_t* arrival, fmoe_stre
     if (!arrival->comm) return 0;                 // the exchange was queued whole
     Comm* c = (Comm*)arrival->comm;
     cudaStream_t st = (cudaStream_t)stream;
-    FMOE_CUDA_TRY(cudaStreamWaitEvent(st, c->peer.join, 0));
-    return launch_move(c, nullptr, arrival->out, arrival->plan, arrival->n_expert, arrival->in_rows, arrival->out_rows,
+    // (a fused gather has no input buffer of its own: its rows came out of a GEMM's epilogue)
+    const int64_t in_rows = arrival->gather == 2 ? ((int64_t)1 << 31) - 1 : arrival->in_rows;
+    if (arrival->gather != 2) FMOE_CUDA_TRY(cudaStreamWaitEvent(st, c->peer.join, 0));
+    return launch_move(c, nullptr, arrival->out, arrival->plan, arrival->n_expert, in_rows, arrival->out_rows,
                        arrival->row_bytes, arrival->gather != 0, st, 2, 0);
 }
 
@@ -1327,7 +1335,7 @@ namespace fmoe {
 int done_words_of(const fmoe_arrival_t* departure, int** done, int** expected, int** ready, int* reserve_sms) {
     *done = *expected = *ready = nullptr;
     *reserve_sms = 0;
-    if (!departure || !departure->comm) return 0;
+    if (!departure || !departure->comm || departure->gather == 2) return 0;
     Comm* c = (Comm*)departure->comm;
     FMOE_REQUIRE(departure->gather && departure->plan, "departure: not the handle of an overlapped gather");
     const int E = departure->n_expert;
@@ -1339,6 +1347,69 @@ int done_words_of(const fmoe_arrival_t* departure, int** done, int** expected, i
     return 0;
 }
 }  // namespace fmoe
+
+namespace fmoe {
+namespace {
+// Tells every peer where this rank receives the rows of the coming exchange (or that it has no room);
+// what the first block of a push kernel does, for exchanges whose rows are stored by another kernel.
+__global__ void peer_announce_kernel(const __grid_constant__ PeerBases b, int rank, int world, unsigned long long my_dest,
+                                     int64_t out_rows, const char* plan, int* status) {
+    const PlanHead* head = (const PlanHead*)plan;
+    const unsigned long long epoch = __ldcg((const unsigned long long*)(b.base[rank] + kSeqOff)) + 1;
+    const int parity = (int)(epoch & 1);
+    const bool room = head->token_rows <= out_rows;
+    const int p = threadIdx.x;
+    if (p < world && p != rank) {
+        unsigned long long* peer_hdr = (unsigned long long*)b.base[p];
+        peer_hdr[kDestOff / 8 + parity * kMaxPeers + rank] = room ? my_dest : kRefused;
+        st_release_sys(peer_hdr + kAnnOff / 8 + parity * kMaxPeers + rank, epoch);
+    }
+    if (p == 0 && !room) atomicOr(status, 64);
+}
+}  // namespace
+
+// What a grouped GEMM needs to store its output rows straight into their owners' memory.
+int remote_out_of(const fmoe_arrival_t* h, GemmRemoteOut* ro) {
+    memset(ro, 0, sizeof(*ro));
+    if (!h || !h->comm || h->gather != 2) return 0;
+    Comm* c = (Comm*)h->comm;
+    FMOE_REQUIRE(c->peer.slot_bytes > 0 && h->plan && c->world <= kRemoteMaxWorld, "remote output: stale handle");
+    const int E = h->n_expert, W = c->world;
+    const PlanDims d = plan_dims(E, W);
+    for (int p = 0; p < W; ++p) ro->base[p] = c->peer.base[p];
+    ro->header = (const unsigned long long*)c->peer.base[c->rank];
+    ro->seq = (const unsigned long long*)(c->peer.base[c->rank] + kSeqOff);
+    ro->src_off = (const int*)((const char*)h->plan + d.lay_off) + (size_t)c->rank * (d.S + 1) + (size_t)c->rank * E;
+    ro->dst_off = (const int*)((const char*)h->plan + d.back_off);
+    ro->counter = c->peer.counter + 3;
+    ro->my_dest = (unsigned long long)((char*)h->out - c->peer.base[c->rank]);
+    ro->timeout_cycles = c->peer.timeout_ns * 2ull;
+    ro->arrived_at = kArrivedOff; ro->ann_at = kAnnOff; ro->dest_at = kDestOff; ro->stride = kMaxPeers;
+    ro->world = W; ro->rank = c->rank; ro->enabled = 1;
+    return 0;
+}
+}  // namespace fmoe
+
+extern "C" int fmoe_peer_gather_fused_begin(fmoe_comm_t comm, void* local_out, const void* plan, int64_t out_rows,
+                                            int64_t row_bytes, int32_t n_expert, fmoe_stream_t stream, fmoe_arrival_t* departure) {
+    FMOE_REQUIRE(comm && departure && plan, "peer exchange: null pointer");
+    Comm* c = (Comm*)comm;
+    memset(departure, 0, sizeof(*departure));
+    if (c->peer.slot_bytes == 0) return FMOE_PEER_UNAVAILABLE;
+    if (c->world > kRemoteMaxWorld || row_bytes <= 0 || row_bytes % 16 != 0 || !lies_in_pool(c, local_out, out_rows * row_bytes))
+        return 0;     // nothing queued: the caller stores the rows locally and gathers them afterwards
+    PeerBases b;
+    for (int p = 0; p < kMaxPeers; ++p) b.base[p] = c->peer.base[p];
+    int* status = device_status_ptr();
+    FMOE_REQUIRE(status, "peer exchange: no device status word");
+    peer_announce_kernel<<<1, 64, 0, (cudaStream_t)stream>>>(b, c->rank, c->world, (unsigned long long)((char*)local_out - c->peer.base[c->rank]),
+                                                            out_rows, (const char*)plan, status);
+    FMOE_CHECK_LAUNCH();
+    departure->comm = comm; departure->plan = plan; departure->out = local_out;
+    departure->in_rows = 0; departure->out_rows = out_rows; departure->row_bytes = row_bytes;
+    departure->n_expert = n_expert; departure->gather = 2;
+    return 0;
+}
 
 extern "C" int fmoe_peer_gather_planned_async(fmoe_comm_t comm, const void* global_in, void* local_out, const void* plan,
                                               int64_t in_rows, int64_t out_rows, int64_t row_bytes, int32_t n_expert,

@@ -637,6 +637,23 @@ def peer_gather_planned_async(output_buf, plan, out_rows, overlap_sms, use):
     return out, PendingArrival(h, (output_buf, out, plan.buf))
 
 
+def peer_gather_fused_begin(like, plan, out_rows):
+    """Prepares a global_gather that the next grouped GEMM performs itself: given the returned handle as
+    ``departure``, that GEMM stores its output rows into the token-side buffers of their owners and
+    writes no expert-side output.  ``like``: a tensor with the rows' width, dtype and device.  Returns
+    (out [out_rows, d], PendingArrival) -- ``finish()`` after the GEMM makes ``out`` readable -- or
+    (None, None) when the receive pool cannot hold ``out`` (nothing was queued)."""
+    _check_cuda(like)
+    out = _recv_empty(like, out_rows)
+    h = _lib.Arrival()
+    with torch.cuda.device(like.device):
+        _run("peer_gather", lib.fmoe_peer_gather_fused_begin, _comm(like.device), _ptr(out), _ptr(plan.buf), out_rows,
+             like.shape[1] * like.element_size(), plan.n_expert, _stream(), ctypes.byref(h))
+    if not h.comm:
+        return None, None
+    return out, PendingArrival(h, (out, plan.buf))
+
+
 def peer_gather_planned(output_buf, plan, out_rows):
     """global_gather driven by a PeerPlan: expert-side rows -> [out_rows, d] token-side buffer."""
     return _planned_move(lib.fmoe_peer_gather_planned, "peer_gather", output_buf, plan, out_rows)

@@ -420,9 +420,10 @@ class PlannedExchange:
     """One layer call's all-to-all-v driven by a plan that lives on the device (fmoe_cuda.PeerPlan):
     the host knows neither the counts nor how many rows arrive; ``fwd_batch_size`` is the capacity
     of the expert-side buffers."""
-    __slots__ = ("plan", "fwd_batch_size", "world_size", "num_expert", "overlap_sms", "pending", "token_rows", "early")
+    __slots__ = ("plan", "fwd_batch_size", "world_size", "num_expert", "overlap_sms", "pending", "token_rows", "early",
+                 "fused_gather")
 
-    def __init__(self, plan, cap_rows, world_size, overlap_sms=0, token_rows=0):
+    def __init__(self, plan, cap_rows, world_size, overlap_sms=0, token_rows=0, fused_gather=False):
         self.plan, self.fwd_batch_size, self.world_size = plan, int(cap_rows), world_size
         self.num_expert = plan.n_expert
         # > 0: the pushes run on that many SMs beside the grouped GEMMs that read (scatter) or write
@@ -430,6 +431,9 @@ class PlannedExchange:
         self.overlap_sms, self.pending = int(overlap_sms), None
         self.token_rows = int(token_rows)       # rows of this rank's token-side buffers
         self.early = None                       # (expert-side tensor, token-side result, pending) of a gather started early
+        # the GEMM before a gather stores its rows straight into their owners' token-side buffers;
+        # FusedExpertMLP takes part; its expert-side outputs are then placeholders nobody may read
+        self.fused_gather = bool(fused_gather)
 
     def flush(self):
         """Closes a scatter whose rows nobody waited for tile by tile, and a gather that was started early."""
@@ -444,6 +448,11 @@ class PlannedExchange:
         forwards its rows as experts complete.  Returns the handle for that GEMM, or None."""
         self.flush()
         self.early = None
+        if self.fused_gather and self.token_rows > 0 and buf.dtype in (torch.bfloat16, torch.float16):
+            out, pend = fmoe_cuda.peer_gather_fused_begin(buf, self.plan, self.token_rows)
+            if pend is not None:
+                self.early = (buf, out, pend)
+                return pend
         if self.overlap_sms <= 0 or self.token_rows <= 0:
             return None
         out, pend = fmoe_cuda.peer_gather_planned_async(buf, self.plan, self.token_rows, self.overlap_sms, use)

@@ -124,10 +124,14 @@ def _fmoe_general_global_forward(inp, gate, expert_fn, policy_fn, experts, num_e
         stored = _no_shadow_flags(world_size, num_expert)
         # the push of the scatter runs beside the experts' first GEMM (and, in the backward pass, beside
         # the input-gradient GEMM of the second layer) when the experts module can wait for rows tile by tile
-        overlap = 0
+        overlap, fused_gather = 0, False
         if getattr(experts, "consumes_arrival", None) is not None and experts.consumes_arrival(inp):
             overlap = int(os.environ.get("FMOE_B200_OVERLAP_SMS", "0"))
-        exch = PlannedExchange(routing.plan, routing.n_recv, world_size, overlap_sms=overlap, token_rows=routing.n_rows)
+            # the experts' last GEMM (and the input-gradient GEMM of their first layer) stores its rows
+            # straight into the token-side buffers of their owners: no gather pass afterwards
+            fused_gather = os.environ.get("FMOE_B200_FUSED_GATHER", "0") == "1"
+        exch = PlannedExchange(routing.plan, routing.n_recv, world_size, overlap_sms=overlap, token_rows=routing.n_rows,
+                               fused_gather=fused_gather)
         n_rows = routing.n_rows
         x = MOEScatterFused.apply(inp, routing.pos, routing.inv, top_k, n_rows, exch)
         x = expert_fn(x, [[experts]], ExpertCounts(routing.own_offsets_dev, exchange=exch), num_expert)

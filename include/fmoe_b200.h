@@ -471,6 +471,18 @@ int fmoe_peer_arrival_finish(const fmoe_arrival_t* arrival, fmoe_stream_t stream
 int fmoe_peer_gather_planned_async(fmoe_comm_t comm, const void* global_in, void* local_out, const void* plan,
                                    int64_t in_rows, int64_t out_rows, int64_t row_bytes, int32_t n_expert,
                                    int32_t overlap_sms, int32_t use, fmoe_stream_t stream, fmoe_arrival_t* departure);
+/* global_gather FUSED into the grouped GEMM that produces its rows: the product queued next with the
+ * handle as `departure` (fmoe_linear_forward_overlapped, or fmoe_linear_backward_overlapped for the input
+ * gradient) stores every output row straight into the token-side buffer of the rank that owns it --
+ * local_out [out_rows, row_bytes] on each rank, which must lie in the receive pool -- and writes no
+ * expert-side output (the y / grad_x argument of that call may be NULL).  This call only tells the peers
+ * where local_out is (one tiny kernel); fmoe_peer_arrival_finish after the product waits, bounded, for the
+ * peers' rows and clears what no row covers.  Replaces cuda/global_exchange.h:115-174 (global_gather) plus
+ * the store of the expert outputs of cuda/parallel_linear.cuh.  Needs bf16/fp16 rows, at most 32 ranks and
+ * a product of `n_expert` groups with n_rows > 0; when local_out is not in the pool it queues NOTHING and
+ * leaves departure->comm NULL (departure->gather is 2 otherwise). */
+int fmoe_peer_gather_fused_begin(fmoe_comm_t comm, void* local_out, const void* plan, int64_t out_rows,
+                                 int64_t row_bytes, int32_t n_expert, fmoe_stream_t stream, fmoe_arrival_t* departure);
 /* fmoe_linear_forward / fmoe_linear_backward_colsum (arguments as there) beside an exchange:
  *   arrival (may be NULL): the scatter that is still delivering x (forward) or grad_y (backward).  The
  *     call consumes the handle: the forward closes the exchange after its product, the backward

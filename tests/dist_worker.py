@@ -386,6 +386,17 @@ def check_layer_bf16(rank, world):
             os.environ["FMOE_B200_OVERLAP_SMS"] = "0"
         for name, v in base.items():
             assert torch.equal(over[name], v), f"overlapped exchange ({sms} SMs) differs in {name}"
+    # the gather done by the GEMM that produces its rows (stores into the owners' buffers): same bits,
+    # alone and together with an overlapped scatter
+    for sms in ("0", "8"):
+        os.environ["FMOE_B200_FUSED_GATHER"], os.environ["FMOE_B200_OVERLAP_SMS"] = "1", sms
+        try:
+            for _ in range(2):
+                over = _run_layer(m, x)
+        finally:
+            os.environ["FMOE_B200_FUSED_GATHER"], os.environ["FMOE_B200_OVERLAP_SMS"] = "0", "0"
+        for name, v in base.items():
+            assert torch.equal(over[name], v), f"gather fused into the GEMM (scatter on {sms} SMs) differs in {name}"
     from fastermoe_b200 import fmoe_cuda as fc
     assert fc.device_status() == 0
     os.environ["FMOE_FUSE_GRAN"] = "1"
@@ -432,8 +443,10 @@ def check_graph_step(rank, world):
         return out.detach().clone(), loss.detach().clone(), xi.grad.clone(), {n: p.grad.clone() for n, p in m.named_parameters()}
 
     want = [eager(x) for x in xs[1:]]
-    for sms in ("0", "8"):                # without and with the pushes running beside the GEMMs (a second stream in the graph)
-        os.environ["FMOE_B200_OVERLAP_SMS"] = sms
+    # without and with the pushes running beside the GEMMs (a second stream in the graph), and with
+    # the gathers done by the GEMMs' own epilogues
+    for sms, fused_gather in (("0", "0"), ("8", "0"), ("0", "1")):
+        os.environ["FMOE_B200_OVERLAP_SMS"], os.environ["FMOE_B200_FUSED_GATHER"] = sms, fused_gather
         try:
             step = GraphedStep(m, xs[0], input_grad=True)
             for x, (out, loss, gx, grads) in zip(xs[1:], want):
@@ -444,7 +457,7 @@ def check_graph_step(rank, world):
                 for n, p in m.named_parameters():
                     assert torch.equal(p.grad, grads[n]), n
         finally:
-            os.environ["FMOE_B200_OVERLAP_SMS"] = "0"
+            os.environ["FMOE_B200_OVERLAP_SMS"] = os.environ["FMOE_B200_FUSED_GATHER"] = "0"
         del step
     from fastermoe_b200 import fmoe_cuda as fc
     assert fc.device_status() == 0
