@@ -430,7 +430,7 @@ class PlannedExchange:
         # (gather) their rows; FusedExpertMLP takes part; the caller sets it only when that module follows
         self.overlap_sms, self.pending = int(overlap_sms), None
         self.token_rows = int(token_rows)       # rows of this rank's token-side buffers
-        self.early = None                       # (expert-side tensor, token-side result, pending) of a gather started early
+        self.early = None                       # (expert-side tensor, token-side result, pending, fused into the GEMM) of a gather started early
         # the GEMM before a gather stores its rows straight into their owners' token-side buffers;
         # FusedExpertMLP takes part; its expert-side outputs are then placeholders nobody may read
         self.fused_gather = bool(fused_gather)
@@ -451,14 +451,14 @@ class PlannedExchange:
         if self.fused_gather and self.token_rows > 0 and buf.dtype in (torch.bfloat16, torch.float16):
             out, pend = fmoe_cuda.peer_gather_fused_begin(buf, self.plan, self.token_rows)
             if pend is not None:
-                self.early = (buf, out, pend)
+                self.early = (buf, out, pend, True)
                 return pend
         if self.overlap_sms <= 0 or self.token_rows <= 0:
             return None
         out, pend = fmoe_cuda.peer_gather_planned_async(buf, self.plan, self.token_rows, self.overlap_sms, use)
         if pend is None:
             return None
-        self.early = (buf, out, pend)
+        self.early = (buf, out, pend, False)
         return pend
 
     def take_pending(self):
@@ -478,6 +478,9 @@ class PlannedExchange:
             early[2].finish()
             if early[0].data_ptr() == buf.data_ptr() and early[1].shape[0] == out_rows:
                 return early[1]                 # the rows are already here
+            if early[3]:
+                raise RuntimeError("the expert-side output of this exchange was never stored (its GEMM sent the rows "
+                                   "to their owners): gather the tensor that GEMM returned, or set FMOE_B200_FUSED_GATHER=0")
         self.flush()
         return fmoe_cuda.peer_gather_planned(buf, self.plan, out_rows)
 

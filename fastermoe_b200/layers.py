@@ -129,7 +129,7 @@ def _fmoe_general_global_forward(inp, gate, expert_fn, policy_fn, experts, num_e
             overlap = int(os.environ.get("FMOE_B200_OVERLAP_SMS", "0"))
             # the experts' last GEMM (and the input-gradient GEMM of their first layer) stores its rows
             # straight into the token-side buffers of their owners: no gather pass afterwards
-            fused_gather = os.environ.get("FMOE_B200_FUSED_GATHER", "0") == "1"
+            fused_gather = os.environ.get("FMOE_B200_FUSED_GATHER", "1") == "1"
         exch = PlannedExchange(routing.plan, routing.n_recv, world_size, overlap_sms=overlap, token_rows=routing.n_rows,
                                fused_gather=fused_gather)
         n_rows = routing.n_rows

@@ -1,4 +1,5 @@
 """Rank bodies of the multi-process tests (spawned by test_dist_gpu.py / test_dist_cpu.py)."""
+import contextlib
 import ctypes
 import os
 import sys
@@ -353,6 +354,22 @@ def gpu_layer_bf16(rank, world, port):
     finish("nccl")
 
 
+@contextlib.contextmanager
+def switches(**kv):
+    """Sets FMOE_B200_<NAME> switches for a block and puts the previous values back."""
+    old = {k: os.environ.get("FMOE_B200_" + k) for k in kv}
+    try:
+        for k, v in kv.items():
+            os.environ["FMOE_B200_" + k] = str(v)
+        yield
+    finally:
+        for k, v in old.items():
+            if v is None:
+                os.environ.pop("FMOE_B200_" + k, None)
+            else:
+                os.environ["FMOE_B200_" + k] = v
+
+
 def check_layer_bf16(rank, world):
     """bf16 shapes that take the tensor-core kernels, smart schedule and shadowing included."""
     from parity import assert_half_close, rms
@@ -361,7 +378,8 @@ def check_layer_bf16(rank, world):
     xs = tens["x"].view(world, T, d)
     m = _make_layer(world, rank, E, d, h, k, "gelu", True, tens, dtype=torch.bfloat16)
     x = xs[rank].bfloat16().cuda()
-    base = _run_layer(m, x)
+    with switches(OVERLAP_SMS=0, FUSED_GATHER=0):      # the plain exchange: push, then the GEMMs
+        base = _run_layer(m, x)
     with torch.no_grad():
         idx, _ = m.gate(x)
     idx_all = [torch.empty_like(idx) for _ in range(world)]
@@ -378,23 +396,17 @@ def check_layer_bf16(rank, world):
                                    msg=lambda s_: f"{name}: {s_}")
     # the scatter's push running beside the GEMM that reads its rows: same bits
     for sms in ("4", "16"):
-        os.environ["FMOE_B200_OVERLAP_SMS"] = sms
-        try:
+        with switches(OVERLAP_SMS=sms, FUSED_GATHER=0):
             for _ in range(2):
                 over = _run_layer(m, x)
-        finally:
-            os.environ["FMOE_B200_OVERLAP_SMS"] = "0"
         for name, v in base.items():
             assert torch.equal(over[name], v), f"overlapped exchange ({sms} SMs) differs in {name}"
     # the gather done by the GEMM that produces its rows (stores into the owners' buffers): same bits,
     # alone and together with an overlapped scatter
     for sms in ("0", "8"):
-        os.environ["FMOE_B200_FUSED_GATHER"], os.environ["FMOE_B200_OVERLAP_SMS"] = "1", sms
-        try:
+        with switches(OVERLAP_SMS=sms, FUSED_GATHER=1):
             for _ in range(2):
                 over = _run_layer(m, x)
-        finally:
-            os.environ["FMOE_B200_FUSED_GATHER"], os.environ["FMOE_B200_OVERLAP_SMS"] = "0", "0"
         for name, v in base.items():
             assert torch.equal(over[name], v), f"gather fused into the GEMM (scatter on {sms} SMs) differs in {name}"
     from fastermoe_b200 import fmoe_cuda as fc
@@ -442,12 +454,12 @@ def check_graph_step(rank, world):
         loss.backward()
         return out.detach().clone(), loss.detach().clone(), xi.grad.clone(), {n: p.grad.clone() for n, p in m.named_parameters()}
 
-    want = [eager(x) for x in xs[1:]]
+    with switches(OVERLAP_SMS=0, FUSED_GATHER=0):
+        want = [eager(x) for x in xs[1:]]
     # without and with the pushes running beside the GEMMs (a second stream in the graph), and with
     # the gathers done by the GEMMs' own epilogues
     for sms, fused_gather in (("0", "0"), ("8", "0"), ("0", "1")):
-        os.environ["FMOE_B200_OVERLAP_SMS"], os.environ["FMOE_B200_FUSED_GATHER"] = sms, fused_gather
-        try:
+        with switches(OVERLAP_SMS=sms, FUSED_GATHER=fused_gather):
             step = GraphedStep(m, xs[0], input_grad=True)
             for x, (out, loss, gx, grads) in zip(xs[1:], want):
                 got_loss = step(x)
@@ -456,8 +468,6 @@ def check_graph_step(rank, world):
                 assert torch.equal(step.input_grad, gx)
                 for n, p in m.named_parameters():
                     assert torch.equal(p.grad, grads[n]), n
-        finally:
-            os.environ["FMOE_B200_OVERLAP_SMS"] = os.environ["FMOE_B200_FUSED_GATHER"] = "0"
         del step
     from fastermoe_b200 import fmoe_cuda as fc
     assert fc.device_status() == 0
