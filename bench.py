@@ -190,7 +190,7 @@ def run_reference(args):
 
 def workload_config(name, n_gpus):
     c = CONFIGS[name]
-    return {"workload": f"BASELINE config {name[1:]} per GPU: MoE MLP layer fwd+bwd, expert-parallel over the GPUs",
+    return {"workload": f"benchmark config {name[1:]} per GPU: MoE MLP layer fwd+bwd, expert-parallel over the GPUs",
             "tokens_per_gpu": c["tokens_per_gpu"], "d_model": c["d_model"], "d_hidden": c["d_hidden"],
             "experts_per_gpu": c["experts_per_gpu"], "top_k": c["top_k"], "activation": c["activation"],
             "routing": c["routing"], "seed": c["seed"], "parallelism": f"ep{n_gpus}",
