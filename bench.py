@@ -20,7 +20,8 @@ Workloads (all synthetic, seeded; "per GPU" sizes, experts sharded over the rank
 
 One "step" = forward + backward (loss = sum of the output) of the layer on one batch.  The printed
 JSON line carries: ``value`` (device-resident inputs), ``e2e`` (inputs copied from pinned host memory
-and the loss read back every step), ``roofline`` of the dominant kernel (the grouped expert GEMM,
+and the loss read back every step -- when the step replays as a CUDA graph, the host reads step i's
+loss, copied to pinned memory, while step i+1 runs), ``roofline`` of the dominant kernel (the grouped expert GEMM,
 timed with CUDA events on the launching stream), ``cpu_baseline`` (the reference's CPU path on a
 bounded sample of the same workload).  With N > 1 it also carries ``parity`` -- an untimed
 self-check of the multi-GPU path against the CPU oracle, run after the timed region -- and, with N = 8
@@ -244,15 +245,17 @@ class Env:
             self.dist.barrier()
         self.torch.cuda.synchronize()
 
-    def timed(self, fn, steps):
-        """ms for `steps` calls: CUDA events on the launching stream, barrier + synchronize on both
-        sides, max over ranks."""
+    def timed(self, fn, steps, after=None):
+        """ms for `steps` calls (and `after()`, if given, inside the timed region): CUDA events on the
+        launching stream, barrier + synchronize on both sides, max over ranks."""
         torch = self.torch
         self.barrier()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
         for _ in range(steps):
             fn()
+        if after is not None:
+            after()
         b.record()
         self.barrier()
         ms = torch.tensor([a.elapsed_time(b)], device=self.dev)
@@ -584,6 +587,35 @@ def parity_checks(env, layer, x_dev):
 
 # ------------------------------------------------------------------------------- main leg
 
+def write_kernel_list(env, step, path, name, steps=3):
+    """Every kernel of `steps` resident steps with its device time (CUPTI through torch.profiler: no
+    replay, no clock control, usable on every rank of a multi-GPU run where a kernel profiler that
+    serialises launches is not), written by rank 0 as a markdown table: launches per step, mean time,
+    share of the summed kernel time, and the step's span on the device."""
+    torch = env.torch
+    from torch.profiler import profile, ProfilerActivity
+    for _ in range(2):
+        step()
+    env.barrier()
+    with profile(activities=[ProfilerActivity.CUDA]) as tp:
+        for _ in range(steps):
+            step()
+        torch.cuda.synchronize()
+    if env.rank != 0:
+        return
+    rows = [(e.key, e.count, e.device_time_total) for e in tp.key_averages() if e.device_time_total > 0]
+    total = sum(r[2] for r in rows) or 1.0
+    ev = [e for e in tp.events() if e.device_type == torch.autograd.DeviceType.CUDA]
+    span = (max(e.time_range.end for e in ev) - min(e.time_range.start for e in ev)) if ev else 0.0
+    with open(path, "w") as f:
+        f.write(f"kernel list of {steps} steps of {name} on rank 0 of {env.world} (torch.profiler, CUDA activities)\n\n")
+        f.write(f"summed kernel time {total / steps:.1f} us per step; first kernel start to last kernel end "
+                f"{span / steps:.1f} us per step (kernels on the side streams overlap the main stream)\n\n")
+        f.write("| kernel | launches/step | mean us | share |\n|---|---|---|---|\n")
+        for key, count, t in sorted(rows, key=lambda r: -r[2]):
+            f.write(f"| {key[:110]} | {count / steps:g} | {t / count:.1f} | {100 * t / total:.1f} % |\n")
+
+
 def run_ours(args):
     import ctypes
     env = Env(args)
@@ -625,12 +657,37 @@ def run_ours(args):
             graphed = GraphedStep(layer, x_dev.detach(), input_grad=True)
             used_graph = True
 
+            # The loss of every step is copied to pinned host memory on the stream and read by the host one
+            # step later, while the next step already runs: the host never leaves the GPU idle to fetch a
+            # scalar (what a training loop that logs its loss does).
+            loss_host = torch.zeros(2, dtype=torch.float32).pin_memory()
+            loss_ready = [torch.cuda.Event(), torch.cuda.Event()]
+            state = {"i": 0, "losses": []}
+
+            def read_previous():
+                if state["i"] > 0:
+                    slot = (state["i"] - 1) & 1
+                    loss_ready[slot].synchronize()
+                    state["losses"].append(float(loss_host[slot]))
+
             def step_e2e_graph():
-                return graphed(take()).item()
+                loss = graphed(take())
+                slot = state["i"] & 1
+                loss_host[slot:slot + 1].copy_(loss.detach().reshape(1), non_blocking=True)
+                loss_ready[slot].record()
+                read_previous()
+                state["i"] += 1
+
+            def read_last():
+                read_previous()
+                state["i"] = 0
 
             for _ in range(2):
                 step_e2e_graph()
-            e2e_ms = env.timed(step_e2e_graph, args.steps)
+            read_last()
+            state["losses"].clear()
+            e2e_ms = env.timed(step_e2e_graph, args.steps, after=read_last)
+            assert len(state["losses"]) == args.steps and all(math.isfinite(v) for v in state["losses"])
             layer.zero_grad(set_to_none=True)
 
     # Per-kernel timing pass: CUDA events around every library call on the launching stream.
@@ -641,6 +698,9 @@ def run_ours(args):
         step_resident()
     dur = tprof.durations_ms()
     fmoe_cuda.set_profile(None)
+
+    if args.kernel_list:
+        write_kernel_list(env, step_resident, args.kernel_list, name)
 
     form = exchange_form(layer, dev) if world > 1 else None
     status = fmoe_cuda.device_status(dev)
@@ -686,7 +746,9 @@ def run_ours(args):
         "e2e": ({"value": e2e_val, "unit": "tokens/s",
                  "h2d_bytes_per_step": x_host.numel() * x_host.element_size(), "d2h_bytes_per_step": 4,
                  "note": "a training step: the batch is copied in, only the scalar loss is read back (the [T,d] "
-                         "output and the gradients stay on the device)",
+                         "output and the gradients stay on the device)" +
+                         ("; graphed steps: every step's loss is copied to pinned host memory and read by the host "
+                          "while the next step runs; eager steps: loss.item() each step" if used_graph else ""),
                  "ms_per_step": e2e_ms / args.steps, "cuda_graph": used_graph,
                  "eager_ms_per_step": e2e_eager_ms / args.steps} if e2e_ms else None),
         "gpu_launches": launches, "clocks": clocks, "roofline": roofline,
@@ -761,6 +823,8 @@ def main():
     ap.add_argument("--extra-steps", type=int, default=10)
     ap.add_argument("--extra-limit-s", type=int, default=420, help="wall-clock limit of the untimed legs")
     ap.add_argument("--no-parity", action="store_true", help="omit the multi-GPU self-check")
+    ap.add_argument("--kernel-list", default=None, metavar="PATH", help="also write a per-kernel device-time table "
+                    "of three resident steps (rank 0) to PATH")
     ap.add_argument("--skip-e2e", action="store_true", help="omit the host-buffer (e2e) leg (profiling runs)")
     ap.add_argument("--skip-cpu", action="store_true", help="omit the CPU baseline leg (profiling runs)")
     args = ap.parse_args()

@@ -389,6 +389,10 @@ struct MoveArgs {
     unsigned int* counter;
     int* status;
     const char* plan;
+    const int64_t* row_of;                 // push of rows that are not stored anywhere yet: token-side row i is
+    const void* row_scale;                 //   row_scale[row_of[i]] * src[row_of[i] / row_div] (no scale: a plain copy)
+    int row_div, row_dtype;
+    int64_t src_rows;
     int* done;                             // overlapped gather: per-expert completion counters of the producing GEMM,
     int* expected;                         //   the counts at which an expert is complete,
     int* ready;                            //   and the word that says those counts are valid
@@ -413,6 +417,32 @@ __device__ __forceinline__ void copy_row(const uint4* __restrict__ s, uint4* __r
         d[c] = v0; d[c + 32] = v1; d[c + 64] = v2; d[c + 96] = v3;
     }
     for (; c < row_vecs; c += 32) d[c] = __ldcg(s + c);
+}
+
+// d[...] = w * s[...] in the rows' own type: one rounding per element, as a kernel that stored the
+// scaled rows first would have produced them.
+template <typename T>
+__device__ __forceinline__ void copy_row_scaled_t(const uint4* __restrict__ s, uint4* __restrict__ d, int64_t row_vecs, int lane, float w) {
+    constexpr int N = 16 / sizeof(T);
+    for (int64_t c = lane; c < row_vecs; c += 32) {
+        uint4 v = __ldcg(s + c);
+        T* e = reinterpret_cast<T*>(&v);
+#pragma unroll
+        for (int i = 0; i < N; ++i) e[i] = from_float<T>(w * to_float<T>(e[i]));
+        d[c] = v;
+    }
+}
+
+__device__ __forceinline__ float scale_at(const void* scale, int dtype, int64_t i) {
+    if (dtype == FMOE_F32) return ((const float*)scale)[i];
+    if (dtype == FMOE_F16) return __half2float(((const __half*)scale)[i]);
+    return __bfloat162float(((const __nv_bfloat16*)scale)[i]);
+}
+
+__device__ __forceinline__ void copy_row_scaled(const uint4* __restrict__ s, uint4* __restrict__ d, int64_t row_vecs, int lane, float w, int dtype) {
+    if (dtype == FMOE_F32) copy_row_scaled_t<float>(s, d, row_vecs, lane, w);
+    else if (dtype == FMOE_F16) copy_row_scaled_t<__half>(s, d, row_vecs, lane, w);
+    else copy_row_scaled_t<__nv_bfloat16>(s, d, row_vecs, lane, w);
 }
 
 constexpr int kMoveThreads = 256, kMoveWarps = kMoveThreads / 32;
@@ -476,8 +506,19 @@ peer_move_kernel(const __grid_constant__ PeerBases b, const __grid_constant__ Mo
         if (kPush) {
             const int sel = L.sel[k];
             if (sel != kLocal && ((s_dead >> sel) & 1ull)) continue;
-            s = src + (int64_t)(L.src[k] + off) * row_vecs;
             dptr = (sel == kLocal ? out : (uint4*)(b.base[sel] + s_dest[sel])) + (int64_t)(L.dst[k] + off) * row_vecs;
+            if (a.row_of) {
+                // the token-side row is produced here: a row of src picked by index, scaled or not
+                const int64_t at = __ldg(a.row_of + L.src[k] + off), from = at / a.row_div;
+                if (at < 0 || from >= a.src_rows) { if (lane == 0) atomicOr(a.status, 8); continue; }
+                s = src + from * row_vecs;
+                if (a.row_scale) {
+                    copy_row_scaled(s, dptr, row_vecs, lane, scale_at(a.row_scale, a.row_dtype, at), a.row_dtype);
+                    continue;
+                }
+            } else {
+                s = src + (int64_t)(L.src[k] + off) * row_vecs;
+            }
         } else {
             s = slot + (int64_t)(L.src[k] + off) * row_vecs;
             dptr = out + (int64_t)(L.dst[k] + off) * row_vecs;
@@ -778,8 +819,18 @@ int launch_plan(Comm* c, int rank, int W, int E, bool exchange, const int64_t* l
     return 0;
 }
 
+// Rows of a push that exist nowhere yet: see MoveArgs::row_of.
+struct RowSource {
+    const int64_t* row_of;
+    int div;
+    const void* scale;
+    int dtype;
+    int64_t src_rows;
+};
+
 int launch_move(Comm* c, const void* in, void* out, const void* plan, int E, int64_t in_rows, int64_t out_rows,
-                int64_t row_bytes, bool reverse, cudaStream_t st, int phases = 3, int overlap_sms = 0, int done_use = 0);
+                int64_t row_bytes, bool reverse, cudaStream_t st, int phases = 3, int overlap_sms = 0, int done_use = 0,
+                const RowSource* rows = nullptr);
 
 bool lies_in_pool(Comm* c, const void* out, int64_t bytes) {
     char* pool = c->peer.base[c->rank] + kHeaderBytes + 2 * c->peer.slot_bytes;
@@ -789,7 +840,8 @@ bool lies_in_pool(Comm* c, const void* out, int64_t bytes) {
 // phases: bit 0 = push, bit 1 = consume.  overlap_sms > 0 (push of a scatter into a pool buffer only):
 // the few-SM push that publishes per-expert arrival flags.
 int launch_move(Comm* c, const void* in, void* out, const void* plan, int E, int64_t in_rows, int64_t out_rows,
-                int64_t row_bytes, bool reverse, cudaStream_t st, int phases, int overlap_sms, int done_use) {
+                int64_t row_bytes, bool reverse, cudaStream_t st, int phases, int overlap_sms, int done_use,
+                const RowSource* rows) {
     FMOE_REQUIRE(row_bytes > 0 && row_bytes % 16 == 0, "peer exchange: row_bytes=%lld (a positive multiple of 16)", (long long)row_bytes);
     FMOE_REQUIRE(in_rows >= 0 && out_rows >= 0 && in_rows < ((int64_t)1 << 31) && out_rows < ((int64_t)1 << 31),
                  "peer exchange: rows in=%lld out=%lld", (long long)in_rows, (long long)out_rows);
@@ -809,6 +861,12 @@ int launch_move(Comm* c, const void* in, void* out, const void* plan, int E, int
     a.timeout_ns = c->peer.timeout_ns; a.counter = c->peer.counter; a.plan = (const char*)plan;
     a.status = device_status_ptr();
     FMOE_REQUIRE(a.status, "peer exchange: no device status word");
+    if (rows) {
+        FMOE_REQUIRE(!reverse && overlap_sms == 0 && rows->row_of && rows->div > 0 && rows->src_rows >= 0,
+                     "peer exchange: indexed rows are for the plain scatter");
+        a.row_of = rows->row_of; a.row_div = rows->div; a.row_scale = rows->scale; a.row_dtype = rows->dtype;
+        a.src_rows = rows->src_rows;
+    }
     const PlanDims d = plan_dims(E, c->world);
     const size_t smem = (size_t)(d.S + 1) * sizeof(int);
     FMOE_REQUIRE(smem <= 40 * 1024, "peer exchange: %d segment slots do not fit the kernels' shared memory", d.S);
@@ -1266,6 +1324,18 @@ extern "C" int fmoe_peer_scatter_planned(fmoe_comm_t comm, const void* local_in,
     Comm* c = (Comm*)comm;
     if (c->peer.slot_bytes == 0) return FMOE_PEER_UNAVAILABLE;
     return launch_move(c, local_in, global_out, plan, n_expert, in_rows, out_rows, row_bytes, false, (cudaStream_t)stream);
+}
+
+extern "C" int fmoe_peer_scatter_planned_rows(fmoe_comm_t comm, const void* src, int64_t src_rows, const int64_t* row_of,
+                                              int32_t row_div, const void* scale, int32_t dtype, void* global_out,
+                                              const void* plan, int64_t in_rows, int64_t out_rows, int64_t row_bytes,
+                                              int32_t n_expert, fmoe_stream_t stream) {
+    FMOE_REQUIRE(comm && row_of && row_div > 0, "peer exchange: null pointer");
+    FMOE_REQUIRE(dtype == FMOE_F32 || dtype == FMOE_F16 || dtype == FMOE_BF16, "peer exchange: dtype %d", dtype);
+    Comm* c = (Comm*)comm;
+    if (c->peer.slot_bytes == 0) return FMOE_PEER_UNAVAILABLE;
+    const RowSource rows{row_of, row_div, scale, dtype, src_rows};
+    return launch_move(c, src, global_out, plan, n_expert, in_rows, out_rows, row_bytes, false, (cudaStream_t)stream, 3, 0, 0, &rows);
 }
 
 extern "C" int fmoe_peer_gather_planned(fmoe_comm_t comm, const void* global_in, void* local_out, const void* plan,

@@ -225,7 +225,7 @@ combine_bwd_fast_kernel(const T* __restrict__ grad_out, const T* __restrict__ bu
                     dot[j] = fmaf(gf[i], xf[i], dot[j]);
                     o[i] = w[j] * gf[i];
                 }
-                *reinterpret_cast<uint4*>(grad_buf + src[j] * d + c0 + ch * step) = pack<T>(o);
+                if (grad_buf) *reinterpret_cast<uint4*>(grad_buf + src[j] * d + c0 + ch * step) = pack<T>(o);
             }
         }
     }
@@ -270,11 +270,11 @@ combine_bwd_kernel(const T* __restrict__ grad_out, const T* __restrict__ buf, co
                     }
 #pragma unroll
                     for (int i = 0; i < N; ++i) o[i] = w * g[i];
-                    *reinterpret_cast<uint4*>(grad_buf + s * d + c0) = pack<T>(o);
+                    if (grad_buf) *reinterpret_cast<uint4*>(grad_buf + s * d + c0) = pack<T>(o);
                 } else {
                     const float g = to_float<T>(grad_out[t * d + c0]);
                     if (grad_score) dot = fmaf(g, to_float<T>(buf[s * d + c0]), dot);
-                    grad_buf[s * d + c0] = from_float<T>(w * g);
+                    if (grad_buf) grad_buf[s * d + c0] = from_float<T>(w * g);
                 }
             }
         }
@@ -542,7 +542,8 @@ extern "C" int fmoe_combine_backward(const void* grad_out, const void* buf, cons
                                      fmoe_stream_t stream) {
     if (int rc = check_typed(n_tokens, top_k, d, dtype)) return rc;
     if (n_tokens == 0) return 0;
-    FMOE_REQUIRE(grad_out && score && grad_buf, "combine_backward: null pointer");
+    // grad_buf may be NULL (only the score gradient is wanted: the rows are produced elsewhere)
+    FMOE_REQUIRE(grad_out && score && (grad_buf || grad_score), "combine_backward: null pointer");
     FMOE_REQUIRE(!grad_score || buf, "combine_backward: grad_score needs the forward buffer");
     cudaStream_t st = (cudaStream_t)stream;
     switch (dtype) {

@@ -15,6 +15,8 @@
 // Gate entries are read with 16-byte loads; within an expert segment positions
 // ascend with the flat index, so results are identical from run to run.
 #include "common.cuh"
+#include <algorithm>
+#include <cooperative_groups.h>
 #include <mutex>
 
 namespace fmoe {
@@ -305,6 +307,142 @@ apply_kernel(int mode, const int64_t* __restrict__ gate, int64_t n, int n_expert
     }
 }
 
+// ---- one launch for small inputs ----------------------------------------------------------------
+// Up to kClMaxCtas * kClWarps warp tiles of at most kClMaxChunks chunks: the four passes above run as
+// ONE thread-block cluster.  The per-tile histograms never leave shared memory: a CTA scans its
+// warps' rows, the CTAs read each other's totals through distributed shared memory between two
+// cluster barriers, every CTA derives the segment starts for itself, and each warp then ranks its
+// tile (whose entries are still in L1) exactly as apply_kernel does.  Same results, one launch
+// instead of four and no scratch traffic: at the size of one layer call (tens of thousands of gate
+// entries) the operators were bound by launch latency.
+constexpr int kClWarps = 16, kClThreads = kClWarps * 32, kClMaxCtas = 8, kClMaxChunks = 16, kClMaxExperts = 512;
+
+__global__ void __launch_bounds__(kClThreads)
+bucket_cluster_kernel(int mode, const int64_t* __restrict__ gate, int64_t n, int n_expert, int chunks,
+                      int64_t* __restrict__ lec64, int64_t* __restrict__ offsets, int32_t* __restrict__ inout,
+                      int64_t* __restrict__ pos, int64_t* __restrict__ inv, int64_t* __restrict__ new_gate, bool vec) {
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    extern __shared__ int32_t shc[];
+    int32_t* hist = shc;                                   // [kClWarps][E]: counts, then prefix inside the CTA, then running positions
+    int32_t* ctot = hist + (size_t)kClWarps * n_expert;    // [E] this CTA's totals (read by the other CTAs)
+    int32_t* cbase = ctot + n_expert;                      // [E] totals of the CTAs before this one
+    int32_t* total = cbase + n_expert;                     // [E]
+    int32_t* seg = total + n_expert;                       // [E] segment starts
+    int32_t* lim = seg + n_expert;                         // [E] the in/out vector as it was on entry
+    __shared__ int64_t s_grand;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const unsigned rank = cluster.block_rank(), n_cta = cluster.num_blocks();
+    int32_t* my = hist + (size_t)warp * n_expert;
+    const int64_t tb = ((int64_t)rank * kClWarps + warp) * (int64_t)chunks * 64;
+    for (int e = lane; e < n_expert; e += 32) my[e] = 0;
+    __syncwarp();
+    for (int it = 0; it < chunks && tb < n; it += 4) {
+        int ea[4], eb[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int64_t c = tb + (int64_t)(it + u) * 64;
+            if (it + u < chunks && c < n) load_chunk(gate, n, c, lane, vec, n_expert, ea[u], eb[u]);
+            else ea[u] = eb[u] = -1;
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            hist_round(ea[u], lane, my);
+            hist_round(eb[u], lane, my);
+        }
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < n_expert; e += kClThreads) {
+        int32_t run = 0;
+        for (int w = 0; w < kClWarps; ++w) {
+            const int32_t h = hist[(size_t)w * n_expert + e];
+            hist[(size_t)w * n_expert + e] = run;
+            run += h;
+        }
+        ctot[e] = run;
+    }
+    cluster.sync();
+    for (int e = threadIdx.x; e < n_expert; e += kClThreads) {
+        int32_t tot = 0, before = 0;
+        for (unsigned r = 0; r < n_cta; ++r) {
+            const int32_t v = cluster.map_shared_rank(ctot, r)[e];
+            if (r < rank) before += v;
+            tot += v;
+        }
+        total[e] = tot;
+        cbase[e] = before;
+        lim[e] = mode == MODE_COUNT_POS ? 0 : inout[e];
+    }
+    cluster.sync();      // nobody reads another CTA's shared memory, or the in/out vector, after this
+    if (mode == MODE_COUNT_POS) {
+        if (warp == 0) {
+            int64_t carry = 0;
+            for (int e0 = 0; e0 < n_expert; e0 += 32) {
+                const int32_t v = e0 + lane < n_expert ? total[e0 + lane] : 0;
+                int32_t incl = v;
+#pragma unroll
+                for (int off = 1; off < 32; off <<= 1) {
+                    const int32_t o = __shfl_up_sync(kFull, incl, off);
+                    if (lane >= off) incl += o;
+                }
+                if (e0 + lane < n_expert) seg[e0 + lane] = (int32_t)carry + incl - v;
+                carry += __shfl_sync(kFull, incl, 31);
+            }
+            if (lane == 0) s_grand = carry;
+        }
+    } else {
+        for (int e = threadIdx.x; e < n_expert; e += kClThreads) seg[e] = mode == MODE_ASSIGN ? lim[e] - total[e] : 0;
+        if (threadIdx.x == 0) s_grand = n;
+    }
+    __syncthreads();
+    if (rank == 0) {
+        for (int e = threadIdx.x; e < n_expert; e += kClThreads) {
+            if (mode == MODE_COUNT_POS) {
+                if (lec64) lec64[e] = total[e];
+                if (offsets) offsets[e] = seg[e];
+            } else if (mode == MODE_ASSIGN) {
+                inout[e] = seg[e];
+            } else {
+                inout[e] = lim[e] - total[e];
+            }
+        }
+        if (mode == MODE_COUNT_POS && offsets && threadIdx.x == 0) offsets[n_expert] = s_grand;
+    }
+    if (tb >= n) return;
+    for (int e = lane; e < n_expert; e += 32) my[e] += seg[e] + cbase[e];
+    __syncwarp();
+    const int64_t grand = (mode == MODE_COUNT_POS && offsets) ? s_grand : n;
+    for (int it0 = 0; it0 < chunks; it0 += 4) {
+        int eas[4], ebs[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int64_t c = tb + (int64_t)(it0 + u) * 64;
+            if (it0 + u < chunks && c < n) load_chunk(gate, n, c, lane, vec, n_expert, eas[u], ebs[u]);
+            else eas[u] = ebs[u] = -1;
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int64_t c = tb + (int64_t)(it0 + u) * 64;
+            if (it0 + u >= chunks || c >= n) break;
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                const int e = half ? ebs[u] : eas[u];
+                const int64_t i = c + half * 32 + lane;
+                const int64_t r = rank_round(e, lane, my);
+                if (i < n) {
+                    if (mode == MODE_PRUNE) {
+                        new_gate[i] = (e >= 0 && r < (int64_t)lim[e]) ? (int64_t)e : (int64_t)-1;
+                    } else {
+                        if (e >= 0) pos[r] = i;
+                        if (inv) inv[i] = r;
+                        if (mode == MODE_COUNT_POS && i >= grand) pos[i] = -1;
+                    }
+                }
+            }
+        }
+    }
+}
+
 // Plain histogram: every warp counts into its own shared-memory row (no atomics
 // between warps), rows are summed at the end, and each block issues one global
 // atomic per non-empty counter.
@@ -380,9 +518,29 @@ int run_bucket(int mode, const int64_t* gate, int64_t n, int n_expert, void* scr
                int64_t* new_gate, cudaStream_t st) {
     FMOE_REQUIRE(scratch != nullptr, "routing: scratch pointer is null");
     FMOE_REQUIRE(((uintptr_t)scratch & 15) == 0, "routing: scratch must be 16-byte aligned");
+    const bool vec = ((uintptr_t)gate & 15) == 0;
+    if (n > 0 && n <= (int64_t)kClMaxCtas * kClWarps * kClMaxChunks * 64 && n_expert <= kClMaxExperts) {
+        // one cluster: as many CTAs as give every warp about 256 entries, at most kClMaxCtas
+        const int n_cta = (int)std::min<int64_t>(kClMaxCtas, ceil_div(n, (int64_t)kClWarps * 256));
+        const int chunks = (int)ceil_div(n, (int64_t)n_cta * kClWarps * 64);
+        const size_t smem = ((size_t)kClWarps + 5) * n_expert * 4;
+        if (int rc = set_smem((const void*)bucket_cluster_kernel, smem)) return rc;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)n_cta);
+        cfg.blockDim = dim3(kClThreads);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = st;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = (unsigned)n_cta; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        FMOE_CUDA_TRY(cudaLaunchKernelEx(&cfg, bucket_cluster_kernel, mode, gate, n, n_expert, chunks, lec64, offsets, inout,
+                                         pos, inv, new_gate, vec));
+        return 0;
+    }
     const Geom g = make_geom(n, n_expert);
     const Scratch s = carve(scratch, n, n_expert);
-    const bool vec = ((uintptr_t)gate & 15) == 0;
     const size_t sm_hist = (size_t)kWarps * n_expert * 4, sm_apply = sm_hist;
     if (int rc = set_smem((const void*)tile_hist_kernel, sm_hist)) return rc;
     if (int rc = set_smem((const void*)apply_kernel, sm_apply)) return rc;

@@ -591,6 +591,23 @@ def peer_scatter_planned(input_buf, plan, out_rows):
     return _planned_move(lib.fmoe_peer_scatter_planned, "peer_scatter", input_buf, plan, out_rows)
 
 
+def peer_scatter_planned_rows(src, row_of, row_div, scale, plan, out_rows):
+    """peer_scatter_planned of rows that are produced on the way: token-side row i is
+    ``src[row_of[i] // row_div]``, times ``scale.flatten()[row_of[i]]`` when ``scale`` is given (rounded
+    once to the rows' dtype).  ``row_of``: int64, one entry per token-side row (more entries are ignored)."""
+    _check_cuda(src, row_of)
+    assert row_of.dtype == torch.int64 and src.dim() == 2 and src.is_contiguous() and row_of.is_contiguous()
+    if scale is not None:
+        _check_cuda(scale)
+        assert scale.dtype == src.dtype and scale.is_contiguous()
+    out = _recv_empty(src, out_rows)
+    with torch.cuda.device(src.device):
+        _run("peer_scatter", lib.fmoe_peer_scatter_planned_rows, _comm(src.device), _ptr(src), src.shape[0], _ptr(row_of),
+             int(row_div), _ptr(scale), _dtype_code(src), _ptr(out), _ptr(plan.buf), row_of.numel(), out_rows,
+             src.shape[1] * src.element_size(), plan.n_expert, _stream())
+    return out
+
+
 class PendingArrival:
     """Rows of a global_scatter that are still on their way (fmoe_arrival_t): give it to the grouped
     GEMM that reads them (``linear_forward_act`` / ``linear_backward_act``), which closes the exchange,
@@ -855,12 +872,14 @@ def combine_forward(buf, inv, score):
     return out
 
 
-def combine_backward(grad_out, buf, inv, score, need_score_grad=True):
+def combine_backward(grad_out, buf, inv, score, need_score_grad=True, need_buf_grad=True):
     """Returns (grad_buf, grad_score) of combine_forward.  Rows of grad_buf that no
-    slot maps to are left unwritten."""
+    slot maps to are left unwritten.  ``need_buf_grad=False``: only the score gradient (grad_buf None)."""
     _check_cuda(grad_out, buf, inv, score)
     n_tokens, top_k = score.shape
-    grad_buf = torch.empty_like(buf)
+    if not (need_score_grad or need_buf_grad):
+        return None, None
+    grad_buf = torch.empty_like(buf) if need_buf_grad else None
     grad_score = torch.empty_like(score) if need_score_grad else None
     with torch.cuda.device(buf.device):
         _run("combine_backward", lib.fmoe_combine_backward, _ptr(grad_out), _ptr(buf), _ptr(inv), _ptr(score), _ptr(grad_buf),

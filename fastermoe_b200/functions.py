@@ -335,10 +335,15 @@ class MOEScatterFused(Function):
     @staticmethod
     def forward(ctx, inp, pos, inv, top_k, n_rows, exch, scattered=None):
         inp = inp.contiguous()
-        # `scattered`: the same local scatter, queued earlier by the caller (at least n_rows rows)
-        buf = scattered if scattered is not None else fmoe_cuda.local_scatter(inp, pos, pos_div=top_k, n_rows=n_rows)
         ctx.exch, ctx.top_k, ctx.n_tokens, ctx.n_rows = exch, top_k, inp.shape[0], n_rows
         ctx.save_for_backward(inv)
+        if scattered is None and exch is not None and hasattr(exch, "scatter_rows"):
+            # the exchange's push reads inp[pos[i] // k] itself: no token-side copy in between
+            buf = exch.scatter_rows(inp, pos, top_k, None, exch.fwd_batch_size)
+            if buf is not None:
+                return buf
+        # `scattered`: the same local scatter, queued earlier by the caller (at least n_rows rows)
+        buf = scattered if scattered is not None else fmoe_cuda.local_scatter(inp, pos, pos_div=top_k, n_rows=n_rows)
         if exch is not None:
             buf = exch.scatter(buf, exch.fwd_batch_size)
         return buf
@@ -360,27 +365,38 @@ class MOEGatherCombine(Function):
     contribute zero, as the zero rows of the reference's ``_local_gather`` do."""
 
     @staticmethod
-    def forward(ctx, buf, inv, score, n_rows, exch):
+    def forward(ctx, buf, inv, score, n_rows, exch, pos=None):
+        """``pos`` (the inverse of ``inv``: pos[i] = flat gate entry of token-side row i), when given,
+        lets the backward's exchange produce its rows on the way."""
         buf = buf.contiguous()
         ctx.exch, ctx.global_rows = exch, buf.shape[0]
         if exch is not None:
             buf = exch.gather(buf, n_rows)
         score_c = score.contiguous().to(buf.dtype)
-        ctx.save_for_backward(buf, inv, score_c)
+        ctx.save_for_backward(buf, inv, score_c, pos)
         ctx.score_dtype = score.dtype
         return fmoe_cuda.combine_forward(buf, inv, score_c)
 
     @staticmethod
     def backward(ctx, grad_out):
-        buf, inv, score = ctx.saved_tensors
-        grad_buf, grad_score = fmoe_cuda.combine_backward(grad_out.contiguous(), buf, inv, score,
-                                                          need_score_grad=ctx.needs_input_grad[2])
+        buf, inv, score, pos = ctx.saved_tensors
         exch = ctx.exch
-        if exch is not None:
-            grad_buf = exch.scatter(grad_buf, ctx.global_rows)
+        grad_out = grad_out.contiguous()
+        grad_buf = None
+        if pos is not None and exch is not None and hasattr(exch, "scatter_rows"):
+            # grad_buf[i] = score[pos[i]] * grad_out[pos[i] // k] is formed by the push itself
+            grad_buf = exch.scatter_rows(grad_out, pos, score.shape[1], score, ctx.global_rows)
+        if grad_buf is not None:
+            _, grad_score = fmoe_cuda.combine_backward(grad_out, buf, inv, score, need_score_grad=ctx.needs_input_grad[2],
+                                                       need_buf_grad=False)
+        else:
+            grad_buf, grad_score = fmoe_cuda.combine_backward(grad_out, buf, inv, score,
+                                                              need_score_grad=ctx.needs_input_grad[2])
+            if exch is not None:
+                grad_buf = exch.scatter(grad_buf, ctx.global_rows)
         if grad_score is not None:
             grad_score = grad_score.to(ctx.score_dtype)
-        return grad_buf, None, grad_score, None, None
+        return grad_buf, None, grad_score, None, None, None
 
 
 class Exchange:
@@ -421,9 +437,9 @@ class PlannedExchange:
     the host knows neither the counts nor how many rows arrive; ``fwd_batch_size`` is the capacity
     of the expert-side buffers."""
     __slots__ = ("plan", "fwd_batch_size", "world_size", "num_expert", "overlap_sms", "pending", "token_rows", "early",
-                 "fused_gather")
+                 "fused_gather", "fused_scatter")
 
-    def __init__(self, plan, cap_rows, world_size, overlap_sms=0, token_rows=0, fused_gather=False):
+    def __init__(self, plan, cap_rows, world_size, overlap_sms=0, token_rows=0, fused_gather=False, fused_scatter=False):
         self.plan, self.fwd_batch_size, self.world_size = plan, int(cap_rows), world_size
         self.num_expert = plan.n_expert
         # > 0: the pushes run on that many SMs beside the grouped GEMMs that read (scatter) or write
@@ -434,6 +450,9 @@ class PlannedExchange:
         # the GEMM before a gather stores its rows straight into their owners' token-side buffers;
         # FusedExpertMLP takes part; its expert-side outputs are then placeholders nobody may read
         self.fused_gather = bool(fused_gather)
+        # the push of a scatter picks (and scales) its rows itself instead of reading a token-side buffer
+        # that a local scatter / the combine's backward would have to write first
+        self.fused_scatter = bool(fused_scatter)
 
     def flush(self):
         """Closes a scatter whose rows nobody waited for tile by tile, and a gather that was started early."""
@@ -471,6 +490,14 @@ class PlannedExchange:
             out, self.pending = fmoe_cuda.peer_scatter_planned_async(buf, self.plan, out_rows, self.overlap_sms)
             return out
         return fmoe_cuda.peer_scatter_planned(buf, self.plan, out_rows)
+
+    def scatter_rows(self, src, row_of, row_div, scale, out_rows):
+        """scatter of the rows ``[scale[row_of[i]] *] src[row_of[i] // row_div]`` without storing them on
+        the token side first; None when this exchange does not take that form."""
+        if not self.fused_scatter or self.overlap_sms > 0:
+            return None
+        self.flush()
+        return fmoe_cuda.peer_scatter_planned_rows(src, row_of, row_div, scale, self.plan, out_rows)
 
     def gather(self, buf, out_rows):
         early, self.early = self.early, None

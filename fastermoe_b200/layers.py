@@ -130,8 +130,10 @@ def _fmoe_general_global_forward(inp, gate, expert_fn, policy_fn, experts, num_e
             # the experts' last GEMM (and the input-gradient GEMM of their first layer) stores its rows
             # straight into the token-side buffers of their owners: no gather pass afterwards
             fused_gather = os.environ.get("FMOE_B200_FUSED_GATHER", "1") == "1"
+        # the scatters' pushes pick (forward) or pick and scale (backward) their rows themselves
+        fused_scatter = overlap == 0 and os.environ.get("FMOE_B200_FUSED_SCATTER", "1") == "1"
         exch = PlannedExchange(routing.plan, routing.n_recv, world_size, overlap_sms=overlap, token_rows=routing.n_rows,
-                               fused_gather=fused_gather)
+                               fused_gather=fused_gather, fused_scatter=fused_scatter)
         n_rows = routing.n_rows
         x = MOEScatterFused.apply(inp, routing.pos, routing.inv, top_k, n_rows, exch)
         x = expert_fn(x, [[experts]], ExpertCounts(routing.own_offsets_dev, exchange=exch), num_expert)
@@ -177,7 +179,8 @@ def _fmoe_general_global_forward(inp, gate, expert_fn, policy_fn, experts, num_e
             x = expert_fn(x, models, fwd_count, num_expert)
 
     if gate_score is not None:
-        out = MOEGatherCombine.apply(x, routing.inv, gate_score.reshape(n_tokens, top_k), n_rows, exch)
+        pos = routing.pos if getattr(exch, "fused_scatter", False) else None
+        out = MOEGatherCombine.apply(x, routing.inv, gate_score.reshape(n_tokens, top_k), n_rows, exch, pos)
     else:
         ones = torch.ones(n_tokens * top_k, 1, dtype=x.dtype, device=x.device)
         out = MOEGatherCombine.apply(x, routing.inv, ones, n_rows, exch)

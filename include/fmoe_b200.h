@@ -433,6 +433,16 @@ int fmoe_peer_plan_read(const void* plan_host, int32_t n_expert, int32_t n_worke
 int fmoe_peer_scatter_planned(fmoe_comm_t comm, const void* local_in, void* global_out, const void* plan,
                               int64_t in_rows, int64_t out_rows, int64_t row_bytes, int32_t n_expert,
                               fmoe_stream_t stream);
+/* fmoe_peer_scatter_planned whose token-side rows are produced on the way instead of being read from a
+ * buffer: row i (i < in_rows entries of row_of) is  src[row_of[i] / row_div]  (scale NULL: the local
+ * scatter of fmoe/functions.py:72-74 with the division by top_k folded in), or that row times
+ * scale[row_of[i]] rounded once to `dtype` (the gradient rows of the gate-score combine,
+ * fmoe/layers.py:319-322 backward).  src has src_rows rows; an index outside it drops the row and raises
+ * status bit 8.  scale has the rows' dtype.  One pass over the data where local scatter + exchange make two. */
+int fmoe_peer_scatter_planned_rows(fmoe_comm_t comm, const void* src, int64_t src_rows, const int64_t* row_of,
+                                   int32_t row_div, const void* scale, int32_t dtype, void* global_out,
+                                   const void* plan, int64_t in_rows, int64_t out_rows, int64_t row_bytes,
+                                   int32_t n_expert, fmoe_stream_t stream);
 int fmoe_peer_gather_planned(fmoe_comm_t comm, const void* global_in, void* local_out, const void* plan,
                              int64_t in_rows, int64_t out_rows, int64_t row_bytes, int32_t n_expert,
                              fmoe_stream_t stream);

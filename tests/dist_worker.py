@@ -278,11 +278,11 @@ def _make_layer(world, rank, E, d, h, k, act, bias, tens, dtype=torch.float32, g
     return m.to(dtype).cuda()
 
 
-def _run_layer(m, x):
+def _run_layer(m, x, loss_weight=None):
     m.zero_grad(set_to_none=True)
     x = x.detach().clone().requires_grad_(True)
     out = m(x)
-    out.sum().backward()
+    (out.sum() if loss_weight is None else (out * loss_weight).sum()).backward()
     g = {"out": out.detach(), "x": x.grad, "w1": m.experts.htoh4.weight.grad.clone(),
          "w2": m.experts.h4toh.weight.grad.clone(), "gate_w": m.gate.gate.weight.grad.clone()}
     if m.experts.htoh4.bias is not None:
@@ -378,7 +378,7 @@ def check_layer_bf16(rank, world):
     xs = tens["x"].view(world, T, d)
     m = _make_layer(world, rank, E, d, h, k, "gelu", True, tens, dtype=torch.bfloat16)
     x = xs[rank].bfloat16().cuda()
-    with switches(OVERLAP_SMS=0, FUSED_GATHER=0):      # the plain exchange: push, then the GEMMs
+    with switches(OVERLAP_SMS=0, FUSED_GATHER=0, FUSED_SCATTER=0):      # local scatter, push, GEMMs, push
         base = _run_layer(m, x)
     with torch.no_grad():
         idx, _ = m.gate(x)
@@ -404,11 +404,24 @@ def check_layer_bf16(rank, world):
     # the gather done by the GEMM that produces its rows (stores into the owners' buffers): same bits,
     # alone and together with an overlapped scatter
     for sms in ("0", "8"):
-        with switches(OVERLAP_SMS=sms, FUSED_GATHER=1):
+        with switches(OVERLAP_SMS=sms, FUSED_GATHER=1, FUSED_SCATTER=0):
             for _ in range(2):
                 over = _run_layer(m, x)
         for name, v in base.items():
             assert torch.equal(over[name], v), f"gather fused into the GEMM (scatter on {sms} SMs) differs in {name}"
+    # the scatters' pushes picking (forward) and scaling (backward) their rows themselves: same bits,
+    # also with an output gradient that differs from element to element
+    lw = torch.randn(x.shape, generator=torch.Generator().manual_seed(7 + rank)).to(x)
+    with switches(OVERLAP_SMS=0, FUSED_GATHER=0, FUSED_SCATTER=0):
+        base_w = _run_layer(m, x, lw)
+    for fg in ("0", "1"):
+        with switches(OVERLAP_SMS=0, FUSED_GATHER=fg, FUSED_SCATTER=1):
+            for _ in range(2):
+                over = _run_layer(m, x)
+            over_w = _run_layer(m, x, lw)
+        for name, v in base.items():
+            assert torch.equal(over[name], v), f"scatter that produces its rows (fused gather {fg}) differs in {name}"
+            assert torch.equal(over_w[name], base_w[name]), f"scatter that scales its rows (fused gather {fg}) differs in {name}"
     from fastermoe_b200 import fmoe_cuda as fc
     assert fc.device_status() == 0
     os.environ["FMOE_FUSE_GRAN"] = "1"
@@ -454,12 +467,12 @@ def check_graph_step(rank, world):
         loss.backward()
         return out.detach().clone(), loss.detach().clone(), xi.grad.clone(), {n: p.grad.clone() for n, p in m.named_parameters()}
 
-    with switches(OVERLAP_SMS=0, FUSED_GATHER=0):
+    with switches(OVERLAP_SMS=0, FUSED_GATHER=0, FUSED_SCATTER=0):
         want = [eager(x) for x in xs[1:]]
     # without and with the pushes running beside the GEMMs (a second stream in the graph), and with
     # the gathers done by the GEMMs' own epilogues
-    for sms, fused_gather in (("0", "0"), ("8", "0"), ("0", "1")):
-        with switches(OVERLAP_SMS=sms, FUSED_GATHER=fused_gather):
+    for sms, fused_gather, fused_scatter in (("0", "0", "0"), ("8", "0", "0"), ("0", "1", "0"), ("0", "1", "1")):
+        with switches(OVERLAP_SMS=sms, FUSED_GATHER=fused_gather, FUSED_SCATTER=fused_scatter):
             step = GraphedStep(m, xs[0], input_grad=True)
             for x, (out, loss, gx, grads) in zip(xs[1:], want):
                 got_loss = step(x)

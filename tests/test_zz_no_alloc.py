@@ -59,15 +59,16 @@ def test_static_scratch_matches_caller_scratch_twice():
 
 def test_static_calls_queued_back_to_back_and_edge_sizes():
     """Calls that follow each other on one stream need no host synchronisation between them and
-    nothing cleared: three calls with different sizes and expert counts (more than 256 experts makes
-    the tile scan run several passes; n = 0 reads nothing) are queued without a sync, then every
+    nothing cleared: calls with different sizes and expert counts (small inputs take the single-launch
+    form, large ones the four passes, where more than 256 experts make the tile scan run several
+    passes; n = 0 reads nothing) are queued without a sync, then every
     output is compared with fmoe_count_and_pos and with the oracle."""
     from fastermoe_b200 import _lib
     from oracle import moe_oracle as O
     lib = _lib.lib
     rng = np.random.default_rng(1)
     stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
-    cases = [(200000, 8), (0, 5), (20000, 300), (777, 1)]
+    cases = [(200000, 8), (0, 5), (20000, 300), (140000, 300), (777, 1)]
     assert all(lib.fmoe_routing_scratch_bytes(n, e) <= lib.fmoe_static_scratch_capacity() for n, e in cases)
     gates, outs = [], []
     for n, n_expert in cases:                               # queued back to back, no sync in between
