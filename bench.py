@@ -18,7 +18,10 @@ Workloads (all synthetic, seeded; "per GPU" sizes, experts sharded over the rank
       shadowing (FMOE_ENABLE_DYNREP=1), in both orders: capacity cuts every expert ("5a"), or experts
       the policy replicates are spared ("5b").
 
-One "step" = forward + backward (loss = sum of the output) of the layer on one batch.  The printed
+One "step" = forward + backward (loss = sum of the output) of the layer on one batch; where the step has
+no host read (N = 1; N > 1 with the device-planned exchange) it is replayed as one CUDA graph through the
+library's GraphedStep (``step_form``; ``eager_ms_per_step`` is the same step launched from Python, and
+``--eager`` times that instead).  The printed
 JSON line carries: ``value`` (device-resident inputs), ``e2e`` (inputs copied from pinned host memory
 and the loss read back every step -- when the step replays as a CUDA graph, the host reads step i's
 loss, copied to pinned memory, while step i+1 runs), ``roofline`` of the dominant kernel (the grouped expert GEMM,
@@ -72,7 +75,7 @@ def measured_peaks():
 
 class ClockSampler:
     """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
-    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+    QUERY = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
              "clocks_event_reasons.sw_power_cap")
 
@@ -83,7 +86,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "25"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
         except OSError:
@@ -93,17 +96,29 @@ class ClockSampler:
         for line in self.proc.stdout:
             self.rows.append([c.strip() for c in line.split(",")])
 
-    def stop(self):
+    def stop(self, t0=None, t1=None):
+        """Summary of the samples taken between the wall-clock times t0 and t1 (all samples when none fall
+        inside, or when no window is given)."""
         if self.proc is None:
             return None
-        time.sleep(0.15)
+        time.sleep(0.05)
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
-        clocks, reasons, mx = [], set(), None
+        import datetime
+        rows = []
         for r in self.rows:
+            try:
+                ts = datetime.datetime.strptime(r[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+            except (ValueError, IndexError):
+                ts = None
+            rows.append((ts, r[1:]))
+        inside = [r for ts, r in rows if ts is not None and t0 is not None and t1 is not None and t0 <= ts <= t1]
+        window = "timed region" if inside else "whole run under load"
+        clocks, reasons, mx = [], set(), None
+        for r in (inside or [r for _, r in rows]):
             try:
                 clocks.append(float(r[0]))
                 mx = float(r[1])
@@ -115,7 +130,7 @@ class ClockSampler:
         if not clocks:
             return None
         return {"sm_mhz": statistics.median(clocks), "sm_max_mhz": mx, "reasons": sorted(reasons),
-                "samples": len(clocks)}
+                "samples": len(clocks), "window": window}
 
 
 # ------------------------------------------------------------------------------- CPU reference arm
@@ -631,15 +646,29 @@ def run_ours(args):
 
     for _ in range(max(args.warmup, 3)):
         step_resident()
-    sampler = ClockSampler(env.local_rank) if rank == 0 else None
-    if sampler:
-        sampler.start()
+    # kernels of this library launched per step (counted on an eager step; a replayed graph runs the same ones)
     prof = fmoe_cuda.Profile()
     fmoe_cuda.set_profile(prof)
-    total_ms = env.timed(step_resident, args.steps)
+    step_resident()
     fmoe_cuda.set_profile(None)
-    clocks = sampler.stop() if sampler else None
-    launches = prof.launches
+    launches = prof.launches * args.steps
+    # A step that never waits on the host (N = 1; N > 1 with the counts swapped through peer memory and the
+    # plan built on the device) is replayed as ONE CUDA graph (fastermoe_b200.GraphedStep, the library's own
+    # public wrapper): the GPU then sees the kernels back to back instead of at the pace of the Python glue.
+    graphable = not args.eager and (world == 1 or "planned on the device" in (exchange_form(layer, dev) or ""))
+    graphed, eager_ms = None, None
+    sampler = ClockSampler(env.local_rank) if rank == 0 else None
+    if sampler:
+        sampler.start()      # early: the tool takes longer to start than the timed region lasts
+    if graphable:
+        from fastermoe_b200 import GraphedStep
+        graphed = GraphedStep(layer, x_dev.detach(), input_grad=True)
+        eager_ms = env.timed(step_resident, args.steps)
+        for _ in range(3):
+            graphed.replay()
+    t_region = time.time()
+    total_ms = env.timed(graphed.replay if graphed is not None else step_resident, args.steps)
+    clocks = sampler.stop(t_region, time.time()) if sampler else None
 
     e2e_ms = e2e_eager_ms = None
     used_graph = False
@@ -647,14 +676,9 @@ def run_ours(args):
         for _ in range(2):
             step_e2e()
         e2e_eager_ms = e2e_ms = env.timed(step_e2e, args.steps)
-        graphable = world == 1 or "planned on the device" in (exchange_form(layer, dev) or "")
-        if graphable:
-            # The step never waits on the host (at N > 1: counts swapped through peer memory, plan built on
-            # the device), so the whole forward+backward is replayed as one CUDA graph
-            # (fastermoe_b200.GraphedStep): per step one device-to-device copy of the prefetched batch
-            # into the captured input, one graph launch, one read of the loss.
-            from fastermoe_b200 import GraphedStep
-            graphed = GraphedStep(layer, x_dev.detach(), input_grad=True)
+        if graphed is not None:
+            # per step one device-to-device copy of the prefetched batch into the captured input, one graph
+            # launch, one read of the loss
             used_graph = True
 
             # The loss of every step is copied to pinned host memory on the stream and read by the host one
@@ -741,6 +765,9 @@ def run_ours(args):
     line = {
         "metric": "moe_layer_fwd_bwd_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
+        "step_form": ("one CUDA graph replay per step (fastermoe_b200.GraphedStep)" if graphed is not None
+                      else "eager: every kernel launched from Python"),
+        "eager_ms_per_step": (eager_ms / args.steps if eager_ms is not None else ms_per_step),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": dict(workload_config(name, world), **({"exchange": form} if world > 1 else {})),
         "e2e": ({"value": e2e_val, "unit": "tokens/s",
@@ -789,6 +816,7 @@ def run_ours(args):
         if extra != "none" and world > 1:
             import gc
             del layer, step_resident, step_e2e, take, x_dev
+            graphed = None
             gc.collect()
             torch.cuda.empty_cache()
             line["configs"] = []
@@ -825,6 +853,7 @@ def main():
     ap.add_argument("--no-parity", action="store_true", help="omit the multi-GPU self-check")
     ap.add_argument("--kernel-list", default=None, metavar="PATH", help="also write a per-kernel device-time table "
                     "of three resident steps (rank 0) to PATH")
+    ap.add_argument("--eager", action="store_true", help="time eager steps even where the step can replay as a CUDA graph")
     ap.add_argument("--skip-e2e", action="store_true", help="omit the host-buffer (e2e) leg (profiling runs)")
     ap.add_argument("--skip-cpu", action="store_true", help="omit the CPU baseline leg (profiling runs)")
     args = ap.parse_args()

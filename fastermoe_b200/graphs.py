@@ -83,3 +83,8 @@ class GraphedStep:
         self.static_input.detach().copy_(x, non_blocking=True)
         self.graph.replay()
         return self.loss
+
+    def replay(self):
+        """The step once more on the batch the captured input buffer already holds."""
+        self.graph.replay()
+        return self.loss
