@@ -12,7 +12,8 @@ Workloads (all synthetic, seeded; "per GPU" sizes, experts sharded over the rank
   c3  8192 tokens, d 2048, h 8192, 4 experts per GPU, gate bias -1.2 ln(rank of expert): Zipf(1.2)
       popularity, the first GPU owns the popular experts.
   c4  16384 tokens, d 4096, h 16384, 1 expert per GPU, two distinct experts per token drawn uniformly,
-      ReLU, no bias; measured with the smart schedule (FMOE_ENABLE_FUSE=1) and with the plain schedule.
+      ReLU, no bias; FMOE_ENABLE_FUSE=1, measured in both forms the flag can select: the exchange fused
+      with the GEMMs on the device-planned path, and the reference-shaped NCCL pipeline (FMOE_B200_SMART=nccl).
   c5  8192 tokens, d 1024, h 4096, 2 experts per GPU, one expert receives 40 % of all assignments,
       capacity ceil(1.2 x tokens) per expert, topology-aware HirGate (2 groups of GPUs), dynamic
       shadowing (FMOE_ENABLE_DYNREP=1), in both orders: capacity cuts every expert ("5a"), or experts
@@ -296,7 +297,8 @@ def hot_bias_for_share(gate_w, share_tokens, seed, d):
 
 
 def build_layer(env, name, variant=None):
-    """Layer + pinned host batch of workload `name`.  variant: c4 "fuse"/"plain"; c5 "5a"/"5b"."""
+    """Layer + pinned host batch of workload `name`.  variant: c4 "fuse" (FMOE_ENABLE_FUSE=1) / "nccl" (the same
+    flag with FMOE_B200_SMART=nccl: the reference-shaped NCCL pipeline); c5 "5a"/"5b"."""
     import torch
     from fastermoe_b200 import FMoETransformerMLP
     from fastermoe_b200.gates import NaiveGate, gen_hir_capacity_gate
@@ -328,7 +330,7 @@ def build_layer(env, name, variant=None):
         os.environ["FMOE_ENABLE_DYNREP"], os.environ["FMOE_POLICY_CONSTANTS"] = "1", "reference"
         gate_cls = gen_hir_capacity_gate(rank, max(world // 2, 1), c["capacity"], spare_shadowed=(variant == "5b"))
     act = {"gelu": torch.nn.GELU(), "relu": torch.nn.ReLU()}[c["activation"]]
-    os.environ["FMOE_ENABLE_FUSE"] = "1" if variant == "fuse" else "0"
+    os.environ["FMOE_ENABLE_FUSE"] = "1" if variant in ("fuse", "nccl") else "0"
     try:
         layer = FMoETransformerMLP(num_expert=E, d_model=d, d_hidden=h, world_size=world, top_k=k, activation=act,
                                    gate=gate_cls, bias=c["bias"])
@@ -401,14 +403,32 @@ def make_steps(env, layer, x_host):
 
 def exchange_form(layer, dev):
     from fastermoe_b200 import fmoe_cuda
-    if layer.enable_fuse:
-        return "smart schedule (NCCL, pipelined with the expert GEMMs)"
+    shadowing = not getattr(layer.policy_fn, "never_shadows", False)
+    if layer.enable_fuse and (shadowing or os.environ.get("FMOE_B200_SMART", "peer") == "nccl"):
+        return "smart schedule in the reference's shape (one NCCL group per pipeline step beside the step's expert GEMMs)"
     if fmoe_cuda.peer_slot_bytes(dev) > 0:
-        sync = (os.environ.get("FMOE_B200_NOSYNC", "1") == "0" or
-                not getattr(layer.policy_fn, "never_shadows", False))
-        return ("direct stores into peer memory over NVLink, " +
-                ("host-planned (count table read back)" if sync else "planned on the device (no host read of the counts)"))
+        sync = os.environ.get("FMOE_B200_NOSYNC", "1") == "0" or shadowing
+        if sync:
+            return "direct stores into peer memory over NVLink, host-planned (count table read back)"
+        return ("direct stores into peer memory over NVLink, planned on the device (no host read of the counts); "
+                "gathers stored by the GEMM epilogues, scatters form their rows on the way" +
+                (" [selected by FMOE_ENABLE_FUSE=1]" if layer.enable_fuse else ""))
     return "NCCL send/receive, one pair per peer"
+
+
+def graph_or_eager(env, layer, x_dev, step_resident, allow=True):
+    """(callable that runs one resident step, description, GraphedStep or None): one CUDA graph replay per
+    step where the step has no host read, else the eager step."""
+    graphable = allow and (env.world == 1 or "planned on the device" in (exchange_form(layer, env.dev) or ""))
+    if graphable:
+        from fastermoe_b200 import GraphedStep
+        try:
+            graphed = GraphedStep(layer, x_dev.detach(), input_grad=True)
+            return graphed.replay, "one CUDA graph replay per step (fastermoe_b200.GraphedStep)", graphed
+        except Exception as e:              # e.g. a receive pool too small for this workload's arena
+            env.torch.cuda.synchronize()
+            return step_resident, f"eager (graph capture failed: {type(e).__name__}: {str(e)[:120]})", None
+    return step_resident, "eager: every kernel launched from Python", None
 
 
 def realised_rows(env, layer, x_dev):
@@ -473,9 +493,33 @@ def measure_config(env, name, variant, steps, warmup):
     from fastermoe_b200 import fmoe_cuda
     layer, x_host = build_layer(env, name, variant)
     step_resident, _, _, x_dev = make_steps(env, layer, x_host)
+    old_smart = os.environ.get("FMOE_B200_SMART")
+    if variant == "nccl":
+        os.environ["FMOE_B200_SMART"] = "nccl"        # read by every forward
+    try:
+        return _measure_built(env, name, variant, steps, warmup, layer, x_host, step_resident, x_dev)
+    finally:
+        if old_smart is None:
+            os.environ.pop("FMOE_B200_SMART", None)
+        else:
+            os.environ["FMOE_B200_SMART"] = old_smart
+
+
+def _measure_built(env, name, variant, steps, warmup, layer, x_host, step_resident, x_dev):
+    import gc
+    torch = env.torch
+    from fastermoe_b200 import fmoe_cuda
     for _ in range(max(warmup, 3)):
         step_resident()
-    ms = env.timed(step_resident, steps) / steps
+    eager_ms = env.timed(step_resident, steps) / steps
+    step, form, graphed = graph_or_eager(env, layer, x_dev, step_resident)
+    if graphed is not None:
+        for _ in range(3):
+            step()
+        ms = env.timed(step, steps) / steps
+    else:
+        ms = eager_ms
+    del step, graphed
     table, kept = realised_rows(env, layer, x_dev)
     rows = table.sum(2).sum(0).tolist()
     status = fmoe_cuda.device_status(env.dev)
@@ -483,6 +527,7 @@ def measure_config(env, name, variant, steps, warmup):
         fmoe_cuda.lib.fmoe_device_status_clear()
     T = CONFIGS[name]["tokens_per_gpu"]
     res = {"config": name + (f" ({variant})" if variant else ""), "tokens_per_s": T * env.world / (ms / 1e3), "ms_per_step": ms,
+           "step_form": form, "eager_ms_per_step": eager_ms,
            "steps": steps, "warmup": max(warmup, 3), "rows_per_gpu": rows, "kept_fraction_of_assignments": kept,
            "exchange": exchange_form(layer, env.dev) if env.world > 1 else None, "device_status": status,
            "roofline": layer_roofline(env, name, table, ms), "workload": workload_config(name, env.world)}
@@ -640,7 +685,7 @@ def run_ours(args):
     name = args.config
     c = CONFIGS[name]
     T, d, h, E, k = (c[n] for n in ("tokens_per_gpu", "d_model", "d_hidden", "experts_per_gpu", "top_k"))
-    variant = {"c4": "fuse" if world > 1 else "plain", "c5": "5b"}.get(name)
+    variant = {"c4": "fuse", "c5": "5b"}.get(name)
     layer, x_host = build_layer(env, name, variant)
     step_resident, step_e2e, take, x_dev = make_steps(env, layer, x_host)
 
@@ -655,19 +700,17 @@ def run_ours(args):
     # A step that never waits on the host (N = 1; N > 1 with the counts swapped through peer memory and the
     # plan built on the device) is replayed as ONE CUDA graph (fastermoe_b200.GraphedStep, the library's own
     # public wrapper): the GPU then sees the kernels back to back instead of at the pace of the Python glue.
-    graphable = not args.eager and (world == 1 or "planned on the device" in (exchange_form(layer, dev) or ""))
-    graphed, eager_ms = None, None
+    eager_ms = None
     sampler = ClockSampler(env.local_rank) if rank == 0 else None
     if sampler:
         sampler.start()      # early: the tool takes longer to start than the timed region lasts
-    if graphable:
-        from fastermoe_b200 import GraphedStep
-        graphed = GraphedStep(layer, x_dev.detach(), input_grad=True)
+    step, step_form, graphed = graph_or_eager(env, layer, x_dev, step_resident, allow=not args.eager)
+    if graphed is not None:
         eager_ms = env.timed(step_resident, args.steps)
         for _ in range(3):
-            graphed.replay()
+            step()
     t_region = time.time()
-    total_ms = env.timed(graphed.replay if graphed is not None else step_resident, args.steps)
+    total_ms = env.timed(step, args.steps)
     clocks = sampler.stop(t_region, time.time()) if sampler else None
 
     e2e_ms = e2e_eager_ms = None
@@ -724,7 +767,7 @@ def run_ours(args):
     fmoe_cuda.set_profile(None)
 
     if args.kernel_list:
-        write_kernel_list(env, step_resident, args.kernel_list, name)
+        write_kernel_list(env, step, args.kernel_list, f"{name} ({step_form.split(':')[0].split(' (')[0]})")
 
     form = exchange_form(layer, dev) if world > 1 else None
     status = fmoe_cuda.device_status(dev)
@@ -765,8 +808,7 @@ def run_ours(args):
     line = {
         "metric": "moe_layer_fwd_bwd_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
-        "step_form": ("one CUDA graph replay per step (fastermoe_b200.GraphedStep)" if graphed is not None
-                      else "eager: every kernel launched from Python"),
+        "step_form": step_form,
         "eager_ms_per_step": (eager_ms / args.steps if eager_ms is not None else ms_per_step),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": dict(workload_config(name, world), **({"exchange": form} if world > 1 else {})),
@@ -821,7 +863,7 @@ def run_ours(args):
             torch.cuda.empty_cache()
             line["configs"] = []
             for item in extra.split(","):
-                for variant in {"c4": ("fuse", "plain"), "c5": ("5a", "5b")}.get(item, (None,)):
+                for variant in {"c4": ("fuse", "nccl"), "c5": ("5a", "5b")}.get(item, (None,)):
                     try:
                         line["configs"].append(measure_config(env, item, variant, args.extra_steps, 3))
                     except Exception as e:

@@ -96,6 +96,14 @@ def _fmoe_general_global_forward(inp, gate, expert_fn, policy_fn, experts, num_e
     early = None
     cap_rows = 0
     no_policy = policy_fn is None or getattr(policy_fn, "never_shadows", False)
+    # The smart schedule's aim -- rows travelling while the experts compute (cuda/fused_compute.cuh:289-349)
+    # -- is met on the device-planned path by the GEMMs themselves (outputs stored straight into their
+    # owners' buffers; optionally the scatter's push beside the first product), so the flag selects that path
+    # whenever nothing is shadowed.  FMOE_B200_SMART=nccl keeps the reference's shape: one NCCL group per
+    # pipeline step on a side stream, the step's GEMMs on the compute stream (csrc/fused.cu), which is also
+    # what runs when experts are shadowed.
+    if enable_fuse and no_policy and fused and os.environ.get("FMOE_B200_SMART", "peer") != "nccl":
+        enable_fuse = False
     if world_size > 1 and not enable_fuse:
         # Nothing has to come back to the host when no shadowing policy wants to see the counts, the
         # experts are one fused module (it reads its segment offsets on the device) and the rows

@@ -324,10 +324,16 @@ def check_layer(rank, world):
         for name, v in got.items():
             assert torch.equal(synced[name], v), f"host-planned and device-planned exchange differ in {name}"
         # smart schedule against the plain one, all pipeline granularities
+        m.enable_fuse = True          # nothing shadowed: the flag selects the device-planned path itself
+        same = _run_layer(m, xs[rank].cuda())
+        m.enable_fuse = False
+        for name, v in got.items():
+            assert torch.equal(same[name], v), f"smart-schedule flag without shadows differs in {name}"
         for gran in ("1", "2", "4"):
             os.environ["FMOE_FUSE_GRAN"] = gran
             m.enable_fuse = True
-            fused = _run_layer(m, xs[rank].cuda())
+            with switches(SMART="nccl"):
+                fused = _run_layer(m, xs[rank].cuda())
             m.enable_fuse = False
             for name, v in got.items():
                 torch.testing.assert_close(fused[name], v, rtol=1e-5, atol=2e-5, msg=lambda s, n=name: f"fused {gran} {n}: {s}")
@@ -426,7 +432,8 @@ def check_layer_bf16(rank, world):
     assert fc.device_status() == 0
     os.environ["FMOE_FUSE_GRAN"] = "1"
     m.enable_fuse = True
-    fused = _run_layer(m, x)
+    with switches(SMART="nccl"):
+        fused = _run_layer(m, x)
     m.enable_fuse = False
     for name in ("out", "x", "w1", "w2", "b1", "b2"):
         # the smart schedule accumulates weight gradients step by step in 16 bits
@@ -615,7 +622,8 @@ def gpu_full_size(rank, world, port):
     plain = _run_layer(m, x)
     os.environ["FMOE_FUSE_GRAN"] = "1"
     m.enable_fuse = True
-    fused = _run_layer(m, x)
+    with switches(SMART="nccl"):
+        fused = _run_layer(m, x)
     m.enable_fuse = False
     for name, v in plain.items():
         assert torch.isfinite(v.float()).all(), f"config 4: {name} not finite"
