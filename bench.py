@@ -25,7 +25,7 @@ library's GraphedStep (``step_form``; ``eager_ms_per_step`` is the same step lau
 ``--eager`` times that instead).  The printed
 JSON line carries: ``value`` (device-resident inputs), ``e2e`` (inputs copied from pinned host memory
 and the loss read back every step -- when the step replays as a CUDA graph, the host reads step i's
-loss, copied to pinned memory, while step i+1 runs), ``roofline`` of the dominant kernel (the grouped expert GEMM,
+loss, copied to pinned memory, while the next two steps run), ``roofline`` of the dominant kernel (the grouped expert GEMM,
 timed with CUDA events on the launching stream), ``cpu_baseline`` (the reference's CPU path on a
 bounded sample of the same workload).  With N > 1 it also carries ``parity`` -- an untimed
 self-check of the multi-GPU path against the CPU oracle, run after the timed region -- and, with N = 8
@@ -713,9 +713,14 @@ def run_ours(args):
     total_ms = env.timed(step, args.steps)
     clocks = sampler.stop(t_region, time.time()) if sampler else None
 
-    e2e_ms = e2e_eager_ms = None
+    e2e_ms = e2e_eager_ms = h2d_alone_ms = None
     used_graph = False
     if not args.skip_e2e:
+        # the batch's host-to-device copy on its own, all ranks copying at once: when this is close to the
+        # e2e step time, the step is bound by the host link, not by the layer
+        stage = torch.empty_like(x_dev.detach())
+        h2d_alone_ms = env.timed(lambda: stage.copy_(x_host, non_blocking=True), 10) / 10
+        del stage
         for _ in range(2):
             step_e2e()
         e2e_eager_ms = e2e_ms = env.timed(step_e2e, args.steps)
@@ -724,30 +729,32 @@ def run_ours(args):
             # launch, one read of the loss
             used_graph = True
 
-            # The loss of every step is copied to pinned host memory on the stream and read by the host one
-            # step later, while the next step already runs: the host never leaves the GPU idle to fetch a
-            # scalar (what a training loop that logs its loss does).
-            loss_host = torch.zeros(2, dtype=torch.float32).pin_memory()
-            loss_ready = [torch.cuda.Event(), torch.cuda.Event()]
-            state = {"i": 0, "losses": []}
+            # The loss of every step is copied to pinned host memory on the stream and read by the host up to
+            # two steps later, while the next steps already run: the host never leaves the GPU idle to fetch
+            # a scalar (what a training loop that logs its loss does).
+            lag = 2                      # steps the host may run ahead of the loss it reads
+            loss_host = torch.zeros(lag + 1, dtype=torch.float32).pin_memory()
+            loss_ready = [torch.cuda.Event() for _ in range(lag + 1)]
+            state = {"i": 0, "read": 0, "losses": []}
 
-            def read_previous():
-                if state["i"] > 0:
-                    slot = (state["i"] - 1) & 1
+            def read_until(n):
+                while state["read"] < n:
+                    slot = state["read"] % (lag + 1)
                     loss_ready[slot].synchronize()
                     state["losses"].append(float(loss_host[slot]))
+                    state["read"] += 1
 
             def step_e2e_graph():
                 loss = graphed(take())
-                slot = state["i"] & 1
+                slot = state["i"] % (lag + 1)
                 loss_host[slot:slot + 1].copy_(loss.detach().reshape(1), non_blocking=True)
                 loss_ready[slot].record()
-                read_previous()
                 state["i"] += 1
+                read_until(state["i"] - lag)
 
             def read_last():
-                read_previous()
-                state["i"] = 0
+                read_until(state["i"])
+                state["i"] = state["read"] = 0
 
             for _ in range(2):
                 step_e2e_graph()
@@ -817,8 +824,8 @@ def run_ours(args):
                  "note": "a training step: the batch is copied in, only the scalar loss is read back (the [T,d] "
                          "output and the gradients stay on the device)" +
                          ("; graphed steps: every step's loss is copied to pinned host memory and read by the host "
-                          "while the next step runs; eager steps: loss.item() each step" if used_graph else ""),
-                 "ms_per_step": e2e_ms / args.steps, "cuda_graph": used_graph,
+                          "while the next two steps run; eager steps: loss.item() each step" if used_graph else ""),
+                 "ms_per_step": e2e_ms / args.steps, "cuda_graph": used_graph, "h2d_copy_alone_ms": h2d_alone_ms,
                  "eager_ms_per_step": e2e_eager_ms / args.steps} if e2e_ms else None),
         "gpu_launches": launches, "clocks": clocks, "roofline": roofline,
         "layer_tensor_roofline_frac": layer_frac, "per_op_ms": per_op,
