@@ -32,7 +32,8 @@ class Arrival(ctypes.Structure):
     """Mirror of fmoe_arrival_t."""
     _fields_ = [("comm", c_void_p), ("plan", c_void_p), ("out", c_void_p), ("in_rows", c_int64), ("out_rows", c_int64),
                 ("row_bytes", c_int64), ("n_expert", c_int32), ("overlap_sms", c_int32), ("gather", c_int32),
-                ("use", c_int32)]
+                ("use", c_int32), ("src", c_void_p), ("row_of", c_void_p), ("scale", c_void_p), ("src_rows", c_int64),
+                ("row_div", c_int32), ("dtype", c_int32)]
 
 
 class FusedGeometry(ctypes.Structure):
@@ -117,6 +118,7 @@ _SIGS = {
     "fmoe_peer_arrival_finish": (I32, [P, P]),
     "fmoe_peer_gather_planned_async": (I32, [P, P, P, P, I64, I64, I64, I32, I32, I32, P, P]),
     "fmoe_peer_scatter_planned_rows": (I32, [P, P, I64, P, I32, P, I32, P, P, I64, I64, I64, I32, P]),
+    "fmoe_peer_scatter_fused_begin": (I32, [P, P, I64, P, I32, P, I32, P, P, I64, I64, I64, I32, P, P]),
     "fmoe_peer_gather_fused_begin": (I32, [P, P, P, I64, I64, I32, P, P]),
     "fmoe_linear_forward_overlapped": (I32, [P, P, P, P, P, P, I64, I64, I64, I32, I32, I32, P, P, P]),
     "fmoe_linear_backward_overlapped": (I32, [P, P, P, P, P, P, P, P, P, I64, I64, I64, I32, I32, I32, I32, P, P, P, P]),

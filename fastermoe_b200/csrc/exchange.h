@@ -62,7 +62,10 @@ int arrival_wait_of(const fmoe_arrival_t* arrival, ArrivalWait* w);
 int done_words_of(const fmoe_arrival_t* departure, int** done, int** expected, int** ready, int* reserve_sms);
 // Fills the remote-output description of a fused gather's handle (gather == 2); enabled = 0 otherwise.
 struct GemmRemoteOut;
+struct GemmPushIn;
 int remote_out_of(const fmoe_arrival_t* departure, GemmRemoteOut* ro);
+// The same for the handle of a scatter that the consuming product performs itself (gather == 3).
+int push_in_of(const fmoe_arrival_t* arrival, GemmRemoteOut* ro, GemmPushIn* ps);
 
 // Device address of the status word that bounded waits raise (per device).
 int* device_status_ptr();

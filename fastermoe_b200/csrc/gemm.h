@@ -76,6 +76,32 @@ struct GemmRemoteOut {
     int enabled;
 };
 
+// The global_scatter that delivers a product's ragged-side input, done by the product itself: the two
+// spare warps of every CTA move this GPU's token-side rows to the GPUs that own their experts (plain
+// stores into peer memory, the push list of the exchange plan in expert-major order) and raise the
+// per-(source, expert) arrival flags that the TMA producer warps -- here and on the peers -- wait on
+// (GemmArrival).  The peer context (mapped areas, announcements, completion) is a GemmRemoteOut with
+// enabled = 2.  Rows may be formed on the way: token-side row i is src[row_of[i] / row_div], times
+// scale[row_of[i]] when scale is set (row_of null: row i of src).
+struct GemmPushIn {
+    const void* src;
+    const int64_t* row_of;
+    const void* scale;                 // same element type as the rows
+    int64_t src_rows;
+    int row_div;
+    const int* prefix;                 // push list: [n_slots + 1] first row of each segment in token-side order ...
+    const int* seg_sel;                //   [n_slots] destination rank (local_sel: this GPU)
+    const int* seg_src;                //   [n_slots] first token-side row
+    const int* seg_dst;                //   [n_slots] first row in the destination's expert-side buffer
+    int* seg_done;                     // [n_slots] rows stored so far, zero before the launch (the last CTA clears it)
+    const int64_t* expert_rows;        // rows this GPU receives / sends in this exchange (device words of the plan)
+    const int64_t* token_rows;
+    int64_t in_rows, out_rows;         // capacity of the token-side source / the expert-side buffer
+    int64_t row_vecs;                  // 16-byte pieces per row
+    int n_slots, n_expert, local_sel;
+    int flags_at, flag_sources, flag_experts;   // arrival flags in a header: u64 [2][flag_sources][flag_experts] at byte flags_at
+};
+
 struct LinearArgs {
     const void* x;       // [n_rows, in_feat]
     const void* weight;  // [n_expert, out_feat, in_feat]
@@ -89,6 +115,7 @@ struct LinearArgs {
     const GemmArrival* arrival = nullptr;  // x is still being filled by an exchange
     const GemmDone* done = nullptr;        // y is forwarded expert by expert while the product runs
     const GemmRemoteOut* remote = nullptr; // y is not stored here at all: its rows go to their owners
+    const GemmPushIn* push = nullptr;      // x is delivered by this product's own spare warps (with remote->enabled == 2)
 };
 
 struct LinearBwdArgs {
@@ -114,6 +141,7 @@ struct LinearBwdArgs {
     void* after_ctx = nullptr;
     const GemmDone* done = nullptr;        // grad_x is forwarded expert by expert while its product runs
     const GemmRemoteOut* remote = nullptr; // grad_x is not stored here at all: its rows go to their owners
+    const GemmPushIn* push = nullptr;      // grad_y is delivered by the input-gradient product's own spare warps
 };
 
 int simt_linear_forward(const LinearArgs& a, cudaStream_t st);

@@ -439,6 +439,142 @@ __device__ __forceinline__ void row_load(uint4* q, const uint16_t* src, bool val
     for (int i = 0; i < NCH; ++i) q[i] = valid ? __ldg(reinterpret_cast<const uint4*>(src) + i) : make_uint4(0, 0, 0, 0);
 }
 
+// ---- the spare warps' job when the product delivers its own input rows (GemmPushIn) ------------------
+// Segment k of the push list that holds token-side row `row` (last k with prefix[k] <= row).
+__device__ __forceinline__ int push_find_seg(const int* __restrict__ prefix, int n, int row) {
+    int lo = 0, hi = n - 1;
+    while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (__ldg(prefix + mid) <= row) lo = mid; else hi = mid - 1;
+    }
+    return lo;
+}
+
+template <bool BF16>
+__device__ __forceinline__ uint4 push_scale(uint4 v, float w) {
+    uint32_t* q = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float lo = w * cvt_in<BF16>((uint16_t)(q[i] & 0xffffu)), hi = w * cvt_in<BF16>((uint16_t)(q[i] >> 16));
+        q[i] = cvt_pack<BF16>(lo, hi);
+    }
+    return v;
+}
+
+// Mover `mover` of `movers` (two per CTA, all CTAs of the grid): units of consecutive rows of the push
+// list are dealt round-robin, so that at any time all movers work on one stretch of the list and
+// experts complete one after the other.  After the stores of a unit the warp fences once, books the rows
+// per segment and raises the arrival flag of a (destination, expert) segment that is complete.  Nothing
+// here waits for another GPU: a peer that never announced its buffer (rem_dest 0) gets no rows.
+template <bool BF16>
+__device__ void push_rows(const GemmPushIn& ps, const GemmRemoteOut& ro, const unsigned long long* rem_dest, int mover,
+                          int movers, int lane, unsigned long long epoch, int* status) {
+    const int S = ps.n_slots, W = ro.world, E = ps.n_expert;
+    const bool room = __ldcg(ps.expert_rows) <= ps.out_rows && __ldcg(ps.token_rows) <= ps.in_rows;
+    const int total = room ? __ldg(ps.prefix + S) : 0;
+    const int par = (int)(epoch & 1);
+    const int first_group = (W - 1) * E;              // slots before it hold rows kept for shadowed experts
+    auto flag_of = [&](int k) -> unsigned long long* {
+        const int q = k - first_group, i = q / W, dst = (ro.rank + q % W) % W;
+        if (k < first_group || i >= ps.flag_experts) return nullptr;
+        if (dst != ro.rank && rem_dest[dst] == 0ull) return nullptr;
+        return (unsigned long long*)(ro.base[dst] + ps.flags_at) + ((size_t)par * ps.flag_sources + ro.rank) * ps.flag_experts + i;
+    };
+    if (room && mover == 0) {
+        // segments without rows: their consumers need not wait
+        for (int k = first_group + lane; k < S; k += 32)
+            if (__ldg(ps.prefix + k + 1) == __ldg(ps.prefix + k)) {
+                unsigned long long* f = flag_of(k);
+                if (f) asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(f), "l"(epoch) : "memory");
+            }
+    }
+    // The first round moves small units, so that the first expert's rows are complete (and the tensor-core
+    // warps start) early; later rounds move up to 32 rows per unit: a unit ends with a system fence, which
+    // waits for the stores in flight (10+ microseconds on a busy link), so there should be few of them.
+    const int first_rows = max(4, min(8, total / max(1, movers)));
+    const int later_rows = max(8, min(32, (total - first_rows * movers) / max(1, 3 * movers)));
+    const int first_span = first_rows * movers;
+    bool bad_index = false;
+    for (int round = 0;; ++round) {
+        const int row_lo = round == 0 ? mover * first_rows : first_span + ((round - 1) * movers + mover) * later_rows;
+        if (row_lo >= total) break;
+        const int row_hi = min(row_lo + (round == 0 ? first_rows : later_rows), total);
+        const int k_lo = push_find_seg(ps.prefix, S, row_lo);
+        int row = row_lo, k = k_lo;
+        while (row < row_hi && k < S) {
+            const int k_beg = __ldg(ps.prefix + k), k_end = __ldg(ps.prefix + k + 1), n = min(row_hi, k_end) - row;
+            if (n > 0) {
+                const int sel = __ldg(ps.seg_sel + k), dst = sel == ps.local_sel ? ro.rank : sel;
+                const unsigned long long dest = rem_dest[dst];
+                if (dest) {
+                    const int off = row - k_beg;
+                    uint4* d = (uint4*)(ro.base[dst] + dest) + (int64_t)(__ldg(ps.seg_dst + k) + off) * ps.row_vecs;
+                    const int i0 = __ldg(ps.seg_src + k) + off;
+                    // lane l looks up where row l of the piece comes from (n <= 32), once for the whole piece
+                    int64_t from_l = -1;
+                    float w_l = 1.f;
+                    if (lane < n) {
+                        const int64_t at = ps.row_of ? __ldg(ps.row_of + i0 + lane) : (int64_t)(i0 + lane);
+                        from_l = ps.row_of ? at / ps.row_div : at;
+                        if (at < 0 || (ps.row_of && from_l >= ps.src_rows)) { from_l = -1; bad_index = true; }
+                        else if (ps.scale) w_l = cvt_in<BF16>(__ldg((const uint16_t*)ps.scale + at));
+                    }
+                    // two rows at a time, four 16-byte pieces of each per lane in flight
+                    for (int r = 0; r < n; r += 2) {
+                        const int64_t f0 = __shfl_sync(0xffffffffu, from_l, r), f1 = __shfl_sync(0xffffffffu, from_l, min(r + 1, 31));
+                        const float w0 = __shfl_sync(0xffffffffu, w_l, r), w1 = __shfl_sync(0xffffffffu, w_l, min(r + 1, 31));
+                        const bool ok0 = f0 >= 0, ok1 = r + 1 < n && f1 >= 0;
+                        const uint4* s0 = (const uint4*)ps.src + (ok0 ? f0 : 0) * ps.row_vecs;
+                        const uint4* s1 = (const uint4*)ps.src + (ok1 ? f1 : 0) * ps.row_vecs;
+                        uint4* d0 = d + (int64_t)r * ps.row_vecs;
+                        uint4* d1 = d0 + ps.row_vecs;
+                        for (int64_t c = lane; c < ps.row_vecs; c += 128) {
+                            uint4 v0[4], v1[4];
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                const bool in = c + 32 * j < ps.row_vecs;
+                                v0[j] = in && ok0 ? __ldcg(s0 + c + 32 * j) : make_uint4(0, 0, 0, 0);
+                                v1[j] = in && ok1 ? __ldcg(s1 + c + 32 * j) : make_uint4(0, 0, 0, 0);
+                            }
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                if (c + 32 * j >= ps.row_vecs) break;
+                                if (ok0) d0[c + 32 * j] = ps.scale ? push_scale<BF16>(v0[j], w0) : v0[j];
+                                if (ok1) d1[c + 32 * j] = ps.scale ? push_scale<BF16>(v1[j], w1) : v1[j];
+                            }
+                        }
+                    }
+                }
+                row += n;
+            }
+            ++k;
+        }
+        // this unit's stores are ordered before lane 0's fence by the warp barrier; the fence is cumulative
+        __syncwarp();
+        if (lane == 0) {
+            __threadfence_system();
+            int row2 = row_lo, k2 = k_lo;
+            while (row2 < row_hi && k2 < S) {
+                const int k_beg = __ldg(ps.prefix + k2), k_end = __ldg(ps.prefix + k2 + 1), n = min(row_hi, k_end) - row2;
+                if (n > 0) {
+                    const int before = atomicAdd(ps.seg_done + k2, n);
+                    if (before + n == k_end - k_beg) {
+                        unsigned long long* f = flag_of(k2);
+                        __threadfence_system();   // the other movers' shares were fenced before they were booked
+                        if (f) asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(f), "l"(epoch) : "memory");
+                    }
+                    row2 += n;
+                }
+                ++k2;
+            }
+        }
+        __syncwarp();
+    }
+    bad_index = __any_sync(0xffffffffu, bad_index);
+    if (bad_index && lane == 0) atomicOr(status, 8);
+    if (!room && mover == 0 && lane == 0) atomicOr(status, 64);
+}
+
 struct Tile {
     int e, row0, rows, col0, chunks;  // rows/row0: output rows of the tile (FWD/DGRAD: tokens; WGRAD: weight rows)
     int m_lo, m_hi;                   // WGRAD: contraction range
@@ -472,7 +608,7 @@ template <int MODE, bool BF16, bool CTA2>
 __global__ void __launch_bounds__(THREADS, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const __grid_constant__ HostSegs hs, const __grid_constant__ OutMaps om,
-                    const __grid_constant__ GemmRemoteOut ro, const Params p) {
+                    const __grid_constant__ GemmRemoteOut ro, const __grid_constant__ GemmPushIn ps, const Params p) {
     using C = Cfg<CTA2>;
     constexpr int STAGES = C::STAGES, STAGE_BYTES = C::STAGE_BYTES, TILE_M = C::TILE_M, B_COLS = C::B_COLS;
     // Pairs: TMA completions of both CTAs go straight to the leader's barriers, so the MMA
@@ -547,9 +683,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             *(volatile int*)p.done_ready = 1;
         }
     }
-    const bool remote = MODE != MODE_WGRAD && ro.enabled != 0;
+    // ro.enabled: 1 = the output rows go to their owners (epilogue), 2 = the input rows are delivered by
+    // the spare warps of this kernel on every GPU (ps); both exchange through the peers' announcements.
+    const bool peer = MODE != MODE_WGRAD && ro.enabled != 0;
+    const bool remote = peer && ro.enabled == 1;
     unsigned long long rem_epoch = 0;
-    if (remote) {
+    if (peer) {
         // where every rank wants the rows of this exchange (bounded wait for its announcement)
         rem_epoch = __ldcg(ro.seq) + 1;
         const int par = (int)(rem_epoch & 1);
@@ -764,6 +903,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             }
             if (++acc == 2) { acc = 0; acc_ph ^= 1; }
         }
+    } else if (warp < FIRST_EPI_WARP) {
+        // ---- spare warps: the scatter that delivers this product's input rows -------------------
+        if (peer && ro.enabled == 2)
+            push_rows<BF16>(ps, ro, sh->rem_dest, (int)blockIdx.x * 2 + (warp - 2), (int)gridDim.x * 2, lane, rem_epoch, p.status);
     } else if (warp >= FIRST_EPI_WARP) {
         // ---- epilogue ----------------------------------------------------------
         const int quarter = warp & 3;    // TMEM lanes [32*quarter, +32) are readable by this warp
@@ -1007,7 +1150,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
     tc_fence_before();
     __syncthreads();
-    if (remote && threadIdx.x == 0) {
+    if (peer && threadIdx.x == 0) {
         // every store of this CTA is ordered before the fence by the barrier; the last CTA tells the
         // peers that this GPU's rows of the epoch have landed (arrived[parity][this rank] = epoch)
         __threadfence_system();
@@ -1019,6 +1162,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 unsigned long long* flag = (unsigned long long*)ro.base[q] + ro.arrived_at / 8 + par * ro.stride + ro.rank;
                 asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(flag), "l"(rem_epoch) : "memory");
             }
+            if (ro.enabled == 2)        // the plan may serve another exchange
+                for (int k = 0; k < ps.n_slots; ++k) ps.seg_done[k] = 0;
             *ro.counter = 0;
         }
     }
@@ -1145,11 +1290,14 @@ int cta_cap() {
 }
 
 const GemmRemoteOut kNoRemote = {};
+const GemmPushIn kNoPush = {};
 
 template <int MODE, bool CTA2>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, const HostSegs* hsp, const Params& p_in, int64_t max_tiles,
-           int64_t out_rows, cudaStream_t st, int reserve_sms = 0, const GemmRemoteOut* rop = nullptr) {
+           int64_t out_rows, cudaStream_t st, int reserve_sms = 0, const GemmRemoteOut* rop = nullptr,
+           const GemmPushIn* psp = nullptr) {
     const GemmRemoteOut& ro = rop ? *rop : kNoRemote;
+    const GemmPushIn& ps = psp ? *psp : kNoPush;
     reserve_sms = (reserve_sms + 1) / 2 * 2;      // the kernel beside this one occupies whole SM pairs
     const HostSegs& hs = hsp ? *hsp : kNoSegs;
     Params p = p_in;
@@ -1157,7 +1305,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const HostSegs* hsp, co
     OutMaps om;
     memset(&om, 0, sizeof(om));
     p.tma_store = 0;
-    if (out_rows > 0 && p.out && !ro.enabled) {
+    if (out_rows > 0 && p.out && ro.enabled != 1) {
         if (int rc = make_out_map(&om.out, p.out, out_rows, p.n_out, p.is_bf16 != 0)) return rc;
         if (p.pre_out) {
             if (int rc = make_out_map(&om.out2, p.pre_out, out_rows, p.n_out, p.is_bf16 != 0)) return rc;
@@ -1196,7 +1344,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const HostSegs* hsp, co
         const int cap = std::max(1, std::min(cta_cap(), sm_count() - reserve_sms));
         cfg.gridDim = dim3((unsigned)std::max<int64_t>(1, std::min<int64_t>(max_tiles, cap)));
     }
-    FMOE_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, ma, mb, hs, om, ro, p));
+    FMOE_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, ma, mb, hs, om, ro, ps, p));
     return 0;
 }
 
@@ -1382,8 +1530,8 @@ int tc_linear_forward(const LinearArgs& a, cudaStream_t st) {
         p.done = a.done->done; p.done_expected = a.done->expected; p.done_ready = a.done->ready;
         reserve = std::max(reserve, a.done->reserve_sms);
     }
-    return pair ? launch<MODE_FWD, true>(ma, mb, a.host_segs, p, max_tiles, a.n_rows, st, reserve, a.remote)
-                : launch<MODE_FWD, false>(ma, mb, a.host_segs, p, max_tiles, a.n_rows, st, reserve, a.remote);
+    return pair ? launch<MODE_FWD, true>(ma, mb, a.host_segs, p, max_tiles, a.n_rows, st, reserve, a.remote, a.push)
+                : launch<MODE_FWD, false>(ma, mb, a.host_segs, p, max_tiles, a.n_rows, st, reserve, a.remote, a.push);
 }
 
 // A side stream and a pair of events per device, created on first use: the bias
@@ -1462,8 +1610,8 @@ int tc_linear_backward(const LinearBwdArgs& a, cudaStream_t st) {
             p.done = a.done->done; p.done_expected = a.done->expected; p.done_ready = a.done->ready;
             reserve = std::max(reserve, a.done->reserve_sms);
         }
-        if (int rc = pair ? launch<MODE_DGRAD, true>(ma, mb, a.host_segs, p, max_tiles, a.n_rows, st, reserve, a.remote)
-                          : launch<MODE_DGRAD, false>(ma, mb, a.host_segs, p, max_tiles, a.n_rows, st, reserve, a.remote))
+        if (int rc = pair ? launch<MODE_DGRAD, true>(ma, mb, a.host_segs, p, max_tiles, a.n_rows, st, reserve, a.remote, a.push)
+                          : launch<MODE_DGRAD, false>(ma, mb, a.host_segs, p, max_tiles, a.n_rows, st, reserve, a.remote, a.push))
             return rc;
         if (!closed) {
             if (a.after_input_grad) { if (int rc = a.after_input_grad(a.after_ctx)) return rc; }

@@ -116,14 +116,21 @@ extern "C" int fmoe_linear_backward_colsum(const void* grad_y, const void* x, co
 // ---- the same products on rows that an exchange is still delivering, or that one forwards at once --
 namespace {
 struct FinishCtx { const fmoe_arrival_t* arrival; fmoe_stream_t stream; };
+// Closes an exchange whose rows a product has waited for tile by tile (and, for the handle of a scatter
+// fused into that product, has also delivered: the handle is marked so before it is closed).
+int finish_consumed(const fmoe_arrival_t* arrival, fmoe_stream_t stream) {
+    fmoe_arrival_t h = *arrival;
+    if (h.gather == 3) h.use = 1;
+    return fmoe_peer_arrival_finish(&h, stream);
+}
 int finish_arrival(void* ctx) {
     FinishCtx* f = (FinishCtx*)ctx;
-    return fmoe_peer_arrival_finish(f->arrival, f->stream);
+    return finish_consumed(f->arrival, f->stream);
 }
 int gemm_arrival_of(const fmoe_arrival_t* arrival, GemmArrival* g, bool* pending) {
     ArrivalWait w;
     *pending = false;
-    if (!arrival || arrival->gather) return 0;
+    if (!arrival || (arrival->gather != 0 && arrival->gather != 3)) return 0;
     if (int rc = arrival_wait_of(arrival, &w)) return rc;
     *pending = w.flags != nullptr;
     g->flags = w.flags; g->seq = w.seq; g->src_off = w.src_off; g->world = w.world; g->reserve_sms = w.reserve_sms;
@@ -162,11 +169,19 @@ extern "C" int fmoe_linear_forward_overlapped(const void* x, const void* weight,
         if (int rc = fmoe_peer_arrival_finish(arrival, stream)) return rc;
     }
     if (overlap) a.arrival = &ga;
+    GemmRemoteOut pin;
+    GemmPushIn ps;
+    if (overlap && arrival->gather == 3) {       // the product delivers its own input rows
+        FMOE_REQUIRE(!ro.enabled, "linear_forward: a product cannot both deliver its input and send away its output");
+        if (int rc = push_in_of(arrival, &pin, &ps)) return rc;
+        a.remote = &pin;
+        a.push = &ps;
+    }
     if (leaving) a.done = &gd;
     if (n_rows > 0) {
         if (int rc = dispatch_linear_forward(a, (cudaStream_t)stream)) return rc;
     }
-    return overlap ? fmoe_peer_arrival_finish(arrival, stream) : 0;
+    return overlap ? finish_consumed(arrival, stream) : 0;
 }
 
 extern "C" int fmoe_linear_backward_overlapped(const void* grad_y, const void* x, const void* weight,
@@ -193,12 +208,21 @@ extern "C" int fmoe_linear_backward_overlapped(const void* grad_y, const void* x
     FMOE_REQUIRE(!(leaving || ro.enabled) || (tc && (grad_x || ro.enabled) && n_expert == departure->n_expert),
                  "linear_backward: an overlapped gather was started for a product the tensor-core kernels do not take");
     if (ro.enabled) a.remote = &ro;
-    const bool overlap = arriving && tc && n_expert == arrival->n_expert;
+    // (a scatter fused into the product needs the input-gradient product to run: that one delivers the rows)
+    const bool overlap = arriving && tc && n_expert == arrival->n_expert && (arrival->gather != 3 || (grad_x && n_rows > 0));
     if (arriving && !overlap) {
         if (int rc = fmoe_peer_arrival_finish(arrival, stream)) return rc;
     }
     FinishCtx ctx{arrival, stream};
     if (overlap) { a.arrival = &ga; a.after_input_grad = finish_arrival; a.after_ctx = &ctx; }
+    GemmRemoteOut pin;
+    GemmPushIn ps;
+    if (overlap && arrival->gather == 3) {
+        FMOE_REQUIRE(!ro.enabled, "linear_backward: a product cannot both deliver its input and send away its output");
+        if (int rc = push_in_of(arrival, &pin, &ps)) return rc;
+        a.remote = &pin;
+        a.push = &ps;
+    }
     if (leaving) a.done = &gd;
     return dispatch_linear_backward(a, (cudaStream_t)stream);
 }

@@ -1394,6 +1394,12 @@ extern "C" int fmoe_peer_arrival_finish(const fmoe_arrival_t* arrival, fmoe_stre
     if (!arrival->comm) return 0;                 // the exchange was queued whole
     Comm* c = (Comm*)arrival->comm;
     cudaStream_t st = (cudaStream_t)stream;
+    if (arrival->gather == 3) {
+        // the scatter a product was to perform itself: if none did, the whole exchange runs here
+        const RowSource rows{arrival->row_of, arrival->row_div > 0 ? arrival->row_div : 1, arrival->scale, arrival->dtype, arrival->src_rows};
+        return launch_move(c, arrival->src, arrival->out, arrival->plan, arrival->n_expert, arrival->in_rows, arrival->out_rows,
+                           arrival->row_bytes, false, st, arrival->use ? 2 : 3, 0, 0, arrival->row_of && !arrival->use ? &rows : nullptr);
+    }
     // (a fused gather has no input buffer of its own: its rows came out of a GEMM's epilogue)
     const int64_t in_rows = arrival->gather == 2 ? ((int64_t)1 << 31) - 1 : arrival->in_rows;
     if (arrival->gather != 2) FMOE_CUDA_TRY(cudaStreamWaitEvent(st, c->peer.join, 0));
@@ -1405,7 +1411,7 @@ namespace fmoe {
 int done_words_of(const fmoe_arrival_t* departure, int** done, int** expected, int** ready, int* reserve_sms) {
     *done = *expected = *ready = nullptr;
     *reserve_sms = 0;
-    if (!departure || !departure->comm || departure->gather == 2) return 0;
+    if (!departure || !departure->comm || departure->gather >= 2) return 0;
     Comm* c = (Comm*)departure->comm;
     FMOE_REQUIRE(departure->gather && departure->plan, "departure: not the handle of an overlapped gather");
     const int E = departure->n_expert;
@@ -1423,11 +1429,11 @@ namespace {
 // Tells every peer where this rank receives the rows of the coming exchange (or that it has no room);
 // what the first block of a push kernel does, for exchanges whose rows are stored by another kernel.
 __global__ void peer_announce_kernel(const __grid_constant__ PeerBases b, int rank, int world, unsigned long long my_dest,
-                                     int64_t out_rows, const char* plan, int* status) {
+                                     int64_t out_rows, const char* plan, int* status, int scatter) {
     const PlanHead* head = (const PlanHead*)plan;
     const unsigned long long epoch = __ldcg((const unsigned long long*)(b.base[rank] + kSeqOff)) + 1;
     const int parity = (int)(epoch & 1);
-    const bool room = head->token_rows <= out_rows;
+    const bool room = (scatter ? head->expert_rows : head->token_rows) <= out_rows;
     const int p = threadIdx.x;
     if (p < world && p != rank) {
         unsigned long long* peer_hdr = (unsigned long long*)b.base[p];
@@ -1437,6 +1443,31 @@ __global__ void peer_announce_kernel(const __grid_constant__ PeerBases b, int ra
     if (p == 0 && !room) atomicOr(status, 64);
 }
 }  // namespace
+
+// What a grouped GEMM needs to deliver its own input rows (the handle of fmoe_peer_scatter_fused_begin).
+int push_in_of(const fmoe_arrival_t* h, GemmRemoteOut* ro, GemmPushIn* ps) {
+    memset(ps, 0, sizeof(*ps));
+    memset(ro, 0, sizeof(*ro));
+    if (!h || !h->comm || h->gather != 3) return 0;
+    fmoe_arrival_t as_out = *h;
+    as_out.gather = 2;                             // the peer context is the same as for a fused gather
+    if (int rc = remote_out_of(&as_out, ro)) return rc;
+    ro->enabled = 2;
+    Comm* c = (Comm*)h->comm;
+    const int E = h->n_expert, W = c->world;
+    const PlanDims d = plan_dims(E, W);
+    char* plan = (char*)const_cast<void*>(h->plan);
+    const ListView L = list_view(plan, d, LIST_PUSH_FWD);
+    const PlanHead* head = (const PlanHead*)plan;
+    ps->src = h->src; ps->row_of = h->row_of; ps->scale = h->scale; ps->src_rows = h->src_rows; ps->row_div = h->row_div > 0 ? h->row_div : 1;
+    ps->prefix = L.prefix; ps->seg_sel = L.sel; ps->seg_src = L.src; ps->seg_dst = L.dst;
+    ps->seg_done = (int*)(plan + d.segdone_off);
+    ps->expert_rows = &head->expert_rows; ps->token_rows = &head->token_rows;
+    ps->in_rows = h->in_rows; ps->out_rows = h->out_rows; ps->row_vecs = h->row_bytes / 16;
+    ps->n_slots = d.S; ps->n_expert = E; ps->local_sel = kLocal;
+    ps->flags_at = (int)kExpArrOff; ps->flag_sources = kMaxPeers; ps->flag_experts = kArrivalExperts;
+    return 0;
+}
 
 // What a grouped GEMM needs to store its output rows straight into their owners' memory.
 int remote_out_of(const fmoe_arrival_t* h, GemmRemoteOut* ro) {
@@ -1460,6 +1491,34 @@ int remote_out_of(const fmoe_arrival_t* h, GemmRemoteOut* ro) {
 }
 }  // namespace fmoe
 
+extern "C" int fmoe_peer_scatter_fused_begin(fmoe_comm_t comm, const void* src, int64_t src_rows, const int64_t* row_of,
+                                             int32_t row_div, const void* scale, int32_t dtype, void* global_out,
+                                             const void* plan, int64_t in_rows, int64_t out_rows, int64_t row_bytes,
+                                             int32_t n_expert, fmoe_stream_t stream, fmoe_arrival_t* arrival) {
+    FMOE_REQUIRE(comm && arrival && plan && src, "peer exchange: null pointer");
+    Comm* c = (Comm*)comm;
+    memset(arrival, 0, sizeof(*arrival));
+    if (c->peer.slot_bytes == 0) return FMOE_PEER_UNAVAILABLE;
+    const bool can = c->world <= kRemoteMaxWorld && n_expert <= kArrivalExperts && row_bytes > 0 && row_bytes % 16 == 0 &&
+                     (dtype == FMOE_F16 || dtype == FMOE_BF16) && (row_of || !scale) && (!row_of || row_div > 0) &&
+                     (((uintptr_t)src | (uintptr_t)global_out) & 15) == 0 && in_rows < ((int64_t)1 << 31) &&
+                     out_rows < ((int64_t)1 << 31) && lies_in_pool(c, global_out, out_rows * row_bytes);
+    if (!can) return 0;                       // nothing queued: the caller runs the exchange as a call of its own
+    PeerBases b;
+    for (int p = 0; p < kMaxPeers; ++p) b.base[p] = c->peer.base[p];
+    int* status = device_status_ptr();
+    FMOE_REQUIRE(status, "peer exchange: no device status word");
+    peer_announce_kernel<<<1, 64, 0, (cudaStream_t)stream>>>(b, c->rank, c->world, (unsigned long long)((char*)global_out - c->peer.base[c->rank]),
+                                                            out_rows, (const char*)plan, status, 1);
+    FMOE_CHECK_LAUNCH();
+    arrival->comm = comm; arrival->plan = plan; arrival->out = global_out;
+    arrival->in_rows = in_rows; arrival->out_rows = out_rows; arrival->row_bytes = row_bytes;
+    arrival->n_expert = n_expert; arrival->gather = 3; arrival->use = 0;
+    arrival->src = src; arrival->row_of = row_of; arrival->scale = scale; arrival->src_rows = src_rows;
+    arrival->row_div = row_div; arrival->dtype = dtype;
+    return 0;
+}
+
 extern "C" int fmoe_peer_gather_fused_begin(fmoe_comm_t comm, void* local_out, const void* plan, int64_t out_rows,
                                             int64_t row_bytes, int32_t n_expert, fmoe_stream_t stream, fmoe_arrival_t* departure) {
     FMOE_REQUIRE(comm && departure && plan, "peer exchange: null pointer");
@@ -1473,7 +1532,7 @@ extern "C" int fmoe_peer_gather_fused_begin(fmoe_comm_t comm, void* local_out, c
     int* status = device_status_ptr();
     FMOE_REQUIRE(status, "peer exchange: no device status word");
     peer_announce_kernel<<<1, 64, 0, (cudaStream_t)stream>>>(b, c->rank, c->world, (unsigned long long)((char*)local_out - c->peer.base[c->rank]),
-                                                            out_rows, (const char*)plan, status);
+                                                            out_rows, (const char*)plan, status, 0);
     FMOE_CHECK_LAUNCH();
     departure->comm = comm; departure->plan = plan; departure->out = local_out;
     departure->in_rows = 0; departure->out_rows = out_rows; departure->row_bytes = row_bytes;

@@ -608,6 +608,28 @@ def peer_scatter_planned_rows(src, row_of, row_div, scale, plan, out_rows):
     return out
 
 
+def peer_scatter_fused_begin(src, row_of, row_div, scale, plan, out_rows):
+    """Prepares a peer_scatter_planned_rows that the grouped GEMM consuming its rows performs itself: give the
+    returned PendingArrival to ``linear_forward_act`` / ``linear_backward_act`` as ``arrival``; that product
+    moves the rows with its spare warps while it computes, and closes the exchange.  Returns (out, pending), or
+    (None, None) when the exchange cannot take this form (nothing was queued).  ``finish()`` on a handle that no
+    product took runs the exchange as a call of its own."""
+    _check_cuda(src, row_of)
+    assert row_of.dtype == torch.int64 and src.dim() == 2 and src.is_contiguous() and row_of.is_contiguous()
+    if scale is not None:
+        _check_cuda(scale)
+        assert scale.dtype == src.dtype and scale.is_contiguous()
+    out = _recv_empty(src, out_rows)
+    h = _lib.Arrival()
+    with torch.cuda.device(src.device):
+        _run("peer_scatter", lib.fmoe_peer_scatter_fused_begin, _comm(src.device), _ptr(src), src.shape[0], _ptr(row_of),
+             int(row_div), _ptr(scale), _dtype_code(src), _ptr(out), _ptr(plan.buf), row_of.numel(), out_rows,
+             src.shape[1] * src.element_size(), plan.n_expert, _stream(), ctypes.byref(h))
+    if not h.comm:
+        return None, None
+    return out, PendingArrival(h, (out, src, row_of, scale, plan.buf))
+
+
 class PendingArrival:
     """Rows of a global_scatter that are still on their way (fmoe_arrival_t): give it to the grouped
     GEMM that reads them (``linear_forward_act`` / ``linear_backward_act``), which closes the exchange,

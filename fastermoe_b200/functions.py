@@ -437,9 +437,10 @@ class PlannedExchange:
     the host knows neither the counts nor how many rows arrive; ``fwd_batch_size`` is the capacity
     of the expert-side buffers."""
     __slots__ = ("plan", "fwd_batch_size", "world_size", "num_expert", "overlap_sms", "pending", "token_rows", "early",
-                 "fused_gather", "fused_scatter")
+                 "fused_gather", "fused_scatter", "fused_push")
 
-    def __init__(self, plan, cap_rows, world_size, overlap_sms=0, token_rows=0, fused_gather=False, fused_scatter=False):
+    def __init__(self, plan, cap_rows, world_size, overlap_sms=0, token_rows=0, fused_gather=False, fused_scatter=False,
+                 fused_push=False):
         self.plan, self.fwd_batch_size, self.world_size = plan, int(cap_rows), world_size
         self.num_expert = plan.n_expert
         # > 0: the pushes run on that many SMs beside the grouped GEMMs that read (scatter) or write
@@ -453,6 +454,9 @@ class PlannedExchange:
         # the push of a scatter picks (and scales) its rows itself instead of reading a token-side buffer
         # that a local scatter / the combine's backward would have to write first
         self.fused_scatter = bool(fused_scatter)
+        # ... and the GEMM that consumes those rows is the kernel that moves them (its spare warps push while its
+        # tensor-core warps work on the experts whose rows are complete); FusedExpertMLP takes part
+        self.fused_push = bool(fused_push) and self.fused_scatter
 
     def flush(self):
         """Closes a scatter whose rows nobody waited for tile by tile, and a gather that was started early."""
@@ -497,6 +501,11 @@ class PlannedExchange:
         if not self.fused_scatter or self.overlap_sms > 0:
             return None
         self.flush()
+        if self.fused_push and src.dtype in (torch.bfloat16, torch.float16):
+            out, pend = fmoe_cuda.peer_scatter_fused_begin(src, row_of, row_div, scale, self.plan, out_rows)
+            if pend is not None:
+                self.pending = pend          # the next grouped GEMM takes it (or flush() runs the exchange)
+                return out
         return fmoe_cuda.peer_scatter_planned_rows(src, row_of, row_div, scale, self.plan, out_rows)
 
     def gather(self, buf, out_rows):

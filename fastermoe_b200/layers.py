@@ -140,8 +140,10 @@ def _fmoe_general_global_forward(inp, gate, expert_fn, policy_fn, experts, num_e
             fused_gather = os.environ.get("FMOE_B200_FUSED_GATHER", "1") == "1"
         # the scatters' pushes pick (forward) or pick and scale (backward) their rows themselves
         fused_scatter = overlap == 0 and os.environ.get("FMOE_B200_FUSED_SCATTER", "1") == "1"
+        # ... and the experts' first GEMM (backward: the second layer's input-gradient GEMM) moves them itself
+        fused_push = fused_gather and fused_scatter and os.environ.get("FMOE_B200_FUSED_PUSH", "0") == "1"
         exch = PlannedExchange(routing.plan, routing.n_recv, world_size, overlap_sms=overlap, token_rows=routing.n_rows,
-                               fused_gather=fused_gather, fused_scatter=fused_scatter)
+                               fused_gather=fused_gather, fused_scatter=fused_scatter, fused_push=fused_push)
         n_rows = routing.n_rows
         x = MOEScatterFused.apply(inp, routing.pos, routing.inv, top_k, n_rows, exch)
         x = expert_fn(x, [[experts]], ExpertCounts(routing.own_offsets_dev, exchange=exch), num_expert)

@@ -463,7 +463,15 @@ typedef struct {
     void* out;
     int64_t in_rows, out_rows, row_bytes;
     int32_t n_expert, overlap_sms;
-    int32_t gather, use;   /* gather != 0: handle of fmoe_peer_gather_planned_async (use: which of the plan's two counter sets) */
+    int32_t gather, use;   /* gather: 0 scatter pushed by a kernel of its own; 1 fmoe_peer_gather_planned_async (use: which of
+                              the plan's two counter sets); 2 fmoe_peer_gather_fused_begin; 3 fmoe_peer_scatter_fused_begin
+                              (use 1: the rows have been pushed by the product the handle was given to) */
+    /* gather == 3: where the token-side rows come from (as in fmoe_peer_scatter_planned_rows) */
+    const void* src;
+    const int64_t* row_of;
+    const void* scale;
+    int64_t src_rows;
+    int32_t row_div, dtype;
 } fmoe_arrival_t;
 int fmoe_peer_scatter_planned_async(fmoe_comm_t comm, const void* local_in, void* global_out, const void* plan,
                                     int64_t in_rows, int64_t out_rows, int64_t row_bytes, int32_t n_expert,
@@ -481,6 +489,21 @@ int fmoe_peer_arrival_finish(const fmoe_arrival_t* arrival, fmoe_stream_t stream
 int fmoe_peer_gather_planned_async(fmoe_comm_t comm, const void* global_in, void* local_out, const void* plan,
                                    int64_t in_rows, int64_t out_rows, int64_t row_bytes, int32_t n_expert,
                                    int32_t overlap_sms, int32_t use, fmoe_stream_t stream, fmoe_arrival_t* departure);
+/* global_scatter FUSED into the grouped GEMM that consumes its rows: the product queued next with the handle
+ * as `arrival` (fmoe_linear_forward_overlapped, or fmoe_linear_backward_overlapped, whose input-gradient
+ * product takes it) moves this GPU's token-side rows to the experts' owners with the two spare warps of each
+ * of its CTAs while its tensor-core warps already work on the experts whose rows are complete (per
+ * (source, expert) arrival flags, bounded waits), and closes the exchange.  The rows are given as in
+ * fmoe_peer_scatter_planned_rows (row_of NULL: src holds the token-side rows themselves).  This call only
+ * tells the peers where global_out is; global_out must lie in the receive pool.  Replaces
+ * cuda/global_exchange.h:60-113 (global_scatter) + the wait for it before the experts' first product.  When
+ * it cannot take this form (output outside the pool, more than 32 ranks or 256 experts, rows that are not
+ * 16-bit) it queues NOTHING and leaves arrival->comm NULL.  A handle that no product took is closed by
+ * fmoe_peer_arrival_finish, which then runs the exchange as fmoe_peer_scatter_planned_rows does. */
+int fmoe_peer_scatter_fused_begin(fmoe_comm_t comm, const void* src, int64_t src_rows, const int64_t* row_of,
+                                  int32_t row_div, const void* scale, int32_t dtype, void* global_out, const void* plan,
+                                  int64_t in_rows, int64_t out_rows, int64_t row_bytes, int32_t n_expert,
+                                  fmoe_stream_t stream, fmoe_arrival_t* arrival);
 /* global_gather FUSED into the grouped GEMM that produces its rows: the product queued next with the
  * handle as `departure` (fmoe_linear_forward_overlapped, or fmoe_linear_backward_overlapped for the input
  * gradient) stores every output row straight into the token-side buffer of the rank that owns it --

@@ -384,7 +384,7 @@ def check_layer_bf16(rank, world):
     xs = tens["x"].view(world, T, d)
     m = _make_layer(world, rank, E, d, h, k, "gelu", True, tens, dtype=torch.bfloat16)
     x = xs[rank].bfloat16().cuda()
-    with switches(OVERLAP_SMS=0, FUSED_GATHER=0, FUSED_SCATTER=0):      # local scatter, push, GEMMs, push
+    with switches(OVERLAP_SMS=0, FUSED_GATHER=0, FUSED_SCATTER=0, FUSED_PUSH=0):      # local scatter, push, GEMMs, push
         base = _run_layer(m, x)
     with torch.no_grad():
         idx, _ = m.gate(x)
@@ -428,6 +428,14 @@ def check_layer_bf16(rank, world):
         for name, v in base.items():
             assert torch.equal(over[name], v), f"scatter that produces its rows (fused gather {fg}) differs in {name}"
             assert torch.equal(over_w[name], base_w[name]), f"scatter that scales its rows (fused gather {fg}) differs in {name}"
+    # the scatters done by the GEMMs that consume their rows (spare warps push, tensor-core warps wait per expert)
+    with switches(OVERLAP_SMS=0, FUSED_GATHER=1, FUSED_SCATTER=1, FUSED_PUSH=1):
+        for _ in range(3):
+            over = _run_layer(m, x)
+        over_w = _run_layer(m, x, lw)
+    for name, v in base.items():
+        assert torch.equal(over[name], v), f"scatter fused into the consuming GEMM differs in {name}"
+        assert torch.equal(over_w[name], base_w[name]), f"scaled scatter fused into the consuming GEMM differs in {name}"
     from fastermoe_b200 import fmoe_cuda as fc
     assert fc.device_status() == 0
     os.environ["FMOE_FUSE_GRAN"] = "1"
@@ -474,12 +482,13 @@ def check_graph_step(rank, world):
         loss.backward()
         return out.detach().clone(), loss.detach().clone(), xi.grad.clone(), {n: p.grad.clone() for n, p in m.named_parameters()}
 
-    with switches(OVERLAP_SMS=0, FUSED_GATHER=0, FUSED_SCATTER=0):
+    with switches(OVERLAP_SMS=0, FUSED_GATHER=0, FUSED_SCATTER=0, FUSED_PUSH=0):
         want = [eager(x) for x in xs[1:]]
     # without and with the pushes running beside the GEMMs (a second stream in the graph), and with
     # the gathers done by the GEMMs' own epilogues
-    for sms, fused_gather, fused_scatter in (("0", "0", "0"), ("8", "0", "0"), ("0", "1", "0"), ("0", "1", "1")):
-        with switches(OVERLAP_SMS=sms, FUSED_GATHER=fused_gather, FUSED_SCATTER=fused_scatter):
+    for sms, fused_gather, fused_scatter, fused_push in (("0", "0", "0", "0"), ("8", "0", "0", "0"), ("0", "1", "0", "0"),
+                                                         ("0", "1", "1", "0"), ("0", "1", "1", "1")):
+        with switches(OVERLAP_SMS=sms, FUSED_GATHER=fused_gather, FUSED_SCATTER=fused_scatter, FUSED_PUSH=fused_push):
             step = GraphedStep(m, xs[0], input_grad=True)
             for x, (out, loss, gx, grads) in zip(xs[1:], want):
                 got_loss = step(x)
