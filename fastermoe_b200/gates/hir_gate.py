@@ -39,11 +39,12 @@ class HirGate(NaiveGate):
         self.set_loss(balance_loss_top1(top1_idx, gate_score, self.tot_expert, self.num_expert))
 
         with torch.no_grad():
-            _, _, aec, _, agec = count_by_gate(top2_idx, self.num_expert, self.world_size, require_pos=False)
+            _, _, aec, _, _ = count_by_gate(top2_idx, self.num_expert, self.world_size, require_pos=False)
             w, e = self.world_size, self.num_expert
-            stored = self.policy_fn(aec.view(-1).cpu().view(w, w, e) if w > 1 else aec.cpu().view(1, 1, e),
-                                    agec.view(-1).cpu().view(w, w, e) if w > 1 else agec.cpu().view(1, 1, e),
-                                    e, w, inp.shape[-1], True)
+            # one copy to the host: the table seen from the receivers is its transpose
+            aec_host = aec.view(-1).cpu().view(w, w, e) if w > 1 else aec.cpu().view(1, 1, e)
+            agec_host = aec_host.transpose(0, 1).contiguous()
+            stored = self.policy_fn(aec_host, agec_host, e, w, inp.shape[-1], True)
             self.last_stored = stored.reshape(w, e).cpu()
             # Experts shadowed on every worker are as good as local ones.
             limited = off_node & ~stored.reshape(-1).to(off_node.device)
