@@ -371,24 +371,45 @@ def make_steps(env, layer, x_host):
         out = layer(x_dev)
         out.sum().backward()
 
+    # Four device staging buffers taken in turn (no allocation inside a step): the copy of batch i+1 runs on
+    # the copy stream while step i computes, and waits until the step that last read its buffer is over.
+    # The copy goes in as many parts as the layer signals quiet points (env.quiet: events that a replayed
+    # step records after each of its scatters): a host-to-device copy beside a scatter's stores into peer
+    # memory slowed those kernels by 80 % (measured), beside the GEMMs it costs nothing.
     copy_stream = torch.cuda.Stream(device=dev)
-    pending = {"next": None}
+    stages = [torch.empty_like(x_dev.detach()) for _ in range(4)]
+    pending = {"next": None, "i": 0, "last": None, "free": [None] * 4}
 
     def prefetch():
+        slot = pending["i"] % 4
+        pending["i"] += 1
+        gates = list(getattr(env, "quiet", None) or [None])
+        n_rows = x_host.shape[0]
         with torch.cuda.stream(copy_stream):
-            buf = x_host.to(dev, non_blocking=True)
+            if pending["free"][slot] is not None:
+                copy_stream.wait_event(pending["free"][slot])
+            for part, gate in enumerate(gates):
+                lo, hi = n_rows * part // len(gates), n_rows * (part + 1) // len(gates)
+                if gate is not None:
+                    copy_stream.wait_event(gate)
+                stages[slot][lo:hi].copy_(x_host[lo:hi], non_blocking=True)
             ev = torch.cuda.Event()
             ev.record(copy_stream)
-        return buf, ev
+        return slot, ev
 
     def take():
+        main = torch.cuda.current_stream()
+        if pending["last"] is not None:       # the step that read the previous buffer has been queued by now
+            done = torch.cuda.Event()
+            done.record(main)
+            pending["free"][pending["last"]] = done
         if pending["next"] is None:
             pending["next"] = prefetch()
-        x, ev = pending["next"]
-        torch.cuda.current_stream().wait_event(ev)
-        x.record_stream(torch.cuda.current_stream())
+        slot, ev = pending["next"]
+        main.wait_event(ev)
+        pending["last"] = slot
         pending["next"] = prefetch()
-        return x
+        return stages[slot].detach()
 
     def step_e2e():
         layer.zero_grad(set_to_none=True)
@@ -711,12 +732,23 @@ def run_ours(args):
     # plan built on the device) is replayed as ONE CUDA graph (fastermoe_b200.GraphedStep, the library's own
     # public wrapper): the GPU then sees the kernels back to back instead of at the pace of the Python glue.
     eager_ms = None
+    if world > 1 and not args.eager:
+        # quiet points of a replayed step: an external event after each of its two scatters (forward, backward),
+        # recorded by the graph's own event nodes; the e2e leg's input copies start behind them
+        from fastermoe_b200.functions import set_phase_hook
+        env.quiet = [torch.cuda.Event(external=True), torch.cuda.Event(external=True)]
+        seen = {"n": 0}
+
+        def at_phase(phase):
+            if phase == "scatter_done" and torch.cuda.is_current_stream_capturing():
+                env.quiet[seen["n"] % 2].record()
+                seen["n"] += 1
+        set_phase_hook(at_phase)
     sampler = ClockSampler(env.local_rank) if rank == 0 else None
     if sampler:
         sampler.start()      # early: the tool takes longer to start than the timed region lasts
     step, step_form, graphed = graph_or_eager(env, layer, x_dev, step_resident, allow=not args.eager)
     if graphed is not None:
-        eager_ms = env.timed(step_resident, args.steps)
         for _ in range(3):
             step()
     t_region = time.time()
@@ -731,9 +763,10 @@ def run_ours(args):
         stage = torch.empty_like(x_dev.detach())
         h2d_alone_ms = env.timed(lambda: stage.copy_(x_host, non_blocking=True), 10) / 10
         del stage
-        for _ in range(2):
-            step_e2e()
-        e2e_eager_ms = e2e_ms = env.timed(step_e2e, args.steps)
+        if graphed is None:
+            for _ in range(2):
+                step_e2e()
+            e2e_eager_ms = e2e_ms = env.timed(step_e2e, args.steps)
         if graphed is not None:
             # per step one device-to-device copy of the prefetched batch into the captured input, one graph
             # launch, one read of the loss
@@ -772,7 +805,21 @@ def run_ours(args):
             state["losses"].clear()
             e2e_ms = env.timed(step_e2e_graph, args.steps, after=read_last)
             assert len(state["losses"]) == args.steps and all(math.isfinite(v) for v in state["losses"])
+            if args.kernel_list_e2e:
+                write_kernel_list(env, step_e2e_graph, args.kernel_list_e2e, f"{name} (e2e, graph replay)", steps=6)
+                read_last()
+                state["losses"].clear()
             layer.zero_grad(set_to_none=True)
+            # for comparison, after the legs that count: the same e2e step launched from Python
+            for _ in range(2):
+                step_e2e()
+            e2e_eager_ms = env.timed(step_e2e, args.steps)
+    if getattr(env, "quiet", None):
+        from fastermoe_b200.functions import set_phase_hook
+        set_phase_hook(None)
+        env.quiet = None
+    if graphed is not None:       # likewise the resident step launched from Python
+        eager_ms = env.timed(step_resident, args.steps)
 
     if args.kernel_list:
         write_kernel_list(env, step, args.kernel_list, f"{name} ({step_form.split(':')[0].split(' (')[0]})")
@@ -903,6 +950,7 @@ def main():
     ap.add_argument("--no-parity", action="store_true", help="omit the multi-GPU self-check")
     ap.add_argument("--kernel-list", default=None, metavar="PATH", help="also write a per-kernel device-time table "
                     "of three resident steps (rank 0) to PATH")
+    ap.add_argument("--kernel-list-e2e", default=None, metavar="PATH", help="the same table for six e2e steps")
     ap.add_argument("--eager", action="store_true", help="time eager steps even where the step can replay as a CUDA graph")
     ap.add_argument("--skip-e2e", action="store_true", help="omit the host-buffer (e2e) leg (profiling runs)")
     ap.add_argument("--skip-cpu", action="store_true", help="omit the CPU baseline leg (profiling runs)")

@@ -8,10 +8,10 @@ keeps the names of the reference's ``fmoe_cuda`` extension.
 Attributes are resolved on first use so that ``fastermoe_b200.build`` can be
 imported (to compile the CUDA library) before the library exists.
 """
-__all__ = ["FMoE", "FMoELinear", "FMoETransformerMLP", "DistributedGroupedDataParallel", "GraphedStep"]
+__all__ = ["FMoE", "FMoELinear", "FMoETransformerMLP", "DistributedGroupedDataParallel", "GraphedStep", "set_phase_hook"]
 
 _HOME = {"FMoE": "layers", "FMoELinear": "layers", "FMoETransformerMLP": "transformer",
-         "DistributedGroupedDataParallel": "distributed", "GraphedStep": "graphs"}
+         "DistributedGroupedDataParallel": "distributed", "GraphedStep": "graphs", "set_phase_hook": "functions"}
 
 
 def __getattr__(name):

@@ -70,6 +70,7 @@ struct GemmRemoteOut {
     const int* dst_off;                // [n_expert * world]
     unsigned int* counter;             // zero before the launch: CTAs that have finished
     unsigned long long my_dest;        // where this GPU receives (byte offset in its own area)
+    unsigned long long min_dest;       // announcements below this offset point into the flag header: rejected
     unsigned long long timeout_cycles;
     int arrived_at, ann_at, dest_at, stride;   // header layout
     int world, rank;

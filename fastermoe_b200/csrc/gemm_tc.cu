@@ -708,7 +708,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 }
                 dest = there ? __ldcg(ro.header + ro.dest_at / 8 + par * ro.stride + q) : 0ull;
                 if (!there) atomicOr(p.status, 16);
-                else if (dest == ~0ull || dest == 0ull) { dest = 0ull; atomicOr(p.status, 64); }   // it has no room: its rows are dropped
+                else if (dest == ~0ull || dest < ro.min_dest) { dest = 0ull; atomicOr(p.status, 64); }   // no room (or a bad offset): its rows are dropped
             }
             sh->rem_dest[q] = dest;
         }

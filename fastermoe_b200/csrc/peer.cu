@@ -1484,6 +1484,7 @@ int remote_out_of(const fmoe_arrival_t* h, GemmRemoteOut* ro) {
     ro->dst_off = (const int*)((const char*)h->plan + d.back_off);
     ro->counter = c->peer.counter + 3;
     ro->my_dest = (unsigned long long)((char*)h->out - c->peer.base[c->rank]);
+    ro->min_dest = (unsigned long long)kHeaderBytes;
     ro->timeout_cycles = c->peer.timeout_ns * 2ull;
     ro->arrived_at = kArrivedOff; ro->ann_at = kAnnOff; ro->dest_at = kDestOff; ro->stride = kMaxPeers;
     ro->world = W; ro->rank = c->rank; ro->enabled = 1;

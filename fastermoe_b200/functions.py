@@ -432,6 +432,25 @@ class Exchange:
         return fmoe_cuda.global_gather(buf, self.lec, self.gec, self.stored, out_rows, self.world_size)
 
 
+_phase_hook = None
+
+
+def set_phase_hook(fn):
+    """``fn(name)`` is called on the host at points of a layer call that other traffic may want to
+    avoid or to follow.  So far: ``"scatter_done"`` right after a scatter of the device-planned
+    exchange has been queued on the current stream (its kernels store into the peers' memory; a
+    host-to-device copy that runs beside them slows them down, so an input pipeline can record an
+    event here -- an ``external`` one inside a CUDA graph capture -- and start its copy of the next
+    batch behind it).  ``None`` removes the hook."""
+    global _phase_hook
+    _phase_hook = fn
+
+
+def _phase(name):
+    if _phase_hook is not None:
+        _phase_hook(name)
+
+
 class PlannedExchange:
     """One layer call's all-to-all-v driven by a plan that lives on the device (fmoe_cuda.PeerPlan):
     the host knows neither the counts nor how many rows arrive; ``fwd_batch_size`` is the capacity
@@ -493,7 +512,9 @@ class PlannedExchange:
         if self.overlap_sms > 0:
             out, self.pending = fmoe_cuda.peer_scatter_planned_async(buf, self.plan, out_rows, self.overlap_sms)
             return out
-        return fmoe_cuda.peer_scatter_planned(buf, self.plan, out_rows)
+        out = fmoe_cuda.peer_scatter_planned(buf, self.plan, out_rows)
+        _phase("scatter_done")
+        return out
 
     def scatter_rows(self, src, row_of, row_div, scale, out_rows):
         """scatter of the rows ``[scale[row_of[i]] *] src[row_of[i] // row_div]`` without storing them on
@@ -506,7 +527,9 @@ class PlannedExchange:
             if pend is not None:
                 self.pending = pend          # the next grouped GEMM takes it (or flush() runs the exchange)
                 return out
-        return fmoe_cuda.peer_scatter_planned_rows(src, row_of, row_div, scale, self.plan, out_rows)
+        out = fmoe_cuda.peer_scatter_planned_rows(src, row_of, row_div, scale, self.plan, out_rows)
+        _phase("scatter_done")
+        return out
 
     def gather(self, buf, out_rows):
         early, self.early = self.early, None
