@@ -436,6 +436,16 @@ def check_layer_bf16(rank, world):
     for name, v in base.items():
         assert torch.equal(over[name], v), f"scatter fused into the consuming GEMM differs in {name}"
         assert torch.equal(over_w[name], base_w[name]), f"scaled scatter fused into the consuming GEMM differs in {name}"
+    # the quiet-point hook: once after the forward's scatter, once after the backward's
+    from fastermoe_b200 import set_phase_hook
+    calls = []
+    set_phase_hook(calls.append)
+    try:
+        with switches(OVERLAP_SMS=0, FUSED_PUSH=0):
+            _run_layer(m, x)
+    finally:
+        set_phase_hook(None)
+    assert calls == ["scatter_done", "scatter_done"], calls
     from fastermoe_b200 import fmoe_cuda as fc
     assert fc.device_status() == 0
     os.environ["FMOE_FUSE_GRAN"] = "1"
