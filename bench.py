@@ -388,8 +388,11 @@ def make_steps(env, layer, x_host):
         with torch.cuda.stream(copy_stream):
             if pending["free"][slot] is not None:
                 copy_stream.wait_event(pending["free"][slot])
-            for part, gate in enumerate(gates):
-                lo, hi = n_rows * part // len(gates), n_rows * (part + 1) // len(gates)
+            # the window behind the forward's scatter (until the backward's) is about half as long as the one
+            # behind the backward's (until the next step's): a third of the rows, then the rest
+            cuts = [0, n_rows] if len(gates) == 1 else [0, n_rows // 3, n_rows]
+            for part, gate in enumerate(gates[:len(cuts) - 1]):
+                lo, hi = cuts[part], cuts[part + 1]
                 if gate is not None:
                     copy_stream.wait_event(gate)
                 stages[slot][lo:hi].copy_(x_host[lo:hi], non_blocking=True)
@@ -398,15 +401,15 @@ def make_steps(env, layer, x_host):
         return slot, ev
 
     def take():
-        main = torch.cuda.current_stream()
+        cur = torch.cuda.current_stream()
         if pending["last"] is not None:       # the step that read the previous buffer has been queued by now
             done = torch.cuda.Event()
-            done.record(main)
+            done.record(cur)
             pending["free"][pending["last"]] = done
         if pending["next"] is None:
             pending["next"] = prefetch()
         slot, ev = pending["next"]
-        main.wait_event(ev)
+        cur.wait_event(ev)
         pending["last"] = slot
         pending["next"] = prefetch()
         return stages[slot].detach()
@@ -697,6 +700,12 @@ def write_kernel_list(env, step, path, name, steps=3):
             f.write(f"| {key[:110]} | {count / steps:g} | {t / count:.1f} | {100 * t / total:.1f} % |\n")
 
 
+def progress(env, what):
+    """Progress marker on stderr (rank 0): tells where a run that died was."""
+    if env.rank == 0:
+        print(f"[bench {time.strftime('%H:%M:%S')}] {what}", file=sys.stderr, flush=True)
+
+
 def run_ours(args):
     import ctypes
     env = Env(args)
@@ -710,8 +719,10 @@ def run_ours(args):
     layer, x_host = build_layer(env, name, variant)
     step_resident, step_e2e, take, x_dev = make_steps(env, layer, x_host)
 
+    progress(env, "layer built; warm-up")
     for _ in range(max(args.warmup, 3)):
         step_resident()
+    progress(env, "per-kernel timing pass")
     # Per-kernel timing pass: CUDA events around every library call on the launching stream, eager steps,
     # right after the warm-up (before the long legs below have brought the GPU to its power cap: the roofline's
     # denominator is the burst figure of a kernel timed alone).
@@ -747,7 +758,9 @@ def run_ours(args):
     sampler = ClockSampler(env.local_rank) if rank == 0 else None
     if sampler:
         sampler.start()      # early: the tool takes longer to start than the timed region lasts
+    progress(env, "graph capture")
     step, step_form, graphed = graph_or_eager(env, layer, x_dev, step_resident, allow=not args.eager)
+    progress(env, f"timed region ({step_form[:24]})")
     if graphed is not None:
         for _ in range(3):
             step()
@@ -755,6 +768,7 @@ def run_ours(args):
     total_ms = env.timed(step, args.steps)
     clocks = sampler.stop(t_region, time.time()) if sampler else None
 
+    progress(env, "e2e legs")
     e2e_ms = e2e_eager_ms = h2d_alone_ms = None
     used_graph = False
     if not args.skip_e2e:
@@ -821,6 +835,7 @@ def run_ours(args):
     if graphed is not None:       # likewise the resident step launched from Python
         eager_ms = env.timed(step_resident, args.steps)
 
+    progress(env, "eager comparison legs done")
     if args.kernel_list:
         write_kernel_list(env, step, args.kernel_list, f"{name} ({step_form.split(':')[0].split(' (')[0]})")
 
@@ -902,10 +917,12 @@ def run_ours(args):
                 "sample": f"{CPU_SAMPLE_TOKENS} of {T} tokens, same experts and widths, fp32, 3 timed fwd+bwd steps "
                           f"({cpu_ms:.0f} ms each)"}
         if world > 1:
+            progress(env, "row histogram and layer roofline")
             table_now, _ = realised_rows(env, layer, x_dev)
             line["rows_per_gpu"] = table_now.sum(2).sum(0).tolist()
             line["layer_roofline"] = layer_roofline(env, name, table_now, ms_per_step)
         if world > 1 and not args.no_parity and name == "c2":
+            progress(env, "parity self-check")
             line["parity"] = parity_checks(env, layer, x_dev)
         extra = args.extra
         if extra is None:
@@ -919,6 +936,7 @@ def run_ours(args):
             line["configs"] = []
             for item in extra.split(","):
                 for variant in {"c4": ("fuse", "nccl"), "c5": ("5a", "5b")}.get(item, (None,)):
+                    progress(env, f"extra workload {item} {variant or ''}")
                     try:
                         line["configs"].append(measure_config(env, item, variant, args.extra_steps, 3))
                     except Exception as e:
