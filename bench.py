@@ -579,10 +579,18 @@ def parity_checks(env, layer, x_dev):
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     import dist_worker
     res = {}
+    # the oracle runs on the host: give every rank its share of the cores this process may use
+    # (the launcher sets OMP_NUM_THREADS=1)
+    try:
+        torch.set_num_threads(max(1, len(os.sched_getaffinity(0)) // max(1, min(env.world, 4))))
+    except (AttributeError, RuntimeError):
+        pass
 
     def run(name, fn):
         try:
+            t0 = time.time()
             fn()
+            progress(env, f"  parity {name}: {time.time() - t0:.1f} s")
             ok = True
         except Exception as e:      # the message names the first mismatch
             ok = f"{type(e).__name__}: {str(e)[:300]}"
@@ -964,7 +972,7 @@ def main():
     ap.add_argument("--extra", default=None, help="other workloads to time after it: e.g. c3,c4,c5 or none "
                                                   "(default: all three at 8 GPUs, else none)")
     ap.add_argument("--extra-steps", type=int, default=10)
-    ap.add_argument("--extra-limit-s", type=int, default=420, help="wall-clock limit of the untimed legs")
+    ap.add_argument("--extra-limit-s", type=int, default=600, help="wall-clock limit of the untimed legs")
     ap.add_argument("--no-parity", action="store_true", help="omit the multi-GPU self-check")
     ap.add_argument("--kernel-list", default=None, metavar="PATH", help="also write a per-kernel device-time table "
                     "of three resident steps (rank 0) to PATH")
