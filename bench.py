@@ -31,7 +31,9 @@ bounded sample of the same workload).  With N > 1 it also carries ``parity`` -- 
 self-check of the multi-GPU path against the CPU oracle, run after the timed region -- and, with N = 8
 (or ``--extra``), ``configs``: the other workloads above, each timed with its own warm-up.
 
-``--impl reference`` times the reference's own CPU path alone on the host cores.
+``--kernel-list PATH`` / ``--kernel-list-e2e PATH`` also write a per-kernel device-time table of a few
+resident / e2e steps (CUPTI through torch.profiler; works on every rank count).  Progress markers go to
+stderr.  ``--impl reference`` times the reference's own CPU path alone on the host cores.
 All working sets are several hundred MB per step, larger than the 126 MB L2: no explicit flush.
 """
 import argparse
@@ -659,7 +661,7 @@ def parity_checks(env, layer, x_dev):
         if env.rank == 0:
             want = O.moe_layer_fwd_bwd(xs.detach().float().cpu(), layer.gate.gate.weight.detach().float().cpu(),
                                        layer.gate.gate.bias.detach().float().cpu(), parts["w1"], parts["b1"], parts["w2"],
-                                       parts["b2"], k, act=CFG["activation"], gate_idx=idx.cpu())
+                                       parts["b2"], k, act=CFG["activation"], gate_idx=idx.cpu(), grads_for=("x",))
             torch.testing.assert_close(out.detach().float().cpu(), want["out"], **half_tol(want["out"], 4))
             torch.testing.assert_close(xs.grad.float().cpu(), want["grad_x"], **half_tol(want["grad_x"], 5))
         layer.zero_grad(set_to_none=True)

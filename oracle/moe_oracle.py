@@ -304,15 +304,21 @@ def moe_layer(x, gate_idx, gate_score, w1, b1, w2, b2, act="gelu"):
 
 
 def moe_layer_fwd_bwd(x, gate_w, gate_b, w1, b1, w2, b2, top_k, act="gelu", softmax_scores=False,
-                      gate_idx=None, grad_out=None, score_idx=None):
+                      gate_idx=None, grad_out=None, score_idx=None, grads_for=None):
     """Forward + backward of gate -> experts -> combine on the CPU.  Returns a dict
     with the output and the gradients of every input that requires grad.  The loss is
     ``sum(out * grad_out)`` (``grad_out`` None = ones = out.sum()).  ``gate_idx`` prescribes the
     experts (-1 = pruned entry); ``score_idx`` (default: gate_idx) the experts whose logits give
-    the scores, for gates that compute scores before a capacity limit prunes entries."""
+    the scores, for gates that compute scores before a capacity limit prunes entries.  ``grads_for``: names of
+    the inputs whose gradients are wanted (default: all); the others are used as they are, without a copy."""
     leaves = {}
     for name, t in (("x", x), ("gate_w", gate_w), ("gate_b", gate_b), ("w1", w1), ("b1", b1), ("w2", w2), ("b2", b2)):
-        leaves[name] = None if t is None else t.detach().clone().requires_grad_(True)
+        if t is None:
+            leaves[name] = None
+        elif grads_for is None or name in grads_for:
+            leaves[name] = t.detach().clone().requires_grad_(True)
+        else:
+            leaves[name] = t.detach()
     idx, score, _ = naive_gate(leaves["x"], leaves["gate_w"], leaves["gate_b"], top_k, softmax_scores)
     if gate_idx is not None:
         # Use prescribed indices (e.g. after capacity pruning); scores follow the indices.
@@ -326,7 +332,7 @@ def moe_layer_fwd_bwd(x, gate_w, gate_b, w1, b1, w2, b2, top_k, act="gelu", soft
     loss.backward()
     res = {"out": out.detach(), "gate_idx": idx.detach(), "gate_score": score.detach()}
     for name, t in leaves.items():
-        if t is not None:
+        if t is not None and t.requires_grad:
             res["grad_" + name] = t.grad
     return res
 
