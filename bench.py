@@ -841,7 +841,7 @@ def run_ours(args):
     if getattr(env, "quiet", None):
         from fastermoe_b200.functions import set_phase_hook
         set_phase_hook(None)
-        env.quiet = None
+        env.quiet_keep, env.quiet = env.quiet, None     # the captured graph refers to the events: keep them alive
     if graphed is not None:       # likewise the resident step launched from Python
         eager_ms = env.timed(step_resident, args.steps)
 
