@@ -747,6 +747,66 @@ def cpu_grouped_ddp(rank, world, port):
     finish("gloo")
 
 
+def cpu_megatron_ddp_checkpoint(rank, world, port, root):
+    """The Megatron-style wrapper on real ranks: gradients of replicated tensors are averaged over the
+    data-parallel group, expert tensors are left alone; every rank then writes its checkpoint shard and a
+    rank other than 0 gets back rank 0's replicated tensors with its own experts (optimizer state included)."""
+    init(rank, world, port, "gloo")
+    from fastermoe_b200 import megatron as M
+
+    class Mpu:
+        def get_model_parallel_group(self):
+            return None
+
+        def get_data_parallel_group(self):
+            return dist.group.WORLD
+
+    M.bind(mpu=Mpu())
+    torch.manual_seed(rank)
+    net = torch.nn.ModuleDict({"shared": torch.nn.Linear(4, 4), "experts": torch.nn.Linear(4, 4)})
+    for p in net["shared"].parameters():
+        p.dp_comm = "dp"
+    for p in net["experts"].parameters():
+        p.dp_comm = "none"
+    ddp = M.DistributedDataParallel(net)                       # broadcasts the replicated tensors from rank 0
+    opt = torch.optim.Adam(net.parameters(), lr=0.05)
+    g = torch.Generator().manual_seed(50 + rank)
+    for _ in range(3):
+        opt.zero_grad()
+        (net["experts"](net["shared"](torch.randn(5, 4, generator=g))) ** 2).sum().backward()
+        ddp.allreduce_params()
+        opt.step()
+    shared = [torch.empty_like(net["shared"].weight) for _ in range(world)]
+    dist.all_gather(shared, net["shared"].weight.data)
+    assert all(torch.allclose(shared[0], w) for w in shared), "replicated tensors drifted apart"
+    experts = [torch.empty_like(net["experts"].weight) for _ in range(world)]
+    dist.all_gather(experts, net["experts"].weight.data)
+    assert not torch.allclose(experts[0], experts[1]), "expert tensors were averaged"
+    assert set(ddp.state_dict()) == set(net.state_dict())       # the wrapper's state dict is the module's
+
+    pos = M.GridPosition(dp_rank=rank)
+    M.save_shard(root, 3, net, opt, pos)
+    dist.barrier()
+    if rank == 0:
+        M.write_tracker(root, 3)
+    dist.barrier()
+    want = {k: v.clone() for k, v in net.state_dict().items()}
+    want_opt = opt.state_dict()["state"]
+    with torch.no_grad():
+        for p in net.parameters():
+            p.add_(1.0)                                         # what the load must undo
+    opt2 = torch.optim.Adam(net.parameters(), lr=0.05)
+    blob = M.load_shard(root, net, opt2, pos)
+    assert blob["iteration"] == 3
+    for k, v in net.state_dict().items():
+        assert torch.equal(v, want[k]), k
+    got_opt = opt2.state_dict()["state"]
+    for i in (2, 3):                                            # this rank's experts: its own moments
+        assert torch.equal(got_opt[i]["exp_avg"], want_opt[i]["exp_avg"])
+    M.unbind()
+    finish("gloo")
+
+
 def cpu_slice_allgather(rank, world, port):
     """Slice / AllGather over a model-parallel group (fmoe/functions.py:333-375): the forward of one is
     the backward of the other."""

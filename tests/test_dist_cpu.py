@@ -25,3 +25,7 @@ def test_grouped_data_parallel_over_gloo():
 @pytest.mark.parametrize("world", [2, 3])
 def test_slice_and_allgather_over_gloo(world):
     mp.spawn(dist_worker.cpu_slice_allgather, args=(world, free_port()), nprocs=world, join=True)
+
+
+def test_megatron_wrapper_and_sharded_checkpoint_over_gloo(tmp_path):
+    mp.spawn(dist_worker.cpu_megatron_ddp_checkpoint, args=(2, free_port(), str(tmp_path)), nprocs=2, join=True)
