@@ -25,3 +25,12 @@ def _built_library():
     """The C-ABI library must exist for every test; build it if the tree is fresh."""
     from fastermoe_b200 import build
     build.build()
+
+
+@pytest.fixture(autouse=True)
+def _seeded(request):
+    """Every test draws the same random inputs in every run, whatever ran before it: torch's generators
+    (CPU and CUDA) are seeded from the test's id.  A tolerance that holds is then one that holds again."""
+    import zlib
+    import torch
+    torch.manual_seed(zlib.crc32(request.node.nodeid.encode()) & 0x7FFFFFFF)

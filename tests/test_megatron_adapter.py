@@ -228,6 +228,7 @@ def test_fp16_wrapper_state_keeps_expert_master_copies():
 @pytest.mark.gpu
 def test_megatron_mlp_runs_and_reports_balance(bound):
     bound.balance_strategy = "naive"
+    bound.hidden_size = 256
     model = M.fmoefy(FakeMegatronModel(256, 2), num_experts=4, hidden_hidden_size=512).cuda().bfloat16()
     x = torch.randn(bound.seq_length, bound.micro_batch_size, 256, device="cuda", dtype=torch.bfloat16, requires_grad=True)
     out, bias = model.language_model.transformer.layers[1].mlp(x)

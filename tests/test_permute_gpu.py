@@ -84,6 +84,7 @@ def test_gather_sum(fc, dtype, T, k, d):
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("T,k,d", [(64, 2, 128), (257, 3, 1024), (33, 2, 7)])
 def test_combine_forward_backward(fc, dtype, T, k, d):
+    torch.manual_seed(1000 * T + d)
     g, pos, inv = routing(T, k, 4, 7 * T + d)
     buf = torch.randn(len(pos), d).to(dtype).cuda()
     score = torch.rand(T, k).to(dtype).cuda()
@@ -101,7 +102,10 @@ def test_combine_forward_backward(fc, dtype, T, k, d):
     tol = dict(rtol=1e-5, atol=1e-5) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-2)
     torch.testing.assert_close(got.float(), want, **tol)
     torch.testing.assert_close(gb.float(), bufr.grad, **tol)
-    gtol = tol if dtype == torch.float32 else dict(rtol=3e-2, atol=3e-2 * float(np.sqrt(d)))
+    # the score gradient is a d-term dot product of unit-variance values: two fp32 summation orders differ by
+    # a few ulp x sqrt(d) in absolute terms, whatever the size of the (possibly cancelling) result
+    gtol = (dict(rtol=1e-5, atol=8 * 2.0 ** -23 * float(np.sqrt(d))) if dtype == torch.float32
+            else dict(rtol=3e-2, atol=3e-2 * float(np.sqrt(d))))
     torch.testing.assert_close(gs.float(), scr.grad, **gtol)
     # dense form (no permutation): x [T*k, d]
     xd = torch.randn(T * k, d).to(dtype).cuda()
