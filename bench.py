@@ -448,12 +448,21 @@ def graph_or_eager(env, layer, x_dev, step_resident, allow=True):
     graphable = allow and (env.world == 1 or "planned on the device" in (exchange_form(layer, env.dev) or ""))
     if graphable:
         from fastermoe_b200 import GraphedStep
+        graphed, why = None, ""
         try:
             graphed = GraphedStep(layer, x_dev.detach(), input_grad=True)
-            return graphed.replay, "one CUDA graph replay per step (fastermoe_b200.GraphedStep)", graphed
         except Exception as e:              # e.g. a receive pool too small for this workload's arena
             env.torch.cuda.synchronize()
-            return step_resident, f"eager (graph capture failed: {type(e).__name__}: {str(e)[:120]})", None
+            why = f"{type(e).__name__}: {str(e)[:120]}"
+        # every rank replays or none does: a rank that launches eagerly beside ranks that replay would still
+        # meet them in every exchange, but the legs would no longer measure one thing
+        ok = env.torch.tensor([1 if graphed is not None else 0], device=env.dev)
+        if env.world > 1:
+            env.dist.all_reduce(ok, op=env.dist.ReduceOp.MIN)
+        if int(ok.item()):
+            return graphed.replay, "one CUDA graph replay per step (fastermoe_b200.GraphedStep)", graphed
+        del graphed
+        return step_resident, f"eager (graph capture failed on some rank{': ' + why if why else ''})", None
     return step_resident, "eager: every kernel launched from Python", None
 
 
