@@ -462,6 +462,11 @@ def graph_or_eager(env, layer, x_dev, step_resident, allow=True):
         if int(ok.item()):
             return graphed.replay, "one CUDA graph replay per step (fastermoe_b200.GraphedStep)", graphed
         del graphed
+        # ranks that captured may have waited in vain for the one that did not: start the eager legs clean
+        from fastermoe_b200 import fmoe_cuda
+        env.torch.cuda.synchronize()
+        fmoe_cuda.lib.fmoe_device_status_clear()
+        env.barrier()
         return step_resident, f"eager (graph capture failed on some rank{': ' + why if why else ''})", None
     return step_resident, "eager: every kernel launched from Python", None
 
