@@ -857,6 +857,8 @@ def run_ours(args):
         set_phase_hook(None)
         env.quiet_keep, env.quiet = env.quiet, None     # the captured graph refers to the events: keep them alive
     if graphed is not None:       # likewise the resident step launched from Python
+        for _ in range(3):        # (the allocator hands out fresh blocks again after the graph legs)
+            step_resident()
         eager_ms = env.timed(step_resident, args.steps)
 
     progress(env, "eager comparison legs done")
