@@ -4,14 +4,15 @@
 // They replace the reference's atomic kernels (cuda/local_exchange.cuh:5-61,
 // cuda/balancing.cuh:5-46) by a deterministic counting sort:
 //   1. tile_hist:   every warp owns a contiguous tile of the flat gate array
-//                   and builds the tile's histogram in shared memory with
-//                   __match_any_sync (one add per distinct expert per 32 entries);
+//                   and builds the tile's histogram in its own shared-memory row
+//                   (shared-memory atomics: integer sums, order does not matter);
 //   2. scan_tiles:  per expert, exclusive prefix over tiles (in place, blocks of 256
 //                   tiles in parallel; the block totals are scanned in step 3);
 //   3. finalize:    per-expert totals -> segment starts / limits, and the
 //                   in-place side effects the reference's operators have;
 //   4. apply:       every warp walks its tile again in order, ranks entries by
-//                   (expert, flat index) and writes positions or pruned gates.
+//                   (expert, flat index) with __match_any_sync and writes positions
+//                   or pruned gates.
 // Gate entries are read with 16-byte loads; within an expert segment positions
 // ascend with the flat index, so results are identical from run to run.
 #include "common.cuh"
@@ -106,11 +107,13 @@ __device__ __forceinline__ void load_chunk(const int64_t* __restrict__ gate, int
     }
 }
 
-// One add per distinct expert among the 32 lanes.
-__device__ __forceinline__ void hist_round(int e, int lane, int32_t* my) {
-    const unsigned m = __match_any_sync(kFull, e);
-    if (e >= 0 && lane == __ffs(m) - 1) my[e] += __popc(m);
-    __syncwarp();
+// Counts the 32 lanes' experts into the warp's own shared-memory row.  Native shared-memory atomics: lanes
+// that name the same expert serialise on its counter (a handful per instruction on average), which costs
+// far less issue time than ranking the lanes with __match_any_sync first; integer sums do not depend on
+// the order, so the result is the same from run to run.  (The caller synchronises the warp before it
+// reads the row.)
+__device__ __forceinline__ void hist_round(int e, int /*lane*/, int32_t* my) {
+    if (e >= 0) atomicAdd(my + e, 1);
 }
 
 __global__ void __launch_bounds__(kThreads)
@@ -140,6 +143,7 @@ tile_hist_kernel(const int64_t* __restrict__ gate, int64_t n, int n_expert, int 
             hist_round(eb[u], lane, my);
         }
     }
+    __syncwarp();
     int32_t* out = hist + tile * n_expert;
     for (int e = lane; e < n_expert; e += 32) out[e] = my[e];
 }
