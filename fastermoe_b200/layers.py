@@ -137,7 +137,11 @@ def _fmoe_general_global_forward(inp, gate, expert_fn, policy_fn, experts, num_e
             overlap = int(os.environ.get("FMOE_B200_OVERLAP_SMS", "0"))
             # the experts' last GEMM (and the input-gradient GEMM of their first layer) stores its rows
             # straight into the token-side buffers of their owners: no gather pass afterwards
-            fused_gather = os.environ.get("FMOE_B200_FUSED_GATHER", "1") == "1"
+            # (not when someone else may look at the experts' raw output: a hook on the module, or a subclass
+            # with its own expert_fn -- that tensor is never written in this form)
+            plain_call = getattr(expert_fn, "__func__", None) is FMoE.expert_fn
+            hooked = bool(experts._forward_hooks) or bool(getattr(experts, "_forward_hooks_with_kwargs", None))
+            fused_gather = plain_call and not hooked and os.environ.get("FMOE_B200_FUSED_GATHER", "1") == "1"
         # the scatters' pushes pick (forward) or pick and scale (backward) their rows themselves
         fused_scatter = overlap == 0 and os.environ.get("FMOE_B200_FUSED_SCATTER", "1") == "1"
         # ... and the experts' first GEMM (backward: the second layer's input-gradient GEMM) moves them itself
