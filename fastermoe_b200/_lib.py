@@ -118,6 +118,7 @@ _SIGS = {
     "fmoe_peer_arrival_finish": (I32, [P, P]),
     "fmoe_peer_gather_planned_async": (I32, [P, P, P, P, I64, I64, I64, I32, I32, I32, P, P]),
     "fmoe_peer_scatter_planned_rows": (I32, [P, P, I64, P, I32, P, I32, P, P, I64, I64, I64, I32, P]),
+    "fmoe_abi_sizeof": (ctypes.c_size_t, [ctypes.c_char_p]),
     "fmoe_peer_scatter_fused_begin": (I32, [P, P, I64, P, I32, P, I32, P, P, I64, I64, I64, I32, P, P]),
     "fmoe_peer_gather_fused_begin": (I32, [P, P, P, I64, I64, I32, P, P]),
     "fmoe_linear_forward_overlapped": (I32, [P, P, P, P, P, P, I64, I64, I64, I32, I32, I32, P, P, P]),

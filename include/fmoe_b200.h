@@ -46,6 +46,9 @@ enum { FMOE_ACT_NONE = 0, FMOE_ACT_RELU = 1, FMOE_ACT_GELU = 2 };
 const char* fmoe_last_error_string(void);
 /* Library version, and the compute capability it was built for (100). */
 int fmoe_version(void);
+/* sizeof() of a struct of this header as the library was built ("fmoe_move_t", "fmoe_peer_seg_t", "fmoe_arrival_t",
+ * "fmoe_mlp_params_t", "fmoe_fused_geometry_t"; 0 for an unknown name): lets a binding check its own declarations. */
+size_t fmoe_abi_sizeof(const char* struct_name);
 int fmoe_built_for_sm(void);
 /* Reads the status word that the tensor-core kernels raise when one of their
  * bounded waits expires (0 = none; 1..4 = which wait; 7 = misaligned shared memory;

@@ -133,3 +133,13 @@ def test_pool_allocator_without_a_pool():
     assert _lib.lib.fmoe_pool_alloc(1 << 20, 0, None) is None
     _lib.lib.fmoe_pool_free(ctypes.c_void_p(4096), 1 << 20, 0, None)
     assert _lib.lib.fmoe_peer_pool_bytes(None) == 0
+
+
+def test_struct_mirrors_have_the_library_s_sizes():
+    """The ctypes mirrors of the structs that cross the C ABI are as large as the library's own."""
+    import ctypes
+    from fastermoe_b200 import _lib
+    for name, mirror in (("fmoe_move_t", _lib.Move), ("fmoe_peer_seg_t", _lib.PeerSeg), ("fmoe_arrival_t", _lib.Arrival),
+                         ("fmoe_mlp_params_t", _lib.MlpParams), ("fmoe_fused_geometry_t", _lib.FusedGeometry)):
+        assert _lib.lib.fmoe_abi_sizeof(name.encode()) == ctypes.sizeof(mirror), name
+    assert _lib.lib.fmoe_abi_sizeof(b"no_such_struct") == 0
