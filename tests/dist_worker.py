@@ -807,6 +807,78 @@ def cpu_megatron_ddp_checkpoint(rank, world, port, root):
     finish("gloo")
 
 
+def cpu_megatron_named_checkpoint(rank, world, port, root):
+    """save_checkpoint / load_checkpoint with the reference's signatures, inside a process that has a module
+    named ``megatron`` (a stand-in with the attributes those functions use): data-parallel rank 0 goes through
+    the host framework's own functions, the other rank writes and reads its expert shard."""
+    import types
+    init(rank, world, port, "gloo")
+    native = {"saved": 0, "loaded": 0}
+    args = types.SimpleNamespace(save=root, load=root, no_save_optim=False, no_load_optim=False, finetune=False)
+    mpu = types.SimpleNamespace(get_data_parallel_rank=lambda: rank, get_tensor_model_parallel_rank=lambda: 0,
+                                get_pipeline_model_parallel_rank=lambda: 0,
+                                get_pipeline_model_parallel_world_size=lambda: 1)
+    from fastermoe_b200.megatron import checkpoint as C
+
+    def native_save(iteration, model, optimizer, lr_scheduler):
+        native["saved"] += 1
+        C.save_shard(root, iteration, model, optimizer, C.GridPosition(0), extra={"lr_scheduler": {"step": iteration}})
+        dist.barrier()
+        C.write_tracker(root, iteration)
+        dist.barrier()
+
+    def native_load(model, optimizer, lr_scheduler, load_arg="load"):
+        native["loaded"] += 1
+        blob = C.load_shard(root, model, optimizer, C.GridPosition(0))
+        dist.barrier()
+        return blob["iteration"]
+
+    fake = types.ModuleType("megatron")
+    fake.get_args, fake.mpu = (lambda: args), mpu
+    fake.checkpointing = types.ModuleType("megatron.checkpointing")
+    fake.checkpointing.save_checkpoint, fake.checkpointing.load_checkpoint = native_save, native_load
+    sys.modules["megatron"], sys.modules["megatron.checkpointing"] = fake, fake.checkpointing
+    try:
+        torch.manual_seed(7 + rank)
+        net = torch.nn.ModuleDict({"shared": torch.nn.Linear(3, 3), "experts": torch.nn.Linear(3, 3)})
+        for p in net["experts"].parameters():
+            p.dp_comm = "none"
+        with torch.no_grad():                                  # replicated tensors agree, experts differ
+            for p in net["shared"].parameters():
+                p.copy_(torch.full_like(p, 0.5))
+        opt = torch.optim.SGD(net.parameters(), lr=0.1, momentum=0.9)
+        (net["experts"](net["shared"](torch.ones(2, 3))) ** 2).sum().backward()
+        for p in net["shared"].parameters():                   # what data parallelism does for replicated tensors
+            dist.all_reduce(p.grad)
+            p.grad /= world
+        opt.step()
+        want = {k: v.clone() for k, v in net.state_dict().items()}
+
+        class Sched:
+            state = None
+
+            def load_state_dict(self, sd):
+                self.state = sd
+
+        C.save_checkpoint(12, net, opt, None)
+        assert native["saved"] == (1 if rank == 0 else 0)
+        assert os.path.isfile(C.checkpoint_name(root, 12, C.GridPosition(rank)))
+        with torch.no_grad():
+            for p in net.parameters():
+                p.zero_()
+        sched = Sched()
+        it = C.load_checkpoint(net, torch.optim.SGD(net.parameters(), lr=0.1, momentum=0.9), sched)
+        assert it == 12 and native["loaded"] == (1 if rank == 0 else 0)
+        for k, v in net.state_dict().items():
+            assert torch.equal(v, want[k]), k
+        if rank > 0:
+            assert sched.state == {"step": 12}                 # the scheduler's state comes from rank 0's file
+    finally:
+        sys.modules.pop("megatron", None)
+        sys.modules.pop("megatron.checkpointing", None)
+    finish("gloo")
+
+
 def cpu_slice_allgather(rank, world, port):
     """Slice / AllGather over a model-parallel group (fmoe/functions.py:333-375): the forward of one is
     the backward of the other."""

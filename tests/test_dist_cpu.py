@@ -29,3 +29,7 @@ def test_slice_and_allgather_over_gloo(world):
 
 def test_megatron_wrapper_and_sharded_checkpoint_over_gloo(tmp_path):
     mp.spawn(dist_worker.cpu_megatron_ddp_checkpoint, args=(2, free_port(), str(tmp_path)), nprocs=2, join=True)
+
+
+def test_reference_named_checkpoint_functions_over_gloo(tmp_path):
+    mp.spawn(dist_worker.cpu_megatron_named_checkpoint, args=(2, free_port(), str(tmp_path)), nprocs=2, join=True)
