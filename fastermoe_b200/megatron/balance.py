@@ -64,13 +64,30 @@ def _layers_of(model):
 
 
 def add_balance_log(model, writer, iteration, is_last_rank=None):
-    """Mean over the ranks of every layer's balance loss, written as ``balance-<name>/layer-<i>`` and
-    ``balance-<name>/all`` scalars (fmoe/megatron/balance.py:48-72)."""
-    losses = torch.vstack([l.mlp.gate.get_loss(clear=True) for l in _layers_of(model)]).detach()
-    group = get_torch_default_comm()
+    """Writes the balance figures of the step to a summary writer as ``balance-<name>/layer-<i>`` and
+    ``balance-<name>/all`` (the mean over the layers), averaged over the ranks
+    (fmoe/megatron/balance.py:48-72).  Names: the three imbalance figures the gate hooks recorded, and
+    ``<strategy>_loss`` with the balance loss each layer's gate stored (the gates' losses are cleared)."""
+    layers = _layers_of(model)
+    strategy = getattr(host.get_args(), "balance_strategy", None)
+    if strategy:
+        key = f"{strategy}_loss"
+        balance_dict.setdefault(key, [None] * len(layers))
+        for i, layer in enumerate(layers):
+            loss = layer.mlp.gate.get_loss(clear=True)
+            if loss is not None and i < len(balance_dict[key]):
+                balance_dict[key][i] = loss.detach().reshape(())
+    names = list(balance_dict)
+    device = next((v.device for vals in balance_dict.values() for v in vals if v is not None), torch.device("cpu"))
+    table = torch.full((len(names), max(_num_layers, len(layers))), float("nan"), device=device)
+    for r, name in enumerate(names):
+        for i, v in enumerate(balance_dict[name]):
+            if v is not None:
+                table[r, i] = v.float()
     if torch.distributed.is_initialized():
-        torch.distributed.all_reduce(losses, group=group)
-        losses /= torch.distributed.get_world_size(group=group)
+        group = get_torch_default_comm()
+        torch.distributed.all_reduce(table, group=group)
+        table /= torch.distributed.get_world_size(group=group)
     if is_last_rank is None:
         try:
             from megatron import is_last_rank as native
@@ -79,12 +96,13 @@ def add_balance_log(model, writer, iteration, is_last_rank=None):
             is_last_rank = not torch.distributed.is_initialized() or \
                 torch.distributed.get_rank() == torch.distributed.get_world_size() - 1
     if writer and is_last_rank:
-        for idx, name in enumerate(balance_dict):
-            if idx >= losses.shape[0]:
-                break
-            for layer_id, val in enumerate(losses[idx].reshape(-1)):
-                writer.add_scalar(f"balance-{name}/layer-{layer_id}", val.item(), iteration)
-            writer.add_scalar(f"balance-{name}/all", losses[idx].mean().item(), iteration)
+        for r, name in enumerate(names):
+            row = table[r]
+            seen = ~torch.isnan(row)
+            for i in torch.nonzero(seen).reshape(-1).tolist():
+                writer.add_scalar(f"balance-{name}/layer-{i}", row[i].item(), iteration)
+            if bool(seen.any()):
+                writer.add_scalar(f"balance-{name}/all", row[seen].mean().item(), iteration)
 
 
 def patch_forward_step(forward_step_func, is_pipeline_last_stage=None):

@@ -81,7 +81,7 @@ def test_fmoefy_replaces_every_mlp(bound):
         # Megatron's MLP initialisation: N(0, sigma) in, N(0, sigma / sqrt(2 L)) out, zero biases
         assert abs(float(mlp.experts.htoh4.weight.detach().std()) - 0.02) < 0.002
         assert abs(float(mlp.experts.h4toh.weight.detach().std()) - 0.02 / 2.0) < 0.001
-        assert float(mlp.experts.htoh4.bias.abs().max()) == 0.0
+        assert float(mlp.experts.htoh4.bias.detach().abs().max()) == 0.0
     assert isinstance(layers[0].attn, nn.Linear)                      # nothing else is touched
     prof = M.get_balance_profile()
     assert set(prof) == {"coefficient-variation", "Lmax-over-Lmin", "Lmax-over-Lmean"}
@@ -120,6 +120,36 @@ def test_forward_step_gets_the_balance_loss(bound):
     bound.balance_strategy = "naive"                                    # a gate without a loss: untouched
     step = M.patch_forward_step(lambda it, m: (torch.tensor(10.0), {}), is_pipeline_last_stage=lambda: True)
     assert float(step(None, model)[0]) == 10.0
+
+
+def test_balance_log_and_model_provider(bound):
+    bound.balance_strategy, bound.num_experts, bound.top_k = "gshard", 2, 2
+    provider = M.patch_model_provider(lambda: FakeMegatronModel(64, 2))
+    model = provider()
+    mlps = [l.mlp for l in model.language_model.transformer.layers]
+    assert all(isinstance(m, M.MegatronMLP) for m in mlps)
+    assert mlps[0].experts.htoh4.weight.shape[1] == 4 * 64 // 2           # the dense model's cost per token is kept
+    M.generate_megatron_gate_hook(0, 2)(torch.tensor([[0, 1], [0, 0]]), None, None)
+    mlps[0].gate.set_loss(torch.tensor(0.25))
+    mlps[1].gate.set_loss(torch.tensor(0.75))
+
+    class Writer:
+        def __init__(self):
+            self.rows = {}
+
+        def add_scalar(self, name, value, iteration):
+            self.rows[name] = (value, iteration)
+
+    w = Writer()
+    M.add_balance_log(model, w, 5, is_last_rank=True)
+    assert w.rows["balance-gshard_loss/layer-0"] == (0.25, 5) and w.rows["balance-gshard_loss/layer-1"] == (0.75, 5)
+    assert w.rows["balance-gshard_loss/all"] == (0.5, 5)
+    assert w.rows["balance-Lmax-over-Lmean/layer-0"][0] == pytest.approx(1.5)      # counts [3, 1]
+    assert "balance-Lmax-over-Lmean/layer-1" not in w.rows                          # layer 1 routed nothing
+    assert mlps[0].gate.get_loss() is None                                          # cleared by the log
+    quiet = Writer()
+    M.add_balance_log(model, quiet, 6, is_last_rank=False)
+    assert quiet.rows == {}
 
 
 def test_checkpoint_names():
