@@ -107,6 +107,20 @@ __device__ __forceinline__ void load_chunk(const int64_t* __restrict__ gate, int
     }
 }
 
+// The same 64 entries in whatever order the 16-byte loads deliver them (lane l: entries c+2l and c+2l+1):
+// for passes that only count, the order of the entries inside a chunk does not matter, and the shuffle
+// transpose of load_chunk can be left out.
+__device__ __forceinline__ void load_chunk_unordered(const int64_t* __restrict__ gate, int64_t n, int64_t c,
+                                                     int lane, bool vec, int n_expert, int& ea, int& eb) {
+    if (vec && c + 64 <= n) {
+        const longlong2 v = __ldg(reinterpret_cast<const longlong2*>(gate + c) + lane);
+        ea = sanitize(v.x, n_expert);
+        eb = sanitize(v.y, n_expert);
+    } else {
+        load_chunk(gate, n, c, lane, vec, n_expert, ea, eb);
+    }
+}
+
 // Counts the 32 lanes' experts into the warp's own shared-memory row.  Native shared-memory atomics: lanes
 // that name the same expert serialise on its counter (a handful per instruction on average), which costs
 // far less issue time than ranking the lanes with __match_any_sync first; integer sums do not depend on
@@ -134,7 +148,7 @@ tile_hist_kernel(const int64_t* __restrict__ gate, int64_t n, int n_expert, int 
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
             const int64_t c = base + (int64_t)(it + u) * 64;
-            if (it + u < chunks && c < n) load_chunk(gate, n, c, lane, vec, n_expert, ea[u], eb[u]);
+            if (it + u < chunks && c < n) load_chunk_unordered(gate, n, c, lane, vec, n_expert, ea[u], eb[u]);
             else ea[u] = eb[u] = -1;
         }
 #pragma unroll
@@ -465,7 +479,7 @@ expert_count_kernel(const int64_t* __restrict__ gate, int64_t n, int n_expert,
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
             const int64_t c = ch + u * stride;
-            if (c < n_chunks) load_chunk(gate, n, c * 64, lane, vec, n_expert, ea[u], eb[u]);
+            if (c < n_chunks) load_chunk_unordered(gate, n, c * 64, lane, vec, n_expert, ea[u], eb[u]);
             else ea[u] = eb[u] = -1;
         }
 #pragma unroll
